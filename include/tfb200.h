@@ -1,0 +1,97 @@
+/* tfb200.h - C ABI of the B200 (sm_100a) routed-expert MoE library, libtfb200.so.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream (cudaStream_t passed as void*), enqueues its
+ * work on that stream for the CURRENT device, never synchronises the host and never allocates.  The return value is a
+ * status: 0 ok; -1 a bad argument (nothing was launched); -2 the CUDA runtime refused a call; the text is available
+ * from tfb_last_error() on the calling thread.  Grids are sized by host-known upper bounds and the true counts are read
+ * on the device, so a captured CUDA graph follows new routing on replay.
+ *
+ * Each declaration names the interface of the reference (bertholomus/TensorFold, paths inside its tree) it replaces.
+ * bf16 / fp16 buffers are passed as const void*; int32 buffers as int32_t*.
+ */
+#ifndef TFB200_H
+#define TFB200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- library state ------------------------------------------------------------------------------------------- */
+
+/* Text of the calling thread's last failure (never NULL). */
+const char* tfb_last_error(void);
+
+/* ABI version of this header (1). */
+int tfb_version(void);
+
+/* Launch with programmatic stream serialization (kernels overlap their prologue with the previous kernel's tail and
+ * wait on the device before touching memory).  Returns the previous setting.  Off by default. */
+int tfb_set_pdl(int on);
+
+/* Reads and clears the current device's status word into *status (0: every bounded wait completed; 1: a wait ran out
+ * and the kernel returned early).  Synchronises `stream`.  No reference counterpart: the reference traps instead
+ * (src/tensorfold/cuda/exl3/experts_grouped.cuh:240,259). */
+int tfb_kernel_status(int* status, void* stream);
+
+/* ---- routing ------------------------------------------------------------------------------------------------- */
+
+/* logits[T, NE] fp32 = x[T, D] (bf16, row stride x_stride elements) . rows[NE, D]^T (bf16), fixed summation order.
+ * Replaces moe.router / the Triton kernel _router: src/tensorfold/cuda/moe.py:23-55. */
+int tfb_router(const void* x, int64_t x_stride, const void* rows, float* logits, int T, int D, int NE, void* stream);
+
+/* Per row: the top_k experts among the first E logits (largest first, ties to the lower id), weights
+ * bf16(exp(l_k - l_0) / sum) stored as fp32; when `shared` != 0 one more slot holds id E with weight
+ * bf16(sigmoid(bf16(logits[r, E]))).  pick / wts are [T, top_k + (shared != 0)], NL is the logits' row length.
+ * Replaces moe.select_rows / _topk_rows: src/tensorfold/cuda/moe.py:58-85,103-108. */
+int tfb_select_rows(const float* logits, int NL, int32_t* pick, float* wts, int T, int E, int top_k, int shared,
+                    void* stream);
+
+/* Groups the pairs p = row * slots + slot by ascending expert, pair order kept inside an expert: members[pairs],
+ * items[n, 3] = (expert, first member, count <= tile) in expert order then chunk order, counts = (items, distinct
+ * experts).  Ids outside [0, experts) are left out.  experts <= 1024.  One launch at any pair count.
+ * Replaces the extension entry `plan`: src/tensorfold/cuda/experts.cpp:33-41, experts.cu:157-334 (its rank / hist
+ * scratch is not needed). */
+int tfb_plan(const int32_t* picks, int64_t pairs, int experts, int tile, int32_t* members, int32_t* items,
+             int32_t* counts, void* stream);
+
+/* out[T, D] = sum over slots, in slot order, of wts[T, slots] * y[T, slots, D] (fp32 fma chain from 0), rounded once.
+ * y is fp32 (y_bf16 = 0) or bf16; out is bf16 (out_f32 = 0) or fp32.
+ * Replaces moe.combine / _combine: src/tensorfold/cuda/moe.py:131-151, and combine_kernel of
+ * src/tensorfold/cuda/exl3/experts.cu:181-190 for the fp32 form. */
+int tfb_combine(const void* y, int y_bf16, const float* wts, void* out, int out_f32, int T, int slots, int D,
+                void* stream);
+
+/* ---- MLX affine 4-bit group-64 experts -------------------------------------------------------------------------- */
+
+/* words [E, N, K/8] (uint32, element k of a row at bits 4 (k % 8) of word k / 8), scales and biases [E, N, K/gs]
+ * (2-byte: bf16 or fp16, carried opaquely) -> out int32 [E, N/32, K/gs, 288].  gs must be 64.
+ * Replaces the extension entry `pack`: src/tensorfold/cuda/experts.cpp:58-75, experts_pack.cu. */
+int tfb_pack(const void* words, const void* scales, const void* biases, int gs, void* out, int E, int N, int K,
+             void* stream);
+
+/* pack's inverse on the device (the reference's is torch indexing: src/tensorfold/cuda/experts.py:43-58). */
+int tfb_unpack(const void* blocks, int gs, void* words, void* scales, void* biases, int E, int N, int K, void* stream);
+
+/* The weight values the kernels multiply by, out [E, N, K]: mode 0 fp32 fma(scale, q, bias) (decode form); mode 1 the
+ * prefill form's bf16 weights.  sb_type 0: bf16 scales, 1: fp16 scales.  The hook for the bit-exactness checks
+ * (the reference's twins: src/tensorfold/families/qwen3_5_moe/cuda/weights.py:20-29,
+ * src/tensorfold/cuda/experts_prefill.cu:25-29). */
+int tfb_dequant(const void* blocks, int gs, int sb_type, int mode, void* out, int E, int N, int K, void* stream);
+
+/* Grouped 4-bit expert matmul, decode form, over a plan.  x: bf16 rows of K = kg * gs inputs (row stride x_stride
+ * elements, 16-byte aligned); pair p reads row p / slots when slots > 0, else row p.  w: blocks
+ * [E, nb, kg, M, 288] (M = 2 for epi 2, else 1).  out rows of n = 32 * nb columns, row index = pair id.
+ * epi 0: fp32 out; 1: bf16 relu(bf16 acc)^2; 2: bf16 SwiGLU(matrix 0, matrix 1) clipped at `limit` when > 0;
+ * 3: bf16 out.  max_units = upper bound of items * nb (the grid).  sb_type as tfb_dequant.
+ * Replaces the extension entry `run`: src/tensorfold/cuda/experts.cpp:43-48, experts.cu:130-155,287-351. */
+int tfb_experts_run(int gs, int epi, const void* x, int64_t x_stride, int slots, const void* w, int kg, int nb,
+                    const int32_t* items, const int32_t* counts, const int32_t* members, void* out, int n, float limit,
+                    int64_t max_units, int sb_type, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* TFB200_H */

@@ -1,0 +1,73 @@
+"""ctypes binding of the C-ABI library (``include/tfb200.h``).  No CPU path exists behind these calls."""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_char_p, c_float, c_int, c_int64, c_void_p
+from functools import lru_cache
+from pathlib import Path
+
+LIB_PATH = Path(__file__).resolve().parent / "lib" / "libtfb200.so"
+
+ERR_ARG, ERR_CUDA, ERR_DEVICE = -1, -2, -3
+
+P, I, L, F = c_void_p, c_int, c_int64, c_float
+
+# name -> argument types (every entry point returns int status, except tfb_last_error / tfb_version / tfb_set_pdl)
+SIGNATURES: dict[str, tuple] = {
+    "tfb_router": (P, L, P, P, I, I, I, P),
+    "tfb_select_rows": (P, I, P, P, I, I, I, I, P),
+    "tfb_plan": (P, L, I, I, P, P, P, P),
+    "tfb_combine": (P, I, P, P, I, I, I, I, P),
+    "tfb_pack": (P, P, P, I, P, I, I, I, P),
+    "tfb_unpack": (P, I, P, P, P, I, I, I, P),
+    "tfb_dequant": (P, I, I, I, P, I, I, I, P),
+    "tfb_experts_run": (I, I, P, L, I, P, I, I, P, P, P, P, I, F, L, I, P),
+    "tfb_kernel_status": (P, P),
+}
+
+
+class MissingLibrary(RuntimeError):
+    pass
+
+
+@lru_cache(maxsize=1)
+def lib() -> ctypes.CDLL:
+    if not LIB_PATH.exists():
+        raise MissingLibrary(f"{LIB_PATH} is not built: run `python -m tensorfold_b200.build` (there is no fallback)")
+    handle = ctypes.CDLL(str(LIB_PATH))
+    handle.tfb_last_error.restype = c_char_p
+    handle.tfb_last_error.argtypes = ()
+    handle.tfb_version.restype = c_int
+    handle.tfb_set_pdl.argtypes = (c_int,)
+    handle.tfb_set_pdl.restype = c_int
+    for name, args in SIGNATURES.items():
+        fn = getattr(handle, name)
+        fn.argtypes = args
+        fn.restype = c_int
+    return handle
+
+
+def call(name: str, *args) -> None:
+    """Call an entry point; a bad argument raises ValueError, anything else RuntimeError, with the library's text."""
+
+    handle = lib()
+    rc = getattr(handle, name)(*args)
+    if rc == 0:
+        return
+    text = handle.tfb_last_error().decode("utf-8", "replace")
+    if rc == ERR_ARG:
+        raise ValueError(text)
+    raise RuntimeError(text)
+
+
+def kernel_status(stream: int = 0) -> int:
+    """The device status word (0: every kernel since the last read finished its waits); clears it."""
+
+    out = c_int(0)
+    call("tfb_kernel_status", ctypes.addressof(out), stream)
+    return out.value
+
+
+def set_pdl(on: bool) -> bool:
+    return bool(lib().tfb_set_pdl(1 if on else 0))

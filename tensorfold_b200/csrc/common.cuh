@@ -1,0 +1,171 @@
+// Shared device helpers and the packed expert-block geometry for the sm_100a routed-expert kernels.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace tfb {
+
+// ---- packed affine 4-bit block (group of 64 inputs x 32 output columns, one matrix) ----------------------------
+// 288 int32 = 1152 bytes:
+//   bytes [0, 512)    column tile 0 (block columns 0..15): 32 lanes x 16 bytes, the lane's mma A fragments
+//   bytes [512, 1024) column tile 1 (block columns 16..31)
+//   bytes [1024,1152) 32 (scale, bias) pairs, entry (c % 8) * 4 + c / 8 for block column c: scale in the low half
+// Lane l = 4 * gq + t of a tile holds, for columns gq and gq + 8 of the tile, the 16 inputs 16 t .. 16 t + 15 of the
+// group: uint4 = (col gq inputs 0..7, col gq inputs 8..15, col gq+8 inputs 0..7, col gq+8 inputs 8..15), each word
+// with its nibbles stored as (i0, i2, i4, i6 | i1, i3, i5, i7) so that (w >> 4 m) & 0x000F000F is the pair
+// (input 2 m, input 2 m + 1) in the two 16-bit halves.
+constexpr int GS = 64;                 // inputs a group
+constexpr int COLS = 32;               // output columns a block
+constexpr int BLOCK_WORDS = 288;       // int32 a block
+constexpr int BLOCK_BYTES = BLOCK_WORDS * 4;
+constexpr int TILE_BYTES = 512;
+constexpr int SB_OFFSET = 1024;
+
+constexpr uint32_t NIB_MASK = 0x000F000Fu;
+constexpr uint32_t BF16_128 = 0x43004300u;   // the bf16 pair (128, 128): 128 + q is exact for q in 0..15
+
+enum ScaleType : int { SB_BF16 = 0, SB_FP16 = 1 };
+
+// Position inside the 128-byte scale/bias area of block column c (uint32 index).
+__host__ __device__ __forceinline__ int sb_slot(int c) { return (c & 7) * 4 + (c >> 3); }
+
+// MLX nibble order (i0 .. i7 at bits 0, 4, .. 28) -> (i0, i2, i4, i6, i1, i3, i5, i7)
+__host__ __device__ __forceinline__ uint32_t nib_shuffle(uint32_t w) {
+  uint32_t even = w & 0x0F0F0F0Fu, odd = (w >> 4) & 0x0F0F0F0Fu;   // even: i0,i2,i4,i6 in bytes; odd: i1,i3,i5,i7
+  even = (even | (even >> 4)) & 0x00FF00FFu;
+  even = (even | (even >> 8)) & 0x0000FFFFu;
+  odd = (odd | (odd >> 4)) & 0x00FF00FFu;
+  odd = (odd | (odd >> 8)) & 0x0000FFFFu;
+  return even | (odd << 16);
+}
+
+// nib_shuffle's inverse
+__host__ __device__ __forceinline__ uint32_t nib_unshuffle(uint32_t v) {
+  uint32_t out = 0;
+#pragma unroll
+  for (int m = 0; m < 4; ++m) {
+    out |= ((v >> (4 * m)) & 0xFu) << (8 * m);
+    out |= ((v >> (16 + 4 * m)) & 0xFu) << (8 * m + 4);
+  }
+  return out;
+}
+
+// Where MLX word (block column c, word j of the group's 8) lives inside the block, as a uint32 index.
+__host__ __device__ __forceinline__ int word_slot(int c, int j) {
+  const int tile = c >> 4, cc = c & 15, gq = cc & 7, hi = cc >> 3, t = j >> 1, half = j & 1;
+  return tile * 128 + (gq * 4 + t) * 4 + hi * 2 + half;
+}
+
+__device__ __forceinline__ float bf16_lo(uint32_t v) { return __uint_as_float(v << 16); }
+__device__ __forceinline__ float bf16_hi(uint32_t v) { return __uint_as_float(v & 0xFFFF0000u); }
+__device__ __forceinline__ float round_bf16(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+
+template <int SB>
+__device__ __forceinline__ float sb_to_float(uint32_t half_bits) {
+  if constexpr (SB == SB_FP16) {
+    return __half2float(__ushort_as_half(static_cast<unsigned short>(half_bits & 0xFFFFu)));
+  } else {
+    return __uint_as_float(half_bits << 16);
+  }
+}
+
+// ---- device status word -----------------------------------------------------------------------------------------
+// Kernels never trap: a wait that runs out records a code here and the kernel returns; the host reads it.
+enum KernelStatus : int { ST_OK = 0, ST_WAIT_TIMEOUT = 1, ST_BAD_INDEX = 2 };
+static __device__ int g_kernel_status = 0;   // one copy: the library is built as a single translation unit
+
+// ---- mbarrier / bulk copy (non-multicast) -----------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_addr(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_addr(bar)), "r"(count));
+}
+
+__device__ __forceinline__ void mbar_fence_init() { asm volatile("fence.mbarrier_init.release.cluster;\n" ::); }
+
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_addr(bar)), "r"(bytes)
+               : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_addr(bar)) : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n.reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n}\n"
+      : "=r"(ok)
+      : "r"(smem_addr(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+// Bounded wait: gives up after a few seconds' worth of polls, records ST_WAIT_TIMEOUT and returns false.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+  for (uint32_t spin = 0; spin < (1u << 24); ++spin) {
+    if (mbar_try_wait(bar, parity)) return true;
+  }
+  atomicExch(&g_kernel_status, ST_WAIT_TIMEOUT);
+  return false;
+}
+
+// global -> shared bulk copy of `bytes` (a multiple of 16, both addresses 16-byte aligned), completion on `bar`
+__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(
+                   smem_addr(dst)),
+               "l"(src), "r"(bytes), "r"(smem_addr(bar))
+               : "memory");
+}
+
+__device__ __forceinline__ uint4 ldg_nc(const void* p) {
+  uint4 r;
+  asm volatile("ld.global.nc.v4.u32 {%0, %1, %2, %3}, [%4];\n" : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(p));
+  return r;
+}
+
+__device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+      "{%0, %1, %2, %3};\n"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint32_t comp(const uint4& v, int c) {
+  return c == 0 ? v.x : c == 1 ? v.y : c == 2 ? v.z : v.w;
+}
+
+// Programmatic dependent launch: a kernel launched with the attribute may start early and must wait here before it
+// reads what the previous kernel in the stream wrote; without the attribute both are no-ops.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::); }
+
+// ---- activation epilogues (src/tensorfold/cuda/experts.cuh:57-75 states the roundings) -------------------------
+// SwiGLU on bf16-rounded gate and up: bf16(silu(g)) * u, clipped first when limit > 0; the caller rounds to bf16.
+__device__ __forceinline__ float swiglu(float g, float u, float limit) {
+  float gv = round_bf16(g), uv = round_bf16(u);
+  if (limit > 0.f) {
+    gv = fminf(gv, limit);
+    uv = fminf(fmaxf(uv, -limit), limit);
+  }
+  return round_bf16(gv / (1.f + expf(-gv))) * uv;
+}
+
+__device__ __forceinline__ float relu2(float a) {
+  const float u = fmaxf(round_bf16(a), 0.f);
+  return u * u;
+}
+
+enum Epilogue : int { EPI_F32 = 0, EPI_RELU2 = 1, EPI_SWIGLU = 2, EPI_BF16 = 3 };
+
+}  // namespace tfb

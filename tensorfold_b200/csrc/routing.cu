@@ -1,0 +1,357 @@
+// Router logits, top-k selection with softmax renormalisation, the expert plan (token sort) and the weighted
+// combine. Every result is a function of its own row only, so a row's bits never depend on the call's other rows.
+
+#include "api.h"
+#include "common.cuh"
+
+namespace tfb {
+
+// ================================================================================================================
+// Router: logits[r, e] = sum_k x[r, k] * w[e, k] in fp32, in ONE documented order so a CPU restatement can follow it
+// bit for bit: lane l of 32 walks k = 256 c + 8 l + j (c ascending, j = 0..7) with acc = fma(x, w, acc), then the 32
+// lane sums meet in a butterfly (xor 16, 8, 4, 2, 1).  (Reference: src/tensorfold/cuda/moe.py:23-55 leaves the
+// order to Triton's tl.dot.)
+// ================================================================================================================
+constexpr int R_WARPS = 4, R_ET = 4, R_RT = 8;
+
+__device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
+  f[0] = bf16_lo(v.x); f[1] = bf16_hi(v.x); f[2] = bf16_lo(v.y); f[3] = bf16_hi(v.y);
+  f[4] = bf16_lo(v.z); f[5] = bf16_hi(v.z); f[6] = bf16_lo(v.w); f[7] = bf16_hi(v.w);
+}
+
+__global__ void __launch_bounds__(R_WARPS * 32)
+router_kernel(const __nv_bfloat16* __restrict__ X, int64_t x_stride, const __nv_bfloat16* __restrict__ W,
+              float* __restrict__ out, int T, int D, int NE) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int e0 = (blockIdx.y * R_WARPS + warp) * R_ET;
+  const int r0 = blockIdx.x * R_RT;
+  if (e0 >= NE) return;
+  const int nr = min(R_RT, T - r0), ne = min(R_ET, NE - e0);
+  float acc[R_RT][R_ET];
+#pragma unroll
+  for (int r = 0; r < R_RT; ++r)
+#pragma unroll
+    for (int e = 0; e < R_ET; ++e) acc[r][e] = 0.f;
+  pdl_wait();
+  for (int k = 8 * lane; k < D; k += 256) {
+    float wv[R_ET][8];
+#pragma unroll
+    for (int e = 0; e < R_ET; ++e) {
+      const uint4 v = e < ne ? ldg_nc(W + (size_t)(e0 + e) * D + k) : make_uint4(0u, 0u, 0u, 0u);
+      unpack8(v, wv[e]);
+    }
+#pragma unroll
+    for (int r = 0; r < R_RT; ++r) {
+      if (r < nr) {
+        float xv[8];
+        unpack8(ldg_nc(X + (size_t)(r0 + r) * x_stride + k), xv);
+#pragma unroll
+        for (int e = 0; e < R_ET; ++e)
+#pragma unroll
+          for (int j = 0; j < 8; ++j) acc[r][e] = fmaf(xv[j], wv[e][j], acc[r][e]);
+      }
+    }
+  }
+  pdl_launch_dependents();
+#pragma unroll
+  for (int r = 0; r < R_RT; ++r)
+#pragma unroll
+    for (int e = 0; e < R_ET; ++e) {
+      float a = acc[r][e];
+#pragma unroll
+      for (int m = 16; m >= 1; m >>= 1) a = a + __shfl_xor_sync(0xffffffffu, a, m);
+      if (lane == 0 && r < nr && e < ne) out[(size_t)(r0 + r) * NE + e0 + e] = a;
+    }
+}
+
+// ================================================================================================================
+// Selection: a warp a row.  TOPK rounds of (largest fp32 logit, the lower id among equals), weight
+// bf16(exp(l_k - l_0) / sum_k exp(l_k - l_0)); with a shared expert, slot TOPK = id E with weight
+// bf16(sigmoid(bf16(logit E))).  (src/tensorfold/cuda/moe.py:58-85)
+// ================================================================================================================
+constexpr int S_WARPS = 4;
+
+template <int VPL>
+__global__ void __launch_bounds__(S_WARPS * 32)
+select_kernel(const float* __restrict__ L, int NL, int* __restrict__ pick, float* __restrict__ wts, int T, int E,
+              int top_k, int shared) {
+  const int lane = threadIdx.x & 31;
+  const int r = blockIdx.x * S_WARPS + (threadIdx.x >> 5);
+  if (r >= T) return;
+  pdl_wait();
+  const float NEG = __int_as_float(0xff800000);
+  float v[VPL];
+#pragma unroll
+  for (int i = 0; i < VPL; ++i) {
+    const int e = i * 32 + lane;
+    v[i] = e < E ? L[(size_t)r * NL + e] : NEG;
+  }
+  pdl_launch_dependents();
+  float top = 0.f, total = 0.f, my_ex = 0.f;
+  int my_pick = 0;
+  for (int k = 0; k < top_k; ++k) {
+    float bv = v[0];
+    int bi = lane;
+#pragma unroll
+    for (int i = 1; i < VPL; ++i)
+      if (v[i] > bv) {
+        bv = v[i];
+        bi = i * 32 + lane;
+      }
+#pragma unroll
+    for (int m = 16; m >= 1; m >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, m);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, m);
+      if (ov > bv || (ov == bv && oi < bi)) {
+        bv = ov;
+        bi = oi;
+      }
+    }
+    if (k == 0) top = bv;
+    const float ex = expf(bv - top);
+    total += ex;
+    if (lane == k) {
+      my_pick = bi;
+      my_ex = ex;
+    }
+#pragma unroll
+    for (int i = 0; i < VPL; ++i)
+      if (i * 32 + lane == bi) v[i] = NEG;
+  }
+  const int slots = top_k + (shared ? 1 : 0);
+  if (lane < top_k) {
+    pick[(size_t)r * slots + lane] = my_pick;
+    wts[(size_t)r * slots + lane] = round_bf16(my_ex / total);
+  } else if (lane == top_k && shared) {
+    const float sg = round_bf16(L[(size_t)r * NL + E]);
+    pick[(size_t)r * slots + lane] = E;
+    wts[(size_t)r * slots + lane] = round_bf16(1.f / (1.f + expf(-sg)));
+  }
+}
+
+// ================================================================================================================
+// Plan: pairs p = row * slots + slot grouped by ascending expert, pair order kept inside an expert (a stable counting
+// sort); items (expert, first, count <= tile) in expert order then chunk order; counts = (items, distinct experts).
+// One block: each of the 32 warps owns a contiguous run of pairs, counts them per expert, a scan over warps and over
+// experts gives every (warp, expert) its first slot, and a second walk scatters.  Ids outside [0, E) are left out.
+// (Semantics of src/tensorfold/cuda/experts.cu:157-285, pinned by tests/cuda/test_experts.py:107-134.)
+// ================================================================================================================
+constexpr int PLAN_THREADS = 1024, PLAN_EMAX = 1024;
+
+__device__ int place_items(int c, int E, int T, int* __restrict__ items, int* __restrict__ counts,
+                           int (*wsum)[32]) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int tiles = (c + T - 1) / T;
+  int a = c, b = tiles, u = c > 0 ? 1 : 0;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int ua = __shfl_up_sync(0xffffffffu, a, o), ub = __shfl_up_sync(0xffffffffu, b, o);
+    const int uu = __shfl_up_sync(0xffffffffu, u, o);
+    if (lane >= o) {
+      a += ua;
+      b += ub;
+      u += uu;
+    }
+  }
+  if (lane == 31) {
+    wsum[0][warp] = a;
+    wsum[1][warp] = b;
+    wsum[2][warp] = u;
+  }
+  __syncthreads();
+  if (warp < 3) {
+    int vv = wsum[warp][lane];
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int w = __shfl_up_sync(0xffffffffu, vv, o);
+      if (lane >= o) vv += w;
+    }
+    wsum[warp][lane] = vv;
+  }
+  __syncthreads();
+  const int off = (warp ? wsum[0][warp - 1] : 0) + a - c;
+  const int ioff = (warp ? wsum[1][warp - 1] : 0) + b - tiles;
+  if (tid == 0) {
+    counts[0] = wsum[1][31];
+    counts[1] = wsum[2][31];
+  }
+  if (tid < E)
+    for (int j = 0; j < tiles; ++j) {
+      int* it = items + 3 * (ioff + j);
+      it[0] = tid;
+      it[1] = off + T * j;
+      it[2] = min(T, c - T * j);
+    }
+  return off;
+}
+
+__global__ void __launch_bounds__(PLAN_THREADS)
+plan_kernel(const int* __restrict__ picks, int P, int E, int T, int* __restrict__ members, int* __restrict__ items,
+            int* __restrict__ counts) {
+  extern __shared__ int whist[];                 // [32][E]: pairs of expert e in warp w's run, then their first slot
+  __shared__ int first[PLAN_EMAX];
+  __shared__ int wsum[3][32];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  for (int i = tid; i < 32 * E; i += PLAN_THREADS) whist[i] = 0;
+  const int seg = (((P + 31) / 32 + 31) / 32) * 32;
+  const int p0 = min(P, warp * seg), p1 = min(P, p0 + seg);
+  int* mine = whist + warp * E;
+  pdl_wait();
+  __syncthreads();
+  for (int base = p0; base < p1; base += 32) {
+    const int p = base + lane;
+    const int e = p < p1 ? picks[p] : -1;
+    const bool ok = e >= 0 && e < E;
+    const unsigned peers = __match_any_sync(0xffffffffu, ok ? e : -1 - lane);
+    if (ok && lane == __ffs(peers) - 1) mine[e] += __popc(peers);
+    __syncwarp();
+  }
+  __syncthreads();
+  int c = 0;
+  if (tid < E)
+    for (int w = 0; w < 32; ++w) {
+      const int v = whist[w * E + tid];
+      whist[w * E + tid] = c;
+      c += v;
+    }
+  const int off = place_items(c, E, T, items, counts, wsum);
+  if (tid < E) first[tid] = off;
+  __syncthreads();
+  pdl_launch_dependents();
+  for (int base = p0; base < p1; base += 32) {
+    const int p = base + lane;
+    const int e = p < p1 ? picks[p] : -1;
+    const bool ok = e >= 0 && e < E;
+    const unsigned peers = __match_any_sync(0xffffffffu, ok ? e : -1 - lane);
+    const int rank = __popc(peers & ((1u << lane) - 1u));
+    const int b = ok ? mine[e] : 0;
+    if (ok) members[first[e] + b + rank] = p;
+    __syncwarp();
+    if (ok && rank == 0) mine[e] = b + __popc(peers);
+    __syncwarp();
+  }
+}
+
+// ================================================================================================================
+// Combine: out[r, d] = sum over slots in slot order of wts[r, s] * y[r, s, d] (fp32 fma chain from 0), rounded once.
+// (src/tensorfold/cuda/moe.py:131-151; src/tensorfold/cuda/exl3/experts.cu:181-190 for the fp32-out form.)
+// ================================================================================================================
+template <typename TY, typename TO>
+__global__ void __launch_bounds__(256)
+combine_kernel(const TY* __restrict__ y, const float* __restrict__ wts, TO* __restrict__ out, int S, int D) {
+  const int r = blockIdx.x;
+  const int d = (blockIdx.y * 256 + threadIdx.x) * 4;
+  if (d >= D) return;
+  pdl_wait();
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  for (int s = 0; s < S; ++s) {
+    const float w = wts[(size_t)r * S + s];
+    const TY* src = y + ((size_t)r * S + s) * D + d;
+    float v[4];
+    if constexpr (sizeof(TY) == 4) {
+      const float4 f = *reinterpret_cast<const float4*>(src);
+      v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w;
+    } else {
+      const uint2 u = *reinterpret_cast<const uint2*>(src);
+      v[0] = bf16_lo(u.x); v[1] = bf16_hi(u.x); v[2] = bf16_lo(u.y); v[3] = bf16_hi(u.y);
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[j] = fmaf(w, v[j], acc[j]);
+  }
+  pdl_launch_dependents();
+  TO* dst = out + (size_t)r * D + d;
+  if constexpr (sizeof(TO) == 4) {
+    *reinterpret_cast<float4*>(dst) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+  } else {
+    __nv_bfloat162 a = __floats2bfloat162_rn(acc[0], acc[1]), b = __floats2bfloat162_rn(acc[2], acc[3]);
+    uint2 u;
+    u.x = *reinterpret_cast<uint32_t*>(&a);
+    u.y = *reinterpret_cast<uint32_t*>(&b);
+    *reinterpret_cast<uint2*>(dst) = u;
+  }
+}
+
+}  // namespace tfb
+
+using namespace tfb;
+
+extern "C" int tfb_router(const void* x, int64_t x_stride, const void* rows, float* logits, int T, int D, int NE,
+                          void* stream) {
+  TFB_REQUIRE(x && rows && logits, "router: null pointer");
+  TFB_REQUIRE(T >= 0 && D > 0 && NE > 0, "router: bad sizes T=%d D=%d NE=%d", T, D, NE);
+  TFB_REQUIRE(D % 8 == 0 && x_stride % 8 == 0 && x_stride >= D, "router: D and the row stride must be multiples of 8");
+  TFB_REQUIRE(aligned16(x) && aligned16(rows), "router: x and rows must be 16-byte aligned");
+  if (T == 0) return TFB_OK;
+  const dim3 grid((T + R_RT - 1) / R_RT, (NE + R_WARPS * R_ET - 1) / (R_WARPS * R_ET));
+  return check_cuda(launch(router_kernel, grid, dim3(R_WARPS * 32), 0, static_cast<cudaStream_t>(stream),
+                           static_cast<const __nv_bfloat16*>(x), x_stride, static_cast<const __nv_bfloat16*>(rows),
+                           logits, T, D, NE),
+                    "router");
+}
+
+extern "C" int tfb_select_rows(const float* logits, int NL, int32_t* pick, float* wts, int T, int E, int top_k,
+                               int shared, void* stream) {
+  TFB_REQUIRE(logits && pick && wts, "select_rows: null pointer");
+  TFB_REQUIRE(E >= 1 && E <= 1024, "select_rows: 1..1024 experts, not %d", E);
+  TFB_REQUIRE(top_k >= 1 && top_k <= E && top_k <= 31, "select_rows: top_k=%d must be 1..min(E, 31)", top_k);
+  TFB_REQUIRE(NL >= E + (shared ? 1 : 0), "select_rows: %d logits a row cannot hold %d experts%s", NL, E,
+              shared ? " and the shared gate" : "");
+  if (T <= 0) return TFB_OK;
+  const int grid = (T + S_WARPS - 1) / S_WARPS;
+  auto st = static_cast<cudaStream_t>(stream);
+  const int vpl = (E + 31) / 32;
+#define TFB_SEL(V)                                                                                            \
+  return check_cuda(launch(select_kernel<V>, dim3(grid), dim3(S_WARPS * 32), 0, st, logits, NL, pick, wts, T, E, \
+                           top_k, shared ? 1 : 0),                                                              \
+                    "select_rows")
+  if (vpl <= 4) TFB_SEL(4);
+  if (vpl <= 8) TFB_SEL(8);
+  if (vpl <= 16) TFB_SEL(16);
+  TFB_SEL(32);
+#undef TFB_SEL
+}
+
+extern "C" int tfb_plan(const int32_t* picks, int64_t pairs, int experts, int tile, int32_t* members, int32_t* items,
+                        int32_t* counts, void* stream) {
+  TFB_REQUIRE(picks && members && items && counts, "plan: null pointer");
+  TFB_REQUIRE(experts >= 1 && experts <= PLAN_EMAX, "plan: at most %d experts, not %d", PLAN_EMAX, experts);
+  TFB_REQUIRE(tile >= 1, "plan: items hold at least one pair");
+  TFB_REQUIRE(pairs >= 0 && pairs < (int64_t(1) << 30), "plan: bad pair count");
+  const size_t smem = sizeof(int) * 32 * (size_t)experts;
+  static int configured[64] = {0};
+  int dev = 0;
+  TFB_CUDA(cudaGetDevice(&dev), "plan: cudaGetDevice");
+  if (dev < 64 && !configured[dev]) {
+    TFB_CUDA(cudaFuncSetAttribute(plan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  (int)(sizeof(int) * 32 * PLAN_EMAX)),
+             "plan: shared memory opt-in");
+    configured[dev] = 1;
+  }
+  return check_cuda(launch(plan_kernel, dim3(1), dim3(PLAN_THREADS), smem, static_cast<cudaStream_t>(stream), picks,
+                           (int)pairs, experts, tile, members, items, counts),
+                    "plan");
+}
+
+extern "C" int tfb_combine(const void* y, int y_bf16, const float* wts, void* out, int out_f32, int T, int slots,
+                           int D, void* stream) {
+  TFB_REQUIRE(y && wts && out, "combine: null pointer");
+  TFB_REQUIRE(D > 0 && D % 4 == 0 && slots >= 1, "combine: D must be a multiple of 4 and slots >= 1");
+  TFB_REQUIRE(aligned16(y) && aligned16(out), "combine: y and out must be 16-byte aligned");
+  if (T <= 0) return TFB_OK;
+  const dim3 grid(T, (D + 1023) / 1024);
+  auto st = static_cast<cudaStream_t>(stream);
+  cudaError_t e;
+  if (y_bf16 && out_f32)
+    e = launch(combine_kernel<__nv_bfloat16, float>, grid, dim3(256), 0, st, static_cast<const __nv_bfloat16*>(y), wts,
+               static_cast<float*>(out), slots, D);
+  else if (y_bf16)
+    e = launch(combine_kernel<__nv_bfloat16, __nv_bfloat16>, grid, dim3(256), 0, st,
+               static_cast<const __nv_bfloat16*>(y), wts, static_cast<__nv_bfloat16*>(out), slots, D);
+  else if (out_f32)
+    e = launch(combine_kernel<float, float>, grid, dim3(256), 0, st, static_cast<const float*>(y), wts,
+               static_cast<float*>(out), slots, D);
+  else
+    e = launch(combine_kernel<float, __nv_bfloat16>, grid, dim3(256), 0, st, static_cast<const float*>(y), wts,
+               static_cast<__nv_bfloat16*>(out), slots, D);
+  return check_cuda(e, "combine");
+}

@@ -1,0 +1,5 @@
+// The whole library as one translation unit (the kernels share one device status word and inline helpers).
+#include "api.cu"
+#include "routing.cu"
+#include "pack.cu"
+#include "experts_decode.cu"

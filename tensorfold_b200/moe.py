@@ -1,0 +1,141 @@
+"""Softmax top-k MoE with an optional sigmoid-gated shared expert, on fp32 logits (ties to the lower id).
+
+Mirrors ``src/tensorfold/cuda/moe.py`` of the reference (router, select_rows, select, moe, combine, MoEBuffers,
+Routed, run) over hand-written sm_100a kernels; each row routes and runs on its own.  ``shared=True`` is the
+reference's layout (router rows [E + 1, D], slot k = expert E behind a sigmoid gate); ``shared=False`` drops that
+slot for layers without a shared expert.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from . import _lib
+from . import experts as grouped
+
+
+def _stream(t: torch.Tensor) -> int:
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def router(x: torch.Tensor, rows: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """x [R, D] bf16, rows [NE, D] bf16 (router rows, then the shared expert's gate row if any) -> [R, NE] fp32."""
+
+    if not x.is_cuda:
+        raise ValueError("x must be a CUDA tensor (this library has no CPU path)")
+    if x.dtype != torch.bfloat16 or rows.dtype != torch.bfloat16 or x.dim() != 2 or rows.dim() != 2:
+        raise ValueError("router: x and rows must be 2-D bf16")
+    m, d = x.shape
+    ne = rows.shape[0]
+    if rows.shape[1] != d or x.stride(1) != 1 or not rows.is_contiguous():
+        raise ValueError("router: x [R, D] with unit-stride rows, rows [NE, D] contiguous")
+    if out is None:
+        out = torch.empty((m, ne), dtype=torch.float32, device=x.device)
+    elif out.shape != (m, ne) or out.dtype != torch.float32 or not out.is_contiguous():
+        raise ValueError("router: out must be contiguous fp32 [R, NE]")
+    with torch.cuda.device(x.device):
+        _lib.call("tfb_router", x.data_ptr(), x.stride(0), rows.data_ptr(), out.data_ptr(), m, d, ne, _stream(x))
+    return out
+
+
+class MoEBuffers:
+    """Static scratch for up to ``rows`` rows (CUDA-graph safe); ``prefill`` picks the experts' prefill arithmetic."""
+
+    def __init__(self, rows: int, cfg, device: torch.device | str, *, prefill: bool = False,
+                 shared: bool = True) -> None:
+        extra = 1 if shared else 0
+        slots = cfg.num_experts_per_tok + extra
+        self.rows, self.slots, self.shared = rows, slots, shared
+        self.logits = torch.empty((rows, cfg.num_experts + extra), dtype=torch.float32, device=device)
+        self.pick = torch.empty((rows, slots), dtype=torch.int32, device=device)
+        self.wts = torch.empty((rows, slots), dtype=torch.float32, device=device)
+        self.plan = grouped.Plan(rows, slots, cfg.num_experts + extra, device, prefill=prefill)
+        self.act = torch.empty((rows, slots, cfg.moe_intermediate_size), dtype=torch.bfloat16, device=device)
+        self.y = torch.empty((rows, slots, cfg.hidden_size), dtype=torch.bfloat16 if prefill else torch.float32,
+                             device=device)
+
+
+def select_rows(logits: torch.Tensor, buf: MoEBuffers, top_k: int, experts: int) -> None:
+    """Each row's experts and weights, rows in parallel (buf.pick, buf.wts)."""
+
+    rows, nl = logits.shape
+    shared = buf.slots == top_k + 1
+    if buf.slots not in (top_k, top_k + 1) or rows > buf.rows:
+        raise ValueError(f"{rows} rows of top-{top_k} do not fit buffers of {buf.rows} x {buf.slots}")
+    if logits.dtype != torch.float32 or not logits.is_contiguous():
+        raise ValueError("logits must be contiguous fp32")
+    with torch.cuda.device(logits.device):
+        _lib.call("tfb_select_rows", logits.data_ptr(), nl, buf.pick.data_ptr(), buf.wts.data_ptr(), rows, experts,
+                  top_k, 1 if shared else 0, _stream(logits))
+
+
+def select(logits: torch.Tensor, buf: MoEBuffers, top_k: int, experts: int,
+           tile: int = grouped.PREFILL_TILE) -> None:
+    """Each row's experts and weights (rows in parallel), then the pairs grouped by expert, ``tile`` a prompt's item."""
+
+    select_rows(logits, buf, top_k, experts)
+    grouped.route(buf.pick[:logits.shape[0]], buf.plan, tile)
+
+
+def moe(x: torch.Tensor, router_rows: torch.Tensor, ex: grouped.Experts, buf: MoEBuffers, top_k: int,
+        experts: int) -> MoEBuffers:
+    """Route x [R, D] and run its experts into buf.y [R, slots, D] (bf16 in prefill)."""
+
+    rows = x.shape[0]
+    router(x, router_rows, buf.logits[:rows])
+    select(buf.logits[:rows], buf, top_k, experts)
+    grouped.gate_up(x, ex, buf.plan, buf.act.view(-1, ex.width), rows)
+    grouped.down(buf.act.view(-1, ex.width), ex, buf.plan, buf.y.view(-1, ex.dims), rows)
+    return buf
+
+
+def combine(y: torch.Tensor, wts: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """y [R, S, D] (fp32, or bf16 in prefill) and wts [R, S] fp32 -> [R, D] bf16 (or fp32 when ``out`` is fp32)."""
+
+    rows, slots, dims = y.shape
+    if y.dtype not in (torch.float32, torch.bfloat16) or not y.is_contiguous() or not wts.is_contiguous():
+        raise ValueError("combine: y must be contiguous fp32 or bf16, wts contiguous fp32")
+    if out is None:
+        out = torch.empty((rows, dims), dtype=torch.bfloat16, device=y.device)
+    with torch.cuda.device(y.device):
+        _lib.call("tfb_combine", y.data_ptr(), 1 if y.dtype == torch.bfloat16 else 0, wts.data_ptr(), out.data_ptr(),
+                  1 if out.dtype == torch.float32 else 0, rows, slots, dims, _stream(y))
+    return out
+
+
+@dataclass
+class Routed:
+    """A layer's router rows ([E + 1, D] bf16 with the shared expert's gate row last, or [E, D]) and its experts."""
+
+    router: torch.Tensor
+    experts: grouped.Experts
+    top_k: int
+    shared: bool = True
+
+    @property
+    def count(self) -> int:
+        return self.router.shape[0] - (1 if self.shared else 0)
+
+
+class _Shape:
+    def __init__(self, m: Routed) -> None:
+        self.num_experts_per_tok, self.num_experts = m.top_k, m.count
+        self.moe_intermediate_size, self.hidden_size = m.experts.width, m.experts.dims
+
+
+_scratch: dict[tuple, MoEBuffers] = {}
+
+
+def run(x: torch.Tensor, m: Routed, *, prefill: bool = False) -> torch.Tensor:
+    """x [R, D] bf16 -> [R, D] bf16: its top-k experts by renormalized softmax weight (plus the shared expert)."""
+
+    rows = x.shape[0]
+    size = 1 << max(4, (rows - 1).bit_length())                 # scratch per power of two, reused by every layer
+    key = (size, m.count, m.top_k, m.experts.width, m.experts.dims, prefill, m.shared, x.device)
+    buf = _scratch.get(key)
+    if buf is None:
+        buf = _scratch[key] = MoEBuffers(size, _Shape(m), x.device, prefill=prefill, shared=m.shared)
+    moe(x.contiguous(), m.router, m.experts, buf, m.top_k, m.count)
+    return combine(buf.y[:rows], buf.wts[:rows])

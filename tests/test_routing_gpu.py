@@ -1,0 +1,141 @@
+"""Router, selection, plan and combine on the GPU against the CPU oracle: indices and sort order bit for bit."""
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import bits
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _logits(t, ne, seed):
+    g = torch.Generator().manual_seed(seed)
+    return torch.randn((t, ne), generator=g)
+
+
+@pytest.mark.parametrize("t,d,ne", [(1, 2048, 128), (5, 768, 13), (64, 2048, 129), (300, 256, 50), (17, 6144, 257)])
+def test_router_logits_bit_exact(t, d, ne):
+    from oracle import cpu
+    from tensorfold_b200 import moe
+
+    g = torch.Generator().manual_seed(t + d)
+    x = torch.randn((t, d), generator=g).to(torch.bfloat16)
+    w = (torch.randn((ne, d), generator=g) * 0.02).to(torch.bfloat16)
+    got = moe.router(x.to(DEV), w.to(DEV)).cpu().numpy()
+    assert np.array_equal(got, cpu.router_logits(bits(x), bits(w)))
+
+
+def test_router_rows_do_not_depend_on_the_window():
+    from tensorfold_b200 import moe
+
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn((40, 512), generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn((33, 512), generator=g) * 0.02).to(torch.bfloat16).to(DEV)
+    full = moe.router(x, w)
+    for a, b in ((0, 1), (7, 8), (3, 20), (39, 40)):
+        assert torch.equal(moe.router(x[a:b], w), full[a:b])
+    wide = torch.zeros((40, 1024), dtype=torch.bfloat16, device=DEV)          # strided rows
+    wide[:, :512] = x
+    assert torch.equal(moe.router(wide[:, :512], w), full)
+
+
+class _Cfg:
+    def __init__(self, e, k, ni=64, d=64):
+        self.num_experts, self.num_experts_per_tok, self.moe_intermediate_size, self.hidden_size = e, k, ni, d
+
+
+@pytest.mark.parametrize("t,e,k,shared", [(1, 128, 8, False), (64, 128, 8, False), (40, 64, 10, True),
+                                         (33, 256, 8, True), (9, 160, 8, False), (20, 1000, 6, True), (7, 5, 5, False)])
+def test_select_rows_against_the_oracle(t, e, k, shared):
+    from oracle import cpu
+    from tensorfold_b200 import moe
+
+    logits = _logits(t, e + (1 if shared else 0), 100 + t + e)
+    logits[0, :] = 0.0
+    if t > 2:
+        logits[2, : min(e, 12)] = 1.25
+    buf = moe.MoEBuffers(t, _Cfg(e, k), DEV, shared=shared)
+    moe.select_rows(logits.to(DEV), buf, k, e)
+    pick, wts = buf.pick.cpu().numpy(), buf.wts.cpu().numpy()
+    want_pick, want_wts = cpu.topk_rows(logits.numpy(), e, k, shared)
+    assert np.array_equal(pick, want_pick)                                     # indices: bit exact
+    ln = logits.numpy()
+    for r in range(t):
+        assert pick[r, :k].tolist() == sorted(range(e), key=lambda i: (-ln[r, i], i))[:k]
+    assert pick[0, :k].tolist() == list(range(k))                              # ties go to the lower id
+    # weights: bf16 values within one bf16 ulp of the oracle's (exp's last bits are not pinned by the reference)
+    assert np.array_equal(wts.view(np.uint32) & 0xFFFF, np.zeros_like(wts, dtype=np.uint32))
+    ulp = np.maximum(np.abs(want_wts), 2.0 ** -126) * 2.0 ** -7
+    assert (np.abs(wts - want_wts) <= ulp).all()
+
+
+def want_plan(picks, e, tile):
+    flat = picks.reshape(-1).tolist()
+    items, members = [], []
+    for ex in range(e):
+        pairs = [p for p, v in enumerate(flat) if v == ex]
+        for j in range(0, len(pairs), tile):
+            items.append([ex, len(members) + j, min(tile, len(pairs) - j)])
+        members += pairs
+    return items, members, len(set(flat))
+
+
+@pytest.mark.parametrize("rows,prefill,tile", [(23, False, 64), (23, True, 64), (300, False, 64), (300, True, 64),
+                                              (1500, True, 64), (1500, True, 16), (1, False, 64), (4000, True, 64)])
+def test_plan_groups_pairs_by_expert(rows, prefill, tile):
+    """The reference's plan golden (tests/cuda/test_experts.py:118-134): 7 slots, 50 experts, one expert in every row."""
+
+    from tensorfold_b200 import experts
+
+    slots, e = 7, 50
+    g = torch.Generator().manual_seed(9)
+    picks = torch.stack([torch.randperm(e, generator=g)[:slots] for _ in range(rows)]).to(torch.int32)
+    picks[:, 0] = 3
+    plan = experts.Plan(rows, slots, e, DEV, prefill=prefill)
+    experts.route(picks.to(DEV), plan, tile)
+    assert plan.tile == (tile if prefill else experts.TILE)
+    want_items, want_members, distinct = want_plan(picks, e, plan.tile)
+    n = int(plan.counts[0])
+    assert n == len(want_items) and int(plan.counts[1]) == distinct
+    assert plan.items[:n].tolist() == want_items
+    assert plan.members.tolist() == want_members
+
+
+def test_plan_with_many_experts_and_skipped_ids():
+    from oracle import cpu
+    from tensorfold_b200 import experts
+
+    g = torch.Generator().manual_seed(4)
+    e, rows, slots = 1024, 700, 9
+    picks = torch.randint(0, e + 3, (rows, slots), generator=g).to(torch.int32)     # ids >= e are left out
+    plan = experts.Plan(rows, slots, e, DEV)
+    experts.route(picks.to(DEV), plan)
+    items, members, counts = cpu.plan(picks.numpy(), e, 16)
+    n = int(plan.counts[0])
+    assert n == len(items) and plan.counts.tolist() == counts.tolist()
+    assert np.array_equal(plan.items[:n].cpu().numpy(), items)
+    assert np.array_equal(plan.members[:len(members)].cpu().numpy(), members)
+
+
+@pytest.mark.parametrize("ydtype", [torch.float32, torch.bfloat16])
+def test_combine_slot_order_fma_chain(ydtype):
+    from tensorfold_b200 import moe
+
+    g = torch.Generator().manual_seed(8)
+    t, s, d = 19, 9, 2048
+    y = torch.randn((t, s, d), generator=g).to(ydtype)
+    w = torch.rand((t, s), generator=g).to(torch.bfloat16).float()
+    got = moe.combine(y.to(DEV), w.to(DEV)).cpu()
+    acc = np.zeros((t, d), dtype=np.float64)
+    yf, wf = y.float().numpy().astype(np.float64), w.numpy().astype(np.float64)
+    acc32 = np.zeros((t, d), dtype=np.float32)
+    for k in range(s):
+        acc32 = (wf[:, k:k + 1] * yf[:, k] + acc32.astype(np.float64)).astype(np.float32)   # fma: one rounding a step
+    want = torch.from_numpy(acc32).to(torch.bfloat16)
+    assert (got.view(torch.int16) != want.view(torch.int16)).float().mean() < 1e-4          # double-rounding slack only
+    assert torch.allclose(got.float(), want.float(), rtol=2 ** -7, atol=1e-6)
+    out32 = torch.empty((t, d), dtype=torch.float32, device=DEV)
+    moe.combine(y.to(DEV), w.to(DEV), out32)
+    assert np.abs(out32.cpu().numpy() - acc32).max() <= 1e-6 * np.abs(acc32).max()
