@@ -11,7 +11,7 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda"
 
 # (SwiGLU, limit, experts incl. shared, D, NI, shared slots): small twins of the reference's cases
-CASES = [(True, 0.0, 41, 256, 96, 1), (True, 10.0, 19, 512, 128, 1), (False, 0.0, 12, 384, 192, 2)]
+CASES = [(True, 0.0, 41, 256, 128, 1), (True, 10.0, 19, 512, 128, 1), (False, 0.0, 12, 384, 192, 2)]
 DTYPES = [torch.bfloat16, torch.float16]
 
 
