@@ -1,0 +1,324 @@
+"""Benchmark of the routed-expert MoE layer (affine 4-bit group-64 experts) on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--rows T]
+
+Workload: BASELINE config 2 - one layer, hidden 2048, 128 experts of width 768, top-8 - at 64-token decode (the
+headline line), with 1-token decode and the 2048-token prompt reported beside it under "sweep".  One step = one pass of
+the whole layer (router, top-k, plan, gate/up + SiLU-gate, down, combine) over one batch of seeded synthetic tokens.
+Two independent weight copies (340 MB each, together far beyond the 126 MB L2) alternate step by step.
+
+Prints ONE JSON line (rank 0).  ``--impl reference`` times the CPU restatement of the reference's path (oracle/) on
+the host cores instead.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+METRIC = "moe_layer_tokens_per_s"
+UNIT = "tokens/s"
+SMI_FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+
+def peaks() -> tuple[float, float, str]:
+    """(HBM GB/s, dense bf16 TFLOP/s, which) from MEASURED_PEAKS.json, else the pool's earlier measurement."""
+
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return float(d["hbm_gbs"]), float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons sampled every 100 ms while the timed region runs."""
+
+    def __init__(self, index: int) -> None:
+        self.index, self.proc, self.path = index, None, None
+
+    def __enter__(self):
+        try:
+            f = tempfile.NamedTemporaryFile("w", suffix=".csv", delete=False)
+            self.path = f.name
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={SMI_FIELDS}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.index)], stdout=f, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+        return self
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            time.sleep(0.15)
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self) -> dict:
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if not self.path or not os.path.exists(self.path):
+            return out
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in Path(self.path).read_text().splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                mx.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        os.unlink(self.path)
+        if sm:
+            out.update(sm_mhz=statistics.median(sm), sm_max_mhz=max(mx), reasons=sorted(reasons), samples=len(sm))
+        return out
+
+
+def layer_bytes(shape, rows: int, distinct: int) -> dict:
+    """Algorithmic bytes of one layer call: packed weights of the distinct experts touched + router rows + the tokens
+    in and out; intermediates (logits, plan, act, y) are not counted."""
+
+    d, ni = shape.dims, shape.width
+    per_matrix = ni * d // 2 + ni * (d // 64) * 4
+    ne = shape.experts + (1 if shape.shared else 0)
+    return {"gate_up": distinct * 2 * per_matrix + rows * d * 2, "down": distinct * per_matrix,
+            "layer": distinct * 3 * per_matrix + ne * d * 2 + 2 * rows * d * 2}
+
+
+def cpu_baseline(shape, rows: int, steps: int, warmup: int):
+    """The CPU restatement of the reference's path (oracle/cpu_moe.c, OpenMP over all host cores) on the same
+    synthetic workload; returns (tokens/s, seconds a step, cores)."""
+
+    import numpy as np
+    import torch
+
+    from oracle import cpu
+    from tensorfold_b200 import synthetic
+
+    def b16(t):
+        return t.contiguous().view(torch.int16).numpy().view(np.uint16)
+
+    def tri(m):
+        return m[0].numpy().view(np.uint32), b16(m[1]), b16(m[2])
+
+    gate, up, down = (tri(m) for m in synthetic.affine_layer(shape, "cpu"))
+    x = b16(synthetic.activations(shape, rows, "cpu"))
+    rt = b16(synthetic.router_rows(shape, "cpu"))
+    times = []
+    for i in range(warmup + steps):
+        t0 = time.perf_counter()
+        cpu.moe_layer(x, rt, shape.experts, shape.top_k, shape.shared, gate, up, down, 64, True)
+        if i >= warmup:
+            times.append(time.perf_counter() - t0)
+    sec = sum(times) / len(times)
+    return rows / sec, sec, cpu.threads()
+
+
+def run_reference(args) -> None:
+    """--impl reference: the reference's CPU path (restated in oracle/) on the host cores; rank 0 only."""
+
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    from tensorfold_b200 import synthetic
+
+    shape, rows = synthetic.C2, args.rows
+    value, sec, cores = cpu_baseline(shape, rows, args.steps, args.warmup)
+    sample = f"{rows}-token batch of the c2 layer a step, all experts' math on the host ({cores} threads)"
+    line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": workload_config(shape, rows, args.gpus),
+            "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+            "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line))
+
+
+def workload_config(shape, rows: int, gpus: int) -> dict:
+    return {"workload": f"BASELINE config 2: one MoE layer, {rows}-token decode, hidden {shape.dims}, {shape.experts} "
+                        f"experts x FFN {shape.width}, top-{shape.top_k}, MLX affine 4-bit g64 (fp16 scales)",
+            "rows_per_gpu": rows, "l2": "two 340 MB weight copies alternate (inputs larger than the 126 MB L2)",
+            "parallelism": f"ep{gpus}" if gpus > 1 else "single"}
+
+
+def time_graphs(torch, graphs, steps: int, warmup: int) -> float:
+    """Milliseconds a step: `steps` replays alternating over `graphs`, CUDA events on the current stream."""
+
+    for i in range(warmup):
+        graphs[i % len(graphs)].replay()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for i in range(steps):
+        graphs[i % len(graphs)].replay()
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) / steps
+
+
+def bench_rows(torch, shape, layers, rows: int, steps: int, warmup: int, hbm: float):
+    """Device-resident timing of the whole layer at `rows` tokens plus the gate/up kernel alone."""
+
+    from tensorfold_b200 import experts, moe, synthetic
+
+    dev = layers[0].router.device
+    runners = [moe.Runner(m, rows, device=dev) for m in layers]
+    x = synthetic.activations(shape, rows, dev)
+    for r in runners:
+        r.x.copy_(x)
+    ms = time_graphs(torch, [r.graph for r in runners], steps, warmup)
+    distinct = int(runners[0].buf.plan.counts[1])
+    nbytes = layer_bytes(shape, rows, distinct)
+    # the dominant kernel alone: gate/up over the plan the layer just made, 4 launches a weight copy in one graph
+    reps = 4
+    g = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream(dev)
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.graph(g, stream=side):
+        for _ in range(reps):
+            for r in runners:
+                experts.gate_up(r.x, r.layer.experts, r.buf.plan, r.buf.act.view(-1, shape.width), rows)
+    kms = time_graphs(torch, [g], max(3, steps // 4), 3) / (reps * len(runners))
+    gbs = nbytes["gate_up"] / (kms * 1e-3) / 1e9
+    return {"rows": rows, "ms_per_step": ms, "tokens_per_s": rows / (ms * 1e-3), "distinct_experts": distinct,
+            "layer_bytes": nbytes["layer"], "layer_gbs": nbytes["layer"] / (ms * 1e-3) / 1e9,
+            "layer_frac_of_hbm": nbytes["layer"] / (ms * 1e-3) / 1e9 / hbm,
+            "gate_up_us": kms * 1e3, "gate_up_bytes": nbytes["gate_up"], "gate_up_gbs": gbs,
+            "launches_per_step": runners[0].launches}, runners
+
+
+def bench_e2e(torch, runners, shape, rows: int, steps: int, warmup: int):
+    """The same step through the public API with HOST buffers: pinned tokens in, layer, result back, every step."""
+
+    from tensorfold_b200 import synthetic
+
+    x_host = synthetic.activations(shape, rows, "cpu").pin_memory()
+    out_host = torch.empty((rows, shape.dims), dtype=torch.bfloat16).pin_memory()
+    for i in range(warmup):
+        out_host.copy_(runners[i % len(runners)](x_host), non_blocking=True)
+        torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for i in range(steps):
+        out_host.copy_(runners[i % len(runners)](x_host), non_blocking=True)
+        torch.cuda.current_stream().synchronize()               # the caller reads the result before the next step
+    b.record()
+    torch.cuda.synchronize()
+    ms = a.elapsed_time(b) / steps
+    nbytes = rows * shape.dims * 2
+    return {"value": rows / (ms * 1e-3), "unit": UNIT, "ms_per_step": ms, "h2d_bytes_per_step": nbytes,
+            "d2h_bytes_per_step": nbytes}
+
+
+def run_ours(args) -> None:
+    import torch
+
+    from tensorfold_b200 import _lib, experts, moe, synthetic
+
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a GPU: there is no CPU fallback (use --impl reference for the CPU baseline)")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=dev)
+    hbm, tflops, which = peaks()
+    shape, rows = synthetic.C2, args.rows
+    layers = []
+    for copy in range(2):
+        gate, up, down = synthetic.affine_layer(shape, dev, torch.float16, copy=copy)
+        layers.append(moe.Routed(synthetic.router_rows(shape, dev), experts.make([gate, up], down, 64), shape.top_k,
+                                 shared=shape.shared))
+        del gate, up, down
+    torch.cuda.synchronize()
+
+    with ClockSampler(local) as clocks:
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        head, runners = bench_rows(torch, shape, layers, rows, args.steps, args.warmup, hbm)
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+    e2e = bench_e2e(torch, runners, shape, rows, args.steps, args.warmup)
+    status = _lib.kernel_status()
+    if status != 0:
+        raise SystemExit(f"a kernel recorded device status {status}")
+    ms = head["ms_per_step"]
+    if world > 1:
+        t = torch.tensor([ms, e2e["ms_per_step"]], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, e2e_ms = t.tolist()
+        e2e["ms_per_step"], e2e["value"] = e2e_ms, world * rows / (e2e_ms * 1e-3)
+        e2e["h2d_bytes_per_step"] *= world
+        e2e["d2h_bytes_per_step"] *= world
+    sweep = []
+    if world == 1 and not args.no_sweep:
+        del runners
+        for t_rows in (1, 2048):
+            res, rr = bench_rows(torch, shape, layers, t_rows, max(5, args.steps // 2), args.warmup, hbm)
+            res["form"] = "decode kernels"
+            sweep.append(res)
+            del rr
+    if rank != 0:
+        return
+    value = world * rows / (ms * 1e-3)
+    cpu = None
+    if not args.no_cpu:
+        v, sec, cores = cpu_baseline(shape, rows, 1, 1)
+        cpu = {"value": v, "unit": UNIT, "cores": cores, "kind": "port",
+               "sample": f"2 passes (1 warm-up) of the same {rows}-token layer call, {sec:.2f} s a pass"}
+    line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic", "config": workload_config(shape, rows, world),
+            "clocks": clocks.summary(), "e2e": e2e, "gpu_launches": head["launches_per_step"] * args.steps,
+            "roofline": {"bound": "hbm", "kernel": "decode_kernel<M=2, SwiGLU> (gate/up)",
+                         "achieved": head["gate_up_gbs"], "peak": hbm, "unit": "GB/s",
+                         "frac": head["gate_up_gbs"] / hbm, "peak_source": f"of {which}", "traffic": None,
+                         "bytes_per_launch": head["gate_up_bytes"], "us_per_launch": head["gate_up_us"]},
+            "layer": {k: head[k] for k in ("distinct_experts", "layer_bytes", "layer_gbs", "layer_frac_of_hbm")},
+            "cpu_baseline": cpu, "sweep": sweep}
+    print(json.dumps(line))
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--rows", type=int, default=64, help="tokens a step on each GPU")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-sweep", action="store_true", help="skip the 1-token and 2048-token lines")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    if args.impl == "reference":
+        args.steps = min(args.steps, 400)                        # a bounded CPU sample: a pass takes ~0.3 s
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

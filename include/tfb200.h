@@ -56,6 +56,13 @@ int tfb_select_rows(const float* logits, int NL, int32_t* pick, float* wts, int 
 int tfb_plan(const int32_t* picks, int64_t pairs, int experts, int tile, int32_t* members, int32_t* items,
              int32_t* counts, void* stream);
 
+/* tfb_select_rows followed by tfb_plan in ONE launch (one thread block) for calls of at most
+ * tfb_select_plan_max_rows() rows: same pick / wts / members / items / counts, bit for bit.  The plan covers
+ * E + (shared != 0) experts.  Replaces moe.select for decode-sized calls: src/tensorfold/cuda/moe.py:111-116. */
+int tfb_select_plan_max_rows(void);
+int tfb_select_plan(const float* logits, int NL, int32_t* pick, float* wts, int T, int E, int top_k, int shared,
+                    int tile, int32_t* members, int32_t* items, int32_t* counts, void* stream);
+
 /* out[T, D] = sum over slots, in slot order, of wts[T, slots] * y[T, slots, D] (fp32 fma chain from 0), rounded once.
  * y is fp32 (y_bf16 = 0) or bf16; out is bf16 (out_f32 = 0) or fp32.
  * Replaces moe.combine / _combine: src/tensorfold/cuda/moe.py:131-151, and combine_kernel of
@@ -83,6 +90,7 @@ int tfb_dequant(const void* blocks, int gs, int sb_type, int mode, void* out, in
 /* Grouped 4-bit expert matmul, decode form, over a plan.  x: bf16 rows of K = kg * gs inputs (row stride x_stride
  * elements, 16-byte aligned); pair p reads row p / slots when slots > 0, else row p.  w: blocks
  * [E, nb, kg, M, 288] (M = 2 for epi 2, else 1).  out rows of n = 32 * nb columns, row index = pair id.
+ * Items hold at most 8 pairs in this form (plan with tile 8).
  * epi 0: fp32 out; 1: bf16 relu(bf16 acc)^2; 2: bf16 SwiGLU(matrix 0, matrix 1) clipped at `limit` when > 0;
  * 3: bf16 out.  max_units = upper bound of items * nb (the grid).  sb_type as tfb_dequant.
  * Replaces the extension entry `run`: src/tensorfold/cuda/experts.cpp:43-48, experts.cu:130-155,287-351. */

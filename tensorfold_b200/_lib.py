@@ -18,6 +18,7 @@ SIGNATURES: dict[str, tuple] = {
     "tfb_router": (P, L, P, P, I, I, I, P),
     "tfb_select_rows": (P, I, P, P, I, I, I, I, P),
     "tfb_plan": (P, L, I, I, P, P, P, P),
+    "tfb_select_plan": (P, I, P, P, I, I, I, I, I, P, P, P, P),
     "tfb_combine": (P, I, P, P, I, I, I, I, P),
     "tfb_pack": (P, P, P, I, P, I, I, I, P),
     "tfb_unpack": (P, I, P, P, P, I, I, I, P),
@@ -41,6 +42,8 @@ def lib() -> ctypes.CDLL:
     handle.tfb_version.restype = c_int
     handle.tfb_set_pdl.argtypes = (c_int,)
     handle.tfb_set_pdl.restype = c_int
+    handle.tfb_select_plan_max_rows.restype = c_int
+    handle.tfb_select_plan_max_rows.argtypes = ()
     for name, args in SIGNATURES.items():
         fn = getattr(handle, name)
         fn.argtypes = args

@@ -64,6 +64,60 @@ router_kernel(const __nv_bfloat16* __restrict__ X, int64_t x_stride, const __nv_
     }
 }
 
+// The same arithmetic for few rows: a CTA an expert (its row of W read once into registers), a warp a row at a
+// time, every chunk of the row's inputs in flight at once.  Bits equal router_kernel's.
+constexpr int RR_WARPS = 8, RR_ROWS = 64, RR_CH = 8;
+
+__global__ void __launch_bounds__(RR_WARPS * 32)
+router_rows_kernel(const __nv_bfloat16* __restrict__ X, int64_t x_stride, const __nv_bfloat16* __restrict__ W,
+                   float* __restrict__ out, int T, int D, int NE) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int e = blockIdx.x, rbase = blockIdx.y * RR_ROWS;
+  constexpr int RPW = RR_ROWS / RR_WARPS;
+  float acc[RPW];
+#pragma unroll
+  for (int i = 0; i < RPW; ++i) acc[i] = 0.f;
+  const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+  pdl_wait();
+  for (int kb = 0; kb < D; kb += 256 * RR_CH) {
+    float wv[RR_CH][8];
+#pragma unroll
+    for (int c = 0; c < RR_CH; ++c) {
+      const int k = kb + 256 * c + 8 * lane;
+      unpack8(k < D ? ldg_nc(W + (size_t)e * D + k) : zero, wv[c]);
+    }
+#pragma unroll
+    for (int i = 0; i < RPW; ++i) {
+      const int r = rbase + warp + RR_WARPS * i;
+      if (r >= T) break;
+      uint4 xv[RR_CH];
+#pragma unroll
+      for (int c = 0; c < RR_CH; ++c) {
+        const int k = kb + 256 * c + 8 * lane;
+        xv[c] = k < D ? ldg_nc(X + (size_t)r * x_stride + k) : zero;
+      }
+#pragma unroll
+      for (int c = 0; c < RR_CH; ++c) {
+        if (kb + 256 * c + 8 * lane < D) {
+          float xf[8];
+          unpack8(xv[c], xf);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) acc[i] = fmaf(xf[j], wv[c][j], acc[i]);
+        }
+      }
+    }
+  }
+  pdl_launch_dependents();
+#pragma unroll
+  for (int i = 0; i < RPW; ++i) {
+    const int r = rbase + warp + RR_WARPS * i;
+    float a = acc[i];
+#pragma unroll
+    for (int m = 16; m >= 1; m >>= 1) a = a + __shfl_xor_sync(0xffffffffu, a, m);
+    if (lane == 0 && r < T) out[(size_t)r * NE + e] = a;
+  }
+}
+
 // ================================================================================================================
 // Selection: a warp a row.  TOPK rounds of (largest fp32 logit, the lower id among equals), weight
 // bf16(exp(l_k - l_0) / sum_k exp(l_k - l_0)); with a shared expert, slot TOPK = id E with weight
@@ -71,24 +125,20 @@ router_kernel(const __nv_bfloat16* __restrict__ X, int64_t x_stride, const __nv_
 // ================================================================================================================
 constexpr int S_WARPS = 4;
 
+// One row by one warp: writes the row's slots of pick / wts; returns this lane's pick (lanes < slots) for callers
+// that keep the picks on chip.
 template <int VPL>
-__global__ void __launch_bounds__(S_WARPS * 32)
-select_kernel(const float* __restrict__ L, int NL, int* __restrict__ pick, float* __restrict__ wts, int T, int E,
-              int top_k, int shared) {
-  const int lane = threadIdx.x & 31;
-  const int r = blockIdx.x * S_WARPS + (threadIdx.x >> 5);
-  if (r >= T) return;
-  pdl_wait();
+__device__ __forceinline__ int select_row(const float* __restrict__ Lr, int E, int top_k, int shared, int lane,
+                                          int* __restrict__ pick_row, float* __restrict__ wts_row) {
   const float NEG = __int_as_float(0xff800000);
   float v[VPL];
 #pragma unroll
   for (int i = 0; i < VPL; ++i) {
     const int e = i * 32 + lane;
-    v[i] = e < E ? L[(size_t)r * NL + e] : NEG;
+    v[i] = e < E ? Lr[e] : NEG;
   }
-  pdl_launch_dependents();
   float top = 0.f, total = 0.f, my_ex = 0.f;
-  int my_pick = 0;
+  int my_pick = -1;
   for (int k = 0; k < top_k; ++k) {
     float bv = v[0];
     int bi = lane;
@@ -118,15 +168,29 @@ select_kernel(const float* __restrict__ L, int NL, int* __restrict__ pick, float
     for (int i = 0; i < VPL; ++i)
       if (i * 32 + lane == bi) v[i] = NEG;
   }
-  const int slots = top_k + (shared ? 1 : 0);
   if (lane < top_k) {
-    pick[(size_t)r * slots + lane] = my_pick;
-    wts[(size_t)r * slots + lane] = round_bf16(my_ex / total);
+    pick_row[lane] = my_pick;
+    wts_row[lane] = round_bf16(my_ex / total);
   } else if (lane == top_k && shared) {
-    const float sg = round_bf16(L[(size_t)r * NL + E]);
-    pick[(size_t)r * slots + lane] = E;
-    wts[(size_t)r * slots + lane] = round_bf16(1.f / (1.f + expf(-sg)));
+    const float sg = round_bf16(Lr[E]);
+    my_pick = E;
+    pick_row[lane] = E;
+    wts_row[lane] = round_bf16(1.f / (1.f + expf(-sg)));
   }
+  return my_pick;
+}
+
+template <int VPL>
+__global__ void __launch_bounds__(S_WARPS * 32)
+select_kernel(const float* __restrict__ L, int NL, int* __restrict__ pick, float* __restrict__ wts, int T, int E,
+              int top_k, int shared) {
+  const int lane = threadIdx.x & 31;
+  const int r = blockIdx.x * S_WARPS + (threadIdx.x >> 5);
+  if (r >= T) return;
+  pdl_wait();
+  const int slots = top_k + (shared ? 1 : 0);
+  select_row<VPL>(L + (size_t)r * NL, E, top_k, shared, lane, pick + (size_t)r * slots, wts + (size_t)r * slots);
+  pdl_launch_dependents();
 }
 
 // ================================================================================================================
@@ -185,18 +249,14 @@ __device__ int place_items(int c, int E, int T, int* __restrict__ items, int* __
   return off;
 }
 
-__global__ void __launch_bounds__(PLAN_THREADS)
-plan_kernel(const int* __restrict__ picks, int P, int E, int T, int* __restrict__ members, int* __restrict__ items,
-            int* __restrict__ counts) {
-  extern __shared__ int whist[];                 // [32][E]: pairs of expert e in warp w's run, then their first slot
-  __shared__ int first[PLAN_EMAX];
-  __shared__ int wsum[3][32];
+// The whole block: `picks` may live in global or shared memory.
+__device__ void plan_block(const int* picks, int P, int E, int T, int* __restrict__ members, int* __restrict__ items,
+                           int* __restrict__ counts, int* whist, int* first, int (*wsum)[32]) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   for (int i = tid; i < 32 * E; i += PLAN_THREADS) whist[i] = 0;
   const int seg = (((P + 31) / 32 + 31) / 32) * 32;
   const int p0 = min(P, warp * seg), p1 = min(P, p0 + seg);
   int* mine = whist + warp * E;
-  pdl_wait();
   __syncthreads();
   for (int base = p0; base < p1; base += 32) {
     const int p = base + lane;
@@ -217,7 +277,6 @@ plan_kernel(const int* __restrict__ picks, int P, int E, int T, int* __restrict_
   const int off = place_items(c, E, T, items, counts, wsum);
   if (tid < E) first[tid] = off;
   __syncthreads();
-  pdl_launch_dependents();
   for (int base = p0; base < p1; base += 32) {
     const int p = base + lane;
     const int e = p < p1 ? picks[p] : -1;
@@ -230,6 +289,41 @@ plan_kernel(const int* __restrict__ picks, int P, int E, int T, int* __restrict_
     if (ok && rank == 0) mine[e] = b + __popc(peers);
     __syncwarp();
   }
+}
+
+__global__ void __launch_bounds__(PLAN_THREADS)
+plan_kernel(const int* __restrict__ picks, int P, int E, int T, int* __restrict__ members, int* __restrict__ items,
+            int* __restrict__ counts) {
+  extern __shared__ int whist[];                 // [32][E]: pairs of expert e in warp w's run, then their first slot
+  __shared__ int first[PLAN_EMAX];
+  __shared__ int wsum[3][32];
+  pdl_wait();
+  plan_block(picks, P, E, T, members, items, counts, whist, first, wsum);
+  pdl_launch_dependents();
+}
+
+// Selection and plan of a small call in one block: the 32 warps take rows in turn, the picks stay in shared memory
+// for the plan.  NP = E + (shared != 0) plan experts.  Results equal select_kernel's followed by plan_kernel's.
+template <int VPL>
+__global__ void __launch_bounds__(PLAN_THREADS)
+select_plan_kernel(const float* __restrict__ L, int NL, int* __restrict__ pick, float* __restrict__ wts, int T, int E,
+                   int top_k, int shared, int tile, int* __restrict__ members, int* __restrict__ items,
+                   int* __restrict__ counts) {
+  extern __shared__ int dyn[];                   // whist [32][NP], then the picks [T * slots]
+  __shared__ int first[PLAN_EMAX];
+  __shared__ int wsum[3][32];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int slots = top_k + (shared ? 1 : 0), NP = E + (shared ? 1 : 0);
+  int* picks_sh = dyn + 32 * NP;
+  pdl_wait();
+  for (int r = warp; r < T; r += PLAN_THREADS / 32) {
+    const int mine = select_row<VPL>(L + (size_t)r * NL, E, top_k, shared, lane, pick + (size_t)r * slots,
+                                     wts + (size_t)r * slots);
+    if (lane < slots) picks_sh[r * slots + lane] = mine;
+  }
+  __syncthreads();
+  plan_block(picks_sh, T * slots, NP, tile, members, items, counts, dyn, first, wsum);
+  pdl_launch_dependents();
 }
 
 // ================================================================================================================
@@ -282,6 +376,13 @@ extern "C" int tfb_router(const void* x, int64_t x_stride, const void* rows, flo
   TFB_REQUIRE(D % 8 == 0 && x_stride % 8 == 0 && x_stride >= D, "router: D and the row stride must be multiples of 8");
   TFB_REQUIRE(aligned16(x) && aligned16(rows), "router: x and rows must be 16-byte aligned");
   if (T == 0) return TFB_OK;
+  if (T <= 4 * RR_ROWS) {
+    const dim3 rgrid(NE, (T + RR_ROWS - 1) / RR_ROWS);
+    return check_cuda(launch(router_rows_kernel, rgrid, dim3(RR_WARPS * 32), 0, static_cast<cudaStream_t>(stream),
+                             static_cast<const __nv_bfloat16*>(x), x_stride,
+                             static_cast<const __nv_bfloat16*>(rows), logits, T, D, NE),
+                      "router");
+  }
   const dim3 grid((T + R_RT - 1) / R_RT, (NE + R_WARPS * R_ET - 1) / (R_WARPS * R_ET));
   return check_cuda(launch(router_kernel, grid, dim3(R_WARPS * 32), 0, static_cast<cudaStream_t>(stream),
                            static_cast<const __nv_bfloat16*>(x), x_stride, static_cast<const __nv_bfloat16*>(rows),
@@ -330,6 +431,46 @@ extern "C" int tfb_plan(const int32_t* picks, int64_t pairs, int experts, int ti
   return check_cuda(launch(plan_kernel, dim3(1), dim3(PLAN_THREADS), smem, static_cast<cudaStream_t>(stream), picks,
                            (int)pairs, experts, tile, members, items, counts),
                     "plan");
+}
+
+// Rows the fused selection + plan kernel takes (one block); larger calls use tfb_select_rows then tfb_plan.
+extern "C" int tfb_select_plan_max_rows(void) { return 128; }
+
+extern "C" int tfb_select_plan(const float* logits, int NL, int32_t* pick, float* wts, int T, int E, int top_k,
+                               int shared, int tile, int32_t* members, int32_t* items, int32_t* counts, void* stream) {
+  TFB_REQUIRE(logits && pick && wts && members && items && counts, "select_plan: null pointer");
+  const int NP = E + (shared ? 1 : 0);
+  TFB_REQUIRE(E >= 1 && NP <= PLAN_EMAX, "select_plan: at most %d experts, not %d", PLAN_EMAX, NP);
+  TFB_REQUIRE(top_k >= 1 && top_k <= E && top_k <= 31, "select_plan: top_k=%d must be 1..min(E, 31)", top_k);
+  TFB_REQUIRE(NL >= NP, "select_plan: %d logits a row cannot hold %d experts%s", NL, E,
+              shared ? " and the shared gate" : "");
+  TFB_REQUIRE(T >= 0 && T <= tfb_select_plan_max_rows(), "select_plan: at most %d rows, not %d",
+              tfb_select_plan_max_rows(), T);
+  TFB_REQUIRE(tile >= 1, "select_plan: items hold at least one pair");
+  const int slots = top_k + (shared ? 1 : 0);
+  const size_t smem = sizeof(int) * (32 * (size_t)NP + (size_t)T * slots);
+  auto st = static_cast<cudaStream_t>(stream);
+  const int vpl = (E + 31) / 32;
+  int dev = 0;
+  TFB_CUDA(cudaGetDevice(&dev), "select_plan: cudaGetDevice");
+#define TFB_SP(V)                                                                                                  \
+  do {                                                                                                             \
+    static int configured[64] = {0};                                                                               \
+    if (dev < 64 && !configured[dev]) {                                                                            \
+      TFB_CUDA(cudaFuncSetAttribute(select_plan_kernel<V>, cudaFuncAttributeMaxDynamicSharedMemorySize,            \
+                                    (int)(sizeof(int) * (32 * PLAN_EMAX + 128 * 32))),                             \
+               "select_plan: shared memory opt-in");                                                               \
+      configured[dev] = 1;                                                                                         \
+    }                                                                                                              \
+    return check_cuda(launch(select_plan_kernel<V>, dim3(1), dim3(PLAN_THREADS), smem, st, logits, NL, pick, wts, \
+                             T, E, top_k, shared ? 1 : 0, tile, members, items, counts),                          \
+                      "select_plan");                                                                              \
+  } while (0)
+  if (vpl <= 4) TFB_SP(4);
+  if (vpl <= 8) TFB_SP(8);
+  if (vpl <= 16) TFB_SP(16);
+  TFB_SP(32);
+#undef TFB_SP
 }
 
 extern "C" int tfb_combine(const void* y, int y_bf16, const float* wts, void* out, int out_f32, int T, int slots,

@@ -75,8 +75,20 @@ def select(logits: torch.Tensor, buf: MoEBuffers, top_k: int, experts: int,
            tile: int = grouped.PREFILL_TILE) -> None:
     """Each row's experts and weights (rows in parallel), then the pairs grouped by expert, ``tile`` a prompt's item."""
 
+    rows, nl = logits.shape
+    plan = buf.plan
+    if rows <= _lib.lib().tfb_select_plan_max_rows() and logits.is_contiguous() and logits.dtype == torch.float32:
+        shared = buf.slots == top_k + 1
+        if buf.slots not in (top_k, top_k + 1) or rows > buf.rows or plan.slots != buf.slots:
+            raise ValueError(f"{rows} rows of top-{top_k} do not fit buffers of {buf.rows} x {buf.slots}")
+        plan.tile = tile if plan.prefill else grouped.TILE
+        with torch.cuda.device(logits.device):
+            _lib.call("tfb_select_plan", logits.data_ptr(), nl, buf.pick.data_ptr(), buf.wts.data_ptr(), rows, experts,
+                      top_k, 1 if shared else 0, plan.tile, plan.members.data_ptr(), plan.items.data_ptr(),
+                      plan.counts.data_ptr(), _stream(logits))
+        return
     select_rows(logits, buf, top_k, experts)
-    grouped.route(buf.pick[:logits.shape[0]], buf.plan, tile)
+    grouped.route(buf.pick[:rows], plan, tile)
 
 
 def moe(x: torch.Tensor, router_rows: torch.Tensor, ex: grouped.Experts, buf: MoEBuffers, top_k: int,
@@ -139,3 +151,43 @@ def run(x: torch.Tensor, m: Routed, *, prefill: bool = False) -> torch.Tensor:
         buf = _scratch[key] = MoEBuffers(size, _Shape(m), x.device, prefill=prefill, shared=m.shared)
     moe(x.contiguous(), m.router, m.experts, buf, m.top_k, m.count)
     return combine(buf.y[:rows], buf.wts[:rows])
+
+
+class Runner:
+    """One layer at a fixed row count captured in a CUDA graph: ``runner(x)`` copies ``x`` (host or device) into the
+    static input, replays the layer's launches and returns the static bf16 output [rows, D].
+
+    The reference's families replay their decode steps from CUDA graphs the same way
+    (``src/tensorfold/families/qwen3_5/cuda/forward.py`` tree_forward); the kernels read the routing on the device, so
+    a replay follows the new input's experts."""
+
+    def __init__(self, m: Routed, rows: int, *, prefill: bool = False, device=None) -> None:
+        device = torch.device(device if device is not None else m.router.device)
+        self.layer, self.rows, self.prefill = m, rows, prefill
+        self.x = torch.zeros((rows, m.experts.dims), dtype=torch.bfloat16, device=device)
+        self.buf = MoEBuffers(rows, _Shape(m), device, prefill=prefill, shared=m.shared)
+        self.out = torch.zeros((rows, m.experts.dims), dtype=torch.bfloat16, device=device)
+        self.launches = 5 if rows <= _lib.lib().tfb_select_plan_max_rows() else 6
+        self._stream = torch.cuda.Stream(device)
+        with torch.cuda.device(device):
+            self._stream.wait_stream(torch.cuda.current_stream(device))
+            with torch.cuda.stream(self._stream):
+                self._step()                                       # warm up outside the capture
+            torch.cuda.current_stream(device).wait_stream(self._stream)
+            torch.cuda.synchronize(device)
+            self.graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self.graph, stream=self._stream):
+                self._step()
+
+    def _step(self) -> None:
+        m = self.layer
+        moe(self.x, m.router, m.experts, self.buf, m.top_k, m.count)
+        combine(self.buf.y[:self.rows], self.buf.wts[:self.rows], self.out)
+
+    def replay(self) -> torch.Tensor:
+        self.graph.replay()
+        return self.out
+
+    def __call__(self, x: torch.Tensor) -> torch.Tensor:
+        self.x.copy_(x, non_blocking=True)
+        return self.replay()

@@ -31,7 +31,7 @@ def test_library_exports_every_declared_symbol():
 def test_binding_covers_the_header():
     from tensorfold_b200 import _lib
 
-    bound = set(_lib.SIGNATURES) | {"tfb_last_error", "tfb_version", "tfb_set_pdl"}
+    bound = set(_lib.SIGNATURES) | {"tfb_last_error", "tfb_version", "tfb_set_pdl", "tfb_select_plan_max_rows"}
     assert set(declared()) == bound
 
 

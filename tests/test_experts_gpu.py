@@ -52,6 +52,12 @@ def picks_for(rows, case, seed, hot=None):
     return torch.stack(out).to(torch.int32).to(DEV)
 
 
+def experts_tile():
+    from tensorfold_b200 import experts
+
+    return experts.TILE
+
+
 def run(ex, x, picks):
     from tensorfold_b200 import experts
 
@@ -148,7 +154,7 @@ def test_an_expert_shared_by_many_rows(case):
     alone = torch.cat([run(ex, x[r:r + 1], picks[r:r + 1])[1] for r in range(rows)])
     assert torch.equal(y, alone)
     assert int(plan.counts[1]) == slots
-    assert int(plan.counts[0]) == slots * 3                    # 37 pairs an expert: items of 16, 16 and 5
+    assert int(plan.counts[0]) == slots * -(-37 // experts_tile())   # 37 pairs an expert: full items, then the rest
 
 
 @pytest.mark.parametrize("dtype", DTYPES)

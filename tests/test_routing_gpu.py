@@ -112,7 +112,7 @@ def test_plan_with_many_experts_and_skipped_ids():
     picks = torch.randint(0, e + 3, (rows, slots), generator=g).to(torch.int32)     # ids >= e are left out
     plan = experts.Plan(rows, slots, e, DEV)
     experts.route(picks.to(DEV), plan)
-    items, members, counts = cpu.plan(picks.numpy(), e, 16)
+    items, members, counts = cpu.plan(picks.numpy(), e, experts.TILE)
     n = int(plan.counts[0])
     assert n == len(items) and plan.counts.tolist() == counts.tolist()
     assert np.array_equal(plan.items[:n].cpu().numpy(), items)
@@ -139,3 +139,19 @@ def test_combine_slot_order_fma_chain(ydtype):
     out32 = torch.empty((t, d), dtype=torch.float32, device=DEV)
     moe.combine(y.to(DEV), w.to(DEV), out32)
     assert np.abs(out32.cpu().numpy() - acc32).max() <= 1e-6 * np.abs(acc32).max()
+
+
+@pytest.mark.parametrize("t,e,k,shared", [(1, 128, 8, False), (64, 128, 8, False), (100, 256, 8, True), (128, 1000, 6, True)])
+def test_fused_select_plan_equals_the_two_kernels(t, e, k, shared):
+    from tensorfold_b200 import experts, moe
+
+    logits = _logits(t, e + (1 if shared else 0), 200 + t).to(DEV)
+    a = moe.MoEBuffers(t, _Cfg(e, k), DEV, shared=shared)
+    b = moe.MoEBuffers(t, _Cfg(e, k), DEV, shared=shared)
+    moe.select(logits, a, k, e)                                               # one launch
+    moe.select_rows(logits, b, k, e)
+    experts.route(b.pick[:t], b.plan)
+    assert torch.equal(a.pick, b.pick) and torch.equal(a.wts, b.wts)
+    n = int(b.plan.counts[0])
+    assert torch.equal(a.plan.counts, b.plan.counts) and torch.equal(a.plan.items[:n], b.plan.items[:n])
+    assert torch.equal(a.plan.members, b.plan.members)
