@@ -244,10 +244,12 @@ def run_ours(args) -> None:
 
         dist.init_process_group("nccl", device_id=dev)
     hbm, tflops, which = peaks()
+    _lib.set_pdl(bool(args.pdl))
     shape, rows = synthetic.C2, args.rows
     layers = []
     for copy in range(2):
-        gate, up, down = synthetic.affine_layer(shape, dev, torch.float16, copy=copy)
+        gate, up, down = synthetic.affine_layer(shape, dev, torch.float16 if args.scales == "fp16" else torch.bfloat16,
+                                                 copy=copy)
         layers.append(moe.Routed(synthetic.router_rows(shape, dev), experts.make([gate, up], down, 64), shape.top_k,
                                  shared=shape.shared))
         del gate, up, down
@@ -309,6 +311,8 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--rows", type=int, default=64, help="tokens a step on each GPU")
+    ap.add_argument("--scales", default="fp16", choices=["fp16", "bf16"], help="dtype of the affine scales and biases")
+    ap.add_argument("--pdl", type=int, default=1, help="1: programmatic dependent launch between the layer's kernels")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-sweep", action="store_true", help="skip the 1-token and 2048-token lines")
     args = ap.parse_args()

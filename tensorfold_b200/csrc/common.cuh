@@ -72,6 +72,24 @@ __device__ __forceinline__ float sb_to_float(uint32_t half_bits) {
   }
 }
 
+// the bf16 pair (128 + q0, 128 + q1) of the nibbles at bits sh and sh + 16: one shift, one lop3 ((a & b) | c)
+__device__ __forceinline__ uint32_t nib_pair(uint32_t w, int sh) {
+  uint32_t t = w, r;
+  if (sh) asm("shr.u32 %0, %1, %2;\n" : "=r"(t) : "r"(w), "r"(sh));
+  asm("lop3.b32 %0, %1, %2, %3, 0xEA;\n" : "=r"(r) : "r"(t), "r"(NIB_MASK), "r"(BF16_128));
+  return r;
+}
+
+// (scale, bias) of one column, stored as two 16-bit halves of a word, as fp32
+template <int SB>
+__device__ __forceinline__ float2 sb_pair(uint32_t v) {
+  if constexpr (SB == SB_FP16) {
+    return __half22float2(*reinterpret_cast<const __half2*>(&v));
+  } else {
+    return make_float2(__uint_as_float(v << 16), __uint_as_float(v & 0xFFFF0000u));
+  }
+}
+
 // ---- device status word -----------------------------------------------------------------------------------------
 // Kernels never trap: a wait that runs out records a code here and the kernel returns; the host reads it.
 enum KernelStatus : int { ST_OK = 0, ST_WAIT_TIMEOUT = 1, ST_BAD_INDEX = 2 };

@@ -6,7 +6,7 @@
 // shared-memory ring with bulk async copies (one elected lane issues, an mbarrier a stage), so many kilobytes a warp
 // are in flight while the lanes compute.  The weights are the mma A operand (16 columns x 16 inputs a fragment, read
 // from shared memory as one 128-bit word a lane), the pairs' inputs the B operand (8 pairs).  Nibbles become the
-// exact bf16 values 128 + q with a shift and a lop3; the 128 is taken out again per group in fp32:
+// exact bf16 values 128 + q with a shift and one lop3; the 128 is taken out again per group in fp32:
 // acc += s * sum((128 + q) x) + (b - 128 s) * sum(x), with sum(x) from an all-ones mma.  K-slices meet in shared
 // memory in slice order, so a pair's bits depend on nothing but its own row.
 // (Replaces src/tensorfold/cuda/experts.cu:13-155,287-351: expert_kernel and its launch.)
@@ -20,11 +20,12 @@ constexpr int DEC_WARPS = 4;
 constexpr int DEC_PAIRS = 8;           // pairs an item may hold in this form (the plan's decode tile)
 constexpr int RED_STRIDE = COLS + 1;
 
-template <int M, int STAGES>
+// Q = blocks a warp takes a group: M matrices (gate, up: adjacent in memory) or NCB column blocks of one matrix.
+template <int Q, int STAGES>
 struct DecodeSmem {
-  static constexpr int STAGE_BYTES = M * BLOCK_BYTES;                      // one group a stage
+  static constexpr int STAGE_BYTES = Q * BLOCK_BYTES;                      // one group a stage
   static constexpr int RING_BYTES = DEC_WARPS * STAGES * STAGE_BYTES;
-  static constexpr int RED_BYTES = DEC_WARPS * M * DEC_PAIRS * RED_STRIDE * 4;
+  static constexpr int RED_BYTES = DEC_WARPS * Q * DEC_PAIRS * RED_STRIDE * 4;
   static constexpr int DATA_BYTES = RING_BYTES > RED_BYTES ? RING_BYTES : RED_BYTES;
   static constexpr int BAR_OFFSET = (DATA_BYTES + 15) / 16 * 16;
   static constexpr int TOTAL = BAR_OFFSET + DEC_WARPS * STAGES * 8;
@@ -39,19 +40,21 @@ __device__ __forceinline__ void mma_bf16_zero(float (&d)[4], uint32_t a0, uint32
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.f));
 }
 
-template <int M, int EPI, int SB, int KW, int STAGES>
+template <int M, int NCB, int EPI, int SB, int KW, int STAGES>
 __global__ void __launch_bounds__(DEC_WARPS * 32)
 decode_kernel(const __nv_bfloat16* __restrict__ X, int64_t x_stride, int slots, const uint8_t* __restrict__ W, int KG,
               int NB, const int* __restrict__ items, const int* __restrict__ counts, const int* __restrict__ members,
               void* __restrict__ out, int N, float limit) {
-  using SM = DecodeSmem<M, STAGES>;
-  constexpr int CBC = DEC_WARPS / KW;                 // column blocks a CTA
+  static_assert(M == 1 || NCB == 1, "a warp takes two matrices of one column block, or column blocks of one matrix");
+  constexpr int Q = M * NCB;
+  using SM = DecodeSmem<Q, STAGES>;
+  constexpr int CBC = DEC_WARPS / KW * NCB;           // column blocks a CTA
   extern __shared__ __align__(128) uint8_t smem[];
   __shared__ int pair_id[DEC_PAIRS];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, gq = lane >> 2, t = lane & 3;
   const int nbt = (NB + CBC - 1) / CBC;
   const int it = blockIdx.x / nbt, cbt = blockIdx.x - it * nbt;
-  const int kslice = warp % KW, cbw = warp / KW, cb = cbt * CBC + cbw;
+  const int kslice = warp % KW, cbw = warp / KW, cb = cbt * CBC + cbw * NCB;   // the warp's first column block
 
   uint8_t* ring = smem + warp * (STAGES * SM::STAGE_BYTES);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SM::BAR_OFFSET) + warp * STAGES;
@@ -71,13 +74,19 @@ decode_kernel(const __nv_bfloat16* __restrict__ X, int64_t x_stride, int slots, 
   // this warp's K run: groups [g0, g1) of column block cb
   const int kgw = (KG + KW - 1) / KW;
   const int g0 = min(KG, kslice * kgw), g1 = min(KG, g0 + kgw);
-  const int ng = cb < NB ? g1 - g0 : 0;
+  const int ncb = max(0, min(NCB, NB - cb));          // column blocks of this warp that exist
+  const int ng = ncb > 0 ? g1 - g0 : 0;
+  const size_t cb_stride = (size_t)KG * (M * BLOCK_BYTES);
   const uint8_t* src = W + (((size_t)e * NB + min(cb, NB - 1)) * KG + g0) * (size_t)(M * BLOCK_BYTES);
 
   auto issue = [&](int c) {
     uint64_t* bar = bars + (c % STAGES);
-    mbar_expect_tx(bar, SM::STAGE_BYTES);
-    bulk_g2s(ring + (c % STAGES) * SM::STAGE_BYTES, src + (size_t)c * SM::STAGE_BYTES, SM::STAGE_BYTES, bar);
+    uint8_t* dst = ring + (c % STAGES) * SM::STAGE_BYTES;
+    mbar_expect_tx(bar, (uint32_t)ncb * (M * BLOCK_BYTES));
+#pragma unroll
+    for (int j = 0; j < NCB; ++j)
+      if (j < ncb)
+        bulk_g2s(dst + j * (M * BLOCK_BYTES), src + j * cb_stride + (size_t)c * (M * BLOCK_BYTES), M * BLOCK_BYTES, bar);
   };
   if (lane == 0)
     for (int c = 0; c < STAGES && c < ng; ++c) issue(c);
@@ -85,29 +94,29 @@ decode_kernel(const __nv_bfloat16* __restrict__ X, int64_t x_stride, int slots, 
   if (tid < DEC_PAIRS) pair_id[tid] = tid < cnt ? __ldg(members + first + tid) : -1;
 
   // the lane's pair (B operand column gq) and its input row
-  const bool valid = gq < cnt;
-  const int pr = valid ? __ldg(members + first + gq) : 0;
+  // (lanes past the item's last pair read its first pair's row: an mma column depends on its own inputs only, and
+  // those columns are never stored)
+  const int pr = __ldg(members + first + (gq < cnt ? gq : 0));
   const __nv_bfloat16* xrow = X + (size_t)(slots ? pr / slots : pr) * x_stride + 16 * t + (size_t)g0 * GS;
 
-  float acc[M][2][4];
+  float acc[Q][2][4];
 #pragma unroll
-  for (int m = 0; m < M; ++m)
+  for (int m = 0; m < Q; ++m)
 #pragma unroll
     for (int tt = 0; tt < 2; ++tt)
 #pragma unroll
       for (int i = 0; i < 4; ++i) acc[m][tt][i] = 0.f;
 
-  const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
   const uint32_t ONES = 0x3F803F80u;                  // the bf16 pair (1, 1)
-  uint4 xn0 = zero, xn1 = zero;
-  if (valid && ng > 0) {
+  uint4 xn0 = make_uint4(0u, 0u, 0u, 0u), xn1 = xn0;
+  if (ng > 0) {
     xn0 = ldg_nc(xrow);
     xn1 = ldg_nc(xrow + 8);
   }
   for (int c = 0; c < ng; ++c) {
     const int s = c % STAGES;
     const uint4 x0 = xn0, x1 = xn1;
-    if (valid && c + 1 < ng) {                        // the next group's inputs travel while this one computes
+    if (c + 1 < ng) {                        // the next group's inputs travel while this one computes
       xn0 = ldg_nc(xrow + (c + 1) * GS);
       xn1 = ldg_nc(xrow + (c + 1) * GS + 8);
     }
@@ -120,7 +129,7 @@ decode_kernel(const __nv_bfloat16* __restrict__ X, int64_t x_stride, int slots, 
     if (!mbar_wait(bars + s, (c / STAGES) & 1)) break;
     const uint8_t* blk = ring + s * SM::STAGE_BYTES;
 #pragma unroll
-    for (int m = 0; m < M; ++m) {
+    for (int m = 0; m < Q; ++m) {
       const uint4 sbv = *reinterpret_cast<const uint4*>(blk + m * BLOCK_BYTES + SB_OFFSET + gq * 16);
 #pragma unroll
       for (int tt = 0; tt < 2; ++tt) {
@@ -130,17 +139,16 @@ decode_kernel(const __nv_bfloat16* __restrict__ X, int64_t x_stride, int slots, 
         for (int ks = 0; ks < 4; ++ks) {
           const uint32_t lo = ks < 2 ? w.x : w.y, hi = ks < 2 ? w.z : w.w;
           const int sh = 8 * (ks & 1);
-          const uint32_t a0 = ((lo >> sh) & NIB_MASK) | BF16_128, a1 = ((hi >> sh) & NIB_MASK) | BF16_128;
-          const uint32_t a2 = ((lo >> (sh + 4)) & NIB_MASK) | BF16_128, a3 = ((hi >> (sh + 4)) & NIB_MASK) | BF16_128;
+          const uint32_t a0 = nib_pair(lo, sh), a1 = nib_pair(hi, sh);
+          const uint32_t a2 = nib_pair(lo, sh + 4), a3 = nib_pair(hi, sh + 4);
           if (ks == 0)
             mma_bf16_zero(p, a0, a1, a2, a3, xb[0], xb[1]);
           else
             mma_bf16(p, a0, a1, a2, a3, xb[2 * ks], xb[2 * ks + 1]);
         }
-        const uint32_t sb_lo = comp(sbv, 2 * tt), sb_hi = comp(sbv, 2 * tt + 1);
-        const float s_lo = sb_to_float<SB>(sb_lo & 0xFFFFu), s_hi = sb_to_float<SB>(sb_hi & 0xFFFFu);
-        const float b_lo = fmaf(-128.f, s_lo, sb_to_float<SB>(sb_lo >> 16));
-        const float b_hi = fmaf(-128.f, s_hi, sb_to_float<SB>(sb_hi >> 16));
+        const float2 sb_lo = sb_pair<SB>(comp(sbv, 2 * tt)), sb_hi = sb_pair<SB>(comp(sbv, 2 * tt + 1));
+        const float s_lo = sb_lo.x, s_hi = sb_hi.x;
+        const float b_lo = fmaf(-128.f, s_lo, sb_lo.y), b_hi = fmaf(-128.f, s_hi, sb_hi.y);
         float(&d)[4] = acc[m][tt];
         d[0] = fmaf(xs[0], b_lo, fmaf(p[0], s_lo, d[0]));
         d[1] = fmaf(xs[1], b_lo, fmaf(p[1], s_lo, d[1]));
@@ -157,10 +165,10 @@ decode_kernel(const __nv_bfloat16* __restrict__ X, int64_t x_stride, int slots, 
   __syncthreads();
   float* red = reinterpret_cast<float*>(smem);
 #pragma unroll
-  for (int m = 0; m < M; ++m)
+  for (int m = 0; m < Q; ++m)
 #pragma unroll
     for (int tt = 0; tt < 2; ++tt) {
-      float* base = red + ((warp * M + m) * DEC_PAIRS + 2 * t) * RED_STRIDE + tt * 16 + gq;
+      float* base = red + ((warp * Q + m) * DEC_PAIRS + 2 * t) * RED_STRIDE + tt * 16 + gq;
       base[0] = acc[m][tt][0];
       base[RED_STRIDE] = acc[m][tt][1];
       base[8] = acc[m][tt][2];
@@ -172,12 +180,13 @@ decode_kernel(const __nv_bfloat16* __restrict__ X, int64_t x_stride, int slots, 
     const int col = o & 31, pi = (o >> 5) % DEC_PAIRS, cbo = o / (DEC_PAIRS * COLS);
     const int cbi = cbt * CBC + cbo;
     if (pi >= cnt || cbi >= NB) continue;
+    const int w0 = (cbo / NCB) * KW, q0 = (cbo % NCB) * M;      // first K-slice warp and block of this column block
     float v[M];
 #pragma unroll
     for (int m = 0; m < M; ++m) {
-      float sum = red[(((cbo * KW) * M + m) * DEC_PAIRS + pi) * RED_STRIDE + col];
+      float sum = red[((w0 * Q + q0 + m) * DEC_PAIRS + pi) * RED_STRIDE + col];
 #pragma unroll
-      for (int k = 1; k < KW; ++k) sum += red[(((cbo * KW + k) * M + m) * DEC_PAIRS + pi) * RED_STRIDE + col];
+      for (int k = 1; k < KW; ++k) sum += red[(((w0 + k) * Q + q0 + m) * DEC_PAIRS + pi) * RED_STRIDE + col];
       v[m] = sum;
     }
     const size_t at = (size_t)pair_id[pi] * N + cbi * COLS + col;
@@ -194,17 +203,19 @@ decode_kernel(const __nv_bfloat16* __restrict__ X, int64_t x_stride, int slots, 
 }
 
 // K-slices a CTA for a projection of kg groups: the shape's alone, so a pair's bits never depend on the call.
-__host__ __device__ inline int decode_kslices(int kg) { return kg >= 32 ? 4 : kg >= 16 ? 2 : 1; }
+__host__ __device__ inline int decode_kslices(int kg) { return kg >= 32 ? 4 : kg >= 8 ? 2 : 1; }
 
 template <int M, int EPI, int SB, int KW>
 int launch_decode_kw(const void* x, int64_t x_stride, int slots, const void* w, int kg, int nb, const int* items,
                      const int* counts, const int* members, void* out, int n, float limit, int64_t max_items,
                      cudaStream_t stream) {
   constexpr int STAGES = 4;
-  using SM = DecodeSmem<M, STAGES>;
-  auto* kern = decode_kernel<M, EPI, SB, KW, STAGES>;
+  constexpr int NCB = M == 1 ? 2 : 1;                 // one matrix: a warp shares its inputs between two column blocks
+  using SM = DecodeSmem<M * NCB, STAGES>;
+  auto* kern = decode_kernel<M, NCB, EPI, SB, KW, STAGES>;
   static_assert(SM::TOTAL <= 48 * 1024, "the decode kernel stays within the default shared-memory limit");
-  const int64_t grid = max_items * ((nb + DEC_WARPS / KW - 1) / (DEC_WARPS / KW));
+  constexpr int CBC = DEC_WARPS / KW * NCB;
+  const int64_t grid = max_items * ((nb + CBC - 1) / CBC);
   if (grid >= (int64_t(1) << 31)) return fail(TFB_ERR_ARG, "experts_run: too many units");
   return check_cuda(launch(kern, dim3((unsigned)grid), dim3(DEC_WARPS * 32), (size_t)SM::TOTAL, stream,
                            static_cast<const __nv_bfloat16*>(x), x_stride, slots, static_cast<const uint8_t*>(w), kg,

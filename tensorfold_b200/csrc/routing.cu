@@ -64,9 +64,9 @@ router_kernel(const __nv_bfloat16* __restrict__ X, int64_t x_stride, const __nv_
     }
 }
 
-// The same arithmetic for few rows: a CTA an expert (its row of W read once into registers), a warp a row at a
-// time, every chunk of the row's inputs in flight at once.  Bits equal router_kernel's.
-constexpr int RR_WARPS = 8, RR_ROWS = 64, RR_CH = 8;
+// The same arithmetic for few rows: a CTA an expert and eight rows, a warp a row, every chunk of the row's inputs and
+// of the expert's weights in flight at once (two memory round trips in all).  Bits equal router_kernel's.
+constexpr int RR_WARPS = 8, RR_ROWS = 8, RR_CH = 8;
 
 __global__ void __launch_bounds__(RR_WARPS * 32)
 router_rows_kernel(const __nv_bfloat16* __restrict__ X, int64_t x_stride, const __nv_bfloat16* __restrict__ W,
@@ -127,46 +127,49 @@ constexpr int S_WARPS = 4;
 
 // One row by one warp: writes the row's slots of pick / wts; returns this lane's pick (lanes < slots) for callers
 // that keep the picks on chip.
+// fp32 -> uint32 that orders the same way (both zeros share a key, as they compare equal), and back
+__device__ __forceinline__ uint32_t order_key(float f) {
+  const uint32_t u = f == 0.f ? 0u : __float_as_uint(f);
+  return u ^ (static_cast<uint32_t>(static_cast<int32_t>(u) >> 31) | 0x80000000u);
+}
+__device__ __forceinline__ float order_value(uint32_t k) {
+  return __uint_as_float(k ^ ((k & 0x80000000u) ? 0x80000000u : 0xFFFFFFFFu));
+}
+
 template <int VPL>
 __device__ __forceinline__ int select_row(const float* __restrict__ Lr, int E, int top_k, int shared, int lane,
                                           int* __restrict__ pick_row, float* __restrict__ wts_row) {
-  const float NEG = __int_as_float(0xff800000);
-  float v[VPL];
+  // keys order like the logits; 0 (below every real key) marks a taken or missing entry
+  uint32_t key[VPL];
 #pragma unroll
   for (int i = 0; i < VPL; ++i) {
     const int e = i * 32 + lane;
-    v[i] = e < E ? Lr[e] : NEG;
+    key[i] = e < E ? order_key(Lr[e]) : 0u;
   }
   float top = 0.f, total = 0.f, my_ex = 0.f;
   int my_pick = -1;
   for (int k = 0; k < top_k; ++k) {
-    float bv = v[0];
-    int bi = lane;
+    uint32_t bk = key[0];
+    uint32_t bi = lane;
 #pragma unroll
     for (int i = 1; i < VPL; ++i)
-      if (v[i] > bv) {
-        bv = v[i];
+      if (key[i] > bk) {
+        bk = key[i];
         bi = i * 32 + lane;
       }
-#pragma unroll
-    for (int m = 16; m >= 1; m >>= 1) {
-      const float ov = __shfl_xor_sync(0xffffffffu, bv, m);
-      const int oi = __shfl_xor_sync(0xffffffffu, bi, m);
-      if (ov > bv || (ov == bv && oi < bi)) {
-        bv = ov;
-        bi = oi;
-      }
-    }
-    if (k == 0) top = bv;
-    const float ex = expf(bv - top);
+    const uint32_t mx = __reduce_max_sync(0xffffffffu, bk);
+    const uint32_t idx = __reduce_min_sync(0xffffffffu, bk == mx ? bi : 0xFFFFFFFFu);   // the lower id among equals
+    const float val = order_value(mx);
+    if (k == 0) top = val;
+    const float ex = expf(val - top);
     total += ex;
     if (lane == k) {
-      my_pick = bi;
+      my_pick = (int)idx;
       my_ex = ex;
     }
 #pragma unroll
     for (int i = 0; i < VPL; ++i)
-      if (i * 32 + lane == bi) v[i] = NEG;
+      if (i * 32 + lane == (int)idx) key[i] = 0u;
   }
   if (lane < top_k) {
     pick_row[lane] = my_pick;
@@ -376,7 +379,7 @@ extern "C" int tfb_router(const void* x, int64_t x_stride, const void* rows, flo
   TFB_REQUIRE(D % 8 == 0 && x_stride % 8 == 0 && x_stride >= D, "router: D and the row stride must be multiples of 8");
   TFB_REQUIRE(aligned16(x) && aligned16(rows), "router: x and rows must be 16-byte aligned");
   if (T == 0) return TFB_OK;
-  if (T <= 4 * RR_ROWS) {
+  if (T <= 256) {
     const dim3 rgrid(NE, (T + RR_ROWS - 1) / RR_ROWS);
     return check_cuda(launch(router_rows_kernel, rgrid, dim3(RR_WARPS * 32), 0, static_cast<cudaStream_t>(stream),
                              static_cast<const __nv_bfloat16*>(x), x_stride,
