@@ -24,6 +24,7 @@ SIGNATURES: dict[str, tuple] = {
     "tfb_unpack": (P, I, P, P, P, I, I, I, P),
     "tfb_dequant": (P, I, I, I, P, I, I, I, P),
     "tfb_experts_run": (I, I, P, L, I, P, I, I, P, P, P, P, I, F, L, I, P),
+    "tfb_experts_prefill": (I, I, P, L, I, P, I, I, P, P, P, P, I, F, L, I, P),
     "tfb_kernel_status": (P, P),
 }
 

@@ -127,10 +127,22 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Bounded wait: gives up after a few seconds' worth of polls, records ST_WAIT_TIMEOUT and returns false.
+__device__ __forceinline__ uint64_t global_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %globaltimer;\n" : "=l"(t));
+  return t;
+}
+
+// Bounded wait: gives up after about a second, records ST_WAIT_TIMEOUT and returns false.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-  for (uint32_t spin = 0; spin < (1u << 24); ++spin) {
+  uint64_t start = 0;
+  for (uint32_t spin = 0; spin < (1u << 26); ++spin) {
     if (mbar_try_wait(bar, parity)) return true;
+    if ((spin & 1023u) == 1023u) {
+      const uint64_t now = global_ns();
+      if (start == 0) start = now;
+      else if (now - start > 1000000000ull) break;
+    }
   }
   atomicExch(&g_kernel_status, ST_WAIT_TIMEOUT);
   return false;

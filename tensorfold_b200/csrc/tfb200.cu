@@ -3,3 +3,4 @@
 #include "routing.cu"
 #include "pack.cu"
 #include "experts_decode.cu"
+#include "experts_prefill.cu"

@@ -17,7 +17,7 @@ from . import _lib
 NTW = 4                  # n8 tiles a 32-column block
 COLS = 8 * NTW           # output columns a block
 TILE = 8                 # pairs an item holds (decode form): one mma tile of pairs
-PREFILL_TILE = 64        # the default item of a prompt plan
+PREFILL_TILE = 256       # pairs a prompt item holds: the tensor-core tile's N
 SMALL = 1024             # kept for callers that size scratch by it; this library's plan is one launch at any size
 BLOCK = 288              # int32 words a block of 64 inputs x 32 columns: 1024 B of nibbles + 128 B of scale/bias
 
@@ -173,17 +173,24 @@ def _check_x(x: torch.Tensor, k: int) -> None:
 
 
 def _run(epi: int, x: torch.Tensor, slots: int, w: torch.Tensor, kg: int, nb: int, plan: Plan, out: torch.Tensor,
-         n: int, limit: float, items: int, ex: Experts) -> None:
+         n: int, limit: float, items: int, ex: Experts, prefill: bool = False) -> None:
     _check_x(x, kg * ex.gs)
     want = torch.float32 if epi == 0 else torch.bfloat16
+    if prefill and plan.tile > PREFILL_TILE:
+        raise ValueError(f"a prompt item holds at most {PREFILL_TILE} pairs")
     if out.dtype != want or not out.is_contiguous() or out.shape[-1] != n:
         raise ValueError("out: contiguous rows of n columns of the epilogue's dtype")
     if not w.is_contiguous():
         raise ValueError("w must be contiguous")
     with torch.cuda.device(x.device):
-        _lib.call("tfb_experts_run", ex.gs, epi, x.data_ptr(), x.stride(0), slots, w.data_ptr(), kg, nb,
-                  plan.items.data_ptr(), plan.counts.data_ptr(), plan.members.data_ptr(), out.data_ptr(), n,
-                  float(limit), items * nb, _SB[ex.scale_dtype], _stream(x))
+        if prefill:
+            _lib.call("tfb_experts_prefill", ex.gs, epi, x.data_ptr(), x.stride(0), slots, w.data_ptr(), kg, nb,
+                      plan.items.data_ptr(), plan.counts.data_ptr(), plan.members.data_ptr(), out.data_ptr(), n,
+                      float(limit), items, _SB[ex.scale_dtype], _stream(x))
+        else:
+            _lib.call("tfb_experts_run", ex.gs, epi, x.data_ptr(), x.stride(0), slots, w.data_ptr(), kg, nb,
+                      plan.items.data_ptr(), plan.counts.data_ptr(), plan.members.data_ptr(), out.data_ptr(), n,
+                      float(limit), items * nb, _SB[ex.scale_dtype], _stream(x))
 
 
 def gate_up(x: torch.Tensor, ex: Experts, plan: Plan, out: torch.Tensor, rows: int) -> None:
@@ -191,15 +198,13 @@ def gate_up(x: torch.Tensor, ex: Experts, plan: Plan, out: torch.Tensor, rows: i
 
     items = max_items(rows * plan.slots, plan.experts, plan.tile)
     epi = 2 if ex.swiglu else 1
-    if plan.prefill:
-        raise NotImplementedError("prefill form")
-    _run(epi, x, plan.slots, ex.up, ex.dims // ex.gs, ex.width // COLS, plan, out, ex.width, ex.limit, items, ex)
+    _run(epi, x, plan.slots, ex.up, ex.dims // ex.gs, ex.width // COLS, plan, out, ex.width, ex.limit, items, ex,
+         plan.prefill)
 
 
 def down(act: torch.Tensor, ex: Experts, plan: Plan, out: torch.Tensor, rows: int) -> None:
     """act [R * slots, NI] bf16 -> out [R * slots, D] per pair: fp32, or bf16 on a prefill plan when ``out`` is bf16."""
 
     items = max_items(rows * plan.slots, plan.experts, plan.tile)
-    if plan.prefill:
-        raise NotImplementedError("prefill form")
-    _run(0, act, 0, ex.down, ex.width // ex.gs, ex.dims // COLS, plan, out, ex.dims, 0.0, items, ex)
+    epi = 3 if plan.prefill and out.dtype == torch.bfloat16 else 0
+    _run(epi, act, 0, ex.down, ex.width // ex.gs, ex.dims // COLS, plan, out, ex.dims, 0.0, items, ex, plan.prefill)
