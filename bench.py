@@ -174,13 +174,14 @@ def time_graphs(torch, graphs, steps: int, warmup: int) -> float:
     return a.elapsed_time(b) / steps
 
 
-def bench_rows(torch, shape, layers, rows: int, steps: int, warmup: int, hbm: float):
+def bench_rows(torch, shape, layers, rows: int, steps: int, warmup: int, hbm: float, prefill: bool = False,
+               tflops: float = 0.0):
     """Device-resident timing of the whole layer at `rows` tokens plus the gate/up kernel alone."""
 
     from tensorfold_b200 import experts, moe, synthetic
 
     dev = layers[0].router.device
-    runners = [moe.Runner(m, rows, device=dev) for m in layers]
+    runners = [moe.Runner(m, rows, prefill=prefill, device=dev) for m in layers]
     x = synthetic.activations(shape, rows, dev)
     for r in runners:
         r.x.copy_(x)
@@ -198,7 +199,15 @@ def bench_rows(torch, shape, layers, rows: int, steps: int, warmup: int, hbm: fl
                 experts.gate_up(r.x, r.layer.experts, r.buf.plan, r.buf.act.view(-1, shape.width), rows)
     kms = time_graphs(torch, [g], max(3, steps // 4), 3) / (reps * len(runners))
     gbs = nbytes["gate_up"] / (kms * 1e-3) / 1e9
-    return {"rows": rows, "ms_per_step": ms, "tokens_per_s": rows / (ms * 1e-3), "distinct_experts": distinct,
+    extra = {}
+    if prefill:
+        pairs = rows * runners[0].buf.slots
+        flops_gu, flops_all = pairs * 2 * 2 * shape.dims * shape.width, pairs * 3 * 2 * shape.dims * shape.width
+        extra = {"form": "prefill (tcgen05)", "gate_up_tflops": flops_gu / (kms * 1e-3) / 1e12,
+                 "gate_up_frac_of_bf16_peak": flops_gu / (kms * 1e-3) / 1e12 / tflops if tflops else None,
+                 "layer_tflops": flops_all / (ms * 1e-3) / 1e12,
+                 "layer_frac_of_bf16_peak": flops_all / (ms * 1e-3) / 1e12 / tflops if tflops else None}
+    return {**extra, "rows": rows, "ms_per_step": ms, "tokens_per_s": rows / (ms * 1e-3), "distinct_experts": distinct,
             "layer_bytes": nbytes["layer"], "layer_gbs": nbytes["layer"] / (ms * 1e-3) / 1e9,
             "layer_frac_of_hbm": nbytes["layer"] / (ms * 1e-3) / 1e9 / hbm,
             "gate_up_us": kms * 1e3, "gate_up_bytes": nbytes["gate_up"], "gate_up_gbs": gbs,
@@ -259,7 +268,8 @@ def run_ours(args) -> None:
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
-        head, runners = bench_rows(torch, shape, layers, rows, args.steps, args.warmup, hbm)
+        head, runners = bench_rows(torch, shape, layers, rows, args.steps, args.warmup, hbm, args.form == "prefill",
+                                   tflops)
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
@@ -278,9 +288,9 @@ def run_ours(args) -> None:
     sweep = []
     if world == 1 and not args.no_sweep:
         del runners
-        for t_rows in (1, 2048):
-            res, rr = bench_rows(torch, shape, layers, t_rows, max(5, args.steps // 2), args.warmup, hbm)
-            res["form"] = "decode kernels"
+        for t_rows, pre in ((1, False), (2048, True)):
+            res, rr = bench_rows(torch, shape, layers, t_rows, max(5, args.steps // 2), args.warmup, hbm, pre, tflops)
+            res.setdefault("form", "decode")
             sweep.append(res)
             del rr
     if rank != 0:
@@ -313,6 +323,8 @@ def main() -> None:
     ap.add_argument("--rows", type=int, default=64, help="tokens a step on each GPU")
     ap.add_argument("--scales", default="fp16", choices=["fp16", "bf16"], help="dtype of the affine scales and biases")
     ap.add_argument("--pdl", type=int, default=1, help="1: programmatic dependent launch between the layer's kernels")
+    ap.add_argument("--form", default="decode", choices=["decode", "prefill"],
+                    help="arithmetic form of the headline run (the sweep always uses decode at 1 and prefill at 2048)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-sweep", action="store_true", help="skip the 1-token and 2048-token lines")
     args = ap.parse_args()

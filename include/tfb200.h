@@ -99,7 +99,7 @@ int tfb_experts_run(int gs, int epi, const void* x, int64_t x_stride, int slots,
                     int64_t max_units, int sb_type, void* stream);
 
 /* Grouped 4-bit expert matmul, prefill form (tcgen05 tensor cores, weights dequantised to bf16 with one rounding,
- * one fp32 chain over K).  Arguments as tfb_experts_run, but items may hold up to 256 pairs (plan with tile 256) and
+ * one fp32 chain over K).  Arguments as tfb_experts_run, but items may hold up to 192 pairs (plan with tile <= 192) and
  * max_items = an upper bound of the item count.
  * Replaces the extension entry `prefill`: src/tensorfold/cuda/experts.cpp:50-56, experts_prefill.cu:31-195. */
 int tfb_experts_prefill(int gs, int epi, const void* x, int64_t x_stride, int slots, const void* w, int kg, int nb,

@@ -191,6 +191,17 @@ __device__ __forceinline__ float swiglu(float g, float u, float limit) {
   return round_bf16(gv / (1.f + expf(-gv))) * uv;
 }
 
+// The same with the hardware exponential and reciprocal (the prefill epilogue, where it sits on every output):
+// silu differs from the exact one by a few fp32 ulps before its rounding to bf16.
+__device__ __forceinline__ float swiglu_fast(float g, float u, float limit) {
+  float gv = round_bf16(g), uv = round_bf16(u);
+  if (limit > 0.f) {
+    gv = fminf(gv, limit);
+    uv = fminf(fmaxf(uv, -limit), limit);
+  }
+  return round_bf16(__fdividef(gv, 1.f + __expf(-gv))) * uv;
+}
+
 __device__ __forceinline__ float relu2(float a) {
   const float u = fmaxf(round_bf16(a), 0.f);
   return u * u;

@@ -1,16 +1,16 @@
 // Prefill form of the grouped 4-bit experts: a grouped GEMM on the tcgen05 tensor cores.
 //
-// A CTA owns one unit = (plan item of <= 256 pairs, 128 output columns).  The roles are swapped against the usual
+// A CTA owns one unit = (plan item of <= 192 pairs, 128 output columns).  The roles are swapped against the usual
 // GEMM: the WEIGHTS are the MMA's A operand (M = 128 columns), the item's PAIRS the B operand (N = pairs rounded up to
-// 16, <= 256), so an expert with 140 pairs costs 144 / 128 of a full tile instead of two, and every weight is
+// 16, <= 192), so an expert with 140 pairs costs 144 / 128 of a full tile instead of two, and every weight is
 // dequantised exactly once.  Per group of 64 inputs (one pipeline stage):
-//   warp 4 (producer)  bulk-copies the packed blocks (4 column blocks x M matrices) into a staging buffer and gathers
-//                      the pairs' input rows with 16-byte cp.async into the 128-byte-swizzled B tile;
-//   warps 0-3          turn nibbles into the prefill form's bf16 weights (w = bf16(q * s + b), one rounding) and
+//   warp 13 (a lane)   bulk-copies the packed blocks (4 column blocks x M matrices) into a deep staging ring;
+//   warps 8-11         gather the pairs' input rows with 16-byte cp.async into the 128-byte-swizzled B tile;
+//   warps 0-7          turn nibbles into the prefill form's bf16 weights (w = bf16(q * s + b), one rounding) and
 //                      store them as the K-major, 128-byte-swizzled A tiles;
-//   warp 5 (one lane)  issues tcgen05.mma (cta_group::1, kind::f16, M = 128, K = 16) into fp32 accumulators in tensor
+//   warp 12 (a lane)   issues tcgen05.mma (cta_group::1, kind::f16, M = 128, K = 16) into fp32 accumulators in tensor
 //                      memory (gate at column 0, up at column 256), and commits each stage back to the producer.
-// After the last group warps 0-3 read the accumulators (tcgen05.ld), apply the epilogue and store rows by pair id.
+// After the last group warps 0-11 read the accumulators (tcgen05.ld), apply the epilogue and store rows by pair id.
 // One fp32 chain over K in group order: a pair's bits do not depend on its item, its chunk or the call.
 // (Replaces src/tensorfold/cuda/experts_prefill.cu:31-195: prefill_kernel and its launch.)
 
@@ -20,20 +20,28 @@
 namespace tfb {
 
 constexpr int PF_COLS = 128;            // output columns a unit (MMA M)
-constexpr int PF_MAXP = 256;            // pairs an item may hold (MMA N <= 256)
-constexpr int PF_THREADS = 192;
+constexpr int PF_MAXP = 192;            // pairs an item may hold (MMA N)
 constexpr int PF_CB = PF_COLS / COLS;   // packed column blocks a unit
+constexpr int PF_DQ_WARPS = 8;          // warps 0-7: dequantise, then the epilogue
+constexpr int PF_GA_WARPS = 4;          // warps 8-11: gather the pairs' input rows
+constexpr int PF_MMA_WARP = 12, PF_COPY_WARP = 13;
+constexpr int PF_THREADS = 14 * 32;
+constexpr int PF_GA_PER_THREAD = PF_MAXP * 8 / (PF_GA_WARPS * 32);   // 16-byte chunks a gather thread a stage
 
+// Two rings: operand tiles (A per matrix and B) with SA stages, and the packed blocks as they come from HBM with SP
+// stages (deeper: it hides the HBM latency, and a stage is free again as soon as it has been dequantised).
 template <int M>
 struct PrefillSmem {
-  static constexpr int STAGES = M == 2 ? 3 : 4;
+  static constexpr int SA = M == 2 ? 3 : 4;
+  static constexpr int SP = M == 2 ? 6 : 8;
   static constexpr int A_BYTES = PF_COLS * 128;                 // one matrix: 128 rows of 64 bf16
   static constexpr int B_BYTES = PF_MAXP * 128;
-  static constexpr int PACKED_BYTES = (PF_CB * M * BLOCK_BYTES + 1023) / 1024 * 1024;
-  static constexpr int STAGE_BYTES = M * A_BYTES + B_BYTES + PACKED_BYTES;   // a multiple of 1024
-  static constexpr int TABLE_OFFSET = STAGES * STAGE_BYTES;     // int x_row[256], out_row[256]
-  static constexpr int BAR_OFFSET = TABLE_OFFSET + 2 * PF_MAXP * 4;
-  static constexpr int NBARS = 4 * STAGES + 1;
+  static constexpr int AB_BYTES = M * A_BYTES + B_BYTES;        // a multiple of 1024
+  static constexpr int PACKED_BYTES = PF_CB * M * BLOCK_BYTES;
+  static constexpr int PACKED_OFFSET = SA * AB_BYTES;
+  static constexpr int TABLE_OFFSET = PACKED_OFFSET + SP * PACKED_BYTES;   // int out_row[PF_MAXP]
+  static constexpr int BAR_OFFSET = (TABLE_OFFSET + PF_MAXP * 4 + 15) / 16 * 16;
+  static constexpr int NBARS = 2 * SP + 3 * SA + 1;
   static constexpr int TMEM_OFFSET = BAR_OFFSET + NBARS * 8;
   static constexpr int TOTAL = TMEM_OFFSET + 16 + 1024;         // + slack to align the tiles to 1024 bytes
 };
@@ -120,17 +128,17 @@ prefill_kernel(const __nv_bfloat16* __restrict__ X, int64_t x_stride, int slots,
                int NB, const int* __restrict__ items, const int* __restrict__ counts, const int* __restrict__ members,
                void* __restrict__ out, int N, float limit) {
   using SM = PrefillSmem<M>;
-  constexpr int STAGES = SM::STAGES;
+  constexpr int SA = SM::SA, SP = SM::SP;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  int* x_row = reinterpret_cast<int*>(smem + SM::TABLE_OFFSET);
-  int* out_row = x_row + PF_MAXP;
+  int* out_row = reinterpret_cast<int*>(smem + SM::TABLE_OFFSET);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SM::BAR_OFFSET);
-  uint64_t* packed_full = bars;                  // [STAGES] producer's bulk copy landed
-  uint64_t* b_ready = bars + STAGES;             // [STAGES] the pairs' input rows landed
-  uint64_t* a_ready = bars + 2 * STAGES;         // [STAGES] the four dequantising warps wrote their tiles
-  uint64_t* stage_free = bars + 3 * STAGES;      // [STAGES] the MMAs that read the stage retired
-  uint64_t* acc_ready = bars + 4 * STAGES;
+  uint64_t* packed_full = bars;                  // [SP] the bulk copy landed
+  uint64_t* packed_free = bars + SP;             // [SP] the eight dequantising warps have read it
+  uint64_t* a_ready = bars + 2 * SP;             // [SA] the eight dequantising warps wrote their tiles
+  uint64_t* b_ready = a_ready + SA;              // [SA] the pairs' input rows landed
+  uint64_t* ab_free = b_ready + SA;              // [SA] the MMAs that read the stage retired
+  uint64_t* acc_ready = ab_free + SA;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + SM::TMEM_OFFSET);
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -138,11 +146,14 @@ prefill_kernel(const __nv_bfloat16* __restrict__ X, int64_t x_stride, int slots,
   const int it = blockIdx.x / nct, ct = blockIdx.x - it * nct;
 
   if (tid == 0) {
-    for (int s = 0; s < STAGES; ++s) {
+    for (int s = 0; s < SP; ++s) {
       mbar_init(packed_full + s, 1);
-      mbar_init(b_ready + s, 32);
-      mbar_init(a_ready + s, 4);
-      mbar_init(stage_free + s, 1);
+      mbar_init(packed_free + s, PF_DQ_WARPS);
+    }
+    for (int s = 0; s < SA; ++s) {
+      mbar_init(a_ready + s, PF_DQ_WARPS);
+      mbar_init(b_ready + s, PF_GA_WARPS * 32);
+      mbar_init(ab_free + s, 1);
     }
     mbar_init(acc_ready, 1);
     mbar_fence_init();
@@ -151,17 +162,13 @@ prefill_kernel(const __nv_bfloat16* __restrict__ X, int64_t x_stride, int slots,
   pdl_wait();
   const bool live = it < __ldg(counts);          // uniform over the CTA
   constexpr uint32_t TMEM_COLS = 512;
-  if (live && warp == 5) tmem_alloc(tmem_slot, TMEM_COLS);
+  if (live && warp == PF_MMA_WARP) tmem_alloc(tmem_slot, TMEM_COLS);
   int e = 0, first = 0, cnt = 0;
   if (live) {
     e = __ldg(items + 3 * it);
     first = __ldg(items + 3 * it + 1);
     cnt = min(__ldg(items + 3 * it + 2), PF_MAXP);
-    for (int i = tid; i < PF_MAXP; i += PF_THREADS) {
-      const int p = i < cnt ? __ldg(members + first + i) : -1;
-      out_row[i] = p;
-      x_row[i] = p < 0 ? -1 : (slots ? p / slots : p);
-    }
+    for (int i = tid; i < PF_MAXP; i += PF_THREADS) out_row[i] = i < cnt ? __ldg(members + first + i) : -1;
   }
   tc_fence_before();
   __syncthreads();
@@ -172,102 +179,126 @@ prefill_kernel(const __nv_bfloat16* __restrict__ X, int64_t x_stride, int slots,
   const int cb0 = ct * PF_CB, ncb = min(PF_CB, NB - cb0);        // packed column blocks of this unit
   bool ok = true;
 
-  if (warp == 4) {
-    // ---------------- producer: packed weights (bulk copy) and the pairs' inputs (cp.async gather) ----------------
-    const uint8_t* wsrc = W + ((size_t)e * NB + cb0) * KG * (size_t)(M * BLOCK_BYTES);
-    const size_t cb_stride = (size_t)KG * (M * BLOCK_BYTES);
-    for (int g = 0; g < KG && ok; ++g) {
-      const int s = g % STAGES, round = g / STAGES;
-      if (round > 0) ok = mbar_wait(stage_free + s, (round - 1) & 1);
-      if (!ok) break;
-      uint8_t* stage = smem + s * SM::STAGE_BYTES;
-      if (lane == 0) {
+  if (warp == PF_COPY_WARP) {
+    // ---------------- packed weights: HBM -> the packed ring, as far ahead as the ring allows ----------------
+    if (lane == 0) {
+      const uint8_t* wsrc = W + ((size_t)e * NB + cb0) * KG * (size_t)(M * BLOCK_BYTES);
+      const size_t cb_stride = (size_t)KG * (M * BLOCK_BYTES);
+      for (int g = 0; g < KG && ok; ++g) {
+        const int s = g % SP, round = g / SP;
+        if (round > 0) ok = mbar_wait(packed_free + s, (round - 1) & 1);
+        if (!ok) break;
+        uint8_t* dst = smem + SM::PACKED_OFFSET + s * SM::PACKED_BYTES;
         mbar_expect_tx(packed_full + s, (uint32_t)ncb * (M * BLOCK_BYTES));
         for (int j = 0; j < ncb; ++j)
-          bulk_g2s(stage + M * SM::A_BYTES + SM::B_BYTES + j * (M * BLOCK_BYTES),
-                   wsrc + j * cb_stride + (size_t)g * (M * BLOCK_BYTES), M * BLOCK_BYTES, packed_full + s);
-      }
-      uint8_t* btile = stage + M * SM::A_BYTES;
-      for (int i = lane; i < cnt * 8; i += 32) {
-        const int r = i >> 3, c = i & 7;
-        cp_async16(btile + r * 128 + ((c ^ (r & 7)) << 4), X + (size_t)x_row[r] * x_stride + g * GS + c * 8);
-      }
-      cp_async_commit();
-      if (g > 0) {                                   // the stage before this one has landed: publish it
-        cp_async_wait<1>();
-        fence_async_smem();
-        mbar_arrive(b_ready + (g - 1) % STAGES);
+          bulk_g2s(dst + j * (M * BLOCK_BYTES), wsrc + j * cb_stride + (size_t)g * (M * BLOCK_BYTES), M * BLOCK_BYTES,
+                   packed_full + s);
       }
     }
-    cp_async_wait<0>();
-    fence_async_smem();
-    if (ok) mbar_arrive(b_ready + (KG - 1) % STAGES);
-  } else if (warp == 5) {
+    __syncwarp();
+  } else if (warp == PF_MMA_WARP) {
     // ---------------- MMA issue: one lane ----------------
     if (lane == 0) {
       const uint32_t idesc = umma_idesc(nmma);
       for (int g = 0; g < KG && ok; ++g) {
-        const int s = g % STAGES, ph = (g / STAGES) & 1;
+        const int s = g % SA, ph = (g / SA) & 1;
         ok = mbar_wait(a_ready + s, ph) && mbar_wait(b_ready + s, ph);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t abase = smem_addr(smem + s * SM::STAGE_BYTES), bbase = abase + M * SM::A_BYTES;
+        const uint32_t abase = smem_addr(smem + s * SM::AB_BYTES), bbase = abase + M * SM::A_BYTES;
 #pragma unroll
         for (int m = 0; m < M; ++m)
 #pragma unroll
           for (int ks = 0; ks < 4; ++ks)
             umma(tmem_base + m * 256, umma_desc(abase + m * SM::A_BYTES + ks * 32), umma_desc(bbase + ks * 32), idesc,
                  (g | ks) ? 1u : 0u);
-        umma_commit(stage_free + s);
+        umma_commit(ab_free + s);
       }
       if (ok) umma_commit(acc_ready);
     }
     __syncwarp();
-  } else {
-    // ---------------- warps 0-3: dequantise into the A tiles, then the epilogue ----------------
-    const int gq = lane >> 2, t = lane & 3;
+  } else if (warp >= PF_DQ_WARPS) {
+    // ---------------- warps 8-11: gather the pairs' input rows into the swizzled B tiles ----------------
+    // thread -> chunk c of rows r0, r0 + 16, ...: the row pointers stay in registers for the whole K loop
+    const int gt = tid - PF_DQ_WARPS * 32, c = gt & 7, r0 = gt >> 3;
+    const __nv_bfloat16* rowp[PF_GA_PER_THREAD];
+#pragma unroll
+    for (int j = 0; j < PF_GA_PER_THREAD; ++j) {
+      const int r = r0 + 16 * j;
+      const int p = r < cnt ? out_row[r] : -1;
+      rowp[j] = p < 0 ? nullptr : X + (size_t)(slots ? p / slots : p) * x_stride + c * 8;
+    }
+    const uint32_t boff = (uint32_t)(r0 * 128 + ((c ^ (r0 & 7)) << 4));      // rows 16 apart share r & 7
     for (int g = 0; g < KG && ok; ++g) {
-      const int s = g % STAGES, ph = (g / STAGES) & 1;
-      ok = mbar_wait(packed_full + s, ph);
+      const int s = g % SA, round = g / SA;
+      if (round > 0) ok = mbar_wait(ab_free + s, (round - 1) & 1);
       if (!ok) break;
-      uint8_t* stage = smem + s * SM::STAGE_BYTES;
-      if (warp < ncb) {
-        const uint8_t* blk = stage + M * SM::A_BYTES + SM::B_BYTES + warp * (M * BLOCK_BYTES);
+      uint8_t* btile = smem + s * SM::AB_BYTES + M * SM::A_BYTES + boff;
+#pragma unroll
+      for (int j = 0; j < PF_GA_PER_THREAD; ++j)
+        if (rowp[j]) cp_async16(btile + j * (16 * 128), rowp[j] + g * GS);
+      cp_async_commit();
+      if (g > 0) {                                   // the stage before this one has landed: publish it
+        cp_async_wait<1>();
+        fence_async_smem();
+        mbar_arrive(b_ready + (g - 1) % SA);
+      }
+    }
+    cp_async_wait<0>();
+    fence_async_smem();
+    if (ok) mbar_arrive(b_ready + (KG - 1) % SA);
+  } else {
+    // ---------------- warps 0-7: dequantise into the A tiles ----------------
+    // warp -> packed column block cbw = warp & 3 and its 16-column tile tt = warp >> 2, for every matrix
+    const int gq = lane >> 2, t = lane & 3, cbw = warp & 3, tt = warp >> 2;
+    for (int g = 0; g < KG && ok; ++g) {
+      const int sp = g % SP, sa = g % SA;
+      ok = mbar_wait(packed_full + sp, (g / SP) & 1);
+      if (ok && g >= SA) ok = mbar_wait(ab_free + sa, (g / SA - 1) & 1);
+      if (!ok) break;
+      if (cbw < ncb) {
+        const uint8_t* blk = smem + SM::PACKED_OFFSET + sp * SM::PACKED_BYTES + cbw * (M * BLOCK_BYTES);
 #pragma unroll
         for (int m = 0; m < M; ++m) {
           const uint4 sbv = *reinterpret_cast<const uint4*>(blk + m * BLOCK_BYTES + SB_OFFSET + gq * 16);
+          const uint4 w = *reinterpret_cast<const uint4*>(blk + m * BLOCK_BYTES + tt * TILE_BYTES + lane * 16);
+          const uint32_t sb_lo = comp(sbv, 2 * tt), sb_hi = comp(sbv, 2 * tt + 1);
+          // rows of the A tile: column cbw * 32 + tt * 16 + gq (and + 8); chunks 2 t and 2 t + 1 of the row
+          uint8_t* row = smem + sa * SM::AB_BYTES + m * SM::A_BYTES + (cbw * 32 + tt * 16 + gq) * 128;
 #pragma unroll
-          for (int tt = 0; tt < 2; ++tt) {
-            const uint4 w = *reinterpret_cast<const uint4*>(blk + m * BLOCK_BYTES + tt * TILE_BYTES + lane * 16);
-            const uint32_t sb_lo = comp(sbv, 2 * tt), sb_hi = comp(sbv, 2 * tt + 1);
-            // rows of the A tile: column warp * 32 + tt * 16 + gq (and + 8); chunks 2 t and 2 t + 1 of the row
-            uint8_t* row = stage + m * SM::A_BYTES + (warp * 32 + tt * 16 + gq) * 128;
-#pragma unroll
-            for (int h = 0; h < 4; ++h) {
-              const uint32_t word = comp(w, h);
-              const uint32_t sb = (h & 2) ? sb_hi : sb_lo;
-              uint4 o;
-              o.x = prefill_pair<SB>(nib_pair(word, 0), sb);
-              o.y = prefill_pair<SB>(nib_pair(word, 4), sb);
-              o.z = prefill_pair<SB>(nib_pair(word, 8), sb);
-              o.w = prefill_pair<SB>(nib_pair(word, 12), sb);
-              const int chunk = 2 * t + (h & 1);
-              *reinterpret_cast<uint4*>(row + (h & 2) * 512 + ((chunk ^ gq) << 4)) = o;
-            }
+          for (int h = 0; h < 4; ++h) {
+            const uint32_t word = comp(w, h);
+            const uint32_t sb = (h & 2) ? sb_hi : sb_lo;
+            uint4 o;
+            o.x = prefill_pair<SB>(nib_pair(word, 0), sb);
+            o.y = prefill_pair<SB>(nib_pair(word, 4), sb);
+            o.z = prefill_pair<SB>(nib_pair(word, 8), sb);
+            o.w = prefill_pair<SB>(nib_pair(word, 12), sb);
+            const int chunk = 2 * t + (h & 1);
+            *reinterpret_cast<uint4*>(row + (h & 2) * 512 + ((chunk ^ gq) << 4)) = o;
           }
         }
       }
       fence_async_smem();
       __syncwarp();
-      if (lane == 0) mbar_arrive(a_ready + s);
+      if (lane == 0) {
+        mbar_arrive(packed_free + sp);
+        mbar_arrive(a_ready + sa);
+      }
     }
-    // epilogue: lane = output column warp * 32 + lane of the unit, 16 pairs a load
+  }
+  // ---------------- epilogue: the twelve dequantising and gathering warps ----------------
+  // TMEM lane quarter warp & 3 (output column (warp & 3) * 32 + lane of the unit); the three warps of a quarter take
+  // a third of the pairs each, 16 pairs a load
+  if (warp < PF_DQ_WARPS + PF_GA_WARPS) {
     if (ok) ok = mbar_wait(acc_ready, 0);
     if (ok) {
       tc_fence_after();
-      const int col = ct * PF_COLS + warp * 32 + lane;
-      const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16);
-      for (int j0 = 0; j0 < nmma; j0 += 16) {
+      const int q = warp & 3, part = warp >> 2, col = ct * PF_COLS + q * 32 + lane;
+      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16);
+      const int blocks = nmma / 16, per = (blocks + 2) / 3;
+      const int jb = min(blocks, part * per) * 16, je = min(blocks, (part + 1) * per) * 16;
+      for (int j0 = jb; j0 < je; j0 += 16) {
         uint32_t a[16], b[16];
         tmem_ld16(taddr + j0, a);
         if constexpr (M == 2) tmem_ld16(taddr + 256 + j0, b);
@@ -284,7 +315,7 @@ prefill_kernel(const __nv_bfloat16* __restrict__ X, int64_t x_stride, int slots,
             } else if constexpr (EPI == EPI_RELU2) {
               static_cast<__nv_bfloat16*>(out)[at] = __float2bfloat16_rn(relu2(v));
             } else if constexpr (EPI == EPI_SWIGLU) {
-              static_cast<__nv_bfloat16*>(out)[at] = __float2bfloat16_rn(swiglu(v, __uint_as_float(b[j]), limit));
+              static_cast<__nv_bfloat16*>(out)[at] = __float2bfloat16_rn(swiglu_fast(v, __uint_as_float(b[j]), limit));
             } else {
               static_cast<__nv_bfloat16*>(out)[at] = __float2bfloat16_rn(v);
             }
@@ -296,7 +327,7 @@ prefill_kernel(const __nv_bfloat16* __restrict__ X, int64_t x_stride, int slots,
   pdl_launch_dependents();
   tc_fence_before();
   __syncthreads();
-  if (warp == 5) tmem_dealloc(tmem_base, TMEM_COLS);
+  if (warp == PF_MMA_WARP) tmem_dealloc(tmem_base, TMEM_COLS);
 }
 
 template <int M, int EPI, int SB>
@@ -326,7 +357,7 @@ int launch_prefill(const void* x, int64_t x_stride, int slots, const void* w, in
 
 using namespace tfb;
 
-// Grouped 4-bit expert matmul, prefill form, over a plan whose items hold at most 256 pairs.  Arguments as the
+// Grouped 4-bit expert matmul, prefill form, over a plan whose items hold at most 192 pairs.  Arguments as the
 // reference extension's `prefill` (src/tensorfold/cuda/experts.cpp:50-56); max_items = an upper bound of the items.
 extern "C" int tfb_experts_prefill(int gs, int epi, const void* x, int64_t x_stride, int slots, const void* w, int kg,
                                    int nb, const int32_t* items, const int32_t* counts, const int32_t* members,

@@ -17,7 +17,7 @@ from . import _lib
 NTW = 4                  # n8 tiles a 32-column block
 COLS = 8 * NTW           # output columns a block
 TILE = 8                 # pairs an item holds (decode form): one mma tile of pairs
-PREFILL_TILE = 256       # pairs a prompt item holds: the tensor-core tile's N
+PREFILL_TILE = 192       # pairs a prompt item holds: the tensor-core tile's N
 SMALL = 1024             # kept for callers that size scratch by it; this library's plan is one launch at any size
 BLOCK = 288              # int32 words a block of 64 inputs x 32 columns: 1024 B of nibbles + 128 B of scale/bias
 
