@@ -106,6 +106,45 @@ int tfb_experts_prefill(int gs, int epi, const void* x, int64_t x_stride, int sl
                         const int32_t* items, const int32_t* counts, const int32_t* members, void* out, int n,
                         float limit, int64_t max_items, int sb_type, void* stream);
 
+/* ---- EXL3 trellis-coded experts ------------------------------------------------------------------------------- */
+/* Trellises are int16 [K/16, N/16, 8 * k2] (k2 = half-bits a value, 2..16), read in place; cb 0 = 3inst, 1 = mcg,
+ * 2 = mul1; suh / svh are fp16 [E, n].  K and N are multiples of 128. */
+
+/* W_q [K, N] fp16 of one trellis through the kernels' lane decode (the bit-exactness hook).
+ * Replaces `dequant`: src/tensorfold/cuda/exl3/experts.cpp:132-141, experts_grouped.cuh:287-306. */
+int tfb_exl3_dequant(const void* trellis, void* out, int K, int N, int k2, int cb, void* stream);
+
+/* pick [R, slots] -> uids [maxu] = the distinct routed experts (< E) ascending, ucount [1], members [maxu, maxm] =
+ * row * 32 + slot in row order, -1 after the last.  tmp_members [R * slots], tmp_items [3 * min(R * slots, E)] and
+ * tmp_counts [2] are caller scratch.  E <= 1024, slots <= 32.
+ * Replaces `group`: src/tensorfold/cuda/exl3/experts.cu:19-72,290-310. */
+int tfb_exl3_group(const int32_t* pick, int32_t* uids, int32_t* ucount, int32_t* members, int32_t* tmp_members,
+                   int32_t* tmp_items, int32_t* tmp_counts, int R, int slots, int E, int maxu, int maxm, void* stream);
+
+/* out0 / out1 [R * slots, K] fp16 = fp16(((x * suh) H) / sqrt(128)) for the two matrices of every routed pair; x is
+ * bf16 (x_is_fp16 = 0) or fp16 rows with stride x_stride.
+ * Replaces `rot_in`: src/tensorfold/cuda/exl3/experts.cu:93-111,312-330. */
+int tfb_exl3_rot_in(const void* x, int64_t x_stride, int x_is_fp16, const int32_t* pick, const void* suh0,
+                    const void* suh1, void* out0, void* out1, int R, int K, int slots, int E, void* stream);
+
+/* z [mats, P, N] fp32 = x_m [P, K] fp16 times W_q of each pair's expert, trellis decoded on the fly; tp*: int64 device
+ * pointers [E], k2_*: int32 [E].  Replaces `grouped`: src/tensorfold/cuda/exl3/experts_grouped.cuh:190-284. */
+int tfb_exl3_grouped(const void* x0, const void* x1, const int64_t* tp0, const int64_t* tp1, const int32_t* k2_0,
+                     const int32_t* k2_1, const int32_t* uids, const int32_t* ucount, const int32_t* members, float* z,
+                     int mats, int K, int N, int P, int slots, int cb, int maxm, int maxu, void* stream);
+
+/* xd [P, N] fp16 = rotate(SwiGLU(rotate(z_gate) * svh_g, rotate(z_up) * svh_u) * suh_d); act_mode 0: bf16 roundings,
+ * 1: fp32.  Replaces `gateup_epilogue`: src/tensorfold/cuda/exl3/experts.cu:116-158. */
+int tfb_exl3_gateup_epilogue(const float* z, const int32_t* pick, const void* svh_g, const void* svh_u,
+                             const void* suh_d, void* xd, int P, int N, int E, float limit, int act_mode,
+                             void* stream);
+
+/* y [R * slots, D] fp32 = rotate(z) * svh_d per routed pair; with wts and out (both or neither) also
+ * out [R, D] fp32 = the slot-order fma chain of wts * y.
+ * Replaces `down_epilogue`, `combine`, `down_combine`: src/tensorfold/cuda/exl3/experts.cu:161-237. */
+int tfb_exl3_down_epilogue(const float* z, const int32_t* pick, const void* svh_d, float* y, const float* wts,
+                           float* out, int R, int D, int E, int slots, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -25,6 +25,12 @@ SIGNATURES: dict[str, tuple] = {
     "tfb_dequant": (P, I, I, I, P, I, I, I, P),
     "tfb_experts_run": (I, I, P, L, I, P, I, I, P, P, P, P, I, F, L, I, P),
     "tfb_experts_prefill": (I, I, P, L, I, P, I, I, P, P, P, P, I, F, L, I, P),
+    "tfb_exl3_dequant": (P, P, I, I, I, I, P),
+    "tfb_exl3_group": (P, P, P, P, P, P, P, I, I, I, I, I, P),
+    "tfb_exl3_rot_in": (P, L, I, P, P, P, P, P, I, I, I, I, P),
+    "tfb_exl3_grouped": (P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, P),
+    "tfb_exl3_gateup_epilogue": (P, P, P, P, P, P, I, I, I, F, I, P),
+    "tfb_exl3_down_epilogue": (P, P, P, P, P, P, I, I, I, I, P),
     "tfb_kernel_status": (P, P),
 }
 

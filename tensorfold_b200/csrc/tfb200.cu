@@ -4,3 +4,4 @@
 #include "pack.cu"
 #include "experts_decode.cu"
 #include "experts_prefill.cu"
+#include "exl3.cu"

@@ -1,0 +1,142 @@
+"""Expert parallelism for the routed-expert layer: experts sharded over the ranks of a process group, tokens data
+parallel, one all-to-all each way (dispatch of token rows to the experts' owners, return of the per-pair outputs).
+
+The reference has no expert parallelism (its only multi-GPU mode is 2-rank tensor parallelism with an all-gather of
+fp32 partials, ``src/tensorfold/cuda/comm.py:69-76``); this is the sharding the routed path admits on an NVSwitch
+node: expert ``e`` lives on rank ``e // (E / world)``, router rows and the shared expert are replicated, a token's
+pairs travel to their experts and come back as fp32 rows, and the home rank sums them in slot order - so a token's
+result does not depend on the world size.  Collectives are ``torch.distributed.all_to_all_single`` (NCCL over NVLink on
+GPUs; gloo in the CPU tests).  Rows are in the receiver's own memory before any kernel reads them.
+
+The arithmetic is behind a small backend interface so the index logic can be exercised on CPU ranks with a stand-in;
+the product backend (``CudaBackend``) runs this package's CUDA operators and has no CPU path.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+import torch.distributed as dist
+
+
+class CudaBackend:
+    """This rank's share of a layer on its GPU: full router rows, its slice of the routed experts, the shared expert."""
+
+    def __init__(self, router_rows: torch.Tensor, local_experts, top_k: int, experts: int, shared_experts=None,
+                 prefill_pairs: int = 24) -> None:
+        from . import experts as grouped
+        from . import moe
+
+        self.moe, self.grouped = moe, grouped
+        self.router_rows, self.local, self.top_k, self.experts = router_rows, local_experts, top_k, experts
+        self.shared = shared_experts                      # an Experts object holding the one shared expert, or None
+        self.prefill_pairs = prefill_pairs                # pairs a local expert from which the prefill form is used
+        self.device = router_rows.device
+
+    def route(self, x: torch.Tensor):
+        m = self.moe
+        slots = self.top_k + (1 if self.shared is not None else 0)
+
+        class _Cfg:
+            num_experts_per_tok, num_experts = self.top_k, self.experts
+            moe_intermediate_size, hidden_size = self.local.width, self.local.dims
+
+        buf = m.MoEBuffers(x.shape[0], _Cfg, self.device, shared=self.shared is not None)
+        m.router(x, self.router_rows, buf.logits)
+        m.select_rows(buf.logits, buf, self.top_k, self.experts)
+        assert buf.slots == slots
+        return buf.pick, buf.wts
+
+    def _run(self, ex, rows: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
+        g = self.grouped
+        n = rows.shape[0]
+        y = torch.empty((n, ex.dims), dtype=torch.float32, device=self.device)
+        if n == 0:
+            return y
+        prefill = n >= self.prefill_pairs * ex.count
+        plan = g.Plan(n, 1, ex.count, self.device, prefill=prefill)
+        g.route(ids.view(n, 1).contiguous(), plan)
+        act = torch.empty((n, ex.width), dtype=torch.bfloat16, device=self.device)
+        g.gate_up(rows, ex, plan, act, n)
+        g.down(act, ex, plan, y, n)
+        return y
+
+    def run_experts(self, rows: torch.Tensor, local_ids: torch.Tensor) -> torch.Tensor:
+        return self._run(self.local, rows, local_ids)
+
+    def run_shared(self, x: torch.Tensor) -> torch.Tensor:
+        ids = torch.zeros((x.shape[0],), dtype=torch.int32, device=self.device)
+        return self._run(self.shared, x, ids)
+
+    def combine(self, y: torch.Tensor, wts: torch.Tensor) -> torch.Tensor:
+        return self.moe.combine(y, wts)
+
+
+@dataclass
+class DispatchPlan:
+    """Where a rank's routed pairs go: ``order`` sorts the pairs by owner rank (stable), ``send`` / ``recv`` are the
+    per-peer row counts."""
+
+    order: torch.Tensor
+    send: list
+    recv: list
+
+
+class ExpertParallel:
+    """One MoE layer over ``group``: ``forward(x_local)`` -> this rank's tokens' outputs [T_local, D] bf16."""
+
+    def __init__(self, backend, experts: int, top_k: int, shared: bool, group=None) -> None:
+        self.backend, self.experts, self.top_k, self.shared = backend, experts, top_k, shared
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        if experts % self.world:
+            raise ValueError(f"{experts} experts do not shard evenly over {self.world} ranks")
+        self.per_rank = experts // self.world
+        self.last_plan: DispatchPlan | None = None
+
+    def plan_dispatch(self, pick_routed: torch.Tensor) -> DispatchPlan:
+        """pick_routed [T, k]: owners, a stable sort of the pairs by owner, and the counts exchanged with the peers."""
+
+        owner = (pick_routed.reshape(-1) // self.per_rank).to(torch.int64)
+        order = torch.sort(owner, stable=True).indices
+        send = torch.bincount(owner, minlength=self.world).to(torch.int64)
+        recv = torch.empty_like(send)
+        if self.world > 1:
+            dist.all_to_all_single(recv, send, group=self.group)
+        else:
+            recv.copy_(send)
+        return DispatchPlan(order, send.tolist(), recv.tolist())          # the one host read of a step
+
+    def _exchange(self, rows: torch.Tensor, out_counts: list, in_counts: list) -> torch.Tensor:
+        out = torch.empty((sum(in_counts), *rows.shape[1:]), dtype=rows.dtype, device=rows.device)
+        if self.world > 1:
+            dist.all_to_all_single(out, rows.contiguous(), output_split_sizes=in_counts, input_split_sizes=out_counts,
+                                   group=self.group)
+        else:
+            out.copy_(rows)
+        return out
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        be, k = self.backend, self.top_k
+        rows, dims = x.shape
+        pick, wts = be.route(x)                                            # [T, slots], slot k = the shared expert
+        slots = pick.shape[1]
+        routed = pick[:, :k].contiguous()
+        plan = self.plan_dispatch(routed)
+        self.last_plan = plan
+        pair_rows = (plan.order // k)                                      # the token of each sorted pair
+        send_rows = x.index_select(0, pair_rows)
+        send_ids = (routed.reshape(-1).index_select(0, plan.order) % self.per_rank).to(torch.int32)
+        got_rows = self._exchange(send_rows, plan.send, plan.recv)
+        got_ids = self._exchange(send_ids, plan.send, plan.recv)
+        y_remote = be.run_experts(got_rows, got_ids)                       # [n_recv, D] fp32, one row a pair
+        y_sorted = self._exchange(y_remote, plan.recv, plan.send)          # back in this rank's sorted-pair order
+        y = torch.empty((rows, slots, dims), dtype=y_sorted.dtype, device=x.device)
+        y_routed = torch.empty((rows * k, dims), dtype=y_sorted.dtype, device=x.device)
+        y_routed.index_copy_(0, plan.order, y_sorted)
+        y[:, :k] = y_routed.view(rows, k, dims)
+        if self.shared:
+            y[:, k] = be.run_shared(x)
+        return be.combine(y.contiguous(), wts.contiguous())

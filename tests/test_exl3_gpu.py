@@ -1,0 +1,176 @@
+"""EXL3 routed experts on the GPU through the C ABI: lane decode bit for bit against the oracle and the reference's
+fixtures, grouping order, window invariance, and the layer against float64."""
+
+import math
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+GOLDEN = np.load(Path(__file__).parent / "golden" / "exl3_golden.npz")
+
+
+def _trellis(k, n, k2, gen):
+    v = torch.randint(-32768, 32768, (k // 16, n // 16, 8 * k2), dtype=torch.int32, generator=gen)
+    return v.to(torch.int16).to(DEV).contiguous()
+
+
+def _scale(n, mag, gen):
+    sign = torch.randint(0, 2, (n,), generator=gen).float() * 2 - 1
+    return (sign * (torch.rand((n,), generator=gen) + 0.5) * mag).half().to(DEV)
+
+
+@pytest.mark.parametrize("cb", [0, 1, 2])
+@pytest.mark.parametrize("k2", list(range(2, 17)))
+def test_decode_matches_the_bitstream(cb, k2):
+    """Every codebook and width (half-integer rates included) against the numpy restatement, bit for bit."""
+
+    from oracle import exl3 as ref
+    from tensorfold_b200.exl3 import experts
+
+    g = torch.Generator().manual_seed(100 * cb + k2)
+    t = _trellis(48, 32, k2, g)
+    got = experts.dequant(t, cb).cpu().numpy()
+    want = ref.unpack(t.cpu().numpy(), cb)
+    assert np.array_equal(got.view(np.uint16), want.view(np.uint16))
+
+
+def test_decode_matches_the_reference_fixtures():
+    from tensorfold_b200.exl3 import experts
+
+    for key in GOLDEN.files:
+        if key.startswith("t_cb"):
+            cb = int(key[4])
+            got = experts.dequant(torch.from_numpy(GOLDEN[key]).to(DEV), cb).cpu().numpy()
+            assert np.array_equal(got.view(np.uint16), GOLDEN["w" + key[1:]]), key
+
+
+def _layer(E, D, I, k2s, cb, seed):
+    from tensorfold_b200.exl3 import experts
+
+    g = torch.Generator().manual_seed(seed)
+    gate, up, down = [], [], []
+    for e in range(E):
+        kg, ku, kd = k2s[e]
+        gate.append((_trellis(D, I, kg, g), _scale(D, 1 / math.sqrt(D), g), _scale(I, 1.0, g)))
+        up.append((_trellis(D, I, ku, g), _scale(D, 1 / math.sqrt(D), g), _scale(I, 1.0, g)))
+        down.append((_trellis(I, D, kd, g), _scale(I, 1 / math.sqrt(I), g), _scale(D, 0.25, g)))
+    return experts.prepare(gate, up, down, cb), (gate, up, down)
+
+
+def _picks(E, R, k, gen, shared=False):
+    sel = torch.stack([torch.randperm(E, generator=gen)[:k] for _ in range(R)]).to(torch.int32)
+    w = torch.rand((R, k), generator=gen) * 0.2 + 0.05
+    if shared:
+        sel = torch.cat([sel, torch.full((R, 1), E, dtype=torch.int32)], 1)
+        w = torch.cat([w, torch.ones((R, 1))], 1)
+    return sel.to(DEV).contiguous(), w.float().to(DEV).contiguous()
+
+
+def test_grouping_order():
+    from oracle import exl3 as ref
+    from tensorfold_b200.exl3 import experts
+
+    E, R, k = 24, 40, 6
+    ex, _ = _layer(E, 128, 128, [(4, 4, 4)] * E, 0, 3)
+    g = torch.Generator().manual_seed(5)
+    sel, _ = _picks(E, R, k, g, shared=True)
+    s = experts.Scratch(ex, R, k + 1)
+    experts.group(sel, s, R, E)
+    uids, members = ref.group(sel.cpu().numpy(), E)
+    n = int(s.count[0])
+    ids, mem = s.window(R)
+    assert n == len(uids) and ids[:n].tolist() == uids.tolist()
+    assert np.array_equal(mem[:n].cpu().numpy(), members)
+
+
+MIXED = [
+    (2, lambda e: (4 + 2 * (e % 3), 4 + 2 * (e % 3), 4 + 2 * ((e + 1) % 3))),
+    (2, lambda e: ((2, 3, 5, 6, 7, 8, 10, 12, 14, 16)[e % 10],) * 2 + ((3, 5, 7, 8, 16)[e % 5],)),
+    (1, lambda e: ((2, 4, 6, 8, 10, 12, 14, 16)[e % 8],) * 2 + ((4, 6, 8)[e % 3],)),
+    (0, lambda e: ((2, 4, 6, 8, 10, 12, 14, 16)[(e + 3) % 8],) * 2 + ((8, 6, 16)[e % 3],)),
+]
+
+
+@pytest.mark.parametrize("cb,kfun", MIXED, ids=[f"cb{m[0]}_{i}" for i, m in enumerate(MIXED)])
+def test_mixed_width_rows_are_independent_and_match_float64(cb, kfun):
+    """A width per expert matrix: each row gives identical bits alone and inside windows of 1..128 rows, and the
+    layer agrees with the float64 reference (the bar of tests/cuda/test_exl3_experts.py:181-205: 1e-2 of the max)."""
+
+    from oracle import exl3 as ref
+    from tensorfold_b200 import _lib
+    from tensorfold_b200.exl3 import experts
+
+    E, D, I, TOPK = 24, 512, 256, 6
+    ex, mats = _layer(E, D, I, [kfun(e) for e in range(E)], cb, seed=11 + cb)
+    g = torch.Generator().manual_seed(3)
+    ROWS = 128
+    x = torch.randn((ROWS, D), generator=g).to(torch.bfloat16).to(DEV)
+    sel, w = _picks(E, ROWS, TOPK, g, shared=True)
+    scratch = experts.Scratch(ex, ROWS, TOPK + 1)
+
+    def run(rows):
+        out = experts.routed(x[rows], sel[rows].contiguous(), w[rows].contiguous(), ex, scratch, None, len(rows))
+        return out.clone()
+
+    full = run(list(range(ROWS)))
+    torch.cuda.synchronize()
+    assert _lib.kernel_status() == 0
+    assert torch.isfinite(full).all()
+    for n in (1, 2, 3, 16, 17, 64, 128):
+        for start in (0, ROWS - n):
+            rows = list(range(start, start + n))
+            assert torch.equal(run(rows), full[rows]), (n, start)
+    mats_np = [[(t.cpu().numpy(), a.cpu().numpy(), b.cpu().numpy()) for t, a, b in m] for m in mats]
+    want = ref.routed(x[:4].float().cpu().numpy(), sel[:4].cpu().numpy(), w[:4].cpu().numpy(), *mats_np, cb)
+    err = np.abs(full[:4].double().cpu().numpy() - want).max() / np.abs(want).max()
+    assert err < 1e-2, err
+
+
+def test_per_slot_output_and_fused_combine_agree():
+    from tensorfold_b200.exl3 import experts
+
+    E, D, I, TOPK, R = 12, 256, 128, 4, 9
+    ex, _ = _layer(E, D, I, [(8, 8, 8)] * E, 0, 21)
+    g = torch.Generator().manual_seed(8)
+    x = torch.randn((R, D), generator=g).to(torch.bfloat16).to(DEV)
+    sel, w = _picks(E, R, TOPK, g)
+    s = experts.Scratch(ex, R, TOPK)
+    y = experts.routed(x, sel, None, ex, s, None, R).clone().view(R, TOPK, D)
+    out = experts.routed(x, sel, w, ex, s, None, R)
+    acc = torch.zeros((R, D), dtype=torch.float32, device=DEV)
+    for k in range(TOPK):
+        acc = torch.addcmul(acc, w[:, k:k + 1], y[:, k])          # not fused: compare with a tolerance
+    assert torch.allclose(out, acc, rtol=1e-5, atol=1e-6)
+    assert torch.equal(s.y[:R * TOPK].view(R, TOPK, D), y)         # the fused launch stores the same per-slot y
+
+
+def test_graph_replay_equals_eager():
+    from tensorfold_b200.exl3 import experts
+
+    E, D, I, TOPK = 16, 256, 128, 4
+    ex, _ = _layer(E, D, I, [(4 + 2 * (e % 3), 6, 8) for e in range(E)], 1, 33)
+    g = torch.Generator().manual_seed(9)
+    for R in (1, 4):
+        x = torch.randn((R, D), generator=g).to(torch.bfloat16).to(DEV)
+        sel, w = _picks(E, R, TOPK, g)
+        s = experts.Scratch(ex, R, TOPK)
+        out = torch.empty((R, D), dtype=torch.float32, device=DEV)
+        experts.routed(x, sel, w, ex, s, out, R)
+        eager = out.clone()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            experts.routed(x, sel, w, ex, s, out, R)
+        out.zero_()
+        graph.replay()
+        assert torch.equal(out, eager)
+        sel2, w2 = _picks(E, R, TOPK, g)
+        sel.copy_(sel2)
+        w.copy_(w2)
+        graph.replay()
+        want = experts.routed(x, sel, w, ex, experts.Scratch(ex, R, TOPK), None, R)
+        assert torch.equal(out, want)
