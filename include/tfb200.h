@@ -121,6 +121,15 @@ int tfb_exl3_dequant(const void* trellis, void* out, int K, int N, int k2, int c
 int tfb_exl3_group(const int32_t* pick, int32_t* uids, int32_t* ucount, int32_t* members, int32_t* tmp_members,
                    int32_t* tmp_items, int32_t* tmp_counts, int R, int slots, int E, int maxu, int maxm, void* stream);
 
+/* tfb_exl3_group without the three scratch arguments: the sort's temporaries sit in an array built into the library
+ * (about 140 KB on every GPU that loads it).  No counterpart in the reference; it exists for hosts that cannot allocate
+ * device memory when they call (all HBM already given to their own pools, or allocation calls banned on the decode
+ * path because they stall the device).  Limits: R * slots <= 32768 pairs, E <= 1024, slots <= 32; larger calls are
+ * refused with an error naming tfb_exl3_group.  The first call on a device resolves the array's address - make it
+ * before any stream capture begins.  Calls on one GPU share the array: do not let two run concurrently. */
+int tfb_exl3_group_static(const int32_t* pick, int32_t* uids, int32_t* ucount, int32_t* members, int R, int slots,
+                          int E, int maxu, int maxm, void* stream);
+
 /* out0 / out1 [R * slots, K] fp16 = fp16(((x * suh) H) / sqrt(128)) for the two matrices of every routed pair; x is
  * bf16 (x_is_fp16 = 0) or fp16 rows with stride x_stride.
  * Replaces `rot_in`: src/tensorfold/cuda/exl3/experts.cu:93-111,312-330. */

@@ -27,6 +27,7 @@ SIGNATURES: dict[str, tuple] = {
     "tfb_experts_prefill": (I, I, P, L, I, P, I, I, P, P, P, P, I, F, L, I, P),
     "tfb_exl3_dequant": (P, P, I, I, I, I, P),
     "tfb_exl3_group": (P, P, P, P, P, P, P, I, I, I, I, I, P),
+    "tfb_exl3_group_static": (P, P, P, P, I, I, I, I, I, P),
     "tfb_exl3_rot_in": (P, L, I, P, P, P, P, P, I, I, I, I, P),
     "tfb_exl3_grouped": (P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, P),
     "tfb_exl3_gateup_epilogue": (P, P, P, P, P, P, I, I, I, F, I, P),

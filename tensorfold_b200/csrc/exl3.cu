@@ -511,3 +511,50 @@ extern "C" int tfb_exl3_down_epilogue(const float* z, const int32_t* pick, const
                            D, E, slots),
                     "exl3_down_epilogue");
 }
+
+// ---- grouping without caller scratch ---------------------------------------------------------------------------
+// For hosts that cannot give this library device memory at call time: a serving process that handed every free byte
+// of HBM to its own pools at start-up (so a later cudaMalloc fails), or a decode loop where allocation calls are
+// banned because they stall the whole device.  The sort's temporaries live in the array below, which every GPU that
+// loads the library carries until the process ends (about 140 KB).
+constexpr int GROUP_STATIC_MAX_PAIRS = 32768;         // R * slots a call may sort
+constexpr int GROUP_STATIC_WORDS = GROUP_STATIC_MAX_PAIRS + 3 * tfb::PLAN_EMAX + 64;
+static __device__ __align__(256) int g_group_scratch[GROUP_STATIC_WORDS];
+static int* g_group_scratch_ptr[64] = {nullptr};      // the array's device address, per device (host code cannot use the symbol itself)
+
+// Same result as tfb_exl3_group, with no scratch arguments.  Limits: R * slots <= 32768, E <= 1024, slots <= 32.
+// The first call on a device looks up the array's device address (cudaGetSymbolAddress) and opts the kernel into its
+// shared-memory size; make that first call before starting any stream capture.  All calls on a device share the one
+// array: two calls whose kernels may run at the same time on that GPU (different streams) would corrupt each other -
+// keep them on one stream or order them with events.  Nothing in the array has to start at zero; a call overwrites
+// what it reads.  Calls no allocating routine.
+extern "C" int tfb_exl3_group_static(const int32_t* pick, int32_t* uids, int32_t* ucount, int32_t* members, int R,
+                                     int slots, int E, int maxu, int maxm, void* stream) {
+  TFB_REQUIRE(pick && uids && ucount && members, "exl3_group_static: null pointer");
+  TFB_REQUIRE(E >= 1 && E <= PLAN_EMAX, "exl3_group_static: at most %d experts, not %d", PLAN_EMAX, E);
+  TFB_REQUIRE(slots >= 1 && slots <= 32, "exl3_group_static: 1..32 slots, not %d", slots);
+  TFB_REQUIRE(R >= 0 && maxu >= 0 && maxm >= 0, "exl3_group_static: bad sizes");
+  TFB_REQUIRE((int64_t)R * slots <= GROUP_STATIC_MAX_PAIRS,
+              "exl3_group_static: %lld pairs exceed the built-in scratch (%d pairs); use tfb_exl3_group with caller "
+              "scratch", (long long)R * slots, GROUP_STATIC_MAX_PAIRS);
+  int dev = 0;
+  TFB_CUDA(cudaGetDevice(&dev), "exl3_group_static: cudaGetDevice");
+  TFB_REQUIRE(dev >= 0 && dev < 64, "exl3_group_static: device index %d out of range", dev);
+  if (g_group_scratch_ptr[dev] == nullptr) {
+    int* ptr = nullptr;
+    TFB_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_group_scratch),
+             "exl3_group_static: cudaGetSymbolAddress");
+    TFB_CUDA(cudaFuncSetAttribute(exl3_group_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  (int)(sizeof(int) * 32 * PLAN_EMAX)),
+             "exl3_group_static: shared memory opt-in");
+    g_group_scratch_ptr[dev] = ptr;
+  }
+  int* base = g_group_scratch_ptr[dev];
+  int* tmp_counts = base;                             // [2] (+ padding to keep the next arrays 256-byte aligned)
+  int* tmp_items = base + 64;                         // [3 * min(pairs, E)]
+  int* tmp_members = base + 64 + 3 * PLAN_EMAX;       // [pairs]
+  return check_cuda(launch(exl3_group_kernel, dim3(1), dim3(PLAN_THREADS), sizeof(int) * 32 * (size_t)E,
+                           static_cast<cudaStream_t>(stream), pick, R * slots, E, slots, tmp_members, tmp_items,
+                           tmp_counts, uids, ucount, members, maxm, maxu),
+                    "exl3_group_static");
+}
