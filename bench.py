@@ -214,6 +214,55 @@ def bench_rows(torch, shape, layers, rows: int, steps: int, warmup: int, hbm: fl
             "launches_per_step": runners[0].launches}, runners
 
 
+def bench_exl3(torch, rows_list, steps: int, warmup: int, hbm: float):
+    """Config 3: the same layer shape with EXL3 experts at 4.00 bits a weight (3inst), router and selection included;
+    two weight copies alternate.  Bytes = trellis + suh/svh of the distinct experts + router rows + tokens."""
+
+    from tensorfold_b200 import moe, synthetic
+    from tensorfold_b200.exl3 import experts as x3
+
+    shape, dev = synthetic.C3, torch.device("cuda", torch.cuda.current_device())
+    router = synthetic.router_rows(shape, dev)
+    layers = [x3.prepare(*synthetic.exl3_layer(shape, dev, 4, copy=c), x3.CB_3INST, device=dev) for c in range(2)]
+
+    class _Cfg:
+        num_experts_per_tok, num_experts = shape.top_k, shape.experts
+        moe_intermediate_size, hidden_size = shape.width, shape.dims
+
+    results = []
+    for rows in rows_list:
+        x = synthetic.activations(shape, rows, dev)
+        graphs, bufs = [], []
+        for ex in layers:
+            buf = moe.MoEBuffers(rows, _Cfg, dev, shared=False)
+            scratch = x3.Scratch(ex, rows, shape.top_k, device=dev)
+            out = torch.empty((rows, shape.dims), dtype=torch.float32, device=dev)
+
+            def step(ex=ex, buf=buf, scratch=scratch, out=out):
+                moe.router(x, router, buf.logits)
+                moe.select_rows(buf.logits, buf, shape.top_k, shape.experts)
+                x3.routed(x, buf.pick, buf.wts, ex, scratch, out, rows)
+
+            step()
+            torch.cuda.synchronize()
+            side = torch.cuda.Stream(dev)
+            side.wait_stream(torch.cuda.current_stream())
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=side):
+                step()
+            graphs.append(g)
+            bufs.append((buf, scratch))
+        ms = time_graphs(torch, graphs, steps, warmup)
+        distinct = int(bufs[0][1].count[0])
+        per_expert = 3 * shape.dims * shape.width // 2 + 2 * (2 * shape.dims + 2 * shape.width) + 2 * (shape.dims + shape.width)
+        nbytes = distinct * per_expert + shape.experts * shape.dims * 2 + rows * shape.dims * (2 + 4)
+        results.append({"form": "exl3 4.00 bpw (config 3)", "rows": rows, "ms_per_step": ms,
+                        "tokens_per_s": rows / (ms * 1e-3), "distinct_experts": distinct, "layer_bytes": nbytes,
+                        "layer_gbs": nbytes / (ms * 1e-3) / 1e9, "layer_frac_of_hbm": nbytes / (ms * 1e-3) / 1e9 / hbm,
+                        "launches_per_step": 8})
+    return results
+
+
 def bench_e2e(torch, runners, shape, rows: int, steps: int, warmup: int):
     """The same step through the public API with HOST buffers: pinned tokens in, layer, result back, every step."""
 
@@ -237,6 +286,69 @@ def bench_e2e(torch, runners, shape, rows: int, steps: int, warmup: int):
             "d2h_bytes_per_step": nbytes}
 
 
+def bench_ep(torch, dist, args, shape, dev, rank: int, world: int):
+    """Expert-parallel step: this rank's `rows` tokens through the layer whose experts are sharded over the ranks
+    (NCCL all-to-all dispatch and return).  Each rank keeps 2 * world copies of its expert slice and rotates them, so a
+    step's weights (a slice is 340 / world MB) never sit in L2.  Returns (ms a step by CUDA events, launches a step)."""
+
+    from tensorfold_b200 import ep, experts, moe, synthetic
+
+    rows, per = args.rows, shape.experts // world
+    router = synthetic.router_rows(shape, dev)
+    copies, graphs = [], []
+    for copy in range(2 * world):
+        gate, up, down = synthetic.affine_layer(shape, dev, torch.float16 if args.scales == "fp16" else torch.bfloat16,
+                                                copy=copy)
+        sl = slice(rank * per, (rank + 1) * per)
+        local = experts.make([tuple(t[sl].contiguous() for t in gate), tuple(t[sl].contiguous() for t in up)],
+                             tuple(t[sl].contiguous() for t in down), 64)
+        copies.append(ep.GatheredExpertParallel(router, local, shape.experts, shape.top_k, rows))
+        del gate, up, down
+    x = synthetic.activations(shape, rows, dev, index=100 + rank)
+    side = torch.cuda.Stream(dev)
+    for layer in copies:                                   # warm up eagerly (NCCL set-up), then capture the step
+        layer.forward(x)
+    torch.cuda.synchronize()
+    dist.barrier()
+    for layer in copies:
+        side.wait_stream(torch.cuda.current_stream())
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=side):
+            layer.forward(x)
+        graphs.append(g)
+    torch.cuda.synchronize()
+    dist.barrier()
+    for i in range(args.warmup):
+        graphs[i % len(graphs)].replay()
+    torch.cuda.synchronize()
+    dist.barrier()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for i in range(args.steps):
+        graphs[i % len(graphs)].replay()
+    b.record()
+    torch.cuda.synchronize()
+    dist.barrier()
+    ms = a.elapsed_time(b) / args.steps
+    # end to end: pinned host tokens in, result back, every step
+    x_host = x.cpu().pin_memory()
+    out_host = torch.empty((rows, shape.dims), dtype=torch.bfloat16).pin_memory()
+    torch.cuda.synchronize()
+    dist.barrier()
+    a.record()
+    for i in range(args.steps):
+        x.copy_(x_host, non_blocking=True)
+        graphs[i % len(graphs)].replay()
+        out_host.copy_(copies[i % len(copies)].out, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+    b.record()
+    torch.cuda.synchronize()
+    dist.barrier()
+    e2e_ms = a.elapsed_time(b) / args.steps
+    return ms, e2e_ms, copies[0].launches   # router, select, plan, gate/up, down, combine
+
+
 def run_ours(args) -> None:
     import torch
 
@@ -256,7 +368,7 @@ def run_ours(args) -> None:
     _lib.set_pdl(bool(args.pdl))
     shape, rows = synthetic.C2, args.rows
     layers = []
-    for copy in range(2):
+    for copy in range(2 if world == 1 else 0):
         gate, up, down = synthetic.affine_layer(shape, dev, torch.float16 if args.scales == "fp16" else torch.bfloat16,
                                                  copy=copy)
         layers.append(moe.Routed(synthetic.router_rows(shape, dev), experts.make([gate, up], down, 64), shape.top_k,
@@ -264,27 +376,51 @@ def run_ours(args) -> None:
         del gate, up, down
     torch.cuda.synchronize()
 
+    if world > 1:
+        if shape.experts % world:
+            raise SystemExit(f"{shape.experts} experts do not shard over {world} ranks")
+        del layers
+        with ClockSampler(local) as clocks:
+            ms, e2e_ms, launches = bench_ep(torch, dist, args, shape, dev, rank, world)
+        t = torch.tensor([ms, e2e_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, e2e_ms = t.tolist()
+        status = _lib.kernel_status()
+        if status != 0:
+            raise SystemExit(f"a kernel recorded device status {status}")
+        if rank == 0:
+            nbytes = rows * shape.dims * 2 * world
+            line = {"metric": METRIC, "value": world * rows / (ms * 1e-3), "unit": UNIT, "n_gpus": world,
+                    "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+                    "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+                    "config": {**workload_config(shape, rows, world),
+                               "l2": f"each rank rotates {2 * world} copies of its {shape.experts // world}-expert slice "
+                                     "(inputs larger than the 126 MB L2)",
+                               "collective": "NCCL all-gather of the tokens, reduce-scatter of the per-pair fp32 rows; the step is one CUDA graph"},
+                    "clocks": clocks.summary(),
+                    "e2e": {"value": world * rows / (e2e_ms * 1e-3), "unit": UNIT, "ms_per_step": e2e_ms,
+                            "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": nbytes},
+                    "gpu_launches": launches * args.steps,
+                    "roofline": {"bound": "hbm", "kernel": "decode_kernel (gate/up) inside the expert-parallel step",
+                                 "achieved": None, "peak": hbm, "unit": "GB/s", "frac": None,
+                                 "peak_source": f"of {which}", "traffic": None,
+                                 "note": "per-kernel roofline is measured at 1 GPU; the multi-GPU step is bounded by "
+                                         "the two collectives"},
+                    "cpu_baseline": None}
+            print(json.dumps(line))
+        dist.barrier()
+        dist.destroy_process_group()
+        return
     with ClockSampler(local) as clocks:
-        if world > 1:
-            dist.barrier()
         torch.cuda.synchronize()
         head, runners = bench_rows(torch, shape, layers, rows, args.steps, args.warmup, hbm, args.form == "prefill",
                                    tflops)
-        if world > 1:
-            dist.barrier()
         torch.cuda.synchronize()
     e2e = bench_e2e(torch, runners, shape, rows, args.steps, args.warmup)
     status = _lib.kernel_status()
     if status != 0:
         raise SystemExit(f"a kernel recorded device status {status}")
     ms = head["ms_per_step"]
-    if world > 1:
-        t = torch.tensor([ms, e2e["ms_per_step"]], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms, e2e_ms = t.tolist()
-        e2e["ms_per_step"], e2e["value"] = e2e_ms, world * rows / (e2e_ms * 1e-3)
-        e2e["h2d_bytes_per_step"] *= world
-        e2e["d2h_bytes_per_step"] *= world
     sweep = []
     if world == 1 and not args.no_sweep:
         del runners
@@ -293,6 +429,9 @@ def run_ours(args) -> None:
             res.setdefault("form", "decode")
             sweep.append(res)
             del rr
+        del layers
+        torch.cuda.empty_cache()
+        sweep += bench_exl3(torch, (1, 64), max(5, args.steps // 2), args.warmup, hbm)
     if rank != 0:
         return
     value = world * rows / (ms * 1e-3)

@@ -33,18 +33,29 @@ router_kernel(const __nv_bfloat16* __restrict__ X, int64_t x_stride, const __nv_
 #pragma unroll
     for (int e = 0; e < R_ET; ++e) acc[r][e] = 0.f;
   pdl_wait();
+  // the next chunk's twelve 16-byte loads travel while this chunk's 256 fmas run
+  const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+  uint4 wn[R_ET], xn[R_RT];
+  auto fetch = [&](int k) {
+#pragma unroll
+    for (int e = 0; e < R_ET; ++e) wn[e] = (e < ne && k < D) ? ldg_nc(W + (size_t)(e0 + e) * D + k) : zero;
+#pragma unroll
+    for (int r = 0; r < R_RT; ++r) xn[r] = (r < nr && k < D) ? ldg_nc(X + (size_t)(r0 + r) * x_stride + k) : zero;
+  };
+  fetch(8 * lane);
   for (int k = 8 * lane; k < D; k += 256) {
     float wv[R_ET][8];
+    uint4 xc[R_RT];
 #pragma unroll
-    for (int e = 0; e < R_ET; ++e) {
-      const uint4 v = e < ne ? ldg_nc(W + (size_t)(e0 + e) * D + k) : make_uint4(0u, 0u, 0u, 0u);
-      unpack8(v, wv[e]);
-    }
+    for (int e = 0; e < R_ET; ++e) unpack8(wn[e], wv[e]);
+#pragma unroll
+    for (int r = 0; r < R_RT; ++r) xc[r] = xn[r];
+    fetch(k + 256);
 #pragma unroll
     for (int r = 0; r < R_RT; ++r) {
       if (r < nr) {
         float xv[8];
-        unpack8(ldg_nc(X + (size_t)(r0 + r) * x_stride + k), xv);
+        unpack8(xc[r], xv);
 #pragma unroll
         for (int e = 0; e < R_ET; ++e)
 #pragma unroll
@@ -203,7 +214,7 @@ select_kernel(const float* __restrict__ L, int NL, int* __restrict__ pick, float
 // experts gives every (warp, expert) its first slot, and a second walk scatters.  Ids outside [0, E) are left out.
 // (Semantics of src/tensorfold/cuda/experts.cu:157-285, pinned by tests/cuda/test_experts.py:107-134.)
 // ================================================================================================================
-constexpr int PLAN_THREADS = 1024, PLAN_EMAX = 1024;
+constexpr int PLAN_THREADS = 1024, PLAN_EMAX = 1024, PLAN_BATCH = 8;
 
 __device__ int place_items(int c, int E, int T, int* __restrict__ items, int* __restrict__ counts,
                            int (*wsum)[32]) {
@@ -261,13 +272,22 @@ __device__ void plan_block(const int* picks, int P, int E, int T, int* __restric
   const int p0 = min(P, warp * seg), p1 = min(P, p0 + seg);
   int* mine = whist + warp * E;
   __syncthreads();
-  for (int base = p0; base < p1; base += 32) {
-    const int p = base + lane;
-    const int e = p < p1 ? picks[p] : -1;
-    const bool ok = e >= 0 && e < E;
-    const unsigned peers = __match_any_sync(0xffffffffu, ok ? e : -1 - lane);
-    if (ok && lane == __ffs(peers) - 1) mine[e] += __popc(peers);
-    __syncwarp();
+  for (int base0 = p0; base0 < p1; base0 += 32 * PLAN_BATCH) {
+    int ev[PLAN_BATCH];                              // the loads of a batch are independent: all in flight at once
+#pragma unroll
+    for (int i = 0; i < PLAN_BATCH; ++i) {
+      const int p = base0 + 32 * i + lane;
+      ev[i] = p < p1 ? picks[p] : -1;
+    }
+#pragma unroll
+    for (int i = 0; i < PLAN_BATCH; ++i) {
+      if (base0 + 32 * i >= p1) break;
+      const int e = ev[i];
+      const bool ok = e >= 0 && e < E;
+      const unsigned peers = __match_any_sync(0xffffffffu, ok ? e : -1 - lane);
+      if (ok && lane == __ffs(peers) - 1) mine[e] += __popc(peers);
+      __syncwarp();
+    }
   }
   __syncthreads();
   int c = 0;
@@ -280,17 +300,26 @@ __device__ void plan_block(const int* picks, int P, int E, int T, int* __restric
   const int off = place_items(c, E, T, items, counts, wsum);
   if (tid < E) first[tid] = off;
   __syncthreads();
-  for (int base = p0; base < p1; base += 32) {
-    const int p = base + lane;
-    const int e = p < p1 ? picks[p] : -1;
-    const bool ok = e >= 0 && e < E;
-    const unsigned peers = __match_any_sync(0xffffffffu, ok ? e : -1 - lane);
-    const int rank = __popc(peers & ((1u << lane) - 1u));
-    const int b = ok ? mine[e] : 0;
-    if (ok) members[first[e] + b + rank] = p;
-    __syncwarp();
-    if (ok && rank == 0) mine[e] = b + __popc(peers);
-    __syncwarp();
+  for (int base0 = p0; base0 < p1; base0 += 32 * PLAN_BATCH) {
+    int ev[PLAN_BATCH];
+#pragma unroll
+    for (int i = 0; i < PLAN_BATCH; ++i) {
+      const int p = base0 + 32 * i + lane;
+      ev[i] = p < p1 ? picks[p] : -1;
+    }
+#pragma unroll
+    for (int i = 0; i < PLAN_BATCH; ++i) {
+      if (base0 + 32 * i >= p1) break;
+      const int p = base0 + 32 * i + lane, e = ev[i];
+      const bool ok = e >= 0 && e < E;
+      const unsigned peers = __match_any_sync(0xffffffffu, ok ? e : -1 - lane);
+      const int rank = __popc(peers & ((1u << lane) - 1u));
+      const int b = ok ? mine[e] : 0;
+      if (ok) members[first[e] + b + rank] = p;
+      __syncwarp();
+      if (ok && rank == 0) mine[e] = b + __popc(peers);
+      __syncwarp();
+    }
   }
 }
 

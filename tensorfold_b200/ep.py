@@ -140,3 +140,63 @@ class ExpertParallel:
         if self.shared:
             y[:, k] = be.run_shared(x)
         return be.combine(y.contiguous(), wts.contiguous())
+
+
+class GatheredExpertParallel:
+    """The same sharding without any host read, so the whole step can sit in a CUDA graph: every rank gathers all
+    ranks' tokens (a few hundred KB), routes them all (identical bits everywhere), runs the pairs that fall on ITS
+    experts into a zeroed per-pair buffer ``y_all`` [T_global * k, D] fp32, and one reduce-scatter hands each home rank
+    its tokens' rows.  Every (token, slot) row is non-zero on exactly one rank, so the sum over ranks is exact and the
+    home rank's slot-order combine gives the one-GPU bits.  Costs more link traffic than the counted all-to-all
+    (``ExpertParallel``) and no latency of a host round trip; NCCL may reduce inside the switch (NVLS)."""
+
+    def __init__(self, router_rows: torch.Tensor, local_experts, experts: int, top_k: int, rows_local: int,
+                 group=None) -> None:
+        from . import experts as grouped
+        from . import moe
+
+        self.moe, self.grouped = moe, grouped
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        if experts % self.world:
+            raise ValueError(f"{experts} experts do not shard evenly over {self.world} ranks")
+        self.per_rank, self.experts, self.top_k = experts // self.world, experts, top_k
+        self.router_rows, self.local, self.rows_local = router_rows, local_experts, rows_local
+        dev, d, k = router_rows.device, local_experts.dims, top_k
+        rows = rows_local * self.world
+        self.rows = rows
+
+        class _Cfg:
+            num_experts_per_tok, num_experts = top_k, experts
+            moe_intermediate_size, hidden_size = local_experts.width, d
+
+        self.x_all = torch.zeros((rows, d), dtype=torch.bfloat16, device=dev)
+        self.buf = moe.MoEBuffers(rows, _Cfg, dev, shared=False)
+        self.plan = grouped.Plan(rows, k, self.per_rank, dev)
+        self.local_pick = torch.zeros((rows, k), dtype=torch.int32, device=dev)
+        self.y_mine = torch.zeros((rows_local * k, d), dtype=torch.float32, device=dev)
+        self.out = torch.zeros((rows_local, d), dtype=torch.bfloat16, device=dev)
+        self.launches = 6
+
+    def forward(self, x_local: torch.Tensor) -> torch.Tensor:
+        m, g, buf, k = self.moe, self.grouped, self.buf, self.top_k
+        if self.world > 1:
+            dist.all_gather_into_tensor(self.x_all, x_local.contiguous(), group=self.group)
+        else:
+            self.x_all.copy_(x_local)
+        m.router(self.x_all, self.router_rows, buf.logits)
+        m.select_rows(buf.logits, buf, k, self.experts)
+        torch.sub(buf.pick, self.rank * self.per_rank, out=self.local_pick)      # ids off this rank fall outside the plan
+        g.route(self.local_pick, self.plan)
+        y_all = buf.y.view(-1, self.local.dims)
+        y_all.zero_()
+        g.gate_up(self.x_all, self.local, self.plan, buf.act.view(-1, self.local.width), self.rows)
+        g.down(buf.act.view(-1, self.local.width), self.local, self.plan, y_all, self.rows)
+        if self.world > 1:
+            dist.reduce_scatter_tensor(self.y_mine, y_all, group=self.group)
+        else:
+            self.y_mine.copy_(y_all)
+        lo = self.rank * self.rows_local
+        wts = buf.wts[lo:lo + self.rows_local]
+        return m.combine(self.y_mine.view(self.rows_local, k, -1), wts, self.out)

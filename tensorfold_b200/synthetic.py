@@ -77,3 +77,34 @@ def affine_layer(shape: LayerShape, device="cuda", scale_dtype=torch.float16, co
     up = affine_matrix(base + 1, e, shape.width, shape.dims, device, scale_dtype)
     down = affine_matrix(base + 2, e, shape.dims, shape.width, device, scale_dtype)
     return gate, up, down
+
+
+C3 = LayerShape("c3", 3, 2048, 128, 768, 8)
+C5 = LayerShape("c5", 5, 4096, 160, 1536, 8)
+
+
+def exl3_matrix(seed: int, k: int, n: int, bits: int, device="cuda"):
+    """(trellis int16 [k/16, n/16, 16 * bits] of uniform 16-bit words, suh fp16 [k], svh fp16 [n] = +-1 x |N(0, 0.02)|)."""
+
+    g = _gen(seed, device)
+    t = torch.randint(-32768, 32768, (k // 16, n // 16, 16 * bits), generator=g, device=device, dtype=torch.int32)
+
+    def scale(m):
+        sign = torch.randint(0, 2, (m,), generator=g, device=device).float() * 2 - 1
+        return (sign * (torch.randn((m,), generator=g, device=device) * 0.02).abs()).half()
+
+    return t.to(torch.int16), scale(k), scale(n)
+
+
+def exl3_layer(shape: LayerShape, device="cuda", bits=4, copy: int = 0):
+    """Per-expert (gate, up, down) triples at ``bits`` per weight; ``bits`` may be a callable (expert, matrix) -> bits
+    for mixed-width stacks (config 5 draws 2..8 per tensor from a seeded generator)."""
+
+    base = 1000 * shape.config + 10 + 1000003 * copy
+    gate, up, down = [], [], []
+    for e in range(shape.experts):
+        b = [bits(e, m) if callable(bits) else bits for m in range(3)]
+        gate.append(exl3_matrix(base + 3 * e, shape.dims, shape.width, b[0], device))
+        up.append(exl3_matrix(base + 3 * e + 1, shape.dims, shape.width, b[1], device))
+        down.append(exl3_matrix(base + 3 * e + 2, shape.width, shape.dims, b[2], device))
+    return gate, up, down

@@ -1,0 +1,75 @@
+"""Expert parallelism on two GPUs over NCCL: every token's output equals the one-GPU layer's, bit for bit (the same
+kernels run on each pair, the home rank sums in slot order).  Needs two devices; skipped otherwise."""
+
+import os
+import socket
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def _worker(rank, world, port, out):
+    sys.path.insert(0, str(ROOT))
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    import torch.distributed as dist
+
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    from tensorfold_b200 import ep, experts, moe, synthetic
+
+    shape, rows = synthetic.SMALL, 20
+    per = shape.experts // world
+    gate, up, down = synthetic.affine_layer(shape, dev)
+    router = synthetic.router_rows(shape, dev)
+    sl = slice(rank * per, (rank + 1) * per)
+    local = experts.make([tuple(t[sl].contiguous() for t in gate), tuple(t[sl].contiguous() for t in up)],
+                         tuple(t[sl].contiguous() for t in down), 64)
+    layer = ep.ExpertParallel(ep.CudaBackend(router, local, shape.top_k, shape.experts), shape.experts, shape.top_k,
+                              False)
+    x = synthetic.activations(shape, rows, dev, index=50 + rank)
+    got = layer.forward(x)
+    full = moe.Routed(router, experts.make([gate, up], down, 64), shape.top_k, shared=False)
+    want = moe.run(x, full)
+    gathered = ep.GatheredExpertParallel(router, local, shape.experts, shape.top_k, rows)
+    got2 = gathered.forward(x).clone()
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        gathered.forward(x)
+    gathered.out.zero_()
+    graph.replay()
+    torch.cuda.synchronize()
+    flags = (bool(torch.equal(got, want)), bool(torch.equal(got2, want)), bool(torch.equal(gathered.out, want)))
+    del graph
+    torch.cuda.synchronize()
+    out.put((rank, flags))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_two_gpus_match_one():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, out)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = [out.get(timeout=300) for _ in procs]
+    assert all(all(flags) for _, flags in results), results        # (counted all-to-all, gathered, gathered in a graph)
+    for p in procs:
+        p.join(timeout=120)
+    assert [p.exitcode for p in procs] == [0, 0]
