@@ -366,6 +366,9 @@ def run_ours(args) -> None:
         dist.init_process_group("nccl", device_id=dev)
     hbm, tflops, which = peaks()
     _lib.set_pdl(bool(args.pdl))
+    if args.exl3_only:
+        print(json.dumps({"sweep": bench_exl3(torch, (1, 64), args.steps, args.warmup, hbm)}))
+        return
     shape, rows = synthetic.C2, args.rows
     layers = []
     for copy in range(2 if world == 1 else 0):
@@ -464,6 +467,8 @@ def main() -> None:
     ap.add_argument("--pdl", type=int, default=1, help="1: programmatic dependent launch between the layer's kernels")
     ap.add_argument("--form", default="decode", choices=["decode", "prefill"],
                     help="arithmetic form of the headline run (the sweep always uses decode at 1 and prefill at 2048)")
+    ap.add_argument("--exl3-only", action="store_true",
+                    help="run only the EXL3 (config 3) lines of the sweep and print them (a profiling aid)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-sweep", action="store_true", help="skip the 1-token and 2048-token lines")
     args = ap.parse_args()

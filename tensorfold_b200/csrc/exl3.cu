@@ -16,8 +16,8 @@ namespace tfb {
 namespace exl3 {
 
 constexpr float HAD_SCALE = 0.08838834764831845f;   // 1 / sqrt(128)
-constexpr int GR_WARPS = 4;                         // K slices a CTA of the grouped kernel
-constexpr int GR_NTB = 4;                           // 16-column tiles a CTA (64 output columns)
+constexpr int GR_WARPS = 4;                         // K slices a CTA of the grouped kernel (part of the arithmetic)
+constexpr int GR_NTB_MAX = 4;                       // 16-column tiles a CTA at most (no effect on the arithmetic)
 constexpr int GR_PAIRS = 8;                         // pairs a CTA (one mma B tile)
 
 // ---- codebooks: two states -> two fp16 values (src/tensorfold/cuda/exl3/format.py:31-48) ------------------------
@@ -33,10 +33,10 @@ __device__ __forceinline__ uint32_t cb_pair(uint32_t s0, uint32_t s1) {
   } else {                                            // 3inst / mcg: the two fp16 halves of the masked product, added
     uint32_t x0 = CB == 1 ? s0 * 0xCBAC1FEDu : s0 * 89226354u + 64248484u;
     uint32_t x1 = CB == 1 ? s1 * 0xCBAC1FEDu : s1 * 89226354u + 64248484u;
-    x0 = (x0 & 0x8FFF8FFFu) ^ 0x3B603B60u;
-    x1 = (x1 & 0x8FFF8FFFu) ^ 0x3B603B60u;
-    const uint32_t lo = __byte_perm(x0, x1, 0x5410), hi = __byte_perm(x0, x1, 0x7632);
-    const __half2 r = __hadd2(*reinterpret_cast<const __half2*>(&lo), *reinterpret_cast<const __half2*>(&hi));
+    asm("lop3.b32 %0, %1, %2, %3, 0x6A;\n" : "=r"(x0) : "r"(x0), "r"(0x8FFF8FFFu), "r"(0x3B603B60u));   // (x & M) ^ F
+    asm("lop3.b32 %0, %1, %2, %3, 0x6A;\n" : "=r"(x1) : "r"(x1), "r"(0x8FFF8FFFu), "r"(0x3B603B60u));
+    const __half2 h0 = *reinterpret_cast<const __half2*>(&x0), h1 = *reinterpret_cast<const __half2*>(&x1);
+    const __half2 r = __halves2half2(__hadd(__low2half(h0), __high2half(h0)), __hadd(__low2half(h1), __high2half(h1)));
     return *reinterpret_cast<const uint32_t*>(&r);
   }
 }
@@ -51,34 +51,52 @@ template <int K2>
 struct Win {
   static constexpr int TW = 4 * K2;                                 // 32-bit words a tile
   static constexpr int SPAN = delta<K2>(7) + 16;                    // stream bits a lane's windows cover
-  static constexpr int NW = (31 + SPAN + 31) / 32;                  // words to read at the worst offset (<= 4)
+  static constexpr int NW = K2 == 8 ? 2 : (31 + SPAN + 31) / 32;    // words a lane reads (worst offset; <= 4)
   static constexpr int NV = (SPAN + 31) / 32;                       // 32-bit chunks of the lane's span
 };
 
-// `tile` points at the tile's first word (global memory).  st[j] = state of value 8 lane + j.
+// The words of a tile a lane needs: NW consecutive words (cyclically) from the one holding the first bit of value
+// 8 lane's window.  4 bits a value (K2 = 8): exactly words lane - 1 and lane.
 template <int K2>
-__device__ __forceinline__ void lane_states(const uint32_t* __restrict__ tile, int lane, uint32_t (&st)[8]) {
-  constexpr int TW = Win<K2>::TW, NW = Win<K2>::NW, NV = Win<K2>::NV;
+__device__ __forceinline__ void lane_words(const uint32_t* __restrict__ tile, int lane, uint32_t (&w)[Win<K2>::NW]) {
+  constexpr int TW = Win<K2>::TW, NW = Win<K2>::NW;
   const int first = 4 * lane * K2 + (K2 >> 1) - 16 + 32 * TW;       // E(8 lane) - 16, made non-negative
   int wi = (first >> 5) % TW;
-  const int off = first & 31;
-  uint32_t w[NW];
 #pragma unroll
   for (int i = 0; i < NW; ++i) {
     w[i] = __ldg(tile + wi);
     wi = wi + 1 == TW ? 0 : wi + 1;
   }
-  // v[i] = stream bits [first + 32 i, first + 32 i + 32)
-  uint32_t v[NV];
+}
+
+// st[j] = state of value 8 lane + j from the lane's words.
+template <int K2>
+__device__ __forceinline__ void lane_states(const uint32_t (&w)[Win<K2>::NW], int lane, uint32_t (&st)[8]) {
+  constexpr int NW = Win<K2>::NW, NV = Win<K2>::NV;
+  if constexpr (K2 == 8) {
+    // windows of 16 bits ending at bit 4 (j + 1) of the lane's own word: three reach back into the word before
+    const uint32_t q = __funnelshift_r(w[1], w[0], 20);
+    st[0] = (q >> 8) & 0xFFFFu;
+    st[1] = (q >> 4) & 0xFFFFu;
+    st[2] = q & 0xFFFFu;
+    st[3] = w[1] >> 16;
+    st[4] = (w[1] >> 12) & 0xFFFFu;
+    st[5] = (w[1] >> 8) & 0xFFFFu;
+    st[6] = (w[1] >> 4) & 0xFFFFu;
+    st[7] = w[1] & 0xFFFFu;
+  } else {
+    const int off = (4 * lane * K2 + (K2 >> 1) - 16 + 32 * Win<K2>::TW) & 31;
+    uint32_t v[NV];                                   // v[i] = stream bits [first + 32 i, first + 32 i + 32)
 #pragma unroll
-  for (int i = 0; i < NV; ++i) v[i] = __funnelshift_l(i + 1 < NW ? w[i + 1] : 0u, w[i], off);
+    for (int i = 0; i < NV; ++i) v[i] = __funnelshift_l(i + 1 < NW ? w[i + 1] : 0u, w[i], off);
 #pragma unroll
-  for (int j = 0; j < 8; ++j) {
-    const int d = delta<K2>(j), i = d >> 5, o = d & 31;
-    if (o <= 16) {
-      st[j] = (v[i] >> (16 - o)) & 0xFFFFu;
-    } else {                                          // the window runs into the next chunk (which exists: d + 16 <= SPAN)
-      st[j] = __funnelshift_l(v[i + 1 < NV ? i + 1 : i], v[i], o) >> 16;
+    for (int j = 0; j < 8; ++j) {
+      const int d = delta<K2>(j), i = d >> 5, o = d & 31;
+      if (o <= 16) {
+        st[j] = (v[i] >> (16 - o)) & 0xFFFFu;
+      } else {                                        // the window runs into the next chunk (d + 16 <= SPAN: it exists)
+        st[j] = __funnelshift_l(v[i + 1 < NV ? i + 1 : i], v[i], o) >> 16;
+      }
     }
   }
 }
@@ -87,13 +105,20 @@ __device__ __forceinline__ void lane_states(const uint32_t* __restrict__ tile, i
 // a0 = (col g, k 2t, 2t+1) = values 0, 1; a1 = (col g + 8, same k) = values 4, 5; a2 = (col g, k + 8) = values 2, 3;
 // a3 = (col g + 8, k + 8) = values 6, 7.
 template <int CB, int K2>
-__device__ __forceinline__ void decode_tile(const uint32_t* __restrict__ tile, int lane, uint32_t (&a)[4]) {
+__device__ __forceinline__ void decode_words(const uint32_t (&w)[Win<K2>::NW], int lane, uint32_t (&a)[4]) {
   uint32_t st[8];
-  lane_states<K2>(tile, lane, st);
+  lane_states<K2>(w, lane, st);
   a[0] = cb_pair<CB>(st[0], st[1]);
   a[2] = cb_pair<CB>(st[2], st[3]);
   a[1] = cb_pair<CB>(st[4], st[5]);
   a[3] = cb_pair<CB>(st[6], st[7]);
+}
+
+template <int CB, int K2>
+__device__ __forceinline__ void decode_tile(const uint32_t* __restrict__ tile, int lane, uint32_t (&a)[4]) {
+  uint32_t w[Win<K2>::NW];
+  lane_words<K2>(tile, lane, w);
+  decode_words<CB, K2>(w, lane, a);
 }
 
 __device__ __forceinline__ void mma_f16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
@@ -104,21 +129,34 @@ __device__ __forceinline__ void mma_f16(float (&d)[4], const uint32_t (&a)[4], u
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-// One warp's k tiles [kt0, kt0 + nkt) of GR_NTB column tiles into acc.
-template <int CB, int K2>
+// One warp's k tiles [kt0, kt0 + nkt) of GR_NTB column tiles into acc; the next row of tiles' words and inputs are
+// loaded before this row is decoded.
+template <int CB, int K2, int GR_NTB>
 __device__ __forceinline__ void warp_tiles(const uint32_t* __restrict__ T, int ntiles, int kt0, int nkt, int nt0,
                                            const __half* __restrict__ x, int lane, float (&acc)[GR_NTB][4]) {
-  constexpr int TW = Win<K2>::TW;
+  constexpr int TW = Win<K2>::TW, NW = Win<K2>::NW;
   const int t = lane & 3;
-  for (int it = 0; it < nkt; ++it) {
-    const int kt = kt0 + it;
-    const uint32_t b0 = *reinterpret_cast<const uint32_t*>(x + kt * 16 + 2 * t);
-    const uint32_t b1 = *reinterpret_cast<const uint32_t*>(x + kt * 16 + 2 * t + 8);
+  uint32_t wn[GR_NTB][NW], bn0, bn1;
+  auto fetch = [&](int kt) {
+    bn0 = *reinterpret_cast<const uint32_t*>(x + kt * 16 + 2 * t);
+    bn1 = *reinterpret_cast<const uint32_t*>(x + kt * 16 + 2 * t + 8);
     const uint32_t* row = T + ((size_t)kt * ntiles + nt0) * TW;
+#pragma unroll
+    for (int i = 0; i < GR_NTB; ++i) lane_words<K2>(row + i * TW, lane, wn[i]);
+  };
+  if (nkt > 0) fetch(kt0);
+  for (int it = 0; it < nkt; ++it) {
+    uint32_t wc[GR_NTB][NW];
+    const uint32_t b0 = bn0, b1 = bn1;
+#pragma unroll
+    for (int i = 0; i < GR_NTB; ++i)
+#pragma unroll
+      for (int j = 0; j < NW; ++j) wc[i][j] = wn[i][j];
+    if (it + 1 < nkt) fetch(kt0 + it + 1);
 #pragma unroll
     for (int i = 0; i < GR_NTB; ++i) {
       uint32_t a[4];
-      decode_tile<CB, K2>(row + i * TW, lane, a);
+      decode_words<CB, K2>(wc[i], lane, a);
       mma_f16(acc[i], a, b0, b1);
     }
   }
@@ -126,7 +164,7 @@ __device__ __forceinline__ void warp_tiles(const uint32_t* __restrict__ T, int n
 
 // Program (routed expert u, 64 columns, matrix x pair tile): up to 8 members times W_q; the four warps split K and
 // meet in warp order.  Z[mat][pair][n] fp32.
-template <int CB>
+template <int CB, int GR_NTB>
 __global__ void __launch_bounds__(GR_WARPS * 32)
 grouped_kernel(const __half* __restrict__ X0, const __half* __restrict__ X1, const int64_t* __restrict__ TP0,
                const int64_t* __restrict__ TP1, const int* __restrict__ K2_0, const int* __restrict__ K2_1,
@@ -161,7 +199,7 @@ grouped_kernel(const __half* __restrict__ X0, const __half* __restrict__ X1, con
   switch (k2) {
 #define TFB_K2(K2_)                                                          \
   case K2_:                                                                  \
-    warp_tiles<CB, K2_>(T, ntiles, kt0, per_warp, nt0, x, lane, acc);        \
+    warp_tiles<CB, K2_, GR_NTB>(T, ntiles, kt0, per_warp, nt0, x, lane, acc); \
     break;
     TFB_K2(2) TFB_K2(3) TFB_K2(4) TFB_K2(5) TFB_K2(6) TFB_K2(7) TFB_K2(8) TFB_K2(9) TFB_K2(10) TFB_K2(11) TFB_K2(12)
     TFB_K2(13) TFB_K2(14) TFB_K2(15) TFB_K2(16)
@@ -459,27 +497,32 @@ extern "C" int tfb_exl3_grouped(const void* x0, const void* x1, const int64_t* t
                                 int maxm, int maxu, void* stream) {
   TFB_REQUIRE(x0 && x1 && tp0 && tp1 && k2_0 && k2_1 && uids && ucount && members && z, "exl3_grouped: null pointer");
   TFB_REQUIRE(mats == 1 || mats == 2, "exl3_grouped: one or two matrices");
-  TFB_REQUIRE(K > 0 && N > 0 && K % (16 * exl3::GR_WARPS) == 0 && N % (16 * exl3::GR_NTB) == 0,
-              "exl3_grouped: K must be a multiple of %d and N of %d", 16 * exl3::GR_WARPS, 16 * exl3::GR_NTB);
+  TFB_REQUIRE(K > 0 && N > 0 && K % (16 * exl3::GR_WARPS) == 0 && N % (16 * exl3::GR_NTB_MAX) == 0,
+              "exl3_grouped: K must be a multiple of %d and N of %d", 16 * exl3::GR_WARPS, 16 * exl3::GR_NTB_MAX);
   TFB_REQUIRE(cb >= 0 && cb <= 2, "exl3_grouped: codebook must be 0 (3inst), 1 (mcg) or 2 (mul1)");
   TFB_REQUIRE(slots >= 1 && slots <= 32 && maxm >= 0 && maxu >= 0, "exl3_grouped: bad sizes");
   if (maxu == 0 || maxm == 0) return TFB_OK;
   const int mtiles = (maxm + exl3::GR_PAIRS - 1) / exl3::GR_PAIRS;
   TFB_REQUIRE((int64_t)mats * mtiles <= 65535, "exl3_grouped: too many pair tiles for one launch");
-  const dim3 grid(maxu, N / (16 * exl3::GR_NTB), mats * mtiles);
+  // column tiles a CTA: fewer when the call is small, so that every SM gets work (columns are independent: no effect
+  // on any result)
+  const int64_t units4 = (int64_t)maxu * (N / 64) * mats * mtiles;
+  const int ntb = units4 >= 1184 ? 4 : units4 >= 592 ? 2 : 1;
+  const dim3 grid(maxu, N / (16 * ntb), mats * mtiles);
   auto st = static_cast<cudaStream_t>(stream);
   auto* h0 = static_cast<const __half*>(x0);
   auto* h1 = static_cast<const __half*>(x1);
-  cudaError_t e;
-  if (cb == 0)
-    e = launch(exl3::grouped_kernel<0>, grid, dim3(exl3::GR_WARPS * 32), 0, st, h0, h1, tp0, tp1, k2_0, k2_1, uids,
-               ucount, members, z, K, N, P, maxm, slots, mtiles);
-  else if (cb == 1)
-    e = launch(exl3::grouped_kernel<1>, grid, dim3(exl3::GR_WARPS * 32), 0, st, h0, h1, tp0, tp1, k2_0, k2_1, uids,
-               ucount, members, z, K, N, P, maxm, slots, mtiles);
-  else
-    e = launch(exl3::grouped_kernel<2>, grid, dim3(exl3::GR_WARPS * 32), 0, st, h0, h1, tp0, tp1, k2_0, k2_1, uids,
-               ucount, members, z, K, N, P, maxm, slots, mtiles);
+  cudaError_t e = cudaSuccess;
+#define TFB_GR(CB_, NTB_)                                                                                          \
+  e = launch(exl3::grouped_kernel<CB_, NTB_>, grid, dim3(exl3::GR_WARPS * 32), 0, st, h0, h1, tp0, tp1, k2_0, k2_1, \
+             uids, ucount, members, z, K, N, P, maxm, slots, mtiles)
+#define TFB_GR_CB(CB_)                  \
+  if (ntb == 4) TFB_GR(CB_, 4);         \
+  else if (ntb == 2) TFB_GR(CB_, 2);    \
+  else TFB_GR(CB_, 1)
+  if (cb == 0) { TFB_GR_CB(0); } else if (cb == 1) { TFB_GR_CB(1); } else { TFB_GR_CB(2); }
+#undef TFB_GR_CB
+#undef TFB_GR
   return check_cuda(e, "exl3_grouped");
 }
 
