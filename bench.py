@@ -27,6 +27,7 @@ ROOT = Path(__file__).resolve().parent
 if str(ROOT) not in sys.path:
     sys.path.insert(0, str(ROOT))
 
+TRAFFIC_GATE_UP_C2_64 = 225056256 + 5437184      # bytes, from the committed ncu capture of the same launch
 METRIC = "moe_layer_tokens_per_s"
 UNIT = "tokens/s"
 SMI_FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
@@ -449,7 +450,10 @@ def run_ours(args) -> None:
             "clocks": clocks.summary(), "e2e": e2e, "gpu_launches": head["launches_per_step"] * args.steps,
             "roofline": {"bound": "hbm", "kernel": "decode_kernel<M=2, SwiGLU> (gate/up)",
                          "achieved": head["gate_up_gbs"], "peak": hbm, "unit": "GB/s",
-                         "frac": head["gate_up_gbs"] / hbm, "peak_source": f"of {which}", "traffic": None,
+                         "frac": head["gate_up_gbs"] / hbm, "peak_source": f"of {which}",
+                         "traffic": TRAFFIC_GATE_UP_C2_64 if (rows, args.form) == (64, "decode") else None,
+                         "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch of this "
+                                           "workload (profiles/decode_kernel_c2_64tokens.md)",
                          "bytes_per_launch": head["gate_up_bytes"], "us_per_launch": head["gate_up_us"]},
             "layer": {k: head[k] for k in ("distinct_experts", "layer_bytes", "layer_gbs", "layer_frac_of_hbm")},
             "cpu_baseline": cpu, "sweep": sweep}
