@@ -63,6 +63,17 @@ int tfb_select_plan_max_rows(void);
 int tfb_select_plan(const float* logits, int NL, int32_t* pick, float* wts, int T, int E, int top_k, int shared,
                     int tile, int32_t* members, int32_t* items, int32_t* counts, void* stream);
 
+/* Expert-parallel forms (no reference counterpart: the reference has no expert parallelism, src/tensorfold/cuda/comm.py
+ * is an all-gather for 2-rank tensor parallelism).  A "window" is the contiguous id range [lo, lo + n) of the experts a
+ * rank owns; plans are made over those ids renumbered from 0, and tfb_combine_window sums only those slots. */
+int tfb_plan_window(const int32_t* picks, int64_t pairs, int lo, int experts, int tile, int32_t* members,
+                    int32_t* items, int32_t* counts, void* stream);
+int tfb_select_plan_window(const float* logits, int NL, int32_t* pick, float* wts, int T, int E, int top_k, int shared,
+                           int tile, int plan_lo, int plan_n, int32_t* members, int32_t* items, int32_t* counts,
+                           void* stream);
+int tfb_combine_window(const void* y, int y_bf16, const float* wts, const int32_t* pick, int lo, int n, void* out,
+                       int out_f32, int T, int slots, int D, void* stream);
+
 /* out[T, D] = sum over slots, in slot order, of wts[T, slots] * y[T, slots, D] (fp32 fma chain from 0), rounded once.
  * y is fp32 (y_bf16 = 0) or bf16; out is bf16 (out_f32 = 0) or fp32.
  * Replaces moe.combine / _combine: src/tensorfold/cuda/moe.py:131-151, and combine_kernel of

@@ -265,7 +265,7 @@ __device__ int place_items(int c, int E, int T, int* __restrict__ items, int* __
 
 // The whole block: `picks` may live in global or shared memory.
 __device__ void plan_block(const int* picks, int P, int E, int T, int* __restrict__ members, int* __restrict__ items,
-                           int* __restrict__ counts, int* whist, int* first, int (*wsum)[32]) {
+                           int* __restrict__ counts, int* whist, int* first, int (*wsum)[32], int lo = 0) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   for (int i = tid; i < 32 * E; i += PLAN_THREADS) whist[i] = 0;
   const int seg = (((P + 31) / 32 + 31) / 32) * 32;
@@ -277,7 +277,7 @@ __device__ void plan_block(const int* picks, int P, int E, int T, int* __restric
 #pragma unroll
     for (int i = 0; i < PLAN_BATCH; ++i) {
       const int p = base0 + 32 * i + lane;
-      ev[i] = p < p1 ? picks[p] : -1;
+      ev[i] = p < p1 ? picks[p] - lo : -1;
     }
 #pragma unroll
     for (int i = 0; i < PLAN_BATCH; ++i) {
@@ -305,7 +305,7 @@ __device__ void plan_block(const int* picks, int P, int E, int T, int* __restric
 #pragma unroll
     for (int i = 0; i < PLAN_BATCH; ++i) {
       const int p = base0 + 32 * i + lane;
-      ev[i] = p < p1 ? picks[p] : -1;
+      ev[i] = p < p1 ? picks[p] - lo : -1;
     }
 #pragma unroll
     for (int i = 0; i < PLAN_BATCH; ++i) {
@@ -325,12 +325,12 @@ __device__ void plan_block(const int* picks, int P, int E, int T, int* __restric
 
 __global__ void __launch_bounds__(PLAN_THREADS)
 plan_kernel(const int* __restrict__ picks, int P, int E, int T, int* __restrict__ members, int* __restrict__ items,
-            int* __restrict__ counts) {
+            int* __restrict__ counts, int lo) {
   extern __shared__ int whist[];                 // [32][E]: pairs of expert e in warp w's run, then their first slot
   __shared__ int first[PLAN_EMAX];
   __shared__ int wsum[3][32];
   pdl_wait();
-  plan_block(picks, P, E, T, members, items, counts, whist, first, wsum);
+  plan_block(picks, P, E, T, members, items, counts, whist, first, wsum, lo);
   pdl_launch_dependents();
 }
 
@@ -340,13 +340,13 @@ template <int VPL>
 __global__ void __launch_bounds__(PLAN_THREADS)
 select_plan_kernel(const float* __restrict__ L, int NL, int* __restrict__ pick, float* __restrict__ wts, int T, int E,
                    int top_k, int shared, int tile, int* __restrict__ members, int* __restrict__ items,
-                   int* __restrict__ counts) {
+                   int* __restrict__ counts, int plan_lo, int plan_n) {
   extern __shared__ int dyn[];                   // whist [32][NP], then the picks [T * slots]
   __shared__ int first[PLAN_EMAX];
   __shared__ int wsum[3][32];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int slots = top_k + (shared ? 1 : 0), NP = E + (shared ? 1 : 0);
-  int* picks_sh = dyn + 32 * NP;
+  const int slots = top_k + (shared ? 1 : 0);
+  int* picks_sh = dyn + 32 * plan_n;
   pdl_wait();
   for (int r = warp; r < T; r += PLAN_THREADS / 32) {
     const int mine = select_row<VPL>(L + (size_t)r * NL, E, top_k, shared, lane, pick + (size_t)r * slots,
@@ -354,7 +354,7 @@ select_plan_kernel(const float* __restrict__ L, int NL, int* __restrict__ pick, 
     if (lane < slots) picks_sh[r * slots + lane] = mine;
   }
   __syncthreads();
-  plan_block(picks_sh, T * slots, NP, tile, members, items, counts, dyn, first, wsum);
+  plan_block(picks_sh, T * slots, plan_n, tile, members, items, counts, dyn, first, wsum, plan_lo);
   pdl_launch_dependents();
 }
 
@@ -362,15 +362,21 @@ select_plan_kernel(const float* __restrict__ L, int NL, int* __restrict__ pick, 
 // Combine: out[r, d] = sum over slots in slot order of wts[r, s] * y[r, s, d] (fp32 fma chain from 0), rounded once.
 // (src/tensorfold/cuda/moe.py:131-151; src/tensorfold/cuda/exl3/experts.cu:181-190 for the fp32-out form.)
 // ================================================================================================================
+// With `pick`: only slots whose expert id lies in [lo, lo + n) take part (the others' rows are not read).
 template <typename TY, typename TO>
 __global__ void __launch_bounds__(256)
-combine_kernel(const TY* __restrict__ y, const float* __restrict__ wts, TO* __restrict__ out, int S, int D) {
+combine_kernel(const TY* __restrict__ y, const float* __restrict__ wts, TO* __restrict__ out, int S, int D,
+               const int* __restrict__ pick, int lo, int n) {
   const int r = blockIdx.x;
   const int d = (blockIdx.y * 256 + threadIdx.x) * 4;
   if (d >= D) return;
   pdl_wait();
   float acc[4] = {0.f, 0.f, 0.f, 0.f};
   for (int s = 0; s < S; ++s) {
+    if (pick != nullptr) {
+      const int e = pick[(size_t)r * S + s] - lo;
+      if (e < 0 || e >= n) continue;
+    }
     const float w = wts[(size_t)r * S + s];
     const TY* src = y + ((size_t)r * S + s) * D + d;
     float v[4];
@@ -444,8 +450,8 @@ extern "C" int tfb_select_rows(const float* logits, int NL, int32_t* pick, float
 #undef TFB_SEL
 }
 
-extern "C" int tfb_plan(const int32_t* picks, int64_t pairs, int experts, int tile, int32_t* members, int32_t* items,
-                        int32_t* counts, void* stream) {
+static int plan_launch(const int32_t* picks, int64_t pairs, int lo, int experts, int tile, int32_t* members,
+                       int32_t* items, int32_t* counts, void* stream) {
   TFB_REQUIRE(picks && members && items && counts, "plan: null pointer");
   TFB_REQUIRE(experts >= 1 && experts <= PLAN_EMAX, "plan: at most %d experts, not %d", PLAN_EMAX, experts);
   TFB_REQUIRE(tile >= 1, "plan: items hold at least one pair");
@@ -461,17 +467,32 @@ extern "C" int tfb_plan(const int32_t* picks, int64_t pairs, int experts, int ti
     configured[dev] = 1;
   }
   return check_cuda(launch(plan_kernel, dim3(1), dim3(PLAN_THREADS), smem, static_cast<cudaStream_t>(stream), picks,
-                           (int)pairs, experts, tile, members, items, counts),
+                           (int)pairs, experts, tile, members, items, counts, lo),
                     "plan");
+}
+
+extern "C" int tfb_plan(const int32_t* picks, int64_t pairs, int experts, int tile, int32_t* members, int32_t* items,
+                        int32_t* counts, void* stream) {
+  return plan_launch(picks, pairs, 0, experts, tile, members, items, counts, stream);
+}
+
+// The plan of the ids in [lo, lo + experts) only, renumbered from 0: an expert-parallel rank's share of the pairs.
+extern "C" int tfb_plan_window(const int32_t* picks, int64_t pairs, int lo, int experts, int tile, int32_t* members,
+                               int32_t* items, int32_t* counts, void* stream) {
+  TFB_REQUIRE(lo >= 0, "plan_window: the window starts at a non-negative id");
+  return plan_launch(picks, pairs, lo, experts, tile, members, items, counts, stream);
 }
 
 // Rows the fused selection + plan kernel takes (one block); larger calls use tfb_select_rows then tfb_plan.
 extern "C" int tfb_select_plan_max_rows(void) { return 128; }
 
-extern "C" int tfb_select_plan(const float* logits, int NL, int32_t* pick, float* wts, int T, int E, int top_k,
-                               int shared, int tile, int32_t* members, int32_t* items, int32_t* counts, void* stream) {
+static int select_plan_launch(const float* logits, int NL, int32_t* pick, float* wts, int T, int E, int top_k,
+                              int shared, int tile, int plan_lo, int plan_n, int32_t* members, int32_t* items,
+                              int32_t* counts, void* stream) {
   TFB_REQUIRE(logits && pick && wts && members && items && counts, "select_plan: null pointer");
   const int NP = E + (shared ? 1 : 0);
+  TFB_REQUIRE(plan_lo >= 0 && plan_n >= 1 && plan_lo + plan_n <= NP, "select_plan: the plan window [%d, %d) leaves "
+              "the %d experts", plan_lo, plan_lo + plan_n, NP);
   TFB_REQUIRE(E >= 1 && NP <= PLAN_EMAX, "select_plan: at most %d experts, not %d", PLAN_EMAX, NP);
   TFB_REQUIRE(top_k >= 1 && top_k <= E && top_k <= 31, "select_plan: top_k=%d must be 1..min(E, 31)", top_k);
   TFB_REQUIRE(NL >= NP, "select_plan: %d logits a row cannot hold %d experts%s", NL, E,
@@ -480,7 +501,7 @@ extern "C" int tfb_select_plan(const float* logits, int NL, int32_t* pick, float
               tfb_select_plan_max_rows(), T);
   TFB_REQUIRE(tile >= 1, "select_plan: items hold at least one pair");
   const int slots = top_k + (shared ? 1 : 0);
-  const size_t smem = sizeof(int) * (32 * (size_t)NP + (size_t)T * slots);
+  const size_t smem = sizeof(int) * (32 * (size_t)plan_n + (size_t)T * slots);
   auto st = static_cast<cudaStream_t>(stream);
   const int vpl = (E + 31) / 32;
   int dev = 0;
@@ -495,7 +516,7 @@ extern "C" int tfb_select_plan(const float* logits, int NL, int32_t* pick, float
       configured[dev] = 1;                                                                                         \
     }                                                                                                              \
     return check_cuda(launch(select_plan_kernel<V>, dim3(1), dim3(PLAN_THREADS), smem, st, logits, NL, pick, wts, \
-                             T, E, top_k, shared ? 1 : 0, tile, members, items, counts),                          \
+                             T, E, top_k, shared ? 1 : 0, tile, members, items, counts, plan_lo, plan_n),        \
                       "select_plan");                                                                              \
   } while (0)
   if (vpl <= 4) TFB_SP(4);
@@ -505,8 +526,23 @@ extern "C" int tfb_select_plan(const float* logits, int NL, int32_t* pick, float
 #undef TFB_SP
 }
 
-extern "C" int tfb_combine(const void* y, int y_bf16, const float* wts, void* out, int out_f32, int T, int slots,
-                           int D, void* stream) {
+extern "C" int tfb_select_plan(const float* logits, int NL, int32_t* pick, float* wts, int T, int E, int top_k,
+                               int shared, int tile, int32_t* members, int32_t* items, int32_t* counts, void* stream) {
+  return select_plan_launch(logits, NL, pick, wts, T, E, top_k, shared, tile, 0, E + (shared ? 1 : 0), members, items,
+                            counts, stream);
+}
+
+// tfb_select_plan whose plan covers only the ids in [plan_lo, plan_lo + plan_n), renumbered from 0 (pick and wts still
+// hold every slot): what an expert-parallel rank needs for the tokens of all ranks.
+extern "C" int tfb_select_plan_window(const float* logits, int NL, int32_t* pick, float* wts, int T, int E, int top_k,
+                                      int shared, int tile, int plan_lo, int plan_n, int32_t* members, int32_t* items,
+                                      int32_t* counts, void* stream) {
+  return select_plan_launch(logits, NL, pick, wts, T, E, top_k, shared, tile, plan_lo, plan_n, members, items, counts,
+                            stream);
+}
+
+static int combine_launch(const void* y, int y_bf16, const float* wts, void* out, int out_f32, int T, int slots, int D,
+                          const int32_t* pick, int lo, int n, void* stream) {
   TFB_REQUIRE(y && wts && out, "combine: null pointer");
   TFB_REQUIRE(D > 0 && D % 4 == 0 && slots >= 1, "combine: D must be a multiple of 4 and slots >= 1");
   TFB_REQUIRE(aligned16(y) && aligned16(out), "combine: y and out must be 16-byte aligned");
@@ -516,15 +552,29 @@ extern "C" int tfb_combine(const void* y, int y_bf16, const float* wts, void* ou
   cudaError_t e;
   if (y_bf16 && out_f32)
     e = launch(combine_kernel<__nv_bfloat16, float>, grid, dim3(256), 0, st, static_cast<const __nv_bfloat16*>(y), wts,
-               static_cast<float*>(out), slots, D);
+               static_cast<float*>(out), slots, D, pick, lo, n);
   else if (y_bf16)
     e = launch(combine_kernel<__nv_bfloat16, __nv_bfloat16>, grid, dim3(256), 0, st,
-               static_cast<const __nv_bfloat16*>(y), wts, static_cast<__nv_bfloat16*>(out), slots, D);
+               static_cast<const __nv_bfloat16*>(y), wts, static_cast<__nv_bfloat16*>(out), slots, D, pick, lo, n);
   else if (out_f32)
     e = launch(combine_kernel<float, float>, grid, dim3(256), 0, st, static_cast<const float*>(y), wts,
-               static_cast<float*>(out), slots, D);
+               static_cast<float*>(out), slots, D, pick, lo, n);
   else
     e = launch(combine_kernel<float, __nv_bfloat16>, grid, dim3(256), 0, st, static_cast<const float*>(y), wts,
-               static_cast<__nv_bfloat16*>(out), slots, D);
+               static_cast<__nv_bfloat16*>(out), slots, D, pick, lo, n);
   return check_cuda(e, "combine");
+}
+
+extern "C" int tfb_combine(const void* y, int y_bf16, const float* wts, void* out, int out_f32, int T, int slots,
+                           int D, void* stream) {
+  return combine_launch(y, y_bf16, wts, out, out_f32, T, slots, D, nullptr, 0, 0, stream);
+}
+
+// tfb_combine over the slots whose expert id pick[T, slots] lies in [lo, lo + n): an expert-parallel rank's partial
+// sum of each token (rows of other ranks' pairs are never read, so y needs no clearing).
+extern "C" int tfb_combine_window(const void* y, int y_bf16, const float* wts, const int32_t* pick, int lo, int n,
+                                  void* out, int out_f32, int T, int slots, int D, void* stream) {
+  TFB_REQUIRE(pick, "combine_window: null pointer");
+  TFB_REQUIRE(lo >= 0 && n >= 1, "combine_window: bad window");
+  return combine_launch(y, y_bf16, wts, out, out_f32, T, slots, D, pick, lo, n, stream);
 }

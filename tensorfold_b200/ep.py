@@ -19,6 +19,8 @@ from dataclasses import dataclass
 import torch
 import torch.distributed as dist
 
+from . import _lib
+
 
 class CudaBackend:
     """This rank's share of a layer on its GPU: full router rows, its slice of the routed experts, the shared expert."""
@@ -151,10 +153,17 @@ class GatheredExpertParallel:
     (``ExpertParallel``) and no latency of a host round trip; NCCL may reduce inside the switch (NVLS)."""
 
     def __init__(self, router_rows: torch.Tensor, local_experts, experts: int, top_k: int, rows_local: int,
-                 group=None) -> None:
+                 group=None, reduce: str = "rows") -> None:
+        """``reduce="rows"``: the per-pair fp32 rows travel (exact: the one-GPU bits).  ``reduce="tokens"``: every rank
+        first sums ITS pairs of each token in slot order (weights applied) and the reduce-scatter adds the ranks'
+        partial sums - k times less link traffic, the same values up to fp32 summation order across ranks."""
+
         from . import experts as grouped
         from . import moe
 
+        if reduce not in ("rows", "tokens"):
+            raise ValueError("reduce must be 'rows' or 'tokens'")
+        self.reduce = reduce
         self.moe, self.grouped = moe, grouped
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
@@ -176,8 +185,11 @@ class GatheredExpertParallel:
         self.plan = grouped.Plan(rows, k, self.per_rank, dev)
         self.local_pick = torch.zeros((rows, k), dtype=torch.int32, device=dev)
         self.y_mine = torch.zeros((rows_local * k, d), dtype=torch.float32, device=dev)
+        self.partial = torch.zeros((rows, d), dtype=torch.float32, device=dev)
+        self.partial_mine = torch.zeros((rows_local, d), dtype=torch.float32, device=dev)
         self.out = torch.zeros((rows_local, d), dtype=torch.bfloat16, device=dev)
-        self.launches = 6
+        self._fused_rows = _lib.lib().tfb_select_plan_max_rows()
+        self.launches = 5 if rows <= self._fused_rows else 6
 
     def forward(self, x_local: torch.Tensor) -> torch.Tensor:
         m, g, buf, k = self.moe, self.grouped, self.buf, self.top_k
@@ -186,13 +198,35 @@ class GatheredExpertParallel:
         else:
             self.x_all.copy_(x_local)
         m.router(self.x_all, self.router_rows, buf.logits)
-        m.select_rows(buf.logits, buf, k, self.experts)
-        torch.sub(buf.pick, self.rank * self.per_rank, out=self.local_pick)      # ids off this rank fall outside the plan
-        g.route(self.local_pick, self.plan)
+        lo, st = self.rank * self.per_rank, torch.cuda.current_stream(self.x_all.device).cuda_stream
+        plan = self.plan
+        plan.tile = g.TILE
+        with torch.cuda.device(self.x_all.device):
+            if self.rows <= self._fused_rows:
+                # selection of every token and the plan of this rank's experts in one launch
+                _lib.call("tfb_select_plan_window", buf.logits.data_ptr(), buf.logits.shape[1], buf.pick.data_ptr(),
+                          buf.wts.data_ptr(), self.rows, self.experts, k, 0, plan.tile, lo, self.per_rank,
+                          plan.members.data_ptr(), plan.items.data_ptr(), plan.counts.data_ptr(), st)
+            else:
+                m.select_rows(buf.logits, buf, k, self.experts)
+                _lib.call("tfb_plan_window", buf.pick.data_ptr(), self.rows * k, lo, self.per_rank, plan.tile,
+                          plan.members.data_ptr(), plan.items.data_ptr(), plan.counts.data_ptr(), st)
         y_all = buf.y.view(-1, self.local.dims)
-        y_all.zero_()
-        g.gate_up(self.x_all, self.local, self.plan, buf.act.view(-1, self.local.width), self.rows)
-        g.down(buf.act.view(-1, self.local.width), self.local, self.plan, y_all, self.rows)
+        if self.reduce == "rows":
+            y_all.zero_()
+        g.gate_up(self.x_all, self.local, plan, buf.act.view(-1, self.local.width), self.rows)
+        g.down(buf.act.view(-1, self.local.width), self.local, plan, y_all, self.rows)
+        if self.reduce == "tokens":
+            # this rank's pairs of every token, weights applied, in slot order; other ranks' rows are never read
+            with torch.cuda.device(self.x_all.device):
+                _lib.call("tfb_combine_window", buf.y.data_ptr(), 0, buf.wts.data_ptr(), buf.pick.data_ptr(), lo,
+                          self.per_rank, self.partial.data_ptr(), 1, self.rows, k, self.local.dims, st)
+            if self.world > 1:
+                dist.reduce_scatter_tensor(self.partial_mine, self.partial, group=self.group)
+            else:
+                self.partial_mine.copy_(self.partial[:self.rows_local])
+            self.out.copy_(self.partial_mine)                     # one rounding to bf16
+            return self.out
         if self.world > 1:
             dist.reduce_scatter_tensor(self.y_mine, y_all, group=self.group)
         else:

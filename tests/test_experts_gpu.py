@@ -253,3 +253,22 @@ def test_layer_against_the_cpu_oracle(rows, shared):
     _, _, o64 = affine.layer64(bits(x), pick, wts, triple_np(gate), triple_np(up), triple_np(down), 64, True)
     assert rel_l2(out.float().cpu().numpy(), o64) <= 1e-2
     assert rel_l2(out.float().cpu().numpy(), affine.bf16_value(o_cpu)) <= 1e-2
+
+
+@pytest.mark.parametrize("reduce", ["rows", "tokens"])
+def test_gathered_expert_parallel_on_one_rank_is_the_layer(reduce):
+    """World size 1: the expert-parallel step (windowed plan and combine included) gives moe.run's output."""
+
+    from tensorfold_b200 import ep, experts, moe, synthetic
+
+    shape, rows = synthetic.SMALL, 33
+    gate, up, down = synthetic.affine_layer(shape, DEV)
+    rt = synthetic.router_rows(shape, DEV)
+    ex = experts.make([gate, up], down, 64)
+    x = synthetic.activations(shape, rows, DEV)
+    want = moe.run(x, moe.Routed(rt, ex, shape.top_k, shared=False))
+    got = ep.GatheredExpertParallel(rt, ex, shape.experts, shape.top_k, rows, reduce=reduce).forward(x)
+    if reduce == "rows":
+        assert torch.equal(got, want)
+    else:
+        assert torch.equal(got, want)          # one rank: the partial sum is the whole slot-order sum

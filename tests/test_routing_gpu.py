@@ -155,3 +155,42 @@ def test_fused_select_plan_equals_the_two_kernels(t, e, k, shared):
     n = int(b.plan.counts[0])
     assert torch.equal(a.plan.counts, b.plan.counts) and torch.equal(a.plan.items[:n], b.plan.items[:n])
     assert torch.equal(a.plan.members, b.plan.members)
+
+
+def test_windowed_plan_and_combine():
+    """The expert-parallel forms: a plan of the ids in [lo, lo + n) renumbered from 0, selection + that plan in one
+    launch, and a combine over those slots only."""
+
+    import ctypes
+
+    from oracle import cpu
+    from tensorfold_b200 import _lib, experts, moe
+
+    t, e, k, lo, n = 96, 128, 8, 32, 48
+    logits = _logits(t, e, 77).to(DEV)
+    buf = moe.MoEBuffers(t, _Cfg(e, k), DEV, shared=False)
+    moe.select_rows(logits, buf, k, e)
+    stream = torch.cuda.current_stream().cuda_stream
+    plan = experts.Plan(t, k, n, DEV)
+    _lib.call("tfb_plan_window", buf.pick.data_ptr(), t * k, lo, n, experts.TILE, plan.members.data_ptr(),
+              plan.items.data_ptr(), plan.counts.data_ptr(), stream)
+    items, members, counts = cpu.plan(buf.pick.cpu().numpy() - lo, n, experts.TILE)
+    cnt = int(plan.counts[0])
+    assert plan.counts.tolist() == counts.tolist()
+    assert np.array_equal(plan.items[:cnt].cpu().numpy(), items)
+    assert np.array_equal(plan.members[:len(members)].cpu().numpy(), members)
+    buf2 = moe.MoEBuffers(t, _Cfg(e, k), DEV, shared=False)
+    plan2 = experts.Plan(t, k, n, DEV)
+    _lib.call("tfb_select_plan_window", logits.data_ptr(), e, buf2.pick.data_ptr(), buf2.wts.data_ptr(), t, e, k, 0,
+              experts.TILE, lo, n, plan2.members.data_ptr(), plan2.items.data_ptr(), plan2.counts.data_ptr(), stream)
+    assert torch.equal(buf2.pick, buf.pick) and torch.equal(buf2.wts, buf.wts)
+    assert torch.equal(plan2.counts, plan.counts) and torch.equal(plan2.items[:cnt], plan.items[:cnt])
+    assert torch.equal(plan2.members[:len(members)], plan.members[:len(members)])
+    d = 256
+    y = torch.randn((t, k, d), device=DEV)
+    out = torch.empty((t, d), dtype=torch.float32, device=DEV)
+    _lib.call("tfb_combine_window", y.data_ptr(), 0, buf.wts.data_ptr(), buf.pick.data_ptr(), lo, n, out.data_ptr(), 1,
+              t, k, d, stream)
+    mask = ((buf.pick >= lo) & (buf.pick < lo + n)).float()
+    want = moe.combine(y * mask[..., None], buf.wts, torch.empty_like(out))     # zeroed rows add exactly nothing
+    assert torch.equal(out, want)
