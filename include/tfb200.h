@@ -109,6 +109,13 @@ int tfb_experts_run(int gs, int epi, const void* x, int64_t x_stride, int slots,
                     const int32_t* items, const int32_t* counts, const int32_t* members, void* out, int n, float limit,
                     int64_t max_units, int sb_type, void* stream);
 
+/* tfb_experts_run over a plan whose items hold up to `tile` = 8 or 16 pairs.  With 16 every weight fragment is
+ * dequantised once for two mma tiles of pairs (worth it from about 9 pairs an expert); a pair's bits do not depend on
+ * the tile.  No reference counterpart (its decode items always hold 16: src/tensorfold/cuda/experts.py:13). */
+int tfb_experts_run_tile(int gs, int epi, const void* x, int64_t x_stride, int slots, const void* w, int kg, int nb,
+                         const int32_t* items, const int32_t* counts, const int32_t* members, void* out, int n,
+                         float limit, int64_t max_units, int sb_type, int tile, void* stream);
+
 /* Grouped 4-bit expert matmul, prefill form (tcgen05 tensor cores, weights dequantised to bf16 with one rounding,
  * one fp32 chain over K).  Arguments as tfb_experts_run, but items may hold up to 192 pairs (plan with tile <= 192) and
  * max_items = an upper bound of the item count.

@@ -27,6 +27,7 @@ SIGNATURES: dict[str, tuple] = {
     "tfb_unpack": (P, I, P, P, P, I, I, I, P),
     "tfb_dequant": (P, I, I, I, P, I, I, I, P),
     "tfb_experts_run": (I, I, P, L, I, P, I, I, P, P, P, P, I, F, L, I, P),
+    "tfb_experts_run_tile": (I, I, P, L, I, P, I, I, P, P, P, P, I, F, L, I, I, P),
     "tfb_experts_prefill": (I, I, P, L, I, P, I, I, P, P, P, P, I, F, L, I, P),
     "tfb_exl3_dequant": (P, P, I, I, I, I, P),
     "tfb_exl3_group": (P, P, P, P, P, P, P, I, I, I, I, I, P),

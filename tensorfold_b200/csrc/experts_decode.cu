@@ -17,7 +17,7 @@
 namespace tfb {
 
 constexpr int DEC_WARPS = 4;
-constexpr int DEC_PAIRS = 8;           // pairs an item may hold in this form (the plan's decode tile)
+constexpr int DEC_PAIRS = 16;          // pairs an item may hold at most in this form: PT mma tiles of 8 (PT = 1 or 2)
 constexpr int RED_STRIDE = COLS + 1;
 
 // Q = blocks a warp takes a group: M matrices (gate, up: adjacent in memory) or NCB column blocks of one matrix.
@@ -40,7 +40,7 @@ __device__ __forceinline__ void mma_bf16_zero(float (&d)[4], uint32_t a0, uint32
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.f));
 }
 
-template <int M, int NCB, int EPI, int SB, int KW, int STAGES>
+template <int M, int NCB, int EPI, int SB, int KW, int STAGES, int PT>
 __global__ void __launch_bounds__(DEC_WARPS * 32)
 decode_kernel(const __nv_bfloat16* __restrict__ X, int64_t x_stride, int slots, const uint8_t* __restrict__ W, int KG,
               int NB, const int* __restrict__ items, const int* __restrict__ counts, const int* __restrict__ members,
@@ -69,7 +69,8 @@ decode_kernel(const __nv_bfloat16* __restrict__ X, int64_t x_stride, int slots, 
   pdl_wait();                                         // the plan (and the inputs) come from the kernels before
   if (it >= __ldg(counts)) return;
   const int e = __ldg(items + 3 * it), first = __ldg(items + 3 * it + 1);
-  const int cnt = min(__ldg(items + 3 * it + 2), DEC_PAIRS);
+  constexpr int PAIRS = 8 * PT;
+  const int cnt = min(__ldg(items + 3 * it + 2), PAIRS);
 
   // this warp's K run: groups [g0, g1) of column block cb
   const int kgw = (KG + KW - 1) / KW;
@@ -93,39 +94,53 @@ decode_kernel(const __nv_bfloat16* __restrict__ X, int64_t x_stride, int slots, 
 
   if (tid < DEC_PAIRS) pair_id[tid] = tid < cnt ? __ldg(members + first + tid) : -1;
 
-  // the lane's pair (B operand column gq) and its input row
+  // the lane's pairs (B operand column gq of each tile of 8) and their input rows
   // (lanes past the item's last pair read its first pair's row: an mma column depends on its own inputs only, and
   // those columns are never stored)
-  const int pr = __ldg(members + first + (gq < cnt ? gq : 0));
-  const __nv_bfloat16* xrow = X + (size_t)(slots ? pr / slots : pr) * x_stride + 16 * t + (size_t)g0 * GS;
+  const __nv_bfloat16* xrow[PT];
+#pragma unroll
+  for (int pt = 0; pt < PT; ++pt) {
+    const int pr = __ldg(members + first + (8 * pt + gq < cnt ? 8 * pt + gq : 0));
+    xrow[pt] = X + (size_t)(slots ? pr / slots : pr) * x_stride + 16 * t + (size_t)g0 * GS;
+  }
 
-  float acc[Q][2][4];
+  float acc[Q][2][PT][4];
 #pragma unroll
   for (int m = 0; m < Q; ++m)
 #pragma unroll
     for (int tt = 0; tt < 2; ++tt)
 #pragma unroll
-      for (int i = 0; i < 4; ++i) acc[m][tt][i] = 0.f;
+      for (int pt = 0; pt < PT; ++pt)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[m][tt][pt][i] = 0.f;
 
   const uint32_t ONES = 0x3F803F80u;                  // the bf16 pair (1, 1)
-  uint4 xn0 = make_uint4(0u, 0u, 0u, 0u), xn1 = xn0;
-  if (ng > 0) {
-    xn0 = ldg_nc(xrow);
-    xn1 = ldg_nc(xrow + 8);
+  uint4 xn[PT][2];
+#pragma unroll
+  for (int pt = 0; pt < PT; ++pt) {
+    xn[pt][0] = xn[pt][1] = make_uint4(0u, 0u, 0u, 0u);
+    if (ng > 0) {
+      xn[pt][0] = ldg_nc(xrow[pt]);
+      xn[pt][1] = ldg_nc(xrow[pt] + 8);
+    }
   }
   for (int c = 0; c < ng; ++c) {
     const int s = c % STAGES;
-    const uint4 x0 = xn0, x1 = xn1;
-    if (c + 1 < ng) {                        // the next group's inputs travel while this one computes
-      xn0 = ldg_nc(xrow + (c + 1) * GS);
-      xn1 = ldg_nc(xrow + (c + 1) * GS + 8);
-    }
-    const uint32_t xb[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
-    // sum of the group's inputs for pairs 2t and 2t + 1 (all-ones A)
-    float xs[4];
-    mma_bf16_zero(xs, ONES, ONES, ONES, ONES, xb[0], xb[1]);
+    uint32_t xb[PT][8];
+    float xs[PT][4];                                  // sum of the group's inputs for pairs 2t and 2t + 1 of each tile
 #pragma unroll
-    for (int ks = 1; ks < 4; ++ks) mma_bf16(xs, ONES, ONES, ONES, ONES, xb[2 * ks], xb[2 * ks + 1]);
+    for (int pt = 0; pt < PT; ++pt) {
+      const uint4 x0 = xn[pt][0], x1 = xn[pt][1];
+      if (c + 1 < ng) {                               // the next group's inputs travel while this one computes
+        xn[pt][0] = ldg_nc(xrow[pt] + (c + 1) * GS);
+        xn[pt][1] = ldg_nc(xrow[pt] + (c + 1) * GS + 8);
+      }
+      xb[pt][0] = x0.x; xb[pt][1] = x0.y; xb[pt][2] = x0.z; xb[pt][3] = x0.w;
+      xb[pt][4] = x1.x; xb[pt][5] = x1.y; xb[pt][6] = x1.z; xb[pt][7] = x1.w;
+      mma_bf16_zero(xs[pt], ONES, ONES, ONES, ONES, xb[pt][0], xb[pt][1]);
+#pragma unroll
+      for (int ks = 1; ks < 4; ++ks) mma_bf16(xs[pt], ONES, ONES, ONES, ONES, xb[pt][2 * ks], xb[pt][2 * ks + 1]);
+    }
     if (!mbar_wait(bars + s, (c / STAGES) & 1)) break;
     const uint8_t* blk = ring + s * SM::STAGE_BYTES;
 #pragma unroll
@@ -134,26 +149,32 @@ decode_kernel(const __nv_bfloat16* __restrict__ X, int64_t x_stride, int slots, 
 #pragma unroll
       for (int tt = 0; tt < 2; ++tt) {
         const uint4 w = *reinterpret_cast<const uint4*>(blk + m * BLOCK_BYTES + tt * TILE_BYTES + lane * 16);
-        float p[4];
+        float p[PT][4];
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks) {
           const uint32_t lo = ks < 2 ? w.x : w.y, hi = ks < 2 ? w.z : w.w;
           const int sh = 8 * (ks & 1);
           const uint32_t a0 = nib_pair(lo, sh), a1 = nib_pair(hi, sh);
           const uint32_t a2 = nib_pair(lo, sh + 4), a3 = nib_pair(hi, sh + 4);
-          if (ks == 0)
-            mma_bf16_zero(p, a0, a1, a2, a3, xb[0], xb[1]);
-          else
-            mma_bf16(p, a0, a1, a2, a3, xb[2 * ks], xb[2 * ks + 1]);
+#pragma unroll
+          for (int pt = 0; pt < PT; ++pt) {           // the fragment is dequantised once for every tile of pairs
+            if (ks == 0)
+              mma_bf16_zero(p[pt], a0, a1, a2, a3, xb[pt][0], xb[pt][1]);
+            else
+              mma_bf16(p[pt], a0, a1, a2, a3, xb[pt][2 * ks], xb[pt][2 * ks + 1]);
+          }
         }
         const float2 sb_lo = sb_pair<SB>(comp(sbv, 2 * tt)), sb_hi = sb_pair<SB>(comp(sbv, 2 * tt + 1));
         const float s_lo = sb_lo.x, s_hi = sb_hi.x;
         const float b_lo = fmaf(-128.f, s_lo, sb_lo.y), b_hi = fmaf(-128.f, s_hi, sb_hi.y);
-        float(&d)[4] = acc[m][tt];
-        d[0] = fmaf(xs[0], b_lo, fmaf(p[0], s_lo, d[0]));
-        d[1] = fmaf(xs[1], b_lo, fmaf(p[1], s_lo, d[1]));
-        d[2] = fmaf(xs[0], b_hi, fmaf(p[2], s_hi, d[2]));
-        d[3] = fmaf(xs[1], b_hi, fmaf(p[3], s_hi, d[3]));
+#pragma unroll
+        for (int pt = 0; pt < PT; ++pt) {
+          float(&d)[4] = acc[m][tt][pt];
+          d[0] = fmaf(xs[pt][0], b_lo, fmaf(p[pt][0], s_lo, d[0]));
+          d[1] = fmaf(xs[pt][1], b_lo, fmaf(p[pt][1], s_lo, d[1]));
+          d[2] = fmaf(xs[pt][0], b_hi, fmaf(p[pt][2], s_hi, d[2]));
+          d[3] = fmaf(xs[pt][1], b_hi, fmaf(p[pt][3], s_hi, d[3]));
+        }
       }
     }
     __syncwarp();
@@ -167,17 +188,19 @@ decode_kernel(const __nv_bfloat16* __restrict__ X, int64_t x_stride, int slots, 
 #pragma unroll
   for (int m = 0; m < Q; ++m)
 #pragma unroll
-    for (int tt = 0; tt < 2; ++tt) {
-      float* base = red + ((warp * Q + m) * DEC_PAIRS + 2 * t) * RED_STRIDE + tt * 16 + gq;
-      base[0] = acc[m][tt][0];
-      base[RED_STRIDE] = acc[m][tt][1];
-      base[8] = acc[m][tt][2];
-      base[RED_STRIDE + 8] = acc[m][tt][3];
-    }
+    for (int tt = 0; tt < 2; ++tt)
+#pragma unroll
+      for (int pt = 0; pt < PT; ++pt) {
+        float* base = red + ((warp * Q + m) * DEC_PAIRS + 8 * pt + 2 * t) * RED_STRIDE + tt * 16 + gq;
+        base[0] = acc[m][tt][pt][0];
+        base[RED_STRIDE] = acc[m][tt][pt][1];
+        base[8] = acc[m][tt][pt][2];
+        base[RED_STRIDE + 8] = acc[m][tt][pt][3];
+      }
   __syncthreads();
-  // thread -> (column block cbo of the CTA, pair, column): CBC * 8 * 32 outputs over 128 threads
-  for (int o = tid; o < CBC * DEC_PAIRS * COLS; o += DEC_WARPS * 32) {
-    const int col = o & 31, pi = (o >> 5) % DEC_PAIRS, cbo = o / (DEC_PAIRS * COLS);
+  // thread -> (column block cbo of the CTA, pair, column): CBC * PAIRS * 32 outputs over 128 threads
+  for (int o = tid; o < CBC * PAIRS * COLS; o += DEC_WARPS * 32) {
+    const int col = o & 31, pi = (o >> 5) % PAIRS, cbo = o / (PAIRS * COLS);
     const int cbi = cbt * CBC + cbo;
     if (pi >= cnt || cbi >= NB) continue;
     const int w0 = (cbo / NCB) * KW, q0 = (cbo % NCB) * M;      // first K-slice warp and block of this column block
@@ -205,14 +228,14 @@ decode_kernel(const __nv_bfloat16* __restrict__ X, int64_t x_stride, int slots, 
 // K-slices a CTA for a projection of kg groups: the shape's alone, so a pair's bits never depend on the call.
 __host__ __device__ inline int decode_kslices(int kg) { return kg >= 32 ? 4 : kg >= 8 ? 2 : 1; }
 
-template <int M, int EPI, int SB, int KW>
+template <int M, int EPI, int SB, int KW, int PT>
 int launch_decode_kw(const void* x, int64_t x_stride, int slots, const void* w, int kg, int nb, const int* items,
                      const int* counts, const int* members, void* out, int n, float limit, int64_t max_items,
                      cudaStream_t stream) {
   constexpr int STAGES = 4;
   constexpr int NCB = M == 1 ? 2 : 1;                 // one matrix: a warp shares its inputs between two column blocks
   using SM = DecodeSmem<M * NCB, STAGES>;
-  auto* kern = decode_kernel<M, NCB, EPI, SB, KW, STAGES>;
+  auto* kern = decode_kernel<M, NCB, EPI, SB, KW, STAGES, PT>;
   static_assert(SM::TOTAL <= 48 * 1024, "the decode kernel stays within the default shared-memory limit");
   constexpr int CBC = DEC_WARPS / KW * NCB;
   const int64_t grid = max_items * ((nb + CBC - 1) / CBC);
@@ -223,19 +246,19 @@ int launch_decode_kw(const void* x, int64_t x_stride, int slots, const void* w, 
                     "experts_run");
 }
 
-template <int M, int EPI, int SB>
+template <int M, int EPI, int SB, int PT>
 int launch_decode(const void* x, int64_t x_stride, int slots, const void* w, int kg, int nb, const int* items,
                   const int* counts, const int* members, void* out, int n, float limit, int64_t max_items,
                   cudaStream_t stream) {
   switch (decode_kslices(kg)) {
     case 4:
-      return launch_decode_kw<M, EPI, SB, 4>(x, x_stride, slots, w, kg, nb, items, counts, members, out, n, limit,
+      return launch_decode_kw<M, EPI, SB, 4, PT>(x, x_stride, slots, w, kg, nb, items, counts, members, out, n, limit,
                                              max_items, stream);
     case 2:
-      return launch_decode_kw<M, EPI, SB, 2>(x, x_stride, slots, w, kg, nb, items, counts, members, out, n, limit,
+      return launch_decode_kw<M, EPI, SB, 2, PT>(x, x_stride, slots, w, kg, nb, items, counts, members, out, n, limit,
                                              max_items, stream);
     default:
-      return launch_decode_kw<M, EPI, SB, 1>(x, x_stride, slots, w, kg, nb, items, counts, members, out, n, limit,
+      return launch_decode_kw<M, EPI, SB, 1, PT>(x, x_stride, slots, w, kg, nb, items, counts, members, out, n, limit,
                                              max_items, stream);
   }
 }
@@ -244,12 +267,9 @@ int launch_decode(const void* x, int64_t x_stride, int slots, const void* w, int
 
 using namespace tfb;
 
-// Grouped 4-bit expert matmul, decode form.  Arguments as the reference extension's `run`
-// (src/tensorfold/cuda/experts.cpp:43-48): epi 0 fp32 out, 1 relu^2, 2 SwiGLU over (gate, up), 3 bf16 out.
-// max_units = an upper bound of items * nb, as the reference passes it.
-extern "C" int tfb_experts_run(int gs, int epi, const void* x, int64_t x_stride, int slots, const void* w, int kg,
-                               int nb, const int32_t* items, const int32_t* counts, const int32_t* members, void* out,
-                               int n, float limit, int64_t max_units, int sb_type, void* stream) {
+static int experts_run(int gs, int epi, const void* x, int64_t x_stride, int slots, const void* w, int kg, int nb,
+                       const int32_t* items, const int32_t* counts, const int32_t* members, void* out, int n,
+                       float limit, int64_t max_units, int sb_type, int tile, void* stream) {
   TFB_REQUIRE(gs == GS, "experts_run: groups of %d inputs only, not %d", GS, gs);
   TFB_REQUIRE(x && w && items && counts && members && out, "experts_run: null pointer");
   TFB_REQUIRE(kg >= 1 && nb >= 1 && n == nb * COLS, "experts_run: n must be the column blocks times %d", COLS);
@@ -258,17 +278,43 @@ extern "C" int tfb_experts_run(int gs, int epi, const void* x, int64_t x_stride,
   TFB_REQUIRE(aligned16(w), "experts_run: w must be 16-byte aligned");
   TFB_REQUIRE(slots >= 0 && max_units >= 0 && max_units < (int64_t(1) << 31), "experts_run: bad slots or unit count");
   TFB_REQUIRE(sb_type == SB_BF16 || sb_type == SB_FP16, "experts_run: scales are bf16 (0) or fp16 (1), not %d", sb_type);
+  TFB_REQUIRE(tile == 8 || tile == 16, "experts_run: items of 8 or 16 pairs, not %d", tile);
   const int64_t max_items = (max_units + nb - 1) / nb;
   if (max_items == 0) return TFB_OK;
   auto st = static_cast<cudaStream_t>(stream);
-#define TFB_RUN(EPI_, M_)                                                                                          \
-  if (epi == EPI_)                                                                                                 \
-    return sb_type == SB_BF16                                                                                      \
-               ? launch_decode<M_, EPI_, SB_BF16>(x, x_stride, slots, w, kg, nb, items, counts, members, out, n,   \
-                                                  limit, max_items, st)                                            \
-               : launch_decode<M_, EPI_, SB_FP16>(x, x_stride, slots, w, kg, nb, items, counts, members, out, n,   \
-                                                  limit, max_items, st);
+#define TFB_RUN3(EPI_, M_, SB_)                                                                                    \
+  return tile == 8 ? launch_decode<M_, EPI_, SB_, 1>(x, x_stride, slots, w, kg, nb, items, counts, members, out, n, \
+                                                     limit, max_items, st)                                         \
+                   : launch_decode<M_, EPI_, SB_, 2>(x, x_stride, slots, w, kg, nb, items, counts, members, out, n, \
+                                                     limit, max_items, st)
+#define TFB_RUN(EPI_, M_)                              \
+  if (epi == EPI_) {                                   \
+    if (sb_type == SB_BF16) TFB_RUN3(EPI_, M_, SB_BF16); \
+    TFB_RUN3(EPI_, M_, SB_FP16);                       \
+  }
   TFB_RUN(EPI_F32, 1) TFB_RUN(EPI_RELU2, 1) TFB_RUN(EPI_SWIGLU, 2) TFB_RUN(EPI_BF16, 1)
 #undef TFB_RUN
+#undef TFB_RUN3
   return fail(TFB_ERR_ARG, "experts_run: no kernel for epilogue %d", epi);
+}
+
+// Grouped 4-bit expert matmul, decode form.  Arguments as the reference extension's `run`
+// (src/tensorfold/cuda/experts.cpp:43-48): epi 0 fp32 out, 1 relu^2, 2 SwiGLU over (gate, up), 3 bf16 out.
+// max_units = an upper bound of items * nb, as the reference passes it.  Items hold at most 8 pairs.
+extern "C" int tfb_experts_run(int gs, int epi, const void* x, int64_t x_stride, int slots, const void* w, int kg,
+                               int nb, const int32_t* items, const int32_t* counts, const int32_t* members, void* out,
+                               int n, float limit, int64_t max_units, int sb_type, void* stream) {
+  return experts_run(gs, epi, x, x_stride, slots, w, kg, nb, items, counts, members, out, n, limit, max_units, sb_type,
+                     8, stream);
+}
+
+// The same over a plan whose items hold up to `tile` = 8 or 16 pairs: with 16 a weight fragment is dequantised once
+// for two mma tiles of pairs, which pays when experts see 9 or more pairs each (expert-parallel ranks, larger decode
+// batches).  A pair's bits do not depend on the tile.
+extern "C" int tfb_experts_run_tile(int gs, int epi, const void* x, int64_t x_stride, int slots, const void* w, int kg,
+                                    int nb, const int32_t* items, const int32_t* counts, const int32_t* members,
+                                    void* out, int n, float limit, int64_t max_units, int sb_type, int tile,
+                                    void* stream) {
+  return experts_run(gs, epi, x, x_stride, slots, w, kg, nb, items, counts, members, out, n, limit, max_units, sb_type,
+                     tile, stream);
 }

@@ -182,7 +182,9 @@ class GatheredExpertParallel:
 
         self.x_all = torch.zeros((rows, d), dtype=torch.bfloat16, device=dev)
         self.buf = moe.MoEBuffers(rows, _Cfg, dev, shared=False)
-        self.plan = grouped.Plan(rows, k, self.per_rank, dev)
+        # about rows * k / experts pairs reach each local expert: from 9 on, items of 16 halve the passes over the weights
+        wide = rows * k > 8 * experts
+        self.plan = grouped.Plan(rows, k, self.per_rank, dev, decode_tile=grouped.WIDE_TILE if wide else grouped.TILE)
         self.local_pick = torch.zeros((rows, k), dtype=torch.int32, device=dev)
         self.y_mine = torch.zeros((rows_local * k, d), dtype=torch.float32, device=dev)
         self.partial = torch.zeros((rows, d), dtype=torch.float32, device=dev)
@@ -200,7 +202,7 @@ class GatheredExpertParallel:
         m.router(self.x_all, self.router_rows, buf.logits)
         lo, st = self.rank * self.per_rank, torch.cuda.current_stream(self.x_all.device).cuda_stream
         plan = self.plan
-        plan.tile = g.TILE
+        plan.tile = plan.decode_tile
         with torch.cuda.device(self.x_all.device):
             if self.rows <= self._fused_rows:
                 # selection of every token and the plan of this rank's experts in one launch

@@ -17,6 +17,7 @@ from . import _lib
 NTW = 4                  # n8 tiles a 32-column block
 COLS = 8 * NTW           # output columns a block
 TILE = 8                 # pairs an item holds (decode form): one mma tile of pairs
+WIDE_TILE = 16           # the decode form's other item size: two mma tiles share one dequantisation
 PREFILL_TILE = 192       # pairs a prompt item holds: the tensor-core tile's N
 SMALL = 1024             # kept for callers that size scratch by it; this library's plan is one launch at any size
 BLOCK = 288              # int32 words a block of 64 inputs x 32 columns: 1024 B of nibbles + 128 B of scale/bias
@@ -138,10 +139,13 @@ class Plan:
     """Scratch grouping pairs by expert: members, items (expert, first, count), counts [items, distinct experts]."""
 
     def __init__(self, rows: int, slots: int, experts: int, device: torch.device | str, *,
-                 prefill: bool = False) -> None:
+                 prefill: bool = False, decode_tile: int = TILE) -> None:
+        if decode_tile not in (TILE, WIDE_TILE):
+            raise ValueError(f"decode items hold {TILE} or {WIDE_TILE} pairs")
         pairs = rows * slots
         self.rows, self.slots, self.experts, self.prefill = rows, slots, experts, prefill
-        self.tile = PREFILL_TILE if prefill else TILE
+        self.decode_tile = decode_tile
+        self.tile = PREFILL_TILE if prefill else decode_tile
         self.members = torch.zeros((pairs,), dtype=torch.int32, device=device)
         self.items = torch.zeros((max_items(pairs, experts, TILE), 3), dtype=torch.int32, device=device)
         self.counts = torch.zeros((2,), dtype=torch.int32, device=device)
@@ -158,7 +162,7 @@ def route(picks: torch.Tensor, plan: Plan, tile: int = PREFILL_TILE) -> None:
     if picks.dtype != torch.int32 or not picks.is_contiguous():
         raise ValueError("picks must be contiguous int32")
     _need_cuda(picks, "picks")
-    plan.tile = tile if plan.prefill else TILE
+    plan.tile = tile if plan.prefill else plan.decode_tile
     if plan.tile < TILE:
         raise ValueError(f"items hold at least {TILE} pairs")
     with torch.cuda.device(picks.device):
@@ -188,9 +192,9 @@ def _run(epi: int, x: torch.Tensor, slots: int, w: torch.Tensor, kg: int, nb: in
                       plan.items.data_ptr(), plan.counts.data_ptr(), plan.members.data_ptr(), out.data_ptr(), n,
                       float(limit), items, _SB[ex.scale_dtype], _stream(x))
         else:
-            _lib.call("tfb_experts_run", ex.gs, epi, x.data_ptr(), x.stride(0), slots, w.data_ptr(), kg, nb,
+            _lib.call("tfb_experts_run_tile", ex.gs, epi, x.data_ptr(), x.stride(0), slots, w.data_ptr(), kg, nb,
                       plan.items.data_ptr(), plan.counts.data_ptr(), plan.members.data_ptr(), out.data_ptr(), n,
-                      float(limit), items * nb, _SB[ex.scale_dtype], _stream(x))
+                      float(limit), items * nb, _SB[ex.scale_dtype], plan.tile, _stream(x))
 
 
 def gate_up(x: torch.Tensor, ex: Experts, plan: Plan, out: torch.Tensor, rows: int) -> None:

@@ -81,7 +81,7 @@ def select(logits: torch.Tensor, buf: MoEBuffers, top_k: int, experts: int,
         shared = buf.slots == top_k + 1
         if buf.slots not in (top_k, top_k + 1) or rows > buf.rows or plan.slots != buf.slots:
             raise ValueError(f"{rows} rows of top-{top_k} do not fit buffers of {buf.rows} x {buf.slots}")
-        plan.tile = tile if plan.prefill else grouped.TILE
+        plan.tile = tile if plan.prefill else plan.decode_tile
         with torch.cuda.device(logits.device):
             _lib.call("tfb_select_plan", logits.data_ptr(), nl, buf.pick.data_ptr(), buf.wts.data_ptr(), rows, experts,
                       top_k, 1 if shared else 0, plan.tile, plan.members.data_ptr(), plan.items.data_ptr(),

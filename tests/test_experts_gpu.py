@@ -272,3 +272,23 @@ def test_gathered_expert_parallel_on_one_rank_is_the_layer(reduce):
         assert torch.equal(got, want)
     else:
         assert torch.equal(got, want)          # one rank: the partial sum is the whole slot-order sum
+
+
+@pytest.mark.parametrize("case", CASES)
+def test_items_of_16_pairs_give_the_same_bits(case):
+    from tensorfold_b200 import experts
+
+    ex, _, _ = build(case, 51)
+    rows = 60
+    x = (torch.randn((rows, ex.dims), device=DEV) * 0.5).to(torch.bfloat16)
+    picks = picks_for(rows, case, 9, hot=0)                       # every row on the same experts: full items
+    act, y, plan8 = run(ex, x, picks)
+    slots = picks.shape[1]
+    plan = experts.Plan(rows, slots, ex.count, DEV, decode_tile=experts.WIDE_TILE)
+    experts.route(picks.contiguous(), plan)
+    act16 = torch.empty_like(act)
+    y16 = torch.empty_like(y)
+    experts.gate_up(x, ex, plan, act16, rows)
+    experts.down(act16, ex, plan, y16, rows)
+    assert torch.equal(act16, act) and torch.equal(y16, y)
+    assert int(plan.counts[0]) < int(plan8.counts[0])
