@@ -182,8 +182,9 @@ class GatheredExpertParallel:
 
         self.x_all = torch.zeros((rows, d), dtype=torch.bfloat16, device=dev)
         self.buf = moe.MoEBuffers(rows, _Cfg, dev, shared=False)
-        # about rows * k / experts pairs reach each local expert: from 9 on, items of 16 halve the passes over the weights
-        wide = rows * k > 8 * experts
+        # about rows * k / experts pairs reach each local expert: from 12 on, items of 16 (one dequantisation for two
+        # mma tiles) beat two passes of items of 8; below that the leaner 8-pair kernel wins (measured at 8 an expert)
+        wide = rows * k >= 12 * experts
         self.plan = grouped.Plan(rows, k, self.per_rank, dev, decode_tile=grouped.WIDE_TILE if wide else grouped.TILE)
         self.local_pick = torch.zeros((rows, k), dtype=torch.int32, device=dev)
         self.y_mine = torch.zeros((rows_local * k, d), dtype=torch.float32, device=dev)

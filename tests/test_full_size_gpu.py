@@ -99,3 +99,111 @@ def test_config3_exl3_layer_rows_and_float64():
     want = ref.routed(x[:2].float().cpu().numpy(), pick, wts, *mats, ref.CB_3INST)
     err = np.abs(full[:2].double().cpu().numpy() - want).max() / np.abs(want).max()
     assert err < 1e-2, err
+
+
+def test_config4_large_experts_with_shared_expert_and_skewed_routing():
+    """Config 4's layer (hidden 6144, 256 experts x FFN 2048, top-8 + a shared expert, 256 tokens, Zipf-skewed router)
+    on one GPU: routing against the sorted order, a few rows against the CPU oracle, and row invariance."""
+
+    from oracle import affine, cpu
+    from tensorfold_b200 import experts, moe, synthetic
+
+    shape = synthetic.C4
+    gate, up, down = synthetic.affine_layer(shape, DEV)
+    rt = synthetic.router_rows(shape, DEV)
+    layer = moe.Routed(rt, experts.make([gate, up], down, 64), shape.top_k, shared=True)
+    rows = 256
+    x = synthetic.activations(shape, rows, DEV)
+    buf = moe.MoEBuffers(rows, moe._Shape(layer), DEV, shared=True)
+    moe.router(x, rt, buf.logits)
+    buf.logits[:, :shape.experts] += synthetic.zipf_bias(shape, 1.1, DEV)          # uneven expert loads
+    moe.select(buf.logits, buf, shape.top_k, shape.experts)
+    ex = layer.experts
+    experts.gate_up(x, ex, buf.plan, buf.act.view(-1, ex.width), rows)
+    experts.down(buf.act.view(-1, ex.width), ex, buf.plan, buf.y.view(-1, ex.dims), rows)
+    out = moe.combine(buf.y, buf.wts)
+    logits = buf.logits.cpu().numpy()
+    pick = buf.pick.cpu().numpy()
+    for r in range(0, rows, 17):
+        want = sorted(range(shape.experts), key=lambda i: (-logits[r, i], i))[:shape.top_k]
+        assert pick[r, :shape.top_k].tolist() == want and pick[r, shape.top_k] == shape.experts
+    counts = np.bincount(pick[:, :shape.top_k].reshape(-1), minlength=shape.experts)
+    assert counts.max() > 8 * max(1, int(np.median(counts)))                       # the skew is real
+    # three rows against the float64 reference over the experts they use
+    sel = [0, 100, 255]
+    used = sorted(set(pick[sel].reshape(-1).tolist()))
+    remap = {e: i for i, e in enumerate(used)}
+    sub = lambda m: tuple(t[used].contiguous() for t in m)                         # noqa: E731
+    pk = np.vectorize(remap.get)(pick[sel]).astype(np.int32)
+    _, _, o64 = affine.layer64(bits(x[sel]), pk, buf.wts[sel].cpu().numpy(), triple_np(sub(gate)), triple_np(sub(up)),
+                               triple_np(sub(down)), 64, True)
+    assert rel_l2(out[sel].float().cpu().numpy(), o64) <= 1e-2
+    # a row alone: same bits
+    buf1 = moe.MoEBuffers(1, moe._Shape(layer), DEV, shared=True)
+    buf1.logits.copy_(buf.logits[100:101])
+    moe.select(buf1.logits, buf1, shape.top_k, shape.experts)
+    experts.gate_up(x[100:101], ex, buf1.plan, buf1.act.view(-1, ex.width), 1)
+    experts.down(buf1.act.view(-1, ex.width), ex, buf1.plan, buf1.y.view(-1, ex.dims), 1)
+    assert torch.equal(moe.combine(buf1.y, buf1.wts), out[100:101])
+
+
+def test_config5_mixed_width_exl3_stack():
+    """Config 5's shape (hidden 4096, 160 experts x FFN 1536, top-8, a seeded width of 2..8 bits per tensor), two of
+    its eight layers with a bf16 residual add between them, at 1, 8 and 32 tokens: finite, rows independent of the
+    window, and layer one within 1e-2 of float64 for two rows."""
+
+    import random
+
+    from oracle import exl3 as ref
+    from tensorfold_b200 import moe, synthetic
+    from tensorfold_b200.exl3 import experts as x3
+
+    shape = synthetic.C5
+    rng = random.Random(5005)
+    widths = {}
+
+    def bits_of(layer):
+        return lambda e, m: widths.setdefault((layer, e, m), rng.choice((2, 3, 4, 5, 6, 7, 8)))
+
+    layers, mats0 = [], None
+    for li in range(2):
+        gate, up, down = synthetic.exl3_layer(shape, DEV, bits_of(li), copy=li)
+        if li == 0:
+            mats0 = (gate, up, down)
+        layers.append((x3.prepare(gate, up, down, x3.CB_3INST, device=DEV),
+                       synthetic.router_rows(shape, DEV)))
+    assert len({v for v in widths.values()}) == 7
+
+    class _Cfg:
+        num_experts_per_tok, num_experts = shape.top_k, shape.experts
+        moe_intermediate_size, hidden_size = shape.width, shape.dims
+
+    def stack(h):
+        rows = h.shape[0]
+        first = None
+        for ex, rt in layers:
+            buf = moe.MoEBuffers(rows, _Cfg, DEV, shared=False)
+            moe.router(h, rt, buf.logits)
+            moe.select_rows(buf.logits, buf, shape.top_k, shape.experts)
+            y = x3.routed(h, buf.pick, buf.wts, ex, x3.Scratch(ex, rows, shape.top_k), None, rows)
+            if first is None:
+                first = (y.clone(), buf.pick.clone(), buf.wts.clone())
+            h = (h.float() + y).to(torch.bfloat16)                                 # residual add in bf16
+        return h, first
+
+    x = synthetic.activations(shape, 32, DEV)
+    full, (y0, pick0, wts0) = stack(x)
+    assert torch.isfinite(full.float()).all()
+    for a, b in ((0, 1), (3, 11), (31, 32)):
+        part, _ = stack(x[a:b])
+        assert torch.equal(part, full[a:b])
+    gate, up, down = mats0
+    used = sorted(set(pick0[:2].reshape(-1).tolist()))
+    mats = [[None] * shape.experts for _ in range(3)]
+    for e in used:
+        for m, src in enumerate((gate, up, down)):
+            mats[m][e] = tuple(t.cpu().numpy() for t in src[e])
+    want = ref.routed(x[:2].float().cpu().numpy(), pick0[:2].cpu().numpy(), wts0[:2].cpu().numpy(), *mats,
+                      ref.CB_3INST)
+    err = np.abs(y0[:2].double().cpu().numpy() - want).max() / np.abs(want).max()
+    assert err < 1e-2, err
