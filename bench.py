@@ -287,6 +287,14 @@ def bench_e2e(torch, runners, shape, rows: int, steps: int, warmup: int):
             "d2h_bytes_per_step": nbytes}
 
 
+COLLECTIVE = {
+    "tokens": "NCCL all-gather of the tokens, reduce-scatter of fp32 per-token partial sums",
+    "rows": "NCCL all-gather of the tokens, reduce-scatter of fp32 per-pair rows (exact)",
+    "peer": "own kernels over NVLink peer memory: pull of the tokens, push of fp32 per-token partial sums, two flag "
+            "barriers (no collective library on the step)",
+}
+
+
 def bench_ep(torch, dist, args, shape, dev, rank: int, world: int):
     """Expert-parallel step: this rank's `rows` tokens through the layer whose experts are sharded over the ranks
     (NCCL all-to-all dispatch and return).  Each rank keeps 2 * world copies of its expert slice and rotates them, so a
@@ -303,7 +311,11 @@ def bench_ep(torch, dist, args, shape, dev, rank: int, world: int):
         sl = slice(rank * per, (rank + 1) * per)
         local = experts.make([tuple(t[sl].contiguous() for t in gate), tuple(t[sl].contiguous() for t in up)],
                              tuple(t[sl].contiguous() for t in down), 64)
-        copies.append(ep.GatheredExpertParallel(router, local, shape.experts, shape.top_k, rows, reduce=args.ep_reduce))
+        if args.ep_reduce == "peer":
+            copies.append(ep.PeerExpertParallel(router, local, shape.experts, shape.top_k, rows))
+        else:
+            copies.append(ep.GatheredExpertParallel(router, local, shape.experts, shape.top_k, rows,
+                                                    reduce=args.ep_reduce))
         del gate, up, down
     x = synthetic.activations(shape, rows, dev, index=100 + rank)
     side = torch.cuda.Stream(dev)
@@ -400,7 +412,7 @@ def run_ours(args) -> None:
                     "config": {**workload_config(shape, rows, world),
                                "l2": f"each rank rotates {2 * world} copies of its {shape.experts // world}-expert slice "
                                      "(inputs larger than the 126 MB L2)",
-                               "collective": "NCCL all-gather of the tokens, reduce-scatter of fp32 " + ("per-token partial sums" if args.ep_reduce == "tokens" else "per-pair rows (exact)") + "; the step is one CUDA graph"},
+                               "collective": COLLECTIVE[args.ep_reduce] + "; the step is one CUDA graph"},
                     "clocks": clocks.summary(),
                     "e2e": {"value": world * rows / (e2e_ms * 1e-3), "unit": UNIT, "ms_per_step": e2e_ms,
                             "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": nbytes},
@@ -473,7 +485,7 @@ def main() -> None:
                     help="arithmetic form of the headline run (the sweep always uses decode at 1 and prefill at 2048)")
     ap.add_argument("--exl3-only", action="store_true",
                     help="run only the EXL3 (config 3) lines of the sweep and print them (a profiling aid)")
-    ap.add_argument("--ep-reduce", default="tokens", choices=["tokens", "rows"],
+    ap.add_argument("--ep-reduce", default="tokens", choices=["tokens", "rows", "peer"],
                     help="multi-GPU return path: per-token partial sums (default) or exact per-pair rows")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-sweep", action="store_true", help="skip the 1-token and 2048-token lines")

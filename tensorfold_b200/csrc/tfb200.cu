@@ -5,3 +5,4 @@
 #include "experts_decode.cu"
 #include "experts_prefill.cu"
 #include "exl3.cu"
+#include "peer.cu"

@@ -237,3 +237,96 @@ class GatheredExpertParallel:
         lo = self.rank * self.rows_local
         wts = buf.wts[lo:lo + self.rows_local]
         return m.combine(self.y_mine.view(self.rows_local, k, -1), wts, self.out)
+
+
+class PeerExpertParallel:
+    """``GatheredExpertParallel`` with both exchanges done by this library's own kernels over NVLink peer memory
+    (``csrc/peer.cu``): no collective-library call on the step.  Every rank stages its rows in its window, a flag
+    barrier, every rank pulls all rows; the per-token partial sums of a rank's experts (slot order, weights applied)
+    are stored straight into the home rank's window by the kernel that forms them, a second flag barrier, and the home
+    rank adds the ranks' rows in rank order and rounds once.  Values equal ``reduce="tokens"`` of the gathered form up
+    to fp32 summation order across ranks (here the order is fixed: rank 0, 1, ...).
+
+    The windows are one ``torch.distributed._symmetric_memory`` allocation a rank (plain peer mappings; multicast is
+    not used).  Waits are bounded: a rank that never arrives shows up as a non-zero ``_lib.kernel_status()``."""
+
+    def __init__(self, router_rows: torch.Tensor, local_experts, experts: int, top_k: int, rows_local: int,
+                 group=None) -> None:
+        import os
+
+        from . import experts as grouped
+        from . import moe
+
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        import torch.distributed._symmetric_memory as symm
+
+        self.moe, self.grouped = moe, grouped
+        self.group = group if group is not None else dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
+        if experts % self.world:
+            raise ValueError(f"{experts} experts do not shard evenly over {self.world} ranks")
+        self.per_rank, self.experts, self.top_k = experts // self.world, experts, top_k
+        self.router_rows, self.local, self.rows_local = router_rows, local_experts, rows_local
+        dev, d, k = router_rows.device, local_experts.dims, top_k
+        rows = rows_local * self.world
+        self.rows = rows
+
+        class _Cfg:
+            num_experts_per_tok, num_experts = top_k, experts
+            moe_intermediate_size, hidden_size = local_experts.width, d
+
+        self.x_bytes = rows_local * d * 2
+        self.p_bytes = rows * d * 4
+        self.x_offset = 256
+        self.p_offset = self.x_offset + 2 * self.x_bytes
+        total = self.p_offset + 2 * self.p_bytes
+        if self.x_bytes % 16 or 2 * self.world * 4 > self.x_offset:
+            raise ValueError("rows_local * dims must be a multiple of 8 and at most 32 ranks")
+        self.window = symm.empty(total, dtype=torch.uint8, device=dev)
+        self.window.zero_()
+        torch.cuda.synchronize(dev)
+        self.handle = symm.rendezvous(self.window, self.group)
+        ptrs = list(self.handle.buffer_ptrs)
+        self.windows = torch.tensor(ptrs, dtype=torch.int64, device=dev)
+        self.count = torch.zeros(2, dtype=torch.int32, device=dev)
+        dist.barrier(self.group)                                  # every window is zeroed before any flag is written
+
+        self.x_all = torch.zeros((rows, d), dtype=torch.bfloat16, device=dev)
+        self.buf = moe.MoEBuffers(rows, _Cfg, dev, shared=False)
+        wide = rows * k >= 12 * experts
+        self.plan = grouped.Plan(rows, k, self.per_rank, dev, decode_tile=grouped.WIDE_TILE if wide else grouped.TILE)
+        self.out = torch.zeros((rows_local, d), dtype=torch.bfloat16, device=dev)
+        self._fused_rows = _lib.lib().tfb_select_plan_max_rows()
+        self.launches = (9 if rows <= self._fused_rows else 10)
+
+    def forward(self, x_local: torch.Tensor) -> torch.Tensor:
+        m, g, buf, k, d = self.moe, self.grouped, self.buf, self.top_k, self.local.dims
+        dev = self.x_all.device
+        st = torch.cuda.current_stream(dev).cuda_stream
+        win, wins, cnt = self.window.data_ptr(), self.windows.data_ptr(), self.count.data_ptr()
+        lo = self.rank * self.per_rank
+        plan = self.plan
+        plan.tile = plan.decode_tile
+        x_local = x_local.contiguous()
+        with torch.cuda.device(dev):
+            _lib.call("tfb_peer_stage", x_local.data_ptr(), win, self.x_offset, self.x_bytes, cnt, st)
+            _lib.call("tfb_peer_barrier", wins, self.rank, self.world, 0, cnt, st)
+            _lib.call("tfb_peer_gather", wins, self.world, self.x_offset, self.x_bytes, self.x_all.data_ptr(), cnt, st)
+            m.router(self.x_all, self.router_rows, buf.logits)
+            if self.rows <= self._fused_rows:
+                _lib.call("tfb_select_plan_window", buf.logits.data_ptr(), buf.logits.shape[1], buf.pick.data_ptr(),
+                          buf.wts.data_ptr(), self.rows, self.experts, k, 0, plan.tile, lo, self.per_rank,
+                          plan.members.data_ptr(), plan.items.data_ptr(), plan.counts.data_ptr(), st)
+            else:
+                m.select_rows(buf.logits, buf, k, self.experts)
+                _lib.call("tfb_plan_window", buf.pick.data_ptr(), self.rows * k, lo, self.per_rank, plan.tile,
+                          plan.members.data_ptr(), plan.items.data_ptr(), plan.counts.data_ptr(), st)
+            y_all = buf.y.view(-1, d)
+            g.gate_up(self.x_all, self.local, plan, buf.act.view(-1, self.local.width), self.rows)
+            g.down(buf.act.view(-1, self.local.width), self.local, plan, y_all, self.rows)
+            _lib.call("tfb_combine_push", buf.y.data_ptr(), buf.wts.data_ptr(), buf.pick.data_ptr(), lo, self.per_rank,
+                      wins, self.p_offset, self.p_bytes, self.rank, self.rows_local, self.rows, k, d, cnt, st)
+            _lib.call("tfb_peer_barrier", wins, self.rank, self.world, 1, cnt, st)
+            _lib.call("tfb_peer_sum", win, self.p_offset, self.p_bytes, self.world, self.rows_local, d,
+                      self.out.data_ptr(), cnt, st)
+        return self.out

@@ -58,6 +58,90 @@ def _worker(rank, world, port, out):
     dist.destroy_process_group()
 
 
+def _peer_worker(rank, world, port, out):
+    try:
+        _peer_body(rank, world, port, out)
+    except Exception as err:                                         # reported instead of a silent queue time-out
+        out.put((rank, (False, repr(err))))
+        raise
+
+
+def _peer_body(rank, world, port, out):
+    """The peer-memory form: three eager steps (both buffer parities), then two replays of a captured step."""
+
+    sys.path.insert(0, str(ROOT))
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    import torch.distributed as dist
+
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    from tensorfold_b200 import _lib, ep, experts, moe, synthetic
+
+    shape, rows = synthetic.SMALL, 24
+    per = shape.experts // world
+    gate, up, down = synthetic.affine_layer(shape, dev)
+    router = synthetic.router_rows(shape, dev)
+    sl = slice(rank * per, (rank + 1) * per)
+    local = experts.make([tuple(t[sl].contiguous() for t in gate), tuple(t[sl].contiguous() for t in up)],
+                         tuple(t[sl].contiguous() for t in down), 64)
+    full = moe.Routed(router, experts.make([gate, up], down, 64), shape.top_k, shared=False)
+    nccl = ep.GatheredExpertParallel(router, local, shape.experts, shape.top_k, rows, reduce="tokens")
+    peer = ep.PeerExpertParallel(router, local, shape.experts, shape.top_k, rows)
+    flags = []
+    xs = [synthetic.activations(shape, rows, dev, index=70 + 2 * i + rank) for i in range(5)]
+    for x in xs[:3]:
+        got = peer.forward(x).clone()
+        ref = nccl.forward(x).clone()
+        want = moe.run(x, full).float()
+        # two ranks: a + b in either order is the same fp32 value, so the NCCL partial-sum form gives the same bits
+        flags.append(bool(torch.equal(got, ref)) and bool((got.float() - want).norm() / want.norm() < 1e-2))
+    torch.cuda.synchronize()
+    x_in = xs[3].clone()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        peer.forward(x_in)
+    for x in xs[3:]:
+        x_in.copy_(x)
+        peer.out.zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+        flags.append(bool(torch.equal(peer.out, nccl.forward(x))))
+    flags.append(_lib.kernel_status() == 0)
+    del graph
+    torch.cuda.synchronize()
+    out.put((rank, tuple(flags)))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def _run_two(worker):
+    import torch.multiprocessing as mp
+
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    procs = [ctx.Process(target=worker, args=(r, 2, port, out)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = [out.get(timeout=240) for _ in procs]
+    for p in procs:
+        p.join(timeout=120)
+    return results, [p.exitcode for p in procs]
+
+
+def test_peer_memory_form_matches_nccl_form():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    results, codes = _run_two(_peer_worker)
+    assert all(all(flags) for _, flags in results), results
+    assert codes == [0, 0]
+
+
 def test_two_gpus_match_one():
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
