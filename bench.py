@@ -319,15 +319,23 @@ def bench_ep(torch, dist, args, shape, dev, rank: int, world: int):
         del gate, up, down
     x = synthetic.activations(shape, rows, dev, index=100 + rank)
     side = torch.cuda.Stream(dev)
-    for layer in copies:                                   # warm up eagerly (NCCL set-up), then capture the step
-        layer.forward(x)
+    if args.ep_reduce == "peer":                           # the tokens live in each copy's window; nothing to stage
+        inputs = [layer.tokens for layer in copies]
+        for t in inputs:
+            t.copy_(x)
+        steps = [layer.forward for layer in copies]
+    else:
+        inputs = [x] * len(copies)
+        steps = [(lambda layer=layer: layer.forward(x)) for layer in copies]
+    for step in steps:                                     # warm up eagerly (NCCL set-up), then capture the step
+        step()
     torch.cuda.synchronize()
     dist.barrier()
-    for layer in copies:
+    for step in steps:
         side.wait_stream(torch.cuda.current_stream())
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g, stream=side):
-            layer.forward(x)
+            step()
         graphs.append(g)
     torch.cuda.synchronize()
     dist.barrier()
@@ -351,7 +359,7 @@ def bench_ep(torch, dist, args, shape, dev, rank: int, world: int):
     dist.barrier()
     a.record()
     for i in range(args.steps):
-        x.copy_(x_host, non_blocking=True)
+        inputs[i % len(inputs)].copy_(x_host, non_blocking=True)
         graphs[i % len(graphs)].replay()
         out_host.copy_(copies[i % len(copies)].out, non_blocking=True)
         torch.cuda.current_stream().synchronize()
@@ -485,8 +493,9 @@ def main() -> None:
                     help="arithmetic form of the headline run (the sweep always uses decode at 1 and prefill at 2048)")
     ap.add_argument("--exl3-only", action="store_true",
                     help="run only the EXL3 (config 3) lines of the sweep and print them (a profiling aid)")
-    ap.add_argument("--ep-reduce", default="tokens", choices=["tokens", "rows", "peer"],
-                    help="multi-GPU return path: per-token partial sums (default) or exact per-pair rows")
+    ap.add_argument("--ep-reduce", default="peer", choices=["tokens", "rows", "peer"],
+                    help="multi-GPU exchanges: own kernels over NVLink peer memory (default), or NCCL with per-token "
+                         "partial sums / exact per-pair rows")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-sweep", action="store_true", help="skip the 1-token and 2048-token lines")
     args = ap.parse_args()

@@ -276,19 +276,19 @@ class PeerExpertParallel:
             moe_intermediate_size, hidden_size = local_experts.width, d
 
         self.x_bytes = rows_local * d * 2
-        self.p_bytes = rows * d * 4
         self.x_offset = 256
-        self.p_offset = self.x_offset + 2 * self.x_bytes
-        total = self.p_offset + 2 * self.p_bytes
+        self.p_offset = self.x_offset + self.x_bytes
+        total = self.p_offset + rows * d * 4
         if self.x_bytes % 16 or 2 * self.world * 4 > self.x_offset:
             raise ValueError("rows_local * dims must be a multiple of 8 and at most 32 ranks")
         self.window = symm.empty(total, dtype=torch.uint8, device=dev)
         self.window.zero_()
         torch.cuda.synchronize(dev)
         self.handle = symm.rendezvous(self.window, self.group)
-        ptrs = list(self.handle.buffer_ptrs)
-        self.windows = torch.tensor(ptrs, dtype=torch.int64, device=dev)
-        self.count = torch.zeros(2, dtype=torch.int32, device=dev)
+        self.windows = torch.tensor(list(self.handle.buffer_ptrs), dtype=torch.int64, device=dev)
+        self.step = torch.zeros(1, dtype=torch.int32, device=dev)
+        # this rank's token buffer inside its window: a caller may write its rows here and call forward() without them
+        self.tokens = self.window[self.x_offset:self.p_offset].view(torch.bfloat16).view(rows_local, d)
         dist.barrier(self.group)                                  # every window is zeroed before any flag is written
 
         self.x_all = torch.zeros((rows, d), dtype=torch.bfloat16, device=dev)
@@ -297,21 +297,24 @@ class PeerExpertParallel:
         self.plan = grouped.Plan(rows, k, self.per_rank, dev, decode_tile=grouped.WIDE_TILE if wide else grouped.TILE)
         self.out = torch.zeros((rows_local, d), dtype=torch.bfloat16, device=dev)
         self._fused_rows = _lib.lib().tfb_select_plan_max_rows()
-        self.launches = (9 if rows <= self._fused_rows else 10)
+        self.launches = 7 if rows <= self._fused_rows else 8    # + 1 when forward() is given rows to stage
 
-    def forward(self, x_local: torch.Tensor) -> torch.Tensor:
+    def forward(self, x_local: torch.Tensor | None = None) -> torch.Tensor:
+        """``x_local`` [rows_local, D] bf16, or None when the caller has written its rows into ``self.tokens``."""
+
         m, g, buf, k, d = self.moe, self.grouped, self.buf, self.top_k, self.local.dims
         dev = self.x_all.device
         st = torch.cuda.current_stream(dev).cuda_stream
-        win, wins, cnt = self.window.data_ptr(), self.windows.data_ptr(), self.count.data_ptr()
+        win, wins, step = self.window.data_ptr(), self.windows.data_ptr(), self.step.data_ptr()
         lo = self.rank * self.per_rank
         plan = self.plan
         plan.tile = plan.decode_tile
-        x_local = x_local.contiguous()
         with torch.cuda.device(dev):
-            _lib.call("tfb_peer_stage", x_local.data_ptr(), win, self.x_offset, self.x_bytes, cnt, st)
-            _lib.call("tfb_peer_barrier", wins, self.rank, self.world, 0, cnt, st)
-            _lib.call("tfb_peer_gather", wins, self.world, self.x_offset, self.x_bytes, self.x_all.data_ptr(), cnt, st)
+            if x_local is not None:
+                x_local = x_local.contiguous()
+                _lib.call("tfb_peer_stage", x_local.data_ptr(), win, self.x_offset, self.x_bytes, st)
+            _lib.call("tfb_peer_gather", wins, self.rank, self.world, self.x_offset, self.x_bytes,
+                      self.x_all.data_ptr(), step, st)
             m.router(self.x_all, self.router_rows, buf.logits)
             if self.rows <= self._fused_rows:
                 _lib.call("tfb_select_plan_window", buf.logits.data_ptr(), buf.logits.shape[1], buf.pick.data_ptr(),
@@ -325,8 +328,7 @@ class PeerExpertParallel:
             g.gate_up(self.x_all, self.local, plan, buf.act.view(-1, self.local.width), self.rows)
             g.down(buf.act.view(-1, self.local.width), self.local, plan, y_all, self.rows)
             _lib.call("tfb_combine_push", buf.y.data_ptr(), buf.wts.data_ptr(), buf.pick.data_ptr(), lo, self.per_rank,
-                      wins, self.p_offset, self.p_bytes, self.rank, self.rows_local, self.rows, k, d, cnt, st)
-            _lib.call("tfb_peer_barrier", wins, self.rank, self.world, 1, cnt, st)
-            _lib.call("tfb_peer_sum", win, self.p_offset, self.p_bytes, self.world, self.rows_local, d,
-                      self.out.data_ptr(), cnt, st)
+                      wins, self.p_offset, self.rank, self.rows_local, self.rows, k, d, step, st)
+            _lib.call("tfb_peer_sum", wins, self.rank, self.p_offset, self.world, self.rows_local, d,
+                      self.out.data_ptr(), step, st)
         return self.out
