@@ -77,16 +77,19 @@ int tfb_combine_window(const void* y, int y_bf16, const float* wts, const int32_
 /* Expert parallelism over NVLink peer memory (no reference counterpart, as above): the token exchange and the return of
  * the results done by this library's kernels with plain loads and stores to the peers' windows, no collective library
  * on the path.  `windows` is a DEVICE array of `world` pointers: entry i is rank i's window as mapped into this process
- * (entry `rank` is this rank's own memory).  A window holds [2][world] uint32 barrier flags (zero at start), the token
- * buffer of x_bytes at x_offset and the result buffer of world * rows_local * D * 4 bytes at p_offset.  `step` is one
- * uint32 in device memory, zero at start, counted up by tfb_combine_push.  One step, the same on every rank:
- *   [tfb_peer_stage, or the caller writes its tokens into the window]  tfb_peer_gather (tokens barrier, then pull)
- *   router .. down   tfb_combine_push   tfb_peer_sum (results barrier, then sum in rank order).
+ * (entry `rank` is this rank's own memory).  A window holds [2][world] uint32 barrier flags (zero at start), the regions
+ * the peers pull (the rank's tokens; its rows' experts and weights) and the result buffer of world * rows_local * D * 4
+ * bytes at p_offset.  `step` is one uint32 in device memory, zero at start, counted up by tfb_combine_push.  One step,
+ * the same on every rank:
+ *   [tfb_peer_stage, or the caller writes its tokens into the window]  router and selection of the rank's own rows,
+ *   written into the window   tfb_peer_gather (tokens barrier, then pull)   plan of the rank's experts   gate/up
+ *   down   tfb_combine_push   tfb_peer_sum (results barrier, then sum in rank order).
  * A barrier's wait gives up after about a second and sets the device status word (tfb_kernel_status); it needs every
  * rank's kernel to be running at the same time, so the ranks must be separate GPUs. */
 int tfb_peer_stage(const void* x_local, void* window, int64_t x_offset, int64_t x_bytes, void* stream);
-int tfb_peer_gather(void* const* windows, int rank, int world, int64_t x_offset, int64_t x_bytes, void* x_all,
-                    const void* step, void* stream);
+/* nseg <= 4 regions (host arrays): seg_dst[s][r * seg_bytes[s] ...] <- rank r's window + seg_offset[s], every r. */
+int tfb_peer_gather(void* const* windows, int rank, int world, int nseg, const int64_t* seg_offset,
+                    const int64_t* seg_bytes, void* const* seg_dst, const void* step, void* stream);
 /* tfb_combine_window with fp32 output, each token's row stored into its home rank's result buffer, slot `rank`. */
 int tfb_combine_push(const float* y, const float* wts, const int32_t* pick, int lo, int n, void* const* windows,
                      int64_t p_offset, int rank, int rows_local, int T, int slots, int D, void* step, void* stream);

@@ -37,7 +37,7 @@ SIGNATURES: dict[str, tuple] = {
     "tfb_exl3_gateup_epilogue": (P, P, P, P, P, P, I, I, I, F, I, P),
     "tfb_exl3_down_epilogue": (P, P, P, P, P, P, I, I, I, I, P),
     "tfb_peer_stage": (P, P, L, L, P),
-    "tfb_peer_gather": (P, I, I, L, L, P, P, P),
+    "tfb_peer_gather": (P, I, I, I, P, P, P, P, P),
     "tfb_combine_push": (P, P, P, I, I, P, L, I, I, I, I, I, P, P),
     "tfb_peer_sum": (P, I, L, I, I, I, P, P, P),
     "tfb_kernel_status": (P, P),

@@ -1,7 +1,8 @@
 // Expert parallelism over NVLink peer memory: the two exchanges of an expert-parallel step done by this library's own
 // kernels with plain loads and stores to the peers' buffers (no NCCL call, no TMA, no multicast):
-//   * tokens: every rank copies its rows into its own window; after a flag barrier each rank PULLS all ranks' rows into
-//     a local buffer (a few hundred KB) and the layer's kernels read only local memory;
+//   * tokens: every rank has its rows, and the experts and weights it selected for them, in its own window; after a
+//     flag barrier each rank PULLS all ranks' rows and selections into local buffers (a few hundred KB) and the layer's
+//     kernels read only local memory;
 //   * results: the kernel that forms a rank's per-token partial sums (its experts' slots, weights applied, slot order)
 //     PUSHES each token's row straight into the home rank's slot for this rank; after a second flag barrier the home
 //     rank adds the ranks' rows in rank order and rounds to bf16.
@@ -77,17 +78,28 @@ peer_stage_kernel(const uint4* __restrict__ x_local, uint8_t* __restrict__ windo
   pdl_launch_dependents();
 }
 
-// Tokens barrier, then x_all [world * rows, D] <- every rank's token buffer.  step[0] = steps completed so far.
+// Tokens barrier, then up to PEER_SEGS regions of every rank's window are pulled into local buffers:
+// dst[s][r * bytes[s] ...] <- windows[r] + offset[s], for every rank r.  step[0] = steps completed so far.
+constexpr int PEER_SEGS = 4;
+struct PeerSegs {
+  int64_t offset[PEER_SEGS], units[PEER_SEGS];   // units of 16 bytes
+  uint4* dst[PEER_SEGS];
+  int n;
+};
+
 __global__ void __launch_bounds__(256)
-peer_gather_kernel(uint8_t* const* __restrict__ windows, int rank, int world, int64_t x_offset, int64_t x_bytes,
-                   uint4* __restrict__ x_all, const uint32_t* __restrict__ step) {
+peer_gather_kernel(uint8_t* const* __restrict__ windows, int rank, int world, PeerSegs segs,
+                   const uint32_t* __restrict__ step) {
   pdl_wait();
   peer_barrier(windows, rank, world, 0, step[0] + 1);
-  const int64_t per = x_bytes / 16;
+  int64_t per = 0;
+  for (int s = 0; s < segs.n; ++s) per += segs.units[s];
   for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < per * world; i += (int64_t)gridDim.x * 256) {
     const int r = (int)(i / per);
-    const int64_t j = i - (int64_t)r * per;
-    x_all[i] = ld_relaxed_sys_v4(windows[r] + x_offset + j * 16);
+    int64_t j = i - (int64_t)r * per;
+    int sg = 0;
+    while (sg + 1 < segs.n && j >= segs.units[sg]) j -= segs.units[sg++];
+    segs.dst[sg][(int64_t)r * segs.units[sg] + j] = ld_relaxed_sys_v4(windows[r] + segs.offset[sg] + j * 16);
   }
   pdl_launch_dependents();
 }
@@ -152,8 +164,8 @@ peer_sum_kernel(uint8_t* const* __restrict__ windows, int rank, int64_t p_offset
 using namespace tfb;
 
 // windows: DEVICE array of `world` pointers, entry i = rank i's window as mapped into this process (entry `rank` is
-// this rank's own).  A window holds: [2][world] uint32 barrier flags, the token buffer of x_bytes at x_offset, the
-// result buffer of world * rows * D * 4 bytes at p_offset.  step: 1 uint32 in device memory (zero at start).
+// this rank's own).  A window holds: [2][world] uint32 barrier flags, the regions the peers pull (tokens, selections),
+// the result buffer of world * rows * D * 4 bytes at p_offset.  step: 1 uint32 in device memory (zero at start).
 
 extern "C" int tfb_peer_stage(const void* x_local, void* window, int64_t x_offset, int64_t x_bytes, void* stream) {
   TFB_REQUIRE(x_local && window, "peer_stage: null pointer");
@@ -164,16 +176,27 @@ extern "C" int tfb_peer_stage(const void* x_local, void* window, int64_t x_offse
                     "peer_stage");
 }
 
-extern "C" int tfb_peer_gather(void* const* windows, int rank, int world, int64_t x_offset, int64_t x_bytes,
-                               void* x_all, const void* step, void* stream) {
-  TFB_REQUIRE(windows && x_all && step, "peer_gather: null pointer");
+extern "C" int tfb_peer_gather(void* const* windows, int rank, int world, int nseg, const int64_t* seg_offset,
+                               const int64_t* seg_bytes, void* const* seg_dst, const void* step, void* stream) {
+  TFB_REQUIRE(windows && seg_offset && seg_bytes && seg_dst && step, "peer_gather: null pointer");
   TFB_REQUIRE(world >= 1 && world <= 32 && rank >= 0 && rank < world, "peer_gather: rank %d of %d", rank, world);
-  TFB_REQUIRE(x_bytes > 0 && x_bytes % 16 == 0 && x_offset % 16 == 0 && aligned16(x_all), "peer_gather: 16-byte units");
-  const int64_t n = x_bytes / 16 * world;
+  TFB_REQUIRE(nseg >= 1 && nseg <= PEER_SEGS, "peer_gather: 1..%d regions, not %d", PEER_SEGS, nseg);
+  PeerSegs segs = {};
+  segs.n = nseg;
+  int64_t n = 0;
+  for (int s = 0; s < nseg; ++s) {
+    TFB_REQUIRE(seg_bytes[s] > 0 && seg_bytes[s] % 16 == 0 && seg_offset[s] % 16 == 0 && seg_dst[s] &&
+                    aligned16(seg_dst[s]),
+                "peer_gather: region %d is not in 16-byte units", s);
+    segs.offset[s] = seg_offset[s];
+    segs.units[s] = seg_bytes[s] / 16;
+    segs.dst[s] = static_cast<uint4*>(seg_dst[s]);
+    n += segs.units[s] * world;
+  }
   const int grid = (int)((n + 255) / 256 < 592 ? (n + 255) / 256 : 592);
   return check_cuda(launch(peer_gather_kernel, dim3(grid), dim3(256), 0, static_cast<cudaStream_t>(stream),
-                           reinterpret_cast<uint8_t* const*>(windows), rank, world, x_offset, x_bytes,
-                           static_cast<uint4*>(x_all), static_cast<const uint32_t*>(step)),
+                           reinterpret_cast<uint8_t* const*>(windows), rank, world, segs,
+                           static_cast<const uint32_t*>(step)),
                     "peer_gather");
 }
 

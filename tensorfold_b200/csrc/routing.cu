@@ -263,6 +263,18 @@ __device__ int place_items(int c, int E, int T, int* __restrict__ items, int* __
   return off;
 }
 
+// The lanes of the warp whose key equals this lane's (keys < 2^nbits; lanes with ok == false match nobody): one ballot
+// a key bit.  (match.any does the same but walks the distinct keys one by one, ~30 of them in a warp of random picks.)
+__device__ __forceinline__ unsigned same_key_lanes(int e, bool ok, int nbits) {
+  unsigned m = __ballot_sync(0xffffffffu, ok);
+  for (int b = 0; b < nbits; ++b) {
+    const bool bit = (e >> b) & 1;
+    const unsigned bal = __ballot_sync(0xffffffffu, bit);
+    m &= bit ? bal : ~bal;
+  }
+  return ok ? m : 0u;
+}
+
 // The whole block: `picks` may live in global or shared memory.
 __device__ void plan_block(const int* picks, int P, int E, int T, int* __restrict__ members, int* __restrict__ items,
                            int* __restrict__ counts, int* whist, int* first, int (*wsum)[32], int lo = 0) {
@@ -271,6 +283,7 @@ __device__ void plan_block(const int* picks, int P, int E, int T, int* __restric
   const int seg = (((P + 31) / 32 + 31) / 32) * 32;
   const int p0 = min(P, warp * seg), p1 = min(P, p0 + seg);
   int* mine = whist + warp * E;
+  const int nbits = 32 - __clz(max(E - 1, 0));
   __syncthreads();
   for (int base0 = p0; base0 < p1; base0 += 32 * PLAN_BATCH) {
     int ev[PLAN_BATCH];                              // the loads of a batch are independent: all in flight at once
@@ -284,7 +297,7 @@ __device__ void plan_block(const int* picks, int P, int E, int T, int* __restric
       if (base0 + 32 * i >= p1) break;
       const int e = ev[i];
       const bool ok = e >= 0 && e < E;
-      const unsigned peers = __match_any_sync(0xffffffffu, ok ? e : -1 - lane);
+      const unsigned peers = same_key_lanes(e, ok, nbits);
       if (ok && lane == __ffs(peers) - 1) mine[e] += __popc(peers);
       __syncwarp();
     }
@@ -312,7 +325,7 @@ __device__ void plan_block(const int* picks, int P, int E, int T, int* __restric
       if (base0 + 32 * i >= p1) break;
       const int p = base0 + 32 * i + lane, e = ev[i];
       const bool ok = e >= 0 && e < E;
-      const unsigned peers = __match_any_sync(0xffffffffu, ok ? e : -1 - lane);
+      const unsigned peers = same_key_lanes(e, ok, nbits);
       const int rank = __popc(peers & ((1u << lane) - 1u));
       const int b = ok ? mine[e] : 0;
       if (ok) members[first[e] + b + rank] = p;

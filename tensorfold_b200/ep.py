@@ -191,7 +191,7 @@ class GatheredExpertParallel:
         self.partial = torch.zeros((rows, d), dtype=torch.float32, device=dev)
         self.partial_mine = torch.zeros((rows_local, d), dtype=torch.float32, device=dev)
         self.out = torch.zeros((rows_local, d), dtype=torch.bfloat16, device=dev)
-        self._fused_rows = _lib.lib().tfb_select_plan_max_rows()
+        self._fused_rows = moe.fused_select_rows()
         self.launches = 5 if rows <= self._fused_rows else 6
 
     def forward(self, x_local: torch.Tensor) -> torch.Tensor:
@@ -240,18 +240,20 @@ class GatheredExpertParallel:
 
 
 class PeerExpertParallel:
-    """``GatheredExpertParallel`` with both exchanges done by this library's own kernels over NVLink peer memory
-    (``csrc/peer.cu``): no collective-library call on the step.  Every rank stages its rows in its window, a flag
-    barrier, every rank pulls all rows; the per-token partial sums of a rank's experts (slot order, weights applied)
-    are stored straight into the home rank's window by the kernel that forms them, a second flag barrier, and the home
-    rank adds the ranks' rows in rank order and rounds once.  Values equal ``reduce="tokens"`` of the gathered form up
-    to fp32 summation order across ranks (here the order is fixed: rank 0, 1, ...).
+    """The expert-parallel step with both exchanges done by this library's own kernels over NVLink peer memory
+    (``csrc/peer.cu``): no collective-library call on the step.  Every rank routes ITS rows (router and selection, as on
+    one GPU) with the selections written into its window beside the rows; a flag barrier; every rank pulls all ranks'
+    rows and selections, plans the pairs of its experts and runs them; the per-token partial sums of a rank's experts
+    (slot order, weights applied) are stored straight into the home rank's window by the kernel that forms them; a
+    second flag barrier; the home rank adds the ranks' rows in rank order and rounds once.  Values equal
+    ``GatheredExpertParallel(reduce="tokens")`` up to fp32 summation order across ranks (here fixed: rank 0, 1, ...).
 
     The windows are one ``torch.distributed._symmetric_memory`` allocation a rank (plain peer mappings; multicast is
     not used).  Waits are bounded: a rank that never arrives shows up as a non-zero ``_lib.kernel_status()``."""
 
     def __init__(self, router_rows: torch.Tensor, local_experts, experts: int, top_k: int, rows_local: int,
                  group=None) -> None:
+        import ctypes
         import os
 
         from . import experts as grouped
@@ -271,33 +273,47 @@ class PeerExpertParallel:
         rows = rows_local * self.world
         self.rows = rows
 
-        class _Cfg:
-            num_experts_per_tok, num_experts = top_k, experts
-            moe_intermediate_size, hidden_size = local_experts.width, d
+        def up(n: int) -> int:
+            return (n + 255) // 256 * 256
 
-        self.x_bytes = rows_local * d * 2
+        x_bytes, s_bytes = rows_local * d * 2, rows_local * k * 4
+        if x_bytes % 16 or s_bytes % 16 or 2 * self.world * 4 > 256:
+            raise ValueError("rows_local * dims and rows_local * top_k must be multiples of 8, and at most 32 ranks")
         self.x_offset = 256
-        self.p_offset = self.x_offset + self.x_bytes
+        self.pick_offset = self.x_offset + up(x_bytes)
+        self.wts_offset = self.pick_offset + up(s_bytes)
+        self.p_offset = self.wts_offset + up(s_bytes)
+        self.x_bytes = x_bytes
         total = self.p_offset + rows * d * 4
-        if self.x_bytes % 16 or 2 * self.world * 4 > self.x_offset:
-            raise ValueError("rows_local * dims must be a multiple of 8 and at most 32 ranks")
         self.window = symm.empty(total, dtype=torch.uint8, device=dev)
         self.window.zero_()
         torch.cuda.synchronize(dev)
         self.handle = symm.rendezvous(self.window, self.group)
         self.windows = torch.tensor(list(self.handle.buffer_ptrs), dtype=torch.int64, device=dev)
         self.step = torch.zeros(1, dtype=torch.int32, device=dev)
-        # this rank's token buffer inside its window: a caller may write its rows here and call forward() without them
-        self.tokens = self.window[self.x_offset:self.p_offset].view(torch.bfloat16).view(rows_local, d)
+        win = self.window
+        # this rank's rows inside its window: a caller may write them here and call forward() without an argument
+        self.tokens = win[self.x_offset:self.x_offset + x_bytes].view(torch.bfloat16).view(rows_local, d)
+        self.pick_mine = win[self.pick_offset:self.pick_offset + s_bytes].view(torch.int32).view(rows_local, k)
+        self.wts_mine = win[self.wts_offset:self.wts_offset + s_bytes].view(torch.float32).view(rows_local, k)
         dist.barrier(self.group)                                  # every window is zeroed before any flag is written
 
+        class _Cfg:
+            num_experts_per_tok, num_experts = top_k, experts
+            moe_intermediate_size, hidden_size = local_experts.width, d
+
+        self.logits = torch.zeros((rows_local, experts), dtype=torch.float32, device=dev)
         self.x_all = torch.zeros((rows, d), dtype=torch.bfloat16, device=dev)
-        self.buf = moe.MoEBuffers(rows, _Cfg, dev, shared=False)
+        self.buf = moe.MoEBuffers(rows, _Cfg, dev, shared=False)   # pick / wts of all rows, act, y
+        self._seg = (
+            (ctypes.c_int64 * 3)(self.x_offset, self.pick_offset, self.wts_offset),
+            (ctypes.c_int64 * 3)(x_bytes, s_bytes, s_bytes),
+            (ctypes.c_void_p * 3)(self.x_all.data_ptr(), self.buf.pick.data_ptr(), self.buf.wts.data_ptr()),
+        )
         wide = rows * k >= 12 * experts
         self.plan = grouped.Plan(rows, k, self.per_rank, dev, decode_tile=grouped.WIDE_TILE if wide else grouped.TILE)
         self.out = torch.zeros((rows_local, d), dtype=torch.bfloat16, device=dev)
-        self._fused_rows = _lib.lib().tfb_select_plan_max_rows()
-        self.launches = 7 if rows <= self._fused_rows else 8    # + 1 when forward() is given rows to stage
+        self.launches = 8                                         # + 1 when forward() is given rows to stage
 
     def forward(self, x_local: torch.Tensor | None = None) -> torch.Tensor:
         """``x_local`` [rows_local, D] bf16, or None when the caller has written its rows into ``self.tokens``."""
@@ -313,17 +329,13 @@ class PeerExpertParallel:
             if x_local is not None:
                 x_local = x_local.contiguous()
                 _lib.call("tfb_peer_stage", x_local.data_ptr(), win, self.x_offset, self.x_bytes, st)
-            _lib.call("tfb_peer_gather", wins, self.rank, self.world, self.x_offset, self.x_bytes,
-                      self.x_all.data_ptr(), step, st)
-            m.router(self.x_all, self.router_rows, buf.logits)
-            if self.rows <= self._fused_rows:
-                _lib.call("tfb_select_plan_window", buf.logits.data_ptr(), buf.logits.shape[1], buf.pick.data_ptr(),
-                          buf.wts.data_ptr(), self.rows, self.experts, k, 0, plan.tile, lo, self.per_rank,
-                          plan.members.data_ptr(), plan.items.data_ptr(), plan.counts.data_ptr(), st)
-            else:
-                m.select_rows(buf.logits, buf, k, self.experts)
-                _lib.call("tfb_plan_window", buf.pick.data_ptr(), self.rows * k, lo, self.per_rank, plan.tile,
-                          plan.members.data_ptr(), plan.items.data_ptr(), plan.counts.data_ptr(), st)
+            m.router(self.tokens, self.router_rows, self.logits)
+            _lib.call("tfb_select_rows", self.logits.data_ptr(), self.logits.shape[1], self.pick_mine.data_ptr(),
+                      self.wts_mine.data_ptr(), self.rows_local, self.experts, k, 0, st)
+            _lib.call("tfb_peer_gather", wins, self.rank, self.world, 3, self._seg[0], self._seg[1], self._seg[2],
+                      step, st)
+            _lib.call("tfb_plan_window", buf.pick.data_ptr(), self.rows * k, lo, self.per_rank, plan.tile,
+                      plan.members.data_ptr(), plan.items.data_ptr(), plan.counts.data_ptr(), st)
             y_all = buf.y.view(-1, d)
             g.gate_up(self.x_all, self.local, plan, buf.act.view(-1, self.local.width), self.rows)
             g.down(buf.act.view(-1, self.local.width), self.local, plan, y_all, self.rows)
