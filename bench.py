@@ -271,13 +271,15 @@ def bench_e2e(torch, runners, shape, rows: int, steps: int, warmup: int):
 
     x_host = synthetic.activations(shape, rows, "cpu").pin_memory()
     out_host = torch.empty((rows, shape.dims), dtype=torch.bfloat16).pin_memory()
+    for r in runners:
+        r.bind_host(x_host, out_host)                           # the copies become nodes of the step's graph
     for i in range(warmup):
-        out_host.copy_(runners[i % len(runners)](x_host), non_blocking=True)
+        runners[i % len(runners)].replay_host()
         torch.cuda.synchronize()
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     a.record()
     for i in range(steps):
-        out_host.copy_(runners[i % len(runners)](x_host), non_blocking=True)
+        runners[i % len(runners)].replay_host()
         torch.cuda.current_stream().synchronize()               # the caller reads the result before the next step
     b.record()
     torch.cuda.synchronize()
@@ -357,11 +359,24 @@ def bench_ep(torch, dist, args, shape, dev, rank: int, world: int):
     out_host = torch.empty((rows, shape.dims), dtype=torch.bfloat16).pin_memory()
     torch.cuda.synchronize()
     dist.barrier()
+    host_graphs = []
+    for step, inp, layer in zip(steps, inputs, copies):    # the same step with its host copies as graph nodes
+        side.wait_stream(torch.cuda.current_stream())
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=side):
+            inp.copy_(x_host, non_blocking=True)
+            step()
+            out_host.copy_(layer.out, non_blocking=True)
+        host_graphs.append(g)
+    torch.cuda.synchronize()
+    dist.barrier()
+    for i in range(min(args.warmup, len(host_graphs))):
+        host_graphs[i].replay()
+    torch.cuda.synchronize()
+    dist.barrier()
     a.record()
     for i in range(args.steps):
-        inputs[i % len(inputs)].copy_(x_host, non_blocking=True)
-        graphs[i % len(graphs)].replay()
-        out_host.copy_(copies[i % len(copies)].out, non_blocking=True)
+        host_graphs[i % len(host_graphs)].replay()
         torch.cuda.current_stream().synchronize()
     b.record()
     torch.cuda.synchronize()

@@ -200,3 +200,28 @@ class Runner:
     def __call__(self, x: torch.Tensor) -> torch.Tensor:
         self.x.copy_(x, non_blocking=True)
         return self.replay()
+
+    def bind_host(self, x_host: torch.Tensor, out_host: torch.Tensor) -> None:
+        """Capture the step together with its copies from ``x_host`` and to ``out_host`` (both pinned host memory, the
+        caller's staging buffers): ``replay_host()`` is then one graph launch a step, copies included."""
+
+        want = (self.rows, self.layer.experts.dims)
+        for t in (x_host, out_host):
+            if t.device.type != "cpu" or not t.is_pinned() or tuple(t.shape) != want or t.dtype != torch.bfloat16:
+                raise ValueError(f"host buffers must be pinned bf16 tensors of shape {want}")
+        self.x_host, self.out_host = x_host, out_host
+        device = self.x.device
+        with torch.cuda.device(device):
+            self._stream.wait_stream(torch.cuda.current_stream(device))
+            self.host_graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self.host_graph, stream=self._stream):
+                self.x.copy_(x_host, non_blocking=True)
+                self._step()
+                out_host.copy_(self.out, non_blocking=True)
+
+    def replay_host(self) -> torch.Tensor:
+        """Tokens from the bound host buffer through the layer into the bound host buffer (asynchronous: synchronise
+        the current stream before reading it)."""
+
+        self.host_graph.replay()
+        return self.out_host
