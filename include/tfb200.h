@@ -93,9 +93,18 @@ int tfb_peer_gather(void* const* windows, int rank, int world, int nseg, const i
 /* tfb_combine_window with fp32 output, each token's row stored into its home rank's result buffer, slot `rank`. */
 int tfb_combine_push(const float* y, const float* wts, const int32_t* pick, int lo, int n, void* const* windows,
                      int64_t p_offset, int rank, int rows_local, int T, int slots, int D, void* step, void* stream);
-/* out[rows_local, D] (bf16) = the ranks' partial sums added in rank order, rounded once. */
+/* The same hand-over for partial sums another kernel formed: row r of partial [T, D] fp32 goes to its home rank. */
+int tfb_peer_push(const float* partial, void* const* windows, int64_t p_offset, int rank, int rows_local, int T, int D,
+                  void* step, void* stream);
+/* Selections as the owner of experts [lo, lo + n) sees them: its ids renumbered from 0 with their weights, every other
+ * slot as id n (skipped by the expert kernels) with weight 0. */
+int tfb_window_picks(const int32_t* pick, const float* wts, int lo, int n, int32_t* pick_out, float* wts_out,
+                     int count, void* stream);
+/* out[rows_local, D] (bf16, or fp32 with out_f32) = the ranks' partial sums added in rank order, then, when given,
+ * extra_w[j * extra_w_stride] * extra[j, :] (the replicated shared expert of the rank's own rows); rounded once. */
 int tfb_peer_sum(void* const* windows, int rank, int64_t p_offset, int world, int rows_local, int D, void* out,
-                 const void* step, void* stream);
+                 int out_f32, const float* extra, const float* extra_w, int extra_w_stride, const void* step,
+                 void* stream);
 
 /* out[T, D] = sum over slots, in slot order, of wts[T, slots] * y[T, slots, D] (fp32 fma chain from 0), rounded once.
  * y is fp32 (y_bf16 = 0) or bf16; out is bf16 (out_f32 = 0) or fp32.

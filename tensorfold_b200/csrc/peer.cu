@@ -133,10 +133,43 @@ combine_push_kernel(const float* __restrict__ y, const float* __restrict__ wts, 
   pdl_launch_dependents();
 }
 
-// Results barrier, then out [rows, D] bf16 = the ranks' rows added in rank order.
+// A rank's partial sums that some other kernel formed (partial [T, D] fp32, row r = token r of the gathered order):
+// each row goes to its home rank's result buffer, slot `rank`.  Counts the step, like combine_push_kernel.
+__global__ void __launch_bounds__(256)
+peer_push_kernel(const float4* __restrict__ partial, uint8_t* const* __restrict__ windows, int64_t p_offset, int rank,
+                 int rows, int D, uint32_t* __restrict__ step) {
+  const int r = blockIdx.x;
+  pdl_wait();
+  if (blockIdx.x == 0 && threadIdx.x == 0) step[0] += 1;
+  const int home = r / rows, j = r - home * rows;
+  float4* dst = reinterpret_cast<float4*>(windows[home] + p_offset) + ((size_t)rank * rows + j) * (D / 4);
+  for (int i = threadIdx.x; i < D / 4; i += 256) dst[i] = partial[(size_t)r * (D / 4) + i];
+  pdl_launch_dependents();
+}
+
+// Selections as one rank sees them: ids of its experts [lo, lo + n) renumbered from 0 with their weights, every other
+// slot as id n (which the expert kernels skip) with weight 0.
+__global__ void __launch_bounds__(256)
+window_picks_kernel(const int* __restrict__ pick, const float* __restrict__ wts, int lo, int n,
+                    int* __restrict__ pick_out, float* __restrict__ wts_out, int count) {
+  pdl_wait();
+  const int i = blockIdx.x * 256 + threadIdx.x;
+  if (i < count) {
+    const int e = pick[i] - lo;
+    const bool mine = e >= 0 && e < n;
+    pick_out[i] = mine ? e : n;
+    wts_out[i] = mine ? wts[i] : 0.f;
+  }
+  pdl_launch_dependents();
+}
+
+// Results barrier, then out [rows, D] = the ranks' rows added in rank order, then (when given) extra_w[j] * extra[j, :]
+// (the replicated shared expert of the rank's own rows), rounded once to bf16 or stored as fp32.
+template <typename TO>
 __global__ void __launch_bounds__(256)
 peer_sum_kernel(uint8_t* const* __restrict__ windows, int rank, int64_t p_offset, int world, int rows, int D,
-                __nv_bfloat16* __restrict__ out, const uint32_t* __restrict__ step) {
+                TO* __restrict__ out, const float* __restrict__ extra, const float* __restrict__ extra_w,
+                int extra_w_stride, const uint32_t* __restrict__ step) {
   pdl_wait();
   peer_barrier(windows, rank, world, 1, step[0]);
   const float* part = reinterpret_cast<const float*>(windows[rank] + p_offset);
@@ -150,11 +183,23 @@ peer_sum_kernel(uint8_t* const* __restrict__ windows, int rank, int64_t p_offset
       acc.z += __uint_as_float(u.z);
       acc.w += __uint_as_float(u.w);
     }
-    __nv_bfloat162 a = __floats2bfloat162_rn(acc.x, acc.y), b = __floats2bfloat162_rn(acc.z, acc.w);
-    uint2 o;
-    o.x = *reinterpret_cast<uint32_t*>(&a);
-    o.y = *reinterpret_cast<uint32_t*>(&b);
-    reinterpret_cast<uint2*>(out)[i] = o;
+    if (extra != nullptr) {
+      const float w = extra_w[(i * 4 / D) * extra_w_stride];
+      const float4 f = reinterpret_cast<const float4*>(extra)[i];
+      acc.x = fmaf(w, f.x, acc.x);
+      acc.y = fmaf(w, f.y, acc.y);
+      acc.z = fmaf(w, f.z, acc.z);
+      acc.w = fmaf(w, f.w, acc.w);
+    }
+    if constexpr (sizeof(TO) == 4) {
+      reinterpret_cast<float4*>(out)[i] = acc;
+    } else {
+      __nv_bfloat162 a = __floats2bfloat162_rn(acc.x, acc.y), b = __floats2bfloat162_rn(acc.z, acc.w);
+      uint2 o;
+      o.x = *reinterpret_cast<uint32_t*>(&a);
+      o.y = *reinterpret_cast<uint32_t*>(&b);
+      reinterpret_cast<uint2*>(out)[i] = o;
+    }
   }
   pdl_launch_dependents();
 }
@@ -214,15 +259,46 @@ extern "C" int tfb_combine_push(const float* y, const float* wts, const int32_t*
                     "combine_push");
 }
 
+extern "C" int tfb_peer_push(const float* partial, void* const* windows, int64_t p_offset, int rank, int rows_local,
+                             int T, int D, void* step, void* stream) {
+  TFB_REQUIRE(partial && windows && step, "peer_push: null pointer");
+  TFB_REQUIRE(D > 0 && D % 4 == 0 && rows_local >= 1 && T >= rows_local && T % rows_local == 0 && aligned16(partial),
+              "peer_push: D %% 4 == 0, T a multiple of the rows a rank, 16-byte aligned rows");
+  TFB_REQUIRE(p_offset % 16 == 0, "peer_push: 16-byte units");
+  return check_cuda(launch(peer_push_kernel, dim3(T), dim3(256), 0, static_cast<cudaStream_t>(stream),
+                           reinterpret_cast<const float4*>(partial), reinterpret_cast<uint8_t* const*>(windows),
+                           p_offset, rank, rows_local, D, static_cast<uint32_t*>(step)),
+                    "peer_push");
+}
+
+extern "C" int tfb_window_picks(const int32_t* pick, const float* wts, int lo, int n, int32_t* pick_out,
+                                float* wts_out, int count, void* stream) {
+  TFB_REQUIRE(pick && wts && pick_out && wts_out, "window_picks: null pointer");
+  TFB_REQUIRE(n >= 1 && lo >= 0 && count >= 0, "window_picks: bad sizes");
+  if (count == 0) return TFB_OK;
+  return check_cuda(launch(window_picks_kernel, dim3((count + 255) / 256), dim3(256), 0,
+                           static_cast<cudaStream_t>(stream), pick, wts, lo, n, pick_out, wts_out, count),
+                    "window_picks");
+}
+
 extern "C" int tfb_peer_sum(void* const* windows, int rank, int64_t p_offset, int world, int rows_local, int D,
-                            void* out, const void* step, void* stream) {
+                            void* out, int out_f32, const float* extra, const float* extra_w, int extra_w_stride,
+                            const void* step, void* stream) {
   TFB_REQUIRE(windows && out && step, "peer_sum: null pointer");
   TFB_REQUIRE(world >= 1 && world <= 32 && rank >= 0 && rank < world, "peer_sum: rank %d of %d", rank, world);
   TFB_REQUIRE(D > 0 && D % 4 == 0 && rows_local >= 1, "peer_sum: bad sizes");
+  TFB_REQUIRE((extra == nullptr) == (extra_w == nullptr), "peer_sum: extra and its weights come together");
+  TFB_REQUIRE(extra == nullptr || (aligned16(extra) && extra_w_stride >= 1), "peer_sum: extra rows 16-byte aligned");
   const int64_t n4 = (int64_t)rows_local * D / 4;
   const int grid = (int)((n4 + 255) / 256 < 592 ? (n4 + 255) / 256 : 592);
-  return check_cuda(launch(peer_sum_kernel, dim3(grid), dim3(256), 0, static_cast<cudaStream_t>(stream),
-                           reinterpret_cast<uint8_t* const*>(windows), rank, p_offset, world, rows_local, D,
-                           static_cast<__nv_bfloat16*>(out), static_cast<const uint32_t*>(step)),
+  auto st = static_cast<cudaStream_t>(stream);
+  auto wins = reinterpret_cast<uint8_t* const*>(windows);
+  auto stp = static_cast<const uint32_t*>(step);
+  if (out_f32)
+    return check_cuda(launch(peer_sum_kernel<float>, dim3(grid), dim3(256), 0, st, wins, rank, p_offset, world,
+                             rows_local, D, static_cast<float*>(out), extra, extra_w, extra_w_stride, stp),
+                      "peer_sum");
+  return check_cuda(launch(peer_sum_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, st, wins, rank, p_offset, world,
+                           rows_local, D, static_cast<__nv_bfloat16*>(out), extra, extra_w, extra_w_stride, stp),
                     "peer_sum");
 }

@@ -239,108 +239,204 @@ class GatheredExpertParallel:
         return m.combine(self.y_mine.view(self.rows_local, k, -1), wts, self.out)
 
 
-class PeerExpertParallel:
-    """The expert-parallel step with both exchanges done by this library's own kernels over NVLink peer memory
-    (``csrc/peer.cu``): no collective-library call on the step.  Every rank routes ITS rows (router and selection, as on
-    one GPU) with the selections written into its window beside the rows; a flag barrier; every rank pulls all ranks'
-    rows and selections, plans the pairs of its experts and runs them; the per-token partial sums of a rank's experts
-    (slot order, weights applied) are stored straight into the home rank's window by the kernel that forms them; a
-    second flag barrier; the home rank adds the ranks' rows in rank order and rounds once.  Values equal
-    ``GatheredExpertParallel(reduce="tokens")`` up to fp32 summation order across ranks (here fixed: rank 0, 1, ...).
+class PeerWindow:
+    """One rank's window of an expert-parallel layer over NVLink peer memory, and the steps every such layer shares
+    (``csrc/peer.cu``): routing of the rank's own rows into the window, the pull of all ranks' rows and selections
+    after the tokens barrier, and the sum of the ranks' partial results after the results barrier.
 
     The windows are one ``torch.distributed._symmetric_memory`` allocation a rank (plain peer mappings; multicast is
     not used).  Waits are bounded: a rank that never arrives shows up as a non-zero ``_lib.kernel_status()``."""
 
-    def __init__(self, router_rows: torch.Tensor, local_experts, experts: int, top_k: int, rows_local: int,
+    def __init__(self, router_rows: torch.Tensor, experts: int, top_k: int, rows_local: int, dims: int, shared: bool,
                  group=None) -> None:
         import ctypes
         import os
 
-        from . import experts as grouped
-        from . import moe
-
         os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         import torch.distributed._symmetric_memory as symm
 
-        self.moe, self.grouped = moe, grouped
         self.group = group if group is not None else dist.group.WORLD
         self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
         if experts % self.world:
             raise ValueError(f"{experts} experts do not shard evenly over {self.world} ranks")
-        self.per_rank, self.experts, self.top_k = experts // self.world, experts, top_k
-        self.router_rows, self.local, self.rows_local = router_rows, local_experts, rows_local
-        dev, d, k = router_rows.device, local_experts.dims, top_k
-        rows = rows_local * self.world
-        self.rows = rows
+        if router_rows.shape[0] != experts + (1 if shared else 0):
+            raise ValueError("router rows: one an expert, plus the shared expert's gate row when there is one")
+        self.per_rank, self.experts, self.top_k, self.shared = experts // self.world, experts, top_k, shared
+        self.lo = self.rank * self.per_rank
+        self.router_rows, self.rows_local, self.dims = router_rows, rows_local, dims
+        self.slots = slots = top_k + (1 if shared else 0)
+        dev, d = router_rows.device, dims
+        self.device = dev
+        self.rows = rows = rows_local * self.world
 
         def up(n: int) -> int:
             return (n + 255) // 256 * 256
 
-        x_bytes, s_bytes = rows_local * d * 2, rows_local * k * 4
+        x_bytes, s_bytes = rows_local * d * 2, rows_local * slots * 4
         if x_bytes % 16 or s_bytes % 16 or 2 * self.world * 4 > 256:
-            raise ValueError("rows_local * dims and rows_local * top_k must be multiples of 8, and at most 32 ranks")
+            raise ValueError("rows_local * dims must be a multiple of 8, rows_local * slots of 4, and at most 32 ranks")
         self.x_offset = 256
         self.pick_offset = self.x_offset + up(x_bytes)
         self.wts_offset = self.pick_offset + up(s_bytes)
         self.p_offset = self.wts_offset + up(s_bytes)
         self.x_bytes = x_bytes
-        total = self.p_offset + rows * d * 4
-        self.window = symm.empty(total, dtype=torch.uint8, device=dev)
-        self.window.zero_()
+        self.window = win = symm.empty(self.p_offset + rows * d * 4, dtype=torch.uint8, device=dev)
+        win.zero_()
         torch.cuda.synchronize(dev)
-        self.handle = symm.rendezvous(self.window, self.group)
+        self.handle = symm.rendezvous(win, self.group)
         self.windows = torch.tensor(list(self.handle.buffer_ptrs), dtype=torch.int64, device=dev)
         self.step = torch.zeros(1, dtype=torch.int32, device=dev)
-        win = self.window
-        # this rank's rows inside its window: a caller may write them here and call forward() without an argument
+        # this rank's rows inside its window: a caller may write them here and run the layer without an argument
         self.tokens = win[self.x_offset:self.x_offset + x_bytes].view(torch.bfloat16).view(rows_local, d)
-        self.pick_mine = win[self.pick_offset:self.pick_offset + s_bytes].view(torch.int32).view(rows_local, k)
-        self.wts_mine = win[self.wts_offset:self.wts_offset + s_bytes].view(torch.float32).view(rows_local, k)
+        self.pick_mine = win[self.pick_offset:self.pick_offset + s_bytes].view(torch.int32).view(rows_local, slots)
+        self.wts_mine = win[self.wts_offset:self.wts_offset + s_bytes].view(torch.float32).view(rows_local, slots)
         dist.barrier(self.group)                                  # every window is zeroed before any flag is written
-
-        class _Cfg:
-            num_experts_per_tok, num_experts = top_k, experts
-            moe_intermediate_size, hidden_size = local_experts.width, d
-
-        self.logits = torch.zeros((rows_local, experts), dtype=torch.float32, device=dev)
+        self.logits = torch.zeros((rows_local, router_rows.shape[0]), dtype=torch.float32, device=dev)
         self.x_all = torch.zeros((rows, d), dtype=torch.bfloat16, device=dev)
-        self.buf = moe.MoEBuffers(rows, _Cfg, dev, shared=False)   # pick / wts of all rows, act, y
+        self.pick_all = torch.zeros((rows, slots), dtype=torch.int32, device=dev)
+        self.wts_all = torch.zeros((rows, slots), dtype=torch.float32, device=dev)
         self._seg = (
             (ctypes.c_int64 * 3)(self.x_offset, self.pick_offset, self.wts_offset),
             (ctypes.c_int64 * 3)(x_bytes, s_bytes, s_bytes),
-            (ctypes.c_void_p * 3)(self.x_all.data_ptr(), self.buf.pick.data_ptr(), self.buf.wts.data_ptr()),
+            (ctypes.c_void_p * 3)(self.x_all.data_ptr(), self.pick_all.data_ptr(), self.wts_all.data_ptr()),
         )
-        wide = rows * k >= 12 * experts
-        self.plan = grouped.Plan(rows, k, self.per_rank, dev, decode_tile=grouped.WIDE_TILE if wide else grouped.TILE)
+
+    def _stream(self) -> int:
+        return torch.cuda.current_stream(self.device).cuda_stream
+
+    def route_own(self, x_local: torch.Tensor | None) -> None:
+        """Stage ``x_local`` (unless the caller wrote ``tokens`` itself), then router and selection of the own rows."""
+
+        from . import moe
+
+        st = self._stream()
+        if x_local is not None:
+            x_local = x_local.contiguous()
+            _lib.call("tfb_peer_stage", x_local.data_ptr(), self.window.data_ptr(), self.x_offset, self.x_bytes, st)
+        moe.router(self.tokens, self.router_rows, self.logits)
+        _lib.call("tfb_select_rows", self.logits.data_ptr(), self.logits.shape[1], self.pick_mine.data_ptr(),
+                  self.wts_mine.data_ptr(), self.rows_local, self.experts, self.top_k, 1 if self.shared else 0, st)
+
+    def gather(self) -> None:
+        """Tokens barrier, then all ranks' rows and selections into ``x_all``, ``pick_all``, ``wts_all``."""
+
+        _lib.call("tfb_peer_gather", self.windows.data_ptr(), self.rank, self.world, 3, self._seg[0], self._seg[1],
+                  self._seg[2], self.step.data_ptr(), self._stream())
+
+    def push(self, partial: torch.Tensor) -> None:
+        """partial [rows, D] fp32 (this rank's experts' share of every token) to the tokens' home ranks."""
+
+        _lib.call("tfb_peer_push", partial.data_ptr(), self.windows.data_ptr(), self.p_offset, self.rank,
+                  self.rows_local, self.rows, self.dims, self.step.data_ptr(), self._stream())
+
+    def sum(self, out: torch.Tensor, extra: torch.Tensor | None = None) -> None:
+        """Results barrier, then out [rows_local, D] (bf16 or fp32) = the ranks' shares in rank order (+ the shared
+        expert's rows ``extra`` weighted by the own rows' last slot)."""
+
+        ew = self.wts_mine.data_ptr() + 4 * self.top_k if extra is not None else 0
+        _lib.call("tfb_peer_sum", self.windows.data_ptr(), self.rank, self.p_offset, self.world, self.rows_local,
+                  self.dims, out.data_ptr(), 1 if out.dtype == torch.float32 else 0,
+                  extra.data_ptr() if extra is not None else 0, ew, self.slots, self.step.data_ptr(), self._stream())
+
+
+class PeerExpertParallel:
+    """The expert-parallel step of the affine 4-bit experts with both exchanges done by this library's own kernels over
+    NVLink peer memory (``PeerWindow``): no collective-library call on the step.  Every rank routes ITS rows (router
+    and selection, as on one GPU) with the selections written into its window beside the rows; a flag barrier; every
+    rank pulls all ranks' rows and selections, plans the pairs of its experts and runs them; the per-token partial sums
+    of a rank's experts (slot order, weights applied) are stored straight into the home rank's window by the kernel that
+    forms them; a second flag barrier; the home rank adds the ranks' rows in rank order and rounds once.  A shared
+    expert (``shared_experts``: an ``Experts`` of one expert, replicated; the router's last row is its gate) runs on
+    the rank's own rows with no exchange and joins the final sum.  Values equal
+    ``GatheredExpertParallel(reduce="tokens")`` up to fp32 summation order across ranks (here fixed: rank 0, 1, ...)."""
+
+    def __init__(self, router_rows: torch.Tensor, local_experts, experts: int, top_k: int, rows_local: int,
+                 group=None, shared_experts=None) -> None:
+        from . import experts as grouped
+        from . import moe
+
+        self.moe, self.grouped = moe, grouped
+        shared = shared_experts is not None
+        self.win = w = PeerWindow(router_rows, experts, top_k, rows_local, local_experts.dims, shared, group)
+        self.local, self.shared_ex, self.rows_local, self.top_k = local_experts, shared_experts, rows_local, top_k
+        self.world, self.rank, self.rows, self.tokens = w.world, w.rank, w.rows, w.tokens
+        dev, d, rows, slots = w.device, w.dims, w.rows, w.slots
+        self.act = torch.zeros((rows * slots, local_experts.width), dtype=torch.bfloat16, device=dev)
+        self.y = torch.zeros((rows * slots, d), dtype=torch.float32, device=dev)
+        wide = rows * top_k >= 12 * experts
+        self.plan = grouped.Plan(rows, slots, w.per_rank, dev,
+                                 decode_tile=grouped.WIDE_TILE if wide else grouped.TILE)
         self.out = torch.zeros((rows_local, d), dtype=torch.bfloat16, device=dev)
         self.launches = 8                                         # + 1 when forward() is given rows to stage
+        if shared:
+            if shared_experts.count != 1 or shared_experts.dims != d:
+                raise ValueError("shared_experts holds the one replicated expert of the layer's width")
+            # every own row is one pair of expert 0: the plan never changes
+            wide_s = rows_local >= 12
+            self.plan_s = grouped.Plan(rows_local, 1, 1, dev, decode_tile=grouped.WIDE_TILE if wide_s else grouped.TILE)
+            grouped.route(torch.zeros((rows_local, 1), dtype=torch.int32, device=dev), self.plan_s)
+            self.act_s = torch.zeros((rows_local, shared_experts.width), dtype=torch.bfloat16, device=dev)
+            self.y_s = torch.zeros((rows_local, d), dtype=torch.float32, device=dev)
+            self.launches += 2
+            torch.cuda.synchronize(dev)
 
     def forward(self, x_local: torch.Tensor | None = None) -> torch.Tensor:
         """``x_local`` [rows_local, D] bf16, or None when the caller has written its rows into ``self.tokens``."""
 
-        m, g, buf, k, d = self.moe, self.grouped, self.buf, self.top_k, self.local.dims
-        dev = self.x_all.device
-        st = torch.cuda.current_stream(dev).cuda_stream
-        win, wins, step = self.window.data_ptr(), self.windows.data_ptr(), self.step.data_ptr()
-        lo = self.rank * self.per_rank
+        g, w, k, d = self.grouped, self.win, self.top_k, self.win.dims
         plan = self.plan
         plan.tile = plan.decode_tile
-        with torch.cuda.device(dev):
-            if x_local is not None:
-                x_local = x_local.contiguous()
-                _lib.call("tfb_peer_stage", x_local.data_ptr(), win, self.x_offset, self.x_bytes, st)
-            m.router(self.tokens, self.router_rows, self.logits)
-            _lib.call("tfb_select_rows", self.logits.data_ptr(), self.logits.shape[1], self.pick_mine.data_ptr(),
-                      self.wts_mine.data_ptr(), self.rows_local, self.experts, k, 0, st)
-            _lib.call("tfb_peer_gather", wins, self.rank, self.world, 3, self._seg[0], self._seg[1], self._seg[2],
-                      step, st)
-            _lib.call("tfb_plan_window", buf.pick.data_ptr(), self.rows * k, lo, self.per_rank, plan.tile,
+        with torch.cuda.device(w.device):
+            st = w._stream()
+            w.route_own(x_local)
+            if self.shared_ex is not None:                         # own rows only; runs while the peers arrive
+                g.gate_up(w.tokens, self.shared_ex, self.plan_s, self.act_s, self.rows_local)
+                g.down(self.act_s, self.shared_ex, self.plan_s, self.y_s, self.rows_local)
+            w.gather()
+            _lib.call("tfb_plan_window", w.pick_all.data_ptr(), self.rows * w.slots, w.lo, w.per_rank, plan.tile,
                       plan.members.data_ptr(), plan.items.data_ptr(), plan.counts.data_ptr(), st)
-            y_all = buf.y.view(-1, d)
-            g.gate_up(self.x_all, self.local, plan, buf.act.view(-1, self.local.width), self.rows)
-            g.down(buf.act.view(-1, self.local.width), self.local, plan, y_all, self.rows)
-            _lib.call("tfb_combine_push", buf.y.data_ptr(), buf.wts.data_ptr(), buf.pick.data_ptr(), lo, self.per_rank,
-                      wins, self.p_offset, self.rank, self.rows_local, self.rows, k, d, step, st)
-            _lib.call("tfb_peer_sum", wins, self.rank, self.p_offset, self.world, self.rows_local, d,
-                      self.out.data_ptr(), step, st)
+            g.gate_up(w.x_all, self.local, plan, self.act, self.rows)
+            g.down(self.act, self.local, plan, self.y, self.rows)
+            _lib.call("tfb_combine_push", self.y.data_ptr(), w.wts_all.data_ptr(), w.pick_all.data_ptr(), w.lo,
+                      w.per_rank, w.windows.data_ptr(), w.p_offset, w.rank, self.rows_local, self.rows, w.slots, d,
+                      w.step.data_ptr(), st)
+            w.sum(self.out, self.y_s if self.shared_ex is not None else None)
+        return self.out
+
+
+class PeerExl3ExpertParallel:
+    """The same step for EXL3 routed experts (``exl3.experts.routed`` on the rank's experts): selections are renumbered
+    to the rank's window (other ranks' slots become skipped ids with weight 0), the routed call forms the rank's
+    weighted slot-order share of every token, which is pushed to the home ranks; the sum is fp32 like the one-GPU
+    call's output."""
+
+    def __init__(self, router_rows: torch.Tensor, local_ex, experts: int, top_k: int, rows_local: int, group=None,
+                 limit: float = float("inf")) -> None:
+        from .exl3 import experts as exl3
+
+        self.exl3 = exl3
+        self.win = w = PeerWindow(router_rows, experts, top_k, rows_local, local_ex.dims, False, group)
+        self.local, self.rows_local, self.top_k, self.limit = local_ex, rows_local, top_k, limit
+        self.world, self.rank, self.rows, self.tokens = w.world, w.rank, w.rows, w.tokens
+        dev, d, rows = w.device, w.dims, w.rows
+        self.scratch = exl3.Scratch(local_ex, rows, top_k, device=dev)
+        self.scratch.y.zero_()                                     # skipped slots are read with weight 0: keep them finite
+        self.pick_local = torch.zeros((rows, top_k), dtype=torch.int32, device=dev)
+        self.wts_local = torch.zeros((rows, top_k), dtype=torch.float32, device=dev)
+        self.partial = torch.zeros((rows, d), dtype=torch.float32, device=dev)
+        self.out = torch.zeros((rows_local, d), dtype=torch.float32, device=dev)
+        self.launches = 13
+        torch.cuda.synchronize(dev)
+
+    def forward(self, x_local: torch.Tensor | None = None) -> torch.Tensor:
+        w = self.win
+        with torch.cuda.device(w.device):
+            w.route_own(x_local)
+            w.gather()
+            _lib.call("tfb_window_picks", w.pick_all.data_ptr(), w.wts_all.data_ptr(), w.lo, w.per_rank,
+                      self.pick_local.data_ptr(), self.wts_local.data_ptr(), self.rows * self.top_k, w._stream())
+            self.exl3.routed(w.x_all, self.pick_local, self.wts_local, self.local, self.scratch, self.partial,
+                             self.rows, limit=self.limit)
+            w.push(self.partial)
+            w.sum(self.out)
         return self.out

@@ -108,8 +108,50 @@ def _peer_body(rank, world, port, out):
         graph.replay()
         torch.cuda.synchronize()
         flags.append(bool(torch.equal(peer.out, nccl.forward(x))))
-    flags.append(_lib.kernel_status() == 0)
     del graph
+    torch.cuda.synchronize()
+
+    # a layer with a shared expert: replicated, run on the own rows, joined in the final sum
+    sh = synthetic.SMALL_SHARED
+    gate, up, down = synthetic.affine_layer(sh, dev)
+    router_s = synthetic.router_rows(sh, dev)
+    per = sh.experts // world
+    sl, last = slice(rank * per, (rank + 1) * per), slice(sh.experts, sh.experts + 1)
+
+    def cut(which):
+        return experts.make([tuple(t[which].contiguous() for t in gate), tuple(t[which].contiguous() for t in up)],
+                            tuple(t[which].contiguous() for t in down), 64)
+
+    full_s = moe.Routed(router_s, experts.make([gate, up], down, 64), sh.top_k, shared=True)
+    peer_s = ep.PeerExpertParallel(router_s, cut(sl), sh.experts, sh.top_k, rows, shared_experts=cut(last))
+    for i in range(2):
+        x = synthetic.activations(sh, rows, dev, index=90 + 2 * i + rank)
+        got = peer_s.forward(x).float()
+        want = moe.run(x, full_s).float()
+        flags.append(bool((got - want).norm() / want.norm() < 4e-3))
+
+    # EXL3 routed experts: the rank's share through exl3.routed, fp32 out
+    from tensorfold_b200.exl3 import experts as x3
+
+    eg, eu, ed = synthetic.exl3_layer(shape, dev, 4)
+    ex_full = x3.prepare(eg, eu, ed, x3.CB_3INST, device=dev)
+    ex_mine = x3.prepare(eg[sl], eu[sl], ed[sl], x3.CB_3INST, device=dev)
+    peer_x = ep.PeerExl3ExpertParallel(router, ex_mine, shape.experts, shape.top_k, rows)
+
+    class _Cfg:
+        num_experts_per_tok, num_experts = shape.top_k, shape.experts
+        moe_intermediate_size, hidden_size = shape.width, shape.dims
+
+    buf = moe.MoEBuffers(rows, _Cfg, dev, shared=False)
+    scratch = x3.Scratch(ex_full, rows, shape.top_k, device=dev)
+    for i in range(2):
+        x = synthetic.activations(shape, rows, dev, index=95 + 2 * i + rank)
+        got = peer_x.forward(x).clone()
+        moe.router(x, router, buf.logits)
+        moe.select_rows(buf.logits, buf, shape.top_k, shape.experts)
+        want = x3.routed(x, buf.pick, buf.wts, ex_full, scratch, None, rows)
+        flags.append(bool(torch.isfinite(got).all()) and bool((got - want).norm() / want.norm() < 1e-5))
+    flags.append(_lib.kernel_status() == 0)
     torch.cuda.synchronize()
     out.put((rank, tuple(flags)))
     dist.barrier()
