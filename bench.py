@@ -153,8 +153,10 @@ def run_reference(args) -> None:
     print(json.dumps(line))
 
 
-def workload_config(shape, rows: int, gpus: int) -> dict:
-    return {"workload": f"BASELINE config 2: one MoE layer, {rows}-token decode, hidden {shape.dims}, {shape.experts} "
+def workload_config(shape, rows: int, gpus: int, config: str = "c2") -> dict:
+    what = (f"BASELINE config 4: one MoE layer, {rows * gpus} tokens over the ranks, Zipf-skewed router, one replicated "
+            "shared expert," if config == "c4" else f"BASELINE config 2: one MoE layer, {rows}-token decode,")
+    return {"workload": f"{what} hidden {shape.dims}, {shape.experts} "
                         f"experts x FFN {shape.width}, top-{shape.top_k}, MLX affine 4-bit g64 (fp16 scales)",
             "rows_per_gpu": rows, "l2": "two 340 MB weight copies alternate (inputs larger than the 126 MB L2)",
             "parallelism": f"ep{gpus}" if gpus > 1 else "single"}
@@ -289,6 +291,18 @@ def bench_e2e(torch, runners, shape, rows: int, steps: int, warmup: int):
             "d2h_bytes_per_step": nbytes}
 
 
+def ep_rows(args, shape, world: int) -> int:
+    """Rows a rank: config 2 keeps `--rows` a GPU (weak scaling); config 4 splits its 256 tokens over the ranks."""
+
+    return 256 // world if args.config == "c4" else args.rows
+
+
+def ep_copies(args, world: int) -> int:
+    """Independent weight copies a rank rotates so that a step's weights never sit in the 126 MB L2."""
+
+    return 2 if args.config == "c4" else 2 * world          # a config-4 slice is 5.4 GB / world
+
+
 COLLECTIVE = {
     "tokens": "NCCL all-gather of the tokens, reduce-scatter of fp32 per-token partial sums",
     "rows": "NCCL all-gather of the tokens, reduce-scatter of fp32 per-pair rows (exact)",
@@ -304,17 +318,23 @@ def bench_ep(torch, dist, args, shape, dev, rank: int, world: int):
 
     from tensorfold_b200 import ep, experts, moe, synthetic
 
-    rows, per = args.rows, shape.experts // world
+    rows, per = ep_rows(args, shape, world), shape.experts // world
     router = synthetic.router_rows(shape, dev)
+    bias = synthetic.zipf_bias(shape, 1.1, dev) if args.config == "c4" else None
     copies, graphs = [], []
-    for copy in range(2 * world):
+    for copy in range(ep_copies(args, world)):
         gate, up, down = synthetic.affine_layer(shape, dev, torch.float16 if args.scales == "fp16" else torch.bfloat16,
                                                 copy=copy)
-        sl = slice(rank * per, (rank + 1) * per)
-        local = experts.make([tuple(t[sl].contiguous() for t in gate), tuple(t[sl].contiguous() for t in up)],
-                             tuple(t[sl].contiguous() for t in down), 64)
+
+        def cut(which):
+            return experts.make([tuple(t[which].contiguous() for t in gate), tuple(t[which].contiguous() for t in up)],
+                                tuple(t[which].contiguous() for t in down), 64)
+
+        local = cut(slice(rank * per, (rank + 1) * per))
         if args.ep_reduce == "peer":
-            copies.append(ep.PeerExpertParallel(router, local, shape.experts, shape.top_k, rows))
+            shared = cut(slice(shape.experts, shape.experts + 1)) if shape.shared else None
+            copies.append(ep.PeerExpertParallel(router, local, shape.experts, shape.top_k, rows,
+                                                shared_experts=shared, logit_bias=bias))
         else:
             copies.append(ep.GatheredExpertParallel(router, local, shape.experts, shape.top_k, rows,
                                                     reduce=args.ep_reduce))
@@ -382,7 +402,19 @@ def bench_ep(torch, dist, args, shape, dev, rank: int, world: int):
     torch.cuda.synchronize()
     dist.barrier()
     e2e_ms = a.elapsed_time(b) / args.steps
-    return ms, e2e_ms, copies[0].launches   # router, select, plan, gate/up, down, combine
+    # this rank's algorithmic bytes a step: its touched experts' packed weights, the router rows, its tokens in and out
+    layer = copies[0]
+    nbytes = router.numel() * 2 + 2 * rows * shape.dims * 2
+    if args.ep_reduce == "peer":
+        w = layer.win
+        mine = w.pick_all[:, :shape.top_k].reshape(-1)
+        mine = mine[(mine >= w.lo) & (mine < w.lo + w.per_rank)]
+        nbytes += int(torch.unique(mine).numel()) * local.bytes_per_expert()
+        if shape.shared:
+            nbytes += local.bytes_per_expert()
+    else:
+        nbytes += per * local.bytes_per_expert()
+    return ms, e2e_ms, layer.launches, nbytes
 
 
 def run_ours(args) -> None:
@@ -405,7 +437,11 @@ def run_ours(args) -> None:
     if args.exl3_only:
         print(json.dumps({"sweep": bench_exl3(torch, (1, 64), args.steps, args.warmup, hbm)}))
         return
-    shape, rows = synthetic.C2, args.rows
+    shape, rows = (synthetic.C4 if args.config == "c4" else synthetic.C2), args.rows
+    if args.config == "c4":
+        if world == 1 or args.ep_reduce != "peer":
+            raise SystemExit("--config c4 is the expert-parallel line: run it under torchrun with the peer-memory form")
+        rows = ep_rows(args, shape, world)
     layers = []
     for copy in range(2 if world == 1 else 0):
         gate, up, down = synthetic.affine_layer(shape, dev, torch.float16 if args.scales == "fp16" else torch.bfloat16,
@@ -420,7 +456,7 @@ def run_ours(args) -> None:
             raise SystemExit(f"{shape.experts} experts do not shard over {world} ranks")
         del layers
         with ClockSampler(local) as clocks:
-            ms, e2e_ms, launches = bench_ep(torch, dist, args, shape, dev, rank, world)
+            ms, e2e_ms, launches, rank_bytes = bench_ep(torch, dist, args, shape, dev, rank, world)
         t = torch.tensor([ms, e2e_ms], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms, e2e_ms = t.tolist()
@@ -431,20 +467,22 @@ def run_ours(args) -> None:
             nbytes = rows * shape.dims * 2 * world
             line = {"metric": METRIC, "value": world * rows / (ms * 1e-3), "unit": UNIT, "n_gpus": world,
                     "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
-                    "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-                    "config": {**workload_config(shape, rows, world),
-                               "l2": f"each rank rotates {2 * world} copies of its {shape.experts // world}-expert slice "
-                                     "(inputs larger than the 126 MB L2)",
+                    "scaling": "strong" if args.config == "c4" else "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+                    "config": {**workload_config(shape, rows, world, args.config),
+                               "l2": f"each rank rotates {ep_copies(args, world)} copies of its "
+                                     f"{shape.experts // world}-expert slice (inputs larger than the 126 MB L2)",
                                "collective": COLLECTIVE[args.ep_reduce] + "; the step is one CUDA graph"},
                     "clocks": clocks.summary(),
                     "e2e": {"value": world * rows / (e2e_ms * 1e-3), "unit": UNIT, "ms_per_step": e2e_ms,
                             "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": nbytes},
                     "gpu_launches": launches * args.steps,
-                    "roofline": {"bound": "hbm", "kernel": "decode_kernel (gate/up) inside the expert-parallel step",
-                                 "achieved": None, "peak": hbm, "unit": "GB/s", "frac": None,
-                                 "peak_source": f"of {which}", "traffic": None,
-                                 "note": "per-kernel roofline is measured at 1 GPU; the multi-GPU step is bounded by "
-                                         "the two collectives"},
+                    "roofline": {"bound": "hbm", "kernel": "the whole expert-parallel step on one GPU (rank 0)",
+                                 "achieved": rank_bytes / (ms * 1e-3) / 1e9, "peak": hbm, "unit": "GB/s",
+                                 "frac": rank_bytes / (ms * 1e-3) / 1e9 / hbm, "peak_source": f"of {which}",
+                                 "traffic": None, "bytes_per_step": rank_bytes,
+                                 "note": "algorithmic bytes of rank 0's step (its touched experts' packed weights, "
+                                         "router rows, tokens in and out) over the step time; the per-kernel roofline "
+                                         "with ncu traffic is the 1-GPU line's"},
                     "cpu_baseline": None}
             print(json.dumps(line))
         dist.barrier()
@@ -511,6 +549,9 @@ def main() -> None:
     ap.add_argument("--ep-reduce", default="peer", choices=["tokens", "rows", "peer"],
                     help="multi-GPU exchanges: own kernels over NVLink peer memory (default), or NCCL with per-token "
                          "partial sums / exact per-pair rows")
+    ap.add_argument("--config", default="c2", choices=["c2", "c4"],
+                    help="c2: the headline layer (default); c4: the 256-expert layer with a shared expert and skewed "
+                         "routing, 256 tokens split over the ranks (multi-GPU only)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-sweep", action="store_true", help="skip the 1-token and 2048-token lines")
     args = ap.parse_args()

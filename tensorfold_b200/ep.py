@@ -248,7 +248,7 @@ class PeerWindow:
     not used).  Waits are bounded: a rank that never arrives shows up as a non-zero ``_lib.kernel_status()``."""
 
     def __init__(self, router_rows: torch.Tensor, experts: int, top_k: int, rows_local: int, dims: int, shared: bool,
-                 group=None) -> None:
+                 group=None, logit_bias: torch.Tensor | None = None) -> None:
         import ctypes
         import os
 
@@ -264,6 +264,7 @@ class PeerWindow:
         self.per_rank, self.experts, self.top_k, self.shared = experts // self.world, experts, top_k, shared
         self.lo = self.rank * self.per_rank
         self.router_rows, self.rows_local, self.dims = router_rows, rows_local, dims
+        self.logit_bias = logit_bias                              # [experts] fp32 added to the routed logits, or None
         self.slots = slots = top_k + (1 if shared else 0)
         dev, d = router_rows.device, dims
         self.device = dev
@@ -314,6 +315,8 @@ class PeerWindow:
             x_local = x_local.contiguous()
             _lib.call("tfb_peer_stage", x_local.data_ptr(), self.window.data_ptr(), self.x_offset, self.x_bytes, st)
         moe.router(self.tokens, self.router_rows, self.logits)
+        if self.logit_bias is not None:
+            self.logits[:, :self.experts].add_(self.logit_bias)
         _lib.call("tfb_select_rows", self.logits.data_ptr(), self.logits.shape[1], self.pick_mine.data_ptr(),
                   self.wts_mine.data_ptr(), self.rows_local, self.experts, self.top_k, 1 if self.shared else 0, st)
 
@@ -351,13 +354,14 @@ class PeerExpertParallel:
     ``GatheredExpertParallel(reduce="tokens")`` up to fp32 summation order across ranks (here fixed: rank 0, 1, ...)."""
 
     def __init__(self, router_rows: torch.Tensor, local_experts, experts: int, top_k: int, rows_local: int,
-                 group=None, shared_experts=None) -> None:
+                 group=None, shared_experts=None, logit_bias: torch.Tensor | None = None) -> None:
         from . import experts as grouped
         from . import moe
 
         self.moe, self.grouped = moe, grouped
         shared = shared_experts is not None
-        self.win = w = PeerWindow(router_rows, experts, top_k, rows_local, local_experts.dims, shared, group)
+        self.win = w = PeerWindow(router_rows, experts, top_k, rows_local, local_experts.dims, shared, group,
+                                  logit_bias)
         self.local, self.shared_ex, self.rows_local, self.top_k = local_experts, shared_experts, rows_local, top_k
         self.world, self.rank, self.rows, self.tokens = w.world, w.rank, w.rows, w.tokens
         dev, d, rows, slots = w.device, w.dims, w.rows, w.slots
