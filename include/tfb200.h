@@ -48,6 +48,14 @@ int tfb_router(const void* x, int64_t x_stride, const void* rows, float* logits,
 int tfb_select_rows(const float* logits, int NL, int32_t* pick, float* wts, int T, int E, int top_k, int shared,
                     void* stream);
 
+/* Sigmoid-plus-bias routers: score = sigmoid(logit); the top_k experts by score + bias[e] (ties to the lower id);
+ * weights = the picked scores, over their sum in pick order (+ 1e-20) when norm, times scale; then shared_slots slots
+ * with ids E, E + 1, .. and weight 1.  pick / wts are [T, top_k + shared_slots].
+ * Replaces _topk / select: src/tensorfold/families/glm5_next/cuda/glue.py:351-390 (one shared slot) and _topk of
+ * src/tensorfold/families/nemotron_h/cuda/glue.py:50-100 (two shared halves). */
+int tfb_select_sigmoid(const float* logits, int NL, const float* bias, int32_t* pick, float* wts, int T, int E,
+                       int top_k, int shared_slots, float scale, int norm, void* stream);
+
 /* Groups the pairs p = row * slots + slot by ascending expert, pair order kept inside an expert: members[pairs],
  * items[n, 3] = (expert, first member, count <= tile) in expert order then chunk order, counts = (items, distinct
  * experts).  Ids outside [0, experts) are left out.  experts <= 1024.  One launch at any pair count.
@@ -112,6 +120,10 @@ int tfb_peer_sum(void* const* windows, int rank, int64_t p_offset, int world, in
  * src/tensorfold/cuda/exl3/experts.cu:181-190 for the fp32 form. */
 int tfb_combine(const void* y, int y_bf16, const float* wts, void* out, int out_f32, int T, int slots, int D,
                 void* stream);
+
+/* xs[M, K/gs] fp32 = the sum of each group of gs = 64 inputs of x[M, K] bf16 (row stride x_stride elements).
+ * Replaces group_sums / _group_sums: src/tensorfold/cuda/kernels/qmm.py:137-153. */
+int tfb_group_sums(const void* x, int64_t x_stride, float* xs, int M, int K, int gs, void* stream);
 
 /* ---- MLX affine 4-bit group-64 experts -------------------------------------------------------------------------- */
 

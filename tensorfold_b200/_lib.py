@@ -17,6 +17,7 @@ P, I, L, F = c_void_p, c_int, c_int64, c_float
 SIGNATURES: dict[str, tuple] = {
     "tfb_router": (P, L, P, P, I, I, I, P),
     "tfb_select_rows": (P, I, P, P, I, I, I, I, P),
+    "tfb_select_sigmoid": (P, I, P, P, P, I, I, I, I, F, I, P),
     "tfb_plan": (P, L, I, I, P, P, P, P),
     "tfb_select_plan": (P, I, P, P, I, I, I, I, I, P, P, P, P),
     "tfb_select_plan_window": (P, I, P, P, I, I, I, I, I, I, I, P, P, P, P),
@@ -26,6 +27,7 @@ SIGNATURES: dict[str, tuple] = {
     "tfb_pack": (P, P, P, I, P, I, I, I, P),
     "tfb_unpack": (P, I, P, P, P, I, I, I, P),
     "tfb_dequant": (P, I, I, I, P, I, I, I, P),
+    "tfb_group_sums": (P, L, P, I, I, I, P),
     "tfb_experts_run": (I, I, P, L, I, P, I, I, P, P, P, P, I, F, L, I, P),
     "tfb_experts_run_tile": (I, I, P, L, I, P, I, I, P, P, P, P, I, F, L, I, I, P),
     "tfb_experts_prefill": (I, I, P, L, I, P, I, I, P, P, P, P, I, F, L, I, P),

@@ -21,9 +21,12 @@ constexpr int DEC_PAIRS = 16;          // pairs an item may hold at most in this
 constexpr int RED_STRIDE = COLS + 1;
 
 // Q = blocks a warp takes a group: M matrices (gate, up: adjacent in memory) or NCB column blocks of one matrix.
-template <int Q, int STAGES>
+// A ring slot holds G consecutive groups, fetched by one bulk copy a column block: copies of 4.6 KB stream at the
+// full HBM rate where copies of 2.3 KB reach 0.8 of it and 1.2 KB 0.63 (measured with the arithmetic taken out).
+template <int Q, int G, int SLOTS>
 struct DecodeSmem {
-  static constexpr int STAGE_BYTES = Q * BLOCK_BYTES;                      // one group a stage
+  static constexpr int STAGE_BYTES = G * Q * BLOCK_BYTES;                  // G groups a slot
+  static constexpr int STAGES = SLOTS;
   static constexpr int RING_BYTES = DEC_WARPS * STAGES * STAGE_BYTES;
   static constexpr int RED_BYTES = DEC_WARPS * Q * DEC_PAIRS * RED_STRIDE * 4;
   static constexpr int DATA_BYTES = RING_BYTES > RED_BYTES ? RING_BYTES : RED_BYTES;
@@ -40,14 +43,17 @@ __device__ __forceinline__ void mma_bf16_zero(float (&d)[4], uint32_t a0, uint32
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.f));
 }
 
-template <int M, int NCB, int EPI, int SB, int KW, int STAGES, int PT>
-__global__ void __launch_bounds__(DEC_WARPS * 32, PT == 2 && M == 2 ? 4 : 1)
+template <int M, int NCB, int EPI, int SB, int KW, int G, int STAGES, int PT>
+#ifndef EXP_MINB
+#define EXP_MINB 1
+#endif
+__global__ void __launch_bounds__(DEC_WARPS * 32, PT == 2 && M == 2 ? 4 : (PT == 2 ? 1 : EXP_MINB))
 decode_kernel(const __nv_bfloat16* __restrict__ X, int64_t x_stride, int slots, const uint8_t* __restrict__ W, int KG,
               int NB, const int* __restrict__ items, const int* __restrict__ counts, const int* __restrict__ members,
               void* __restrict__ out, int N, float limit) {
   static_assert(M == 1 || NCB == 1, "a warp takes two matrices of one column block, or column blocks of one matrix");
   constexpr int Q = M * NCB;
-  using SM = DecodeSmem<Q, STAGES>;
+  using SM = DecodeSmem<Q, G, STAGES>;
   constexpr int CBC = DEC_WARPS / KW * NCB;           // column blocks a CTA
   extern __shared__ __align__(128) uint8_t smem[];
   __shared__ int pair_id[DEC_PAIRS];
@@ -80,17 +86,19 @@ decode_kernel(const __nv_bfloat16* __restrict__ X, int64_t x_stride, int slots, 
   const size_t cb_stride = (size_t)KG * (M * BLOCK_BYTES);
   const uint8_t* src = W + (((size_t)e * NB + min(cb, NB - 1)) * KG + g0) * (size_t)(M * BLOCK_BYTES);
 
-  auto issue = [&](int c) {
+  const int nslot = (ng + G - 1) / G;                 // slot fills of this warp's run
+  auto issue = [&](int c) {                           // groups [c G, c G + G) of every column block of the warp
     uint64_t* bar = bars + (c % STAGES);
     uint8_t* dst = ring + (c % STAGES) * SM::STAGE_BYTES;
-    mbar_expect_tx(bar, (uint32_t)ncb * (M * BLOCK_BYTES));
+    const uint32_t bytes = (uint32_t)min(G, ng - c * G) * (M * BLOCK_BYTES);
+    mbar_expect_tx(bar, (uint32_t)ncb * bytes);
 #pragma unroll
     for (int j = 0; j < NCB; ++j)
       if (j < ncb)
-        bulk_g2s(dst + j * (M * BLOCK_BYTES), src + j * cb_stride + (size_t)c * (M * BLOCK_BYTES), M * BLOCK_BYTES, bar);
+        bulk_g2s(dst + j * (G * M * BLOCK_BYTES), src + j * cb_stride + (size_t)c * (G * M * BLOCK_BYTES), bytes, bar);
   };
   if (lane == 0)
-    for (int c = 0; c < STAGES && c < ng; ++c) issue(c);
+    for (int c = 0; c < STAGES && c < nslot; ++c) issue(c);
 
   if (tid < DEC_PAIRS) pair_id[tid] = tid < cnt ? __ldg(members + first + tid) : -1;
 
@@ -125,7 +133,7 @@ decode_kernel(const __nv_bfloat16* __restrict__ X, int64_t x_stride, int slots, 
     }
   }
   for (int c = 0; c < ng; ++c) {
-    const int s = c % STAGES;
+    const int fill = c / G, gi = c - fill * G, s = fill % STAGES;
     uint32_t xb[PT][8];
     float xs[PT][4];                                  // sum of the group's inputs for pairs 2t and 2t + 1 of each tile
 #pragma unroll
@@ -141,14 +149,16 @@ decode_kernel(const __nv_bfloat16* __restrict__ X, int64_t x_stride, int slots, 
 #pragma unroll
       for (int ks = 1; ks < 4; ++ks) mma_bf16(xs[pt], ONES, ONES, ONES, ONES, xb[pt][2 * ks], xb[pt][2 * ks + 1]);
     }
-    if (!mbar_wait(bars + s, (c / STAGES) & 1)) break;
-    const uint8_t* blk = ring + s * SM::STAGE_BYTES;
+    if (gi == 0 && !mbar_wait(bars + s, (fill / STAGES) & 1)) break;
+    // group gi of the slot: matrices of a group are adjacent; column blocks are G groups apart
+    const uint8_t* blk = ring + s * SM::STAGE_BYTES + gi * (M * BLOCK_BYTES);
 #pragma unroll
     for (int m = 0; m < Q; ++m) {
-      const uint4 sbv = *reinterpret_cast<const uint4*>(blk + m * BLOCK_BYTES + SB_OFFSET + gq * 16);
+      const uint8_t* bm = blk + (M == 1 ? m * (G * BLOCK_BYTES) : m * BLOCK_BYTES);
+      const uint4 sbv = *reinterpret_cast<const uint4*>(bm + SB_OFFSET + gq * 16);
 #pragma unroll
       for (int tt = 0; tt < 2; ++tt) {
-        const uint4 w = *reinterpret_cast<const uint4*>(blk + m * BLOCK_BYTES + tt * TILE_BYTES + lane * 16);
+        const uint4 w = *reinterpret_cast<const uint4*>(bm + tt * TILE_BYTES + lane * 16);
         float p[PT][4];
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks) {
@@ -170,15 +180,24 @@ decode_kernel(const __nv_bfloat16* __restrict__ X, int64_t x_stride, int slots, 
 #pragma unroll
         for (int pt = 0; pt < PT; ++pt) {
           float(&d)[4] = acc[m][tt][pt];
+#ifdef EXP_FFMA2
+          const float2 xs2 = make_float2(xs[pt][0], xs[pt][1]);
+          const float2 lo2 = ffma2(xs2, make_float2(b_lo, b_lo),
+                                   ffma2(make_float2(p[pt][0], p[pt][1]), make_float2(s_lo, s_lo), make_float2(d[0], d[1])));
+          const float2 hi2 = ffma2(xs2, make_float2(b_hi, b_hi),
+                                   ffma2(make_float2(p[pt][2], p[pt][3]), make_float2(s_hi, s_hi), make_float2(d[2], d[3])));
+          d[0] = lo2.x; d[1] = lo2.y; d[2] = hi2.x; d[3] = hi2.y;
+#else
           d[0] = fmaf(xs[pt][0], b_lo, fmaf(p[pt][0], s_lo, d[0]));
           d[1] = fmaf(xs[pt][1], b_lo, fmaf(p[pt][1], s_lo, d[1]));
           d[2] = fmaf(xs[pt][0], b_hi, fmaf(p[pt][2], s_hi, d[2]));
           d[3] = fmaf(xs[pt][1], b_hi, fmaf(p[pt][3], s_hi, d[3]));
+#endif
         }
       }
     }
     __syncwarp();
-    if (lane == 0 && c + STAGES < ng) issue(c + STAGES);
+    if (lane == 0 && (gi == G - 1 || c == ng - 1) && fill + STAGES < nslot) issue(fill + STAGES);
   }
   pdl_launch_dependents();
 
@@ -233,12 +252,19 @@ int launch_decode_kw(const void* x, int64_t x_stride, int slots, const void* w, 
                      const int* counts, const int* members, void* out, int n, float limit, int64_t max_items,
                      cudaStream_t stream) {
   // gate/up items of 16 pairs keep more registers a thread, so fewer CTAs share an SM (4, by the launch bounds): each
-  // gets a deeper ring instead (measured: 30.5 -> 27.8 us on 32 pairs an expert; the down projection did not gain)
-  constexpr int STAGES = PT == 2 && M == 2 ? 6 : 4;
+  // gets a deeper ring instead
+#ifndef EXP_G_UP
+#define EXP_G_UP 2
+#define EXP_S_UP 2
+#define EXP_G_DN 2
+#define EXP_S_DN 2
+#endif
+  constexpr int G = M == 2 ? EXP_G_UP : EXP_G_DN;
+  constexpr int STAGES = M == 2 ? (PT == 2 ? EXP_S_UP + 1 : EXP_S_UP) : EXP_S_DN;
   constexpr int NCB = M == 1 ? 2 : 1;                 // one matrix: a warp shares its inputs between two column blocks
-  using SM = DecodeSmem<M * NCB, STAGES>;
-  auto* kern = decode_kernel<M, NCB, EPI, SB, KW, STAGES, PT>;
-  static_assert(SM::TOTAL <= (PT == 2 && M == 2 ? 56 : 48) * 1024, "the decode kernel's shared memory lets 4 (or 6) CTAs share an SM");
+  using SM = DecodeSmem<M * NCB, G, STAGES>;
+  auto* kern = decode_kernel<M, NCB, EPI, SB, KW, G, STAGES, PT>;
+  static_assert(SM::TOTAL <= 100 * 1024, "the decode kernel's shared memory");
   if constexpr (SM::TOTAL > 48 * 1024) {
     static bool configured[64] = {false};
     int dev = 0;

@@ -96,6 +96,25 @@ dequant_kernel(const uint32_t* __restrict__ blocks, void* __restrict__ out, int 
   }
 }
 
+// Sums of each group of 64 inputs of a row, fp32: xs[m, g] (the quantity the matmuls fold the biases with;
+// src/tensorfold/cuda/kernels/qmm.py:137-153).  One warp a (row, group): lane l adds inputs 2 l and 2 l + 1, then a
+// butterfly 16..1 - one stated order.
+__global__ void __launch_bounds__(128)
+group_sums_kernel(const __nv_bfloat16* __restrict__ x, int64_t ldx, float* __restrict__ xs, int M, int KG) {
+  pdl_wait();
+  const int lane = threadIdx.x & 31;
+  const int64_t unit = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (unit < (int64_t)M * KG) {
+    const int m = (int)(unit / KG), g = (int)(unit - (int64_t)m * KG);
+    const uint32_t u = *reinterpret_cast<const uint32_t*>(x + (size_t)m * ldx + g * GS + 2 * lane);
+    float v = bf16_lo(u) + bf16_hi(u);
+#pragma unroll
+    for (int o = 16; o >= 1; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    if (lane == 0) xs[unit] = v;
+  }
+  pdl_launch_dependents();
+}
+
 }  // namespace tfb
 
 using namespace tfb;
@@ -149,4 +168,17 @@ extern "C" int tfb_dequant(const void* blocks, int gs, int sb_type, int mode, vo
     dequant_kernel<SB_FP16><<<grid, 256, 0, st>>>(static_cast<const uint32_t*>(blocks), out, mode, nwords, N, K / 8,
                                                   KG, NB);
   return check_launch("dequant");
+}
+
+extern "C" int tfb_group_sums(const void* x, int64_t x_stride, float* xs, int M, int K, int gs, void* stream) {
+  TFB_REQUIRE(x && xs, "group_sums: null pointer");
+  TFB_REQUIRE(gs == GS && K > 0 && K % GS == 0 && x_stride >= K && x_stride % 2 == 0,
+              "group_sums: groups of %d inputs, K a multiple of it", GS);
+  TFB_REQUIRE((reinterpret_cast<uintptr_t>(x) & 3u) == 0, "group_sums: x must be 4-byte aligned");
+  if (M <= 0) return TFB_OK;
+  const int64_t units = (int64_t)M * (K / GS);
+  return check_cuda(launch(group_sums_kernel, dim3((unsigned)((units + 3) / 4)), dim3(128), 0,
+                           static_cast<cudaStream_t>(stream), static_cast<const __nv_bfloat16*>(x), x_stride, xs, M,
+                           K / GS),
+                    "group_sums");
 }

@@ -207,6 +207,68 @@ select_kernel(const float* __restrict__ L, int NL, int* __restrict__ pick, float
   pdl_launch_dependents();
 }
 
+// Sigmoid-plus-bias selection (the GLM and Nemotron routers): score = sigmoid(logit); the TOPK experts with the
+// largest score + bias (the lower id among equals); weights = the picked scores, divided by their sum in pick order
+// when `norm` (sum + 1e-20), times `scale`; then `shared` slots with ids E, E + 1, .. and weight 1.
+// (src/tensorfold/families/glm5_next/cuda/glue.py:351-390; src/tensorfold/families/nemotron_h/cuda/glue.py:50-100)
+template <int VPL>
+__global__ void __launch_bounds__(S_WARPS * 32)
+select_sigmoid_kernel(const float* __restrict__ L, int NL, const float* __restrict__ bias, int* __restrict__ pick,
+                      float* __restrict__ wts, int T, int E, int top_k, int shared, float scale, int norm) {
+  const int lane = threadIdx.x & 31;
+  const int r = blockIdx.x * S_WARPS + (threadIdx.x >> 5);
+  if (r >= T) return;
+  pdl_wait();
+  const int slots = top_k + shared;
+  const float* Lr = L + (size_t)r * NL;
+  uint32_t key[VPL];
+  float score[VPL];
+#pragma unroll
+  for (int i = 0; i < VPL; ++i) {
+    const int e = i * 32 + lane;
+    score[i] = e < E ? 1.f / (1.f + expf(-Lr[e])) : 0.f;
+    key[i] = e < E ? order_key(score[i] + bias[e]) : 0u;
+    if (e < E && key[i] == 0u) key[i] = 1u;           // -inf / NaN choices still rank above "taken"
+  }
+  float total = 0.f, my_score = 0.f;
+  int my_pick = -1;
+  for (int k = 0; k < top_k; ++k) {
+    uint32_t bk = key[0];
+    uint32_t bi = lane;
+    float bs = score[0];
+#pragma unroll
+    for (int i = 1; i < VPL; ++i)
+      if (key[i] > bk) {
+        bk = key[i];
+        bi = i * 32 + lane;
+        bs = score[i];
+      }
+    const uint32_t mx = __reduce_max_sync(0xffffffffu, bk);
+    const uint32_t idx = __reduce_min_sync(0xffffffffu, bk == mx ? bi : 0xFFFFFFFFu);
+    const float sk = __shfl_sync(0xffffffffu, bs, idx & 31u);      // the owner lane's best is this entry
+    total += sk;
+    if (lane == k) {
+      my_pick = (int)idx;
+      my_score = sk;
+    }
+#pragma unroll
+    for (int i = 0; i < VPL; ++i)
+      if (i * 32 + lane == (int)idx) key[i] = 0u;
+  }
+  int* pick_row = pick + (size_t)r * slots;
+  float* wts_row = wts + (size_t)r * slots;
+  if (lane < top_k) {
+    float w = my_score;
+    if (norm) w = w / (total + 1e-20f);
+    pick_row[lane] = my_pick;
+    wts_row[lane] = w * scale;
+  } else if (lane < slots) {
+    pick_row[lane] = E + (lane - top_k);
+    wts_row[lane] = 1.f;
+  }
+  pdl_launch_dependents();
+}
+
 // ================================================================================================================
 // Plan: pairs p = row * slots + slot grouped by ascending expert, pair order kept inside an expert (a stable counting
 // sort); items (expert, first, count <= tile) in expert order then chunk order; counts = (items, distinct experts).
@@ -482,6 +544,28 @@ static int plan_launch(const int32_t* picks, int64_t pairs, int lo, int experts,
   return check_cuda(launch(plan_kernel, dim3(1), dim3(PLAN_THREADS), smem, static_cast<cudaStream_t>(stream), picks,
                            (int)pairs, experts, tile, members, items, counts, lo),
                     "plan");
+}
+
+extern "C" int tfb_select_sigmoid(const float* logits, int NL, const float* bias, int32_t* pick, float* wts, int T,
+                                  int E, int top_k, int shared_slots, float scale, int norm, void* stream) {
+  TFB_REQUIRE(logits && bias && pick && wts, "select_sigmoid: null pointer");
+  TFB_REQUIRE(E >= 1 && E <= 1024, "select_sigmoid: 1..1024 experts, not %d", E);
+  TFB_REQUIRE(top_k >= 1 && top_k <= E && shared_slots >= 0 && top_k + shared_slots <= 32,
+              "select_sigmoid: top_k=%d and %d shared slots must fit 32 slots", top_k, shared_slots);
+  TFB_REQUIRE(NL >= E, "select_sigmoid: %d logits a row cannot hold %d experts", NL, E);
+  if (T <= 0) return TFB_OK;
+  const int grid = (T + S_WARPS - 1) / S_WARPS;
+  auto st = static_cast<cudaStream_t>(stream);
+  const int vpl = (E + 31) / 32;
+#define TFB_SEL(V)                                                                                             \
+  return check_cuda(launch(select_sigmoid_kernel<V>, dim3(grid), dim3(S_WARPS * 32), 0, st, logits, NL, bias,  \
+                           pick, wts, T, E, top_k, shared_slots, scale, norm ? 1 : 0),                          \
+                    "select_sigmoid")
+  if (vpl <= 4) TFB_SEL(4);
+  if (vpl <= 8) TFB_SEL(8);
+  if (vpl <= 16) TFB_SEL(16);
+  TFB_SEL(32);
+#undef TFB_SEL
 }
 
 extern "C" int tfb_plan(const int32_t* picks, int64_t pairs, int experts, int tile, int32_t* members, int32_t* items,

@@ -71,6 +71,26 @@ def select_rows(logits: torch.Tensor, buf: MoEBuffers, top_k: int, experts: int)
                   top_k, 1 if shared else 0, _stream(logits))
 
 
+def select_sigmoid(logits: torch.Tensor, bias: torch.Tensor, pick: torch.Tensor, wts: torch.Tensor, top_k: int,
+                   experts: int, scale: float, norm: bool, shared_slots: int = 1) -> None:
+    """The sigmoid-plus-bias routers' selection (GLM: ``glue.select``, one shared slot; Nemotron: two): each row's
+    top-k experts by ``sigmoid(logit) + bias`` (ties to the lower id), weights = the picked scores, normalised in pick
+    order when ``norm``, times ``scale``; then the shared slots (ids ``experts``, ``experts + 1``, weight 1)."""
+
+    rows, nl = logits.shape
+    slots = top_k + shared_slots
+    if logits.dtype != torch.float32 or not logits.is_contiguous() or not logits.is_cuda:
+        raise ValueError("logits must be contiguous CUDA fp32")
+    if bias.dtype != torch.float32 or bias.numel() < experts or not bias.is_contiguous():
+        raise ValueError("bias must be contiguous fp32 [experts]")
+    for t, dt in ((pick, torch.int32), (wts, torch.float32)):
+        if t.dtype != dt or not t.is_contiguous() or t.shape[0] < rows or t.shape[1] != slots:
+            raise ValueError(f"pick / wts must be contiguous [{rows}, {slots}] int32 / fp32")
+    with torch.cuda.device(logits.device):
+        _lib.call("tfb_select_sigmoid", logits.data_ptr(), nl, bias.data_ptr(), pick.data_ptr(), wts.data_ptr(), rows,
+                  experts, top_k, shared_slots, float(scale), 1 if norm else 0, _stream(logits))
+
+
 # Up to this many rows the one-block kernel that selects and plans in one launch is used; above it the selection runs
 # on many blocks and the plan follows as its own launch (measured inside a CUDA graph: 5.7 against 8.8 us at 64 rows).
 FUSED_SELECT_ROWS = 32

@@ -172,3 +172,18 @@ def test_cpu_layer_tracks_the_float64_layer(shared):
     assert np.abs(y - y64).max() <= 2e-2 * np.abs(y64).max()
     err = np.linalg.norm(affine.bf16_value(out) - o64) / np.linalg.norm(o64)
     assert err < 1e-2
+
+
+def test_sigmoid_router_restatement_orders_by_choice_then_id():
+    from oracle import routers
+
+    rng = np.random.default_rng(3)
+    logits = rng.standard_normal((6, 20)).astype(np.float32)
+    logits[2, :] = 0.5
+    bias = np.zeros((20,), dtype=np.float32)
+    pick, wts, gap = routers.sigmoid_topk(logits, bias, 4, 1.0, True, 1)
+    assert pick[2, :4].tolist() == [0, 1, 2, 3] and pick[:, 4].tolist() == [20] * 6
+    np.testing.assert_allclose(wts[:, :4].sum(-1), 1.0, rtol=1e-6)
+    for r in (0, 1, 3):
+        assert pick[r, :4].tolist() == np.argsort(-logits[r], kind="stable")[:4].tolist()   # sigmoid is monotone
+    assert gap[2] == 0.0 and (wts[:, 4] == 1.0).all()

@@ -194,3 +194,36 @@ def test_windowed_plan_and_combine():
     mask = ((buf.pick >= lo) & (buf.pick < lo + n)).float()
     want = moe.combine(y * mask[..., None], buf.wts, torch.empty_like(out))     # zeroed rows add exactly nothing
     assert torch.equal(out, want)
+
+
+@pytest.mark.parametrize("experts,top_k,shared,norm", [(64, 6, 1, True), (256, 8, 1, True), (160, 6, 2, False), (33, 4, 0, True)])
+def test_sigmoid_bias_selection_matches_the_sorted_order(experts, top_k, shared, norm):
+    """The GLM / Nemotron routers' selection: picks equal the sort by (-(sigmoid + bias), id), weights the normalised
+    scores; rows whose choices are closer than the exp's rounding are left out of the index check."""
+
+    from oracle import routers
+    from tensorfold_b200 import moe
+
+    rows = 97
+    g = torch.Generator(device="cuda").manual_seed(experts)
+    logits = torch.randn((rows, experts + 3), generator=g, device="cuda") * 2.0
+    bias = torch.randn((experts,), generator=g, device="cuda") * 0.1
+    logits[5, :experts] = 0.25                                   # a row of ties: the lowest ids win
+    bias_t = bias.clone()
+    slots = top_k + shared
+    pick = torch.zeros((rows, slots), dtype=torch.int32, device="cuda")
+    wts = torch.zeros((rows, slots), dtype=torch.float32, device="cuda")
+    moe.select_sigmoid(logits, bias_t, pick, wts, top_k, experts, 2.5, norm, shared)
+    want_pick, want_wts, gap = routers.sigmoid_topk(logits.cpu().numpy(), bias.cpu().numpy(), top_k, 2.5, norm, shared)
+    got_pick, got_wts = pick.cpu().numpy(), wts.cpu().numpy()
+    clear = gap > 1e-6
+    clear[5] = False
+    assert clear.sum() > rows * 0.9
+    assert (got_pick[clear] == want_pick[clear]).all()
+    np.testing.assert_allclose(got_wts[clear], want_wts[clear], rtol=2e-6, atol=1e-7)
+    assert (got_pick[:, top_k:] == np.arange(experts, experts + shared)).all() and (got_wts[:, top_k:] == 1).all()
+    # the tie row: equal scores, so the order is by bias then id - compare with the sort on the same fp32 values
+    score = 1.0 / (1.0 + np.exp(-np.float32(0.25)))
+    choice = (np.float32(score) + bias.cpu().numpy()).astype(np.float32)
+    order = sorted(range(experts), key=lambda i: (-choice[i], i))[:top_k]
+    assert got_pick[5, :top_k].tolist() == order
