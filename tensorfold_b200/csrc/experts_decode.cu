@@ -44,10 +44,7 @@ __device__ __forceinline__ void mma_bf16_zero(float (&d)[4], uint32_t a0, uint32
 }
 
 template <int M, int NCB, int EPI, int SB, int KW, int G, int STAGES, int PT>
-#ifndef EXP_MINB
-#define EXP_MINB 1
-#endif
-__global__ void __launch_bounds__(DEC_WARPS * 32, PT == 2 && M == 2 ? 4 : (PT == 2 ? 1 : EXP_MINB))
+__global__ void __launch_bounds__(DEC_WARPS * 32, PT == 2 && M == 2 ? 4 : 1)
 decode_kernel(const __nv_bfloat16* __restrict__ X, int64_t x_stride, int slots, const uint8_t* __restrict__ W, int KG,
               int NB, const int* __restrict__ items, const int* __restrict__ counts, const int* __restrict__ members,
               void* __restrict__ out, int N, float limit) {
@@ -180,19 +177,13 @@ decode_kernel(const __nv_bfloat16* __restrict__ X, int64_t x_stride, int slots, 
 #pragma unroll
         for (int pt = 0; pt < PT; ++pt) {
           float(&d)[4] = acc[m][tt][pt];
-#ifdef EXP_FFMA2
+          // two fp32 fmas an instruction; each half rounds like fmaf
           const float2 xs2 = make_float2(xs[pt][0], xs[pt][1]);
           const float2 lo2 = ffma2(xs2, make_float2(b_lo, b_lo),
                                    ffma2(make_float2(p[pt][0], p[pt][1]), make_float2(s_lo, s_lo), make_float2(d[0], d[1])));
           const float2 hi2 = ffma2(xs2, make_float2(b_hi, b_hi),
                                    ffma2(make_float2(p[pt][2], p[pt][3]), make_float2(s_hi, s_hi), make_float2(d[2], d[3])));
           d[0] = lo2.x; d[1] = lo2.y; d[2] = hi2.x; d[3] = hi2.y;
-#else
-          d[0] = fmaf(xs[pt][0], b_lo, fmaf(p[pt][0], s_lo, d[0]));
-          d[1] = fmaf(xs[pt][1], b_lo, fmaf(p[pt][1], s_lo, d[1]));
-          d[2] = fmaf(xs[pt][0], b_hi, fmaf(p[pt][2], s_hi, d[2]));
-          d[3] = fmaf(xs[pt][1], b_hi, fmaf(p[pt][3], s_hi, d[3]));
-#endif
         }
       }
     }
@@ -251,20 +242,14 @@ template <int M, int EPI, int SB, int KW, int PT>
 int launch_decode_kw(const void* x, int64_t x_stride, int slots, const void* w, int kg, int nb, const int* items,
                      const int* counts, const int* members, void* out, int n, float limit, int64_t max_items,
                      cudaStream_t stream) {
-  // gate/up items of 16 pairs keep more registers a thread, so fewer CTAs share an SM (4, by the launch bounds): each
-  // gets a deeper ring instead
-#ifndef EXP_G_UP
-#define EXP_G_UP 2
-#define EXP_S_UP 2
-#define EXP_G_DN 2
-#define EXP_S_DN 2
-#endif
-  constexpr int G = M == 2 ? EXP_G_UP : EXP_G_DN;
-  constexpr int STAGES = M == 2 ? (PT == 2 ? EXP_S_UP + 1 : EXP_S_UP) : EXP_S_DN;
+  // two groups a slot, two slots a warp (9.2 KB); gate/up items of 16 pairs keep more registers a thread, so fewer
+  // CTAs share an SM (4, by the launch bounds) and each gets a third slot
+  constexpr int G = 2;
+  constexpr int STAGES = M == 2 && PT == 2 ? 3 : 2;
   constexpr int NCB = M == 1 ? 2 : 1;                 // one matrix: a warp shares its inputs between two column blocks
   using SM = DecodeSmem<M * NCB, G, STAGES>;
   auto* kern = decode_kernel<M, NCB, EPI, SB, KW, G, STAGES, PT>;
-  static_assert(SM::TOTAL <= 100 * 1024, "the decode kernel's shared memory");
+  static_assert(SM::TOTAL <= (M == 2 && PT == 2 ? 56 : 48) * 1024, "the decode kernel's shared memory lets 4 (or 5-6) CTAs share an SM");
   if constexpr (SM::TOTAL > 48 * 1024) {
     static bool configured[64] = {false};
     int dev = 0;
