@@ -27,7 +27,7 @@ ROOT = Path(__file__).resolve().parent
 if str(ROOT) not in sys.path:
     sys.path.insert(0, str(ROOT))
 
-TRAFFIC_GATE_UP_C2_64 = 225056256 + 5437184      # bytes, from the committed ncu capture of the same launch
+TRAFFIC_GATE_UP_C2_64 = 225054208 + 4798464      # bytes, from the committed ncu capture of the same launch
 METRIC = "moe_layer_tokens_per_s"
 UNIT = "tokens/s"
 SMI_FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"

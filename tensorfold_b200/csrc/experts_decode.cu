@@ -44,7 +44,7 @@ __device__ __forceinline__ void mma_bf16_zero(float (&d)[4], uint32_t a0, uint32
 }
 
 template <int M, int NCB, int EPI, int SB, int KW, int G, int STAGES, int PT>
-__global__ void __launch_bounds__(DEC_WARPS * 32, PT == 2 && M == 2 ? 4 : 1)
+__global__ void __launch_bounds__(DEC_WARPS * 32, PT == 2 ? (M == 2 ? 4 : 1) : 5)
 decode_kernel(const __nv_bfloat16* __restrict__ X, int64_t x_stride, int slots, const uint8_t* __restrict__ W, int KG,
               int NB, const int* __restrict__ items, const int* __restrict__ counts, const int* __restrict__ members,
               void* __restrict__ out, int N, float limit) {
