@@ -147,7 +147,8 @@ int tfb_dequant(const void* blocks, int gs, int sb_type, int mode, void* out, in
  * [E, nb, kg, M, 288] (M = 2 for epi 2, else 1).  out rows of n = 32 * nb columns, row index = pair id.
  * Items hold at most 8 pairs in this form (plan with tile 8).
  * epi 0: fp32 out; 1: bf16 relu(bf16 acc)^2; 2: bf16 SwiGLU(matrix 0, matrix 1) clipped at `limit` when > 0;
- * 3: bf16 out.  max_units = upper bound of items * nb (the grid).  sb_type as tfb_dequant.
+ * 3: bf16 out.  max_units = upper bound of items * nb (the grid); the items table must hold that many items (rows
+ * past counts[0] are read, not used).  sb_type as tfb_dequant.
  * Replaces the extension entry `run`: src/tensorfold/cuda/experts.cpp:43-48, experts.cu:130-155,287-351. */
 int tfb_experts_run(int gs, int epi, const void* x, int64_t x_stride, int slots, const void* w, int kg, int nb,
                     const int32_t* items, const int32_t* counts, const int32_t* members, void* out, int n, float limit,

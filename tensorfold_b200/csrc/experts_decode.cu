@@ -70,10 +70,12 @@ decode_kernel(const __nv_bfloat16* __restrict__ X, int64_t x_stride, int slots, 
   __syncwarp();
 
   pdl_wait();                                         // the plan (and the inputs) come from the kernels before
-  if (it >= __ldg(counts)) return;
+  // the item is read together with the count that says whether it exists (its slot is always inside the table)
+  const int n_items = __ldg(counts);
   const int e = __ldg(items + 3 * it), first = __ldg(items + 3 * it + 1);
   constexpr int PAIRS = 8 * PT;
   const int cnt = min(__ldg(items + 3 * it + 2), PAIRS);
+  if (it >= n_items) return;
 
   // this warp's K run: groups [g0, g1) of column block cb
   const int kgw = (KG + KW - 1) / KW;
@@ -235,21 +237,36 @@ decode_kernel(const __nv_bfloat16* __restrict__ X, int64_t x_stride, int slots, 
   }
 }
 
+// SMs of the current device (looked up once a device)
+inline int sm_count() {
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
 // K-slices a CTA for a projection of kg groups: the shape's alone, so a pair's bits never depend on the call.
 __host__ __device__ inline int decode_kslices(int kg) { return kg >= 32 ? 4 : kg >= 8 ? 2 : 1; }
 
-template <int M, int EPI, int SB, int KW, int PT>
+// DEEP: a grid of at most three CTAs an SM (a few tokens) is bound by the latency of a warp's own stream, not by how
+// many CTAs share an SM: four slots put a K slice of eight groups in flight at once.
+template <int M, int EPI, int SB, int KW, int PT, bool DEEP>
 int launch_decode_kw(const void* x, int64_t x_stride, int slots, const void* w, int kg, int nb, const int* items,
                      const int* counts, const int* members, void* out, int n, float limit, int64_t max_items,
                      cudaStream_t stream) {
   // two groups a slot, two slots a warp (9.2 KB); gate/up items of 16 pairs keep more registers a thread, so fewer
   // CTAs share an SM (4, by the launch bounds) and each gets a third slot
   constexpr int G = 2;
-  constexpr int STAGES = M == 2 && PT == 2 ? 3 : 2;
+  constexpr int STAGES = DEEP ? 4 : M == 2 && PT == 2 ? 3 : 2;
   constexpr int NCB = M == 1 ? 2 : 1;                 // one matrix: a warp shares its inputs between two column blocks
   using SM = DecodeSmem<M * NCB, G, STAGES>;
   auto* kern = decode_kernel<M, NCB, EPI, SB, KW, G, STAGES, PT>;
-  static_assert(SM::TOTAL <= (M == 2 && PT == 2 ? 56 : 48) * 1024, "the decode kernel's shared memory lets 4 (or 5-6) CTAs share an SM");
+  static_assert(SM::TOTAL <= (DEEP ? 75 : M == 2 && PT == 2 ? 56 : 48) * 1024, "the decode kernel's shared memory lets 3, 4 or 5 CTAs share an SM");
   if constexpr (SM::TOTAL > 48 * 1024) {
     static bool configured[64] = {false};
     int dev = 0;
@@ -274,16 +291,33 @@ template <int M, int EPI, int SB, int PT>
 int launch_decode(const void* x, int64_t x_stride, int slots, const void* w, int kg, int nb, const int* items,
                   const int* counts, const int* members, void* out, int n, float limit, int64_t max_items,
                   cudaStream_t stream) {
-  switch (decode_kslices(kg)) {
+  const int kw = decode_kslices(kg);
+  if constexpr (PT == 1) {
+    const int cbc = DEC_WARPS / kw * (M == 1 ? 2 : 1);
+    if (max_items * ((nb + cbc - 1) / cbc) <= 3 * sm_count()) {
+      switch (kw) {
+        case 4:
+          return launch_decode_kw<M, EPI, SB, 4, PT, true>(x, x_stride, slots, w, kg, nb, items, counts, members, out,
+                                                           n, limit, max_items, stream);
+        case 2:
+          return launch_decode_kw<M, EPI, SB, 2, PT, true>(x, x_stride, slots, w, kg, nb, items, counts, members, out,
+                                                           n, limit, max_items, stream);
+        default:
+          return launch_decode_kw<M, EPI, SB, 1, PT, true>(x, x_stride, slots, w, kg, nb, items, counts, members, out,
+                                                           n, limit, max_items, stream);
+      }
+    }
+  }
+  switch (kw) {
     case 4:
-      return launch_decode_kw<M, EPI, SB, 4, PT>(x, x_stride, slots, w, kg, nb, items, counts, members, out, n, limit,
-                                             max_items, stream);
+      return launch_decode_kw<M, EPI, SB, 4, PT, false>(x, x_stride, slots, w, kg, nb, items, counts, members, out, n,
+                                                        limit, max_items, stream);
     case 2:
-      return launch_decode_kw<M, EPI, SB, 2, PT>(x, x_stride, slots, w, kg, nb, items, counts, members, out, n, limit,
-                                             max_items, stream);
+      return launch_decode_kw<M, EPI, SB, 2, PT, false>(x, x_stride, slots, w, kg, nb, items, counts, members, out, n,
+                                                        limit, max_items, stream);
     default:
-      return launch_decode_kw<M, EPI, SB, 1, PT>(x, x_stride, slots, w, kg, nb, items, counts, members, out, n, limit,
-                                             max_items, stream);
+      return launch_decode_kw<M, EPI, SB, 1, PT, false>(x, x_stride, slots, w, kg, nb, items, counts, members, out, n,
+                                                        limit, max_items, stream);
   }
 }
 
