@@ -174,3 +174,37 @@ def test_graph_replay_equals_eager():
         graph.replay()
         want = experts.routed(x, sel, w, ex, experts.Scratch(ex, R, TOPK), None, R)
         assert torch.equal(out, want)
+
+
+@pytest.mark.parametrize("bits,cb", [(4, "3inst"), (2, "mcg"), (6, "3inst"), (3.5, "mul1")])
+@pytest.mark.parametrize("m", [1, 9, 128])
+def test_dense_linear_against_float64_and_rows_alone(bits, cb, m):
+    """``exl3.linear.Exl3Linear`` (the experts' kernels on a one-matrix layer): output against the float64 restatement
+    of the reference's forward, W_q bit for bit, a row alone gives the same bits."""
+
+    from oracle import exl3 as ref
+    from tensorfold_b200.exl3 import linear
+
+    k, n = 256, 384
+    g = torch.Generator(device="cuda").manual_seed(int(bits * 10) + m)
+    trellis = torch.randint(-32768, 32768, (k // 16, n // 16, int(16 * bits)), generator=g, device="cuda",
+                            dtype=torch.int32).to(torch.int16)
+    sign = lambda c: (torch.randint(0, 2, (c,), generator=g, device="cuda").float() * 2 - 1)          # noqa: E731
+    suh = (sign(k) * (torch.randn((k,), generator=g, device="cuda") * 0.02).abs()).half()
+    svh = (sign(n) * (torch.randn((n,), generator=g, device="cuda") * 0.02).abs()).half()
+    bias = (torch.randn((n,), generator=g, device="cuda") * 0.01).half()
+    layer = linear.Exl3Linear.from_tensors(trellis, suh, svh, cb, bias)
+    assert layer.k == k and layer.n == n and layer.k2 == int(2 * bits)
+    x = torch.randn((m, k), generator=g, device="cuda").to(torch.bfloat16)
+    got = layer(x, out_dtype=torch.float32)
+    cbid = linear.CODEBOOK_IDS[cb]
+    want = ref.linear(x.double().cpu().numpy(), trellis.cpu().numpy(), suh.cpu().numpy(), svh.cpu().numpy(), cbid)
+    want = want + bias.double().cpu().numpy()
+    err = np.abs(got.double().cpu().numpy() - want).max() / np.abs(want).max()
+    assert err < 2e-3, err
+    assert np.array_equal(layer.unpack().cpu().numpy().view(np.uint16),
+                          ref.unpack(trellis.cpu().numpy(), cbid).astype(np.float16).view(np.uint16))
+    r = m // 2
+    assert torch.equal(layer(x[r:r + 1], out_dtype=torch.float32), got[r:r + 1])
+    with pytest.raises(ValueError):
+        layer(torch.zeros((129, k), dtype=torch.bfloat16, device="cuda"))
