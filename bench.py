@@ -297,6 +297,13 @@ def ep_rows(args, shape, world: int) -> int:
     return 256 // world if args.config == "c4" else args.rows
 
 
+def hot_pairs(args) -> int:
+    """Pairs from which a rank's expert runs through the prompt-form kernel (off unless asked for: at config 4's sizes
+    one prompt-form item is a 70 us serial chain on 16 CTAs, which costs more than the decode items it replaces)."""
+
+    return max(args.hot_pairs, 0)
+
+
 def ep_copies(args, world: int) -> int:
     """Independent weight copies a rank rotates so that a step's weights never sit in the 126 MB L2."""
 
@@ -334,7 +341,8 @@ def bench_ep(torch, dist, args, shape, dev, rank: int, world: int):
         if args.ep_reduce == "peer":
             shared = cut(slice(shape.experts, shape.experts + 1)) if shape.shared else None
             copies.append(ep.PeerExpertParallel(router, local, shape.experts, shape.top_k, rows,
-                                                shared_experts=shared, logit_bias=bias))
+                                                shared_experts=shared, logit_bias=bias,
+                                                hot_pairs=hot_pairs(args)))
         else:
             copies.append(ep.GatheredExpertParallel(router, local, shape.experts, shape.top_k, rows,
                                                     reduce=args.ep_reduce))
@@ -471,7 +479,8 @@ def run_ours(args) -> None:
                     "config": {**workload_config(shape, rows, world, args.config),
                                "l2": f"each rank rotates {ep_copies(args, world)} copies of its "
                                      f"{shape.experts // world}-expert slice (inputs larger than the 126 MB L2)",
-                               "collective": COLLECTIVE[args.ep_reduce] + "; the step is one CUDA graph"},
+                               "collective": COLLECTIVE[args.ep_reduce] + "; the step is one CUDA graph",
+                               "hot_pairs": hot_pairs(args)},
                     "clocks": clocks.summary(),
                     "e2e": {"value": world * rows / (e2e_ms * 1e-3), "unit": UNIT, "ms_per_step": e2e_ms,
                             "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": nbytes},
@@ -552,6 +561,9 @@ def main() -> None:
     ap.add_argument("--config", default="c2", choices=["c2", "c4"],
                     help="c2: the headline layer (default); c4: the 256-expert layer with a shared expert and skewed "
                          "routing, 256 tokens split over the ranks (multi-GPU only)")
+    ap.add_argument("--hot-pairs", type=int, default=-1,
+                    help="expert-parallel peer form: experts with at least this many pairs use the prompt-form kernel "
+                         "(default 0: never)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-sweep", action="store_true", help="skip the 1-token and 2048-token lines")
     args = ap.parse_args()

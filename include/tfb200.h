@@ -76,6 +76,12 @@ int tfb_select_plan(const float* logits, int NL, int32_t* pick, float* wts, int 
  * rank owns; plans are made over those ids renumbered from 0, and tfb_combine_window sums only those slots. */
 int tfb_plan_window(const int32_t* picks, int64_t pairs, int lo, int experts, int tile, int32_t* members,
                     int32_t* items, int32_t* counts, void* stream);
+/* tfb_plan_window with the busy experts set apart: experts with at least `hot` pairs get their items (of up to
+ * big_tile pairs) in big_items / big_counts, for tfb_experts_prefill; the rest stay in items / counts (of up to `tile`
+ * pairs), for tfb_experts_run.  Both tables index the one members array.  No reference counterpart. */
+int tfb_plan_split(const int32_t* picks, int64_t pairs, int lo, int experts, int tile, int big_tile, int hot,
+                   int32_t* members, int32_t* items, int32_t* counts, int32_t* big_items, int32_t* big_counts,
+                   void* stream);
 int tfb_select_plan_window(const float* logits, int NL, int32_t* pick, float* wts, int T, int E, int top_k, int shared,
                            int tile, int plan_lo, int plan_n, int32_t* members, int32_t* items, int32_t* counts,
                            void* stream);

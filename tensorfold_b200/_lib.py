@@ -22,6 +22,7 @@ SIGNATURES: dict[str, tuple] = {
     "tfb_select_plan": (P, I, P, P, I, I, I, I, I, P, P, P, P),
     "tfb_select_plan_window": (P, I, P, P, I, I, I, I, I, I, I, P, P, P, P),
     "tfb_plan_window": (P, L, I, I, I, P, P, P, P),
+    "tfb_plan_split": (P, L, I, I, I, I, I, P, P, P, P, P, P),
     "tfb_combine_window": (P, I, P, P, I, I, P, I, I, I, I, P),
     "tfb_combine": (P, I, P, P, I, I, I, I, P),
     "tfb_pack": (P, P, P, I, P, I, I, I, P),

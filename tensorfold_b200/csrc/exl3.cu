@@ -387,7 +387,7 @@ exl3_group_kernel(const int* __restrict__ picks, int P, int E, int slots, int* _
                   int* __restrict__ ucount, int* __restrict__ members, int maxm, int maxu) {
   extern __shared__ int whist[];
   __shared__ int first[PLAN_EMAX];
-  __shared__ int wsum[3][32];
+  __shared__ int wsum[4][32];
   pdl_wait();
   plan_block(picks, P, E, P + 1, tmp_members, tmp_items, tmp_counts, whist, first, wsum);
   __threadfence_block();

@@ -122,11 +122,14 @@ decode_kernel(const __nv_bfloat16* __restrict__ X, int64_t x_stride, int slots, 
         for (int i = 0; i < 4; ++i) acc[m][tt][pt][i] = 0.f;
 
   const uint32_t ONES = 0x3F803F80u;                  // the bf16 pair (1, 1)
+  // an item of a 16-pair plan that holds at most 8 pairs skips its second tile's loads and arithmetic (the same for
+  // every thread of the CTA), so such a plan costs little where experts have few pairs
+  const bool two = PT == 2 && cnt > 8;
   uint4 xn[PT][2];
 #pragma unroll
   for (int pt = 0; pt < PT; ++pt) {
     xn[pt][0] = xn[pt][1] = make_uint4(0u, 0u, 0u, 0u);
-    if (ng > 0) {
+    if (ng > 0 && (pt == 0 || two)) {
       xn[pt][0] = ldg_nc(xrow[pt]);
       xn[pt][1] = ldg_nc(xrow[pt] + 8);
     }
@@ -137,6 +140,7 @@ decode_kernel(const __nv_bfloat16* __restrict__ X, int64_t x_stride, int slots, 
     float xs[PT][4];                                  // sum of the group's inputs for pairs 2t and 2t + 1 of each tile
 #pragma unroll
     for (int pt = 0; pt < PT; ++pt) {
+      if (pt == 1 && !two) continue;
       const uint4 x0 = xn[pt][0], x1 = xn[pt][1];
       if (c + 1 < ng) {                               // the next group's inputs travel while this one computes
         xn[pt][0] = ldg_nc(xrow[pt] + (c + 1) * GS);
@@ -167,6 +171,7 @@ decode_kernel(const __nv_bfloat16* __restrict__ X, int64_t x_stride, int slots, 
           const uint32_t a2 = nib_pair(lo, sh + 4), a3 = nib_pair(hi, sh + 4);
 #pragma unroll
           for (int pt = 0; pt < PT; ++pt) {           // the fragment is dequantised once for every tile of pairs
+            if (pt == 1 && !two) continue;
             if (ks == 0)
               mma_bf16_zero(p[pt], a0, a1, a2, a3, xb[pt][0], xb[pt][1]);
             else
@@ -178,6 +183,7 @@ decode_kernel(const __nv_bfloat16* __restrict__ X, int64_t x_stride, int slots, 
         const float b_lo = fmaf(-128.f, s_lo, sb_lo.y), b_hi = fmaf(-128.f, s_hi, sb_hi.y);
 #pragma unroll
         for (int pt = 0; pt < PT; ++pt) {
+          if (pt == 1 && !two) continue;
           float(&d)[4] = acc[m][tt][pt];
           // two fp32 fmas an instruction; each half rounds like fmaf
           const float2 xs2 = make_float2(xs[pt][0], xs[pt][1]);

@@ -278,28 +278,40 @@ select_sigmoid_kernel(const float* __restrict__ L, int NL, const float* __restri
 // ================================================================================================================
 constexpr int PLAN_THREADS = 1024, PLAN_EMAX = 1024, PLAN_BATCH = 8;
 
+// A split plan: experts with at least `hot` pairs get their items (of Tb pairs) in a second table, for the prompt-form
+// kernel; the others stay in the first (items of T pairs).  hot = INT_MAX (and no second table): the plain plan.
+struct PlanSplit {
+  int hot, Tb;
+  int* items;        // second table [., 3], or null
+  int* counts;       // [2]: its items, its distinct experts
+};
+
 __device__ int place_items(int c, int E, int T, int* __restrict__ items, int* __restrict__ counts,
-                           int (*wsum)[32]) {
+                           int (*wsum)[32], PlanSplit sp) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int tiles = (c + T - 1) / T;
-  int a = c, b = tiles, u = c > 0 ? 1 : 0;
+  const bool big = c >= sp.hot;
+  const int tiles = big ? 0 : (c + T - 1) / T;
+  const int btiles = big ? (c + sp.Tb - 1) / sp.Tb : 0;
+  int a = c, b = tiles, u = (c > 0 && !big) ? 1 : 0, bb = btiles | ((big ? 1 : 0) << 20);   // items and experts in one scan
 #pragma unroll
   for (int o = 1; o < 32; o <<= 1) {
     const int ua = __shfl_up_sync(0xffffffffu, a, o), ub = __shfl_up_sync(0xffffffffu, b, o);
-    const int uu = __shfl_up_sync(0xffffffffu, u, o);
+    const int uu = __shfl_up_sync(0xffffffffu, u, o), ubb = __shfl_up_sync(0xffffffffu, bb, o);
     if (lane >= o) {
       a += ua;
       b += ub;
       u += uu;
+      bb += ubb;
     }
   }
   if (lane == 31) {
     wsum[0][warp] = a;
     wsum[1][warp] = b;
     wsum[2][warp] = u;
+    wsum[3][warp] = bb;
   }
   __syncthreads();
-  if (warp < 3) {
+  if (warp < 4) {
     int vv = wsum[warp][lane];
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
@@ -311,17 +323,29 @@ __device__ int place_items(int c, int E, int T, int* __restrict__ items, int* __
   __syncthreads();
   const int off = (warp ? wsum[0][warp - 1] : 0) + a - c;
   const int ioff = (warp ? wsum[1][warp - 1] : 0) + b - tiles;
+  const int boff = (((warp ? wsum[3][warp - 1] : 0) + bb) & 0xFFFFF) - btiles;
   if (tid == 0) {
     counts[0] = wsum[1][31];
     counts[1] = wsum[2][31];
+    if (sp.counts != nullptr) {
+      sp.counts[0] = wsum[3][31] & 0xFFFFF;
+      sp.counts[1] = wsum[3][31] >> 20;
+    }
   }
-  if (tid < E)
+  if (tid < E) {
     for (int j = 0; j < tiles; ++j) {
       int* it = items + 3 * (ioff + j);
       it[0] = tid;
       it[1] = off + T * j;
       it[2] = min(T, c - T * j);
     }
+    for (int j = 0; j < btiles; ++j) {
+      int* it = sp.items + 3 * (boff + j);
+      it[0] = tid;
+      it[1] = off + sp.Tb * j;
+      it[2] = min(sp.Tb, c - sp.Tb * j);
+    }
+  }
   return off;
 }
 
@@ -339,7 +363,8 @@ __device__ __forceinline__ unsigned same_key_lanes(int e, bool ok, int nbits) {
 
 // The whole block: `picks` may live in global or shared memory.
 __device__ void plan_block(const int* picks, int P, int E, int T, int* __restrict__ members, int* __restrict__ items,
-                           int* __restrict__ counts, int* whist, int* first, int (*wsum)[32], int lo = 0) {
+                           int* __restrict__ counts, int* whist, int* first, int (*wsum)[32], int lo = 0,
+                           PlanSplit sp = PlanSplit{0x7FFFFFFF, 1, nullptr, nullptr}) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   for (int i = tid; i < 32 * E; i += PLAN_THREADS) whist[i] = 0;
   const int seg = (((P + 31) / 32 + 31) / 32) * 32;
@@ -372,7 +397,7 @@ __device__ void plan_block(const int* picks, int P, int E, int T, int* __restric
       whist[w * E + tid] = c;
       c += v;
     }
-  const int off = place_items(c, E, T, items, counts, wsum);
+  const int off = place_items(c, E, T, items, counts, wsum, sp);
   if (tid < E) first[tid] = off;
   __syncthreads();
   for (int base0 = p0; base0 < p1; base0 += 32 * PLAN_BATCH) {
@@ -400,12 +425,12 @@ __device__ void plan_block(const int* picks, int P, int E, int T, int* __restric
 
 __global__ void __launch_bounds__(PLAN_THREADS)
 plan_kernel(const int* __restrict__ picks, int P, int E, int T, int* __restrict__ members, int* __restrict__ items,
-            int* __restrict__ counts, int lo) {
+            int* __restrict__ counts, int lo, PlanSplit sp) {
   extern __shared__ int whist[];                 // [32][E]: pairs of expert e in warp w's run, then their first slot
   __shared__ int first[PLAN_EMAX];
-  __shared__ int wsum[3][32];
+  __shared__ int wsum[4][32];
   pdl_wait();
-  plan_block(picks, P, E, T, members, items, counts, whist, first, wsum, lo);
+  plan_block(picks, P, E, T, members, items, counts, whist, first, wsum, lo, sp);
   pdl_launch_dependents();
 }
 
@@ -418,7 +443,7 @@ select_plan_kernel(const float* __restrict__ L, int NL, int* __restrict__ pick, 
                    int* __restrict__ counts, int plan_lo, int plan_n) {
   extern __shared__ int dyn[];                   // whist [32][NP], then the picks [T * slots]
   __shared__ int first[PLAN_EMAX];
-  __shared__ int wsum[3][32];
+  __shared__ int wsum[4][32];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int slots = top_k + (shared ? 1 : 0);
   int* picks_sh = dyn + 32 * plan_n;
@@ -526,7 +551,8 @@ extern "C" int tfb_select_rows(const float* logits, int NL, int32_t* pick, float
 }
 
 static int plan_launch(const int32_t* picks, int64_t pairs, int lo, int experts, int tile, int32_t* members,
-                       int32_t* items, int32_t* counts, void* stream) {
+                       int32_t* items, int32_t* counts, void* stream,
+                       PlanSplit sp = PlanSplit{0x7FFFFFFF, 1, nullptr, nullptr}) {
   TFB_REQUIRE(picks && members && items && counts, "plan: null pointer");
   TFB_REQUIRE(experts >= 1 && experts <= PLAN_EMAX, "plan: at most %d experts, not %d", PLAN_EMAX, experts);
   TFB_REQUIRE(tile >= 1, "plan: items hold at least one pair");
@@ -542,7 +568,7 @@ static int plan_launch(const int32_t* picks, int64_t pairs, int lo, int experts,
     configured[dev] = 1;
   }
   return check_cuda(launch(plan_kernel, dim3(1), dim3(PLAN_THREADS), smem, static_cast<cudaStream_t>(stream), picks,
-                           (int)pairs, experts, tile, members, items, counts, lo),
+                           (int)pairs, experts, tile, members, items, counts, lo, sp),
                     "plan");
 }
 
@@ -578,6 +604,16 @@ extern "C" int tfb_plan_window(const int32_t* picks, int64_t pairs, int lo, int 
                                int32_t* items, int32_t* counts, void* stream) {
   TFB_REQUIRE(lo >= 0, "plan_window: the window starts at a non-negative id");
   return plan_launch(picks, pairs, lo, experts, tile, members, items, counts, stream);
+}
+
+extern "C" int tfb_plan_split(const int32_t* picks, int64_t pairs, int lo, int experts, int tile, int big_tile, int hot,
+                              int32_t* members, int32_t* items, int32_t* counts, int32_t* big_items,
+                              int32_t* big_counts, void* stream) {
+  TFB_REQUIRE(lo >= 0, "plan_split: the window starts at a non-negative id");
+  TFB_REQUIRE(big_items && big_counts, "plan_split: null pointer");
+  TFB_REQUIRE(big_tile >= 1 && hot >= 1 && pairs < (1 << 20), "plan_split: bad tile, threshold or pair count");
+  return plan_launch(picks, pairs, lo, experts, tile, members, items, counts, stream,
+                     PlanSplit{hot, big_tile, big_items, big_counts});
 }
 
 // Rows the fused selection + plan kernel takes (one block); larger calls use tfb_select_rows then tfb_plan.

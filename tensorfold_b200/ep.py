@@ -182,9 +182,9 @@ class GatheredExpertParallel:
 
         self.x_all = torch.zeros((rows, d), dtype=torch.bfloat16, device=dev)
         self.buf = moe.MoEBuffers(rows, _Cfg, dev, shared=False)
-        # about rows * k / experts pairs reach each local expert: from 12 on, items of 16 (one dequantisation for two
-        # mma tiles) beat two passes of items of 8; below that the leaner 8-pair kernel wins (measured at 8 an expert)
-        wide = rows * k >= 12 * experts
+        # about rows * k / experts pairs reach each local expert: from 24 on, items of 16 (one dequantisation for two
+        # mma tiles) beat two passes of items of 8; below that the leaner 8-pair kernel wins (measured at 8, 16 and 32)
+        wide = rows * k >= 24 * experts
         self.plan = grouped.Plan(rows, k, self.per_rank, dev, decode_tile=grouped.WIDE_TILE if wide else grouped.TILE)
         self.local_pick = torch.zeros((rows, k), dtype=torch.int32, device=dev)
         self.y_mine = torch.zeros((rows_local * k, d), dtype=torch.float32, device=dev)
@@ -354,7 +354,12 @@ class PeerExpertParallel:
     ``GatheredExpertParallel(reduce="tokens")`` up to fp32 summation order across ranks (here fixed: rank 0, 1, ...)."""
 
     def __init__(self, router_rows: torch.Tensor, local_experts, experts: int, top_k: int, rows_local: int,
-                 group=None, shared_experts=None, logit_bias: torch.Tensor | None = None) -> None:
+                 group=None, shared_experts=None, logit_bias: torch.Tensor | None = None, hot_pairs: int = 0) -> None:
+        """``hot_pairs`` > 0: a rank's experts with at least that many pairs run through the prompt-form kernel (one
+        pass over the expert's weights for up to 192 pairs) instead of one decode item per 8 pairs - for skewed
+        routing, where one rank's busiest experts otherwise set the step time.  Those pairs then carry the prompt
+        form's arithmetic (weights rounded once to bf16), so a token's bits depend on its experts' load."""
+
         from . import experts as grouped
         from . import moe
 
@@ -367,11 +372,11 @@ class PeerExpertParallel:
         dev, d, rows, slots = w.device, w.dims, w.rows, w.slots
         self.act = torch.zeros((rows * slots, local_experts.width), dtype=torch.bfloat16, device=dev)
         self.y = torch.zeros((rows * slots, d), dtype=torch.float32, device=dev)
-        wide = rows * top_k >= 12 * experts
+        wide = rows * top_k >= 24 * experts
         self.plan = grouped.Plan(rows, slots, w.per_rank, dev,
-                                 decode_tile=grouped.WIDE_TILE if wide else grouped.TILE)
+                                 decode_tile=grouped.WIDE_TILE if wide else grouped.TILE, hot=hot_pairs)
         self.out = torch.zeros((rows_local, d), dtype=torch.bfloat16, device=dev)
-        self.launches = 8                                         # + 1 when forward() is given rows to stage
+        self.launches = 8 + (2 if hot_pairs else 0)               # + 1 when forward() is given rows to stage
         if shared:
             if shared_experts.count != 1 or shared_experts.dims != d:
                 raise ValueError("shared_experts holds the one replicated expert of the layer's width")
@@ -397,8 +402,11 @@ class PeerExpertParallel:
                 g.gate_up(w.tokens, self.shared_ex, self.plan_s, self.act_s, self.rows_local)
                 g.down(self.act_s, self.shared_ex, self.plan_s, self.y_s, self.rows_local)
             w.gather()
-            _lib.call("tfb_plan_window", w.pick_all.data_ptr(), self.rows * w.slots, w.lo, w.per_rank, plan.tile,
-                      plan.members.data_ptr(), plan.items.data_ptr(), plan.counts.data_ptr(), st)
+            if plan.hot:
+                g.route_split(w.pick_all, plan, w.lo)
+            else:
+                _lib.call("tfb_plan_window", w.pick_all.data_ptr(), self.rows * w.slots, w.lo, w.per_rank, plan.tile,
+                          plan.members.data_ptr(), plan.items.data_ptr(), plan.counts.data_ptr(), st)
             g.gate_up(w.x_all, self.local, plan, self.act, self.rows)
             g.down(self.act, self.local, plan, self.y, self.rows)
             _lib.call("tfb_combine_push", self.y.data_ptr(), w.wts_all.data_ptr(), w.pick_all.data_ptr(), w.lo,

@@ -139,9 +139,14 @@ class Plan:
     """Scratch grouping pairs by expert: members, items (expert, first, count), counts [items, distinct experts]."""
 
     def __init__(self, rows: int, slots: int, experts: int, device: torch.device | str, *,
-                 prefill: bool = False, decode_tile: int = TILE) -> None:
+                 prefill: bool = False, decode_tile: int = TILE, hot: int = 0) -> None:
+        """``hot`` > 0 (decode plans only): experts with at least that many pairs are planned apart
+        (``route_split``) and run through the prompt-form kernel, the rest through the decode form."""
+
         if decode_tile not in (TILE, WIDE_TILE):
             raise ValueError(f"decode items hold {TILE} or {WIDE_TILE} pairs")
+        if hot and prefill:
+            raise ValueError("a prompt plan has no hot experts to set apart")
         pairs = rows * slots
         self.rows, self.slots, self.experts, self.prefill = rows, slots, experts, prefill
         self.decode_tile = decode_tile
@@ -149,6 +154,11 @@ class Plan:
         self.members = torch.zeros((pairs,), dtype=torch.int32, device=device)
         self.items = torch.zeros((max_items(pairs, experts, TILE), 3), dtype=torch.int32, device=device)
         self.counts = torch.zeros((2,), dtype=torch.int32, device=device)
+        self.hot = int(hot)
+        if self.hot:
+            big = max_items(pairs, experts, PREFILL_TILE)
+            self.big_items = torch.zeros((big, 3), dtype=torch.int32, device=device)
+            self.big_counts = torch.zeros((2,), dtype=torch.int32, device=device)
         self.rank = torch.zeros((1,), dtype=torch.int32, device=device)     # unused here; kept for the surface
         self.hist = torch.zeros((1,), dtype=torch.int32, device=device)
 
@@ -168,6 +178,31 @@ def route(picks: torch.Tensor, plan: Plan, tile: int = PREFILL_TILE) -> None:
     with torch.cuda.device(picks.device):
         _lib.call("tfb_plan", picks.data_ptr(), rows * slots, plan.experts, plan.tile, plan.members.data_ptr(),
                   plan.items.data_ptr(), plan.counts.data_ptr(), _stream(picks))
+
+
+def route_split(picks: torch.Tensor, plan: Plan, lo: int = 0) -> None:
+    """``route`` for a plan made with ``hot``: experts (ids ``lo .. lo + plan.experts``) with at least ``plan.hot``
+    pairs get items of up to ``PREFILL_TILE`` pairs in ``plan.big_items``; the others decode items in ``plan.items``."""
+
+    rows, slots = picks.shape
+    if not plan.hot:
+        raise ValueError("the plan was made without hot=")
+    if slots != plan.slots or rows > plan.rows or picks.dtype != torch.int32 or not picks.is_contiguous():
+        raise ValueError(f"picks {tuple(picks.shape)} do not fit a plan of {plan.rows} x {plan.slots}")
+    _need_cuda(picks, "picks")
+    plan.tile = plan.decode_tile
+    with torch.cuda.device(picks.device):
+        _lib.call("tfb_plan_split", picks.data_ptr(), rows * slots, lo, plan.experts, plan.tile, PREFILL_TILE, plan.hot,
+                  plan.members.data_ptr(), plan.items.data_ptr(), plan.counts.data_ptr(), plan.big_items.data_ptr(),
+                  plan.big_counts.data_ptr(), _stream(picks))
+
+
+class _BigPart:
+    """The hot experts' half of a split plan, shaped like a prompt plan for ``_run``."""
+
+    def __init__(self, plan: Plan) -> None:
+        self.items, self.counts, self.members = plan.big_items, plan.big_counts, plan.members
+        self.tile, self.slots, self.experts, self.prefill = PREFILL_TILE, plan.slots, plan.experts, True
 
 
 def _check_x(x: torch.Tensor, k: int) -> None:
@@ -204,6 +239,10 @@ def gate_up(x: torch.Tensor, ex: Experts, plan: Plan, out: torch.Tensor, rows: i
     epi = 2 if ex.swiglu else 1
     _run(epi, x, plan.slots, ex.up, ex.dims // ex.gs, ex.width // COLS, plan, out, ex.width, ex.limit, items, ex,
          plan.prefill)
+    if plan.hot:                                             # the hot experts' pairs: other rows of the same output
+        big = max_items(rows * plan.slots, plan.experts, PREFILL_TILE)
+        _run(epi, x, plan.slots, ex.up, ex.dims // ex.gs, ex.width // COLS, _BigPart(plan), out, ex.width, ex.limit,
+             big, ex, True)
 
 
 def down(act: torch.Tensor, ex: Experts, plan: Plan, out: torch.Tensor, rows: int) -> None:
@@ -212,3 +251,6 @@ def down(act: torch.Tensor, ex: Experts, plan: Plan, out: torch.Tensor, rows: in
     items = max_items(rows * plan.slots, plan.experts, plan.tile)
     epi = 3 if plan.prefill and out.dtype == torch.bfloat16 else 0
     _run(epi, act, 0, ex.down, ex.width // ex.gs, ex.dims // COLS, plan, out, ex.dims, 0.0, items, ex, plan.prefill)
+    if plan.hot:
+        big = max_items(rows * plan.slots, plan.experts, PREFILL_TILE)
+        _run(epi, act, 0, ex.down, ex.width // ex.gs, ex.dims // COLS, _BigPart(plan), out, ex.dims, 0.0, big, ex, True)

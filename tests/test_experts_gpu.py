@@ -292,3 +292,53 @@ def test_items_of_16_pairs_give_the_same_bits(case):
     experts.down(act16, ex, plan, y16, rows)
     assert torch.equal(act16, act) and torch.equal(y16, y)
     assert int(plan.counts[0]) < int(plan8.counts[0])
+
+
+def test_split_plan_sets_hot_experts_apart_and_keeps_the_cold_pairs_bits():
+    """``Plan(hot=)`` + ``route_split``: experts with at least ``hot`` pairs (here also under a window offset) get
+    prompt-form items, the rest decode items; cold pairs keep their bits, hot pairs stay within the layer tolerance."""
+
+    from tensorfold_b200 import experts
+
+    case = CASES[0]                                      # 41 experts incl. 1 shared
+    ex, _, _ = build(case, 51)
+    rows, hot = 60, 24
+    g = torch.Generator().manual_seed(5)
+    # expert 3 in every row, expert 7 in half of them, the rest spread thin; the shared expert (40) in every row
+    cols = []
+    for r in range(rows):
+        rest = (torch.randperm(30, generator=g)[:3] + 9).tolist()
+        cols.append([3, 7 if r % 2 == 0 else 8] + rest + [40])
+    picks = torch.tensor(cols, dtype=torch.int32, device=DEV)
+    slots = picks.shape[1]
+    x = (torch.randn((rows, ex.dims), device=DEV) * 0.5).to(torch.bfloat16)
+    _, y_plain, _ = run(ex, x, picks)
+    plan = experts.Plan(rows, slots, ex.count, DEV, hot=hot)
+    experts.route_split(picks, plan)
+    counts = np.bincount(picks.cpu().numpy().reshape(-1), minlength=ex.count)
+    n_small, n_big = plan.counts.cpu().tolist(), plan.big_counts.cpu().tolist()
+    hot_ids = [e for e in range(ex.count) if counts[e] >= hot]
+    assert sorted(hot_ids) == [3, 7, 8, 40]
+    assert n_big == [len(hot_ids), len(hot_ids)] and n_small[1] == int((counts > 0).sum()) - len(hot_ids)
+    big = plan.big_items[:n_big[0]].cpu().numpy()
+    small = plan.items[:n_small[0]].cpu().numpy()
+    assert big[:, 0].tolist() == hot_ids and big[:, 2].tolist() == [int(counts[e]) for e in hot_ids]
+    assert not set(small[:, 0].tolist()) & set(hot_ids) and (small[:, 2] <= plan.tile).all()
+    members = plan.members.cpu().numpy()
+    pk = picks.cpu().numpy().reshape(-1)
+    for e, first, cnt in list(big) + list(small):
+        mine = members[first:first + cnt]
+        assert (pk[mine] == e).all() and (np.diff(mine) > 0).all()
+    act = torch.zeros((rows * slots, ex.width), dtype=torch.bfloat16, device=DEV)
+    y = torch.zeros((rows * slots, ex.dims), dtype=torch.float32, device=DEV)
+    experts.gate_up(x, ex, plan, act, rows)
+    experts.down(act, ex, plan, y, rows)
+    cold = torch.from_numpy(~np.isin(pk, hot_ids)).to(DEV)
+    assert torch.equal(y[cold], y_plain[cold])
+    err = (y[~cold].double() - y_plain[~cold].double()).norm() / y_plain[~cold].double().norm()
+    assert 0 < err < 1e-2
+    # a window: only experts 8..39, renumbered from 0
+    sub = experts.Plan(rows, slots, 32, DEV, hot=hot)
+    experts.route_split(picks, sub, lo=8)
+    assert sub.big_items[:sub.big_counts[0].item(), 0].cpu().tolist() == [0]          # expert 8
+    assert int(sub.items[:sub.counts[0].item(), 2].sum()) + int(counts[8]) == int(counts[8:40].sum())
