@@ -436,10 +436,16 @@ def run_ours(args) -> None:
         raise SystemExit("bench.py needs a GPU: there is no CPU fallback (use --impl reference for the CPU baseline)")
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
-    if world > 1:
+    ep_path = world > 1 or args.config == "c4"        # config 4 always runs the expert-parallel code, also on one GPU
+    if ep_path:
         import torch.distributed as dist
 
-        dist.init_process_group("nccl", device_id=dev)
+        if world == 1:                                 # not under torchrun: a group of one
+            os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+            os.environ.setdefault("MASTER_PORT", "29533")
+            dist.init_process_group("nccl", rank=0, world_size=1, device_id=dev)
+        else:
+            dist.init_process_group("nccl", device_id=dev)
     hbm, tflops, which = peaks()
     _lib.set_pdl(bool(args.pdl))
     if args.exl3_only:
@@ -447,11 +453,11 @@ def run_ours(args) -> None:
         return
     shape, rows = (synthetic.C4 if args.config == "c4" else synthetic.C2), args.rows
     if args.config == "c4":
-        if world == 1 or args.ep_reduce != "peer":
-            raise SystemExit("--config c4 is the expert-parallel line: run it under torchrun with the peer-memory form")
+        if args.ep_reduce != "peer":
+            raise SystemExit("--config c4 runs the peer-memory form")
         rows = ep_rows(args, shape, world)
     layers = []
-    for copy in range(2 if world == 1 else 0):
+    for copy in range(0 if ep_path else 2):
         gate, up, down = synthetic.affine_layer(shape, dev, torch.float16 if args.scales == "fp16" else torch.bfloat16,
                                                  copy=copy)
         layers.append(moe.Routed(synthetic.router_rows(shape, dev), experts.make([gate, up], down, 64), shape.top_k,
@@ -459,7 +465,7 @@ def run_ours(args) -> None:
         del gate, up, down
     torch.cuda.synchronize()
 
-    if world > 1:
+    if ep_path:
         if shape.experts % world:
             raise SystemExit(f"{shape.experts} experts do not shard over {world} ranks")
         del layers

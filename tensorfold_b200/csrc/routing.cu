@@ -514,7 +514,9 @@ extern "C" int tfb_router(const void* x, int64_t x_stride, const void* rows, flo
   TFB_REQUIRE(D % 8 == 0 && x_stride % 8 == 0 && x_stride >= D, "router: D and the row stride must be multiples of 8");
   TFB_REQUIRE(aligned16(x) && aligned16(rows), "router: x and rows must be 16-byte aligned");
   if (T == 0) return TFB_OK;
-  if (T <= 256) {
+  // few rows: the row-form kernel (latency of two round trips); measured faster up to 64 rows x 128 experts and
+  // 32 rows x 257 experts, slower from twice that on (it re-reads the rows once an expert); the bits are the same
+  if ((int64_t)T * NE <= 8704) {
     const dim3 rgrid(NE, (T + RR_ROWS - 1) / RR_ROWS);
     return check_cuda(launch(router_rows_kernel, rgrid, dim3(RR_WARPS * 32), 0, static_cast<cudaStream_t>(stream),
                              static_cast<const __nv_bfloat16*>(x), x_stride,
