@@ -51,16 +51,22 @@ router_kernel(const __nv_bfloat16* __restrict__ X, int64_t x_stride, const __nv_
 #pragma unroll
     for (int r = 0; r < R_RT; ++r) xc[r] = xn[r];
     fetch(k + 256);
+    // two rows an instruction (fma.rn.f32x2: each half is the fmaf of its own row, in the same k order); rows past
+    // the last were fetched as zeros and are never stored
 #pragma unroll
-    for (int r = 0; r < R_RT; ++r) {
-      if (r < nr) {
-        float xv[8];
-        unpack8(xc[r], xv);
+    for (int r = 0; r < R_RT; r += 2) {
+      float xa[8], xb[8];
+      unpack8(xc[r], xa);
+      unpack8(xc[r + 1], xb);
 #pragma unroll
-        for (int e = 0; e < R_ET; ++e)
+      for (int e = 0; e < R_ET; ++e)
 #pragma unroll
-          for (int j = 0; j < 8; ++j) acc[r][e] = fmaf(xv[j], wv[e][j], acc[r][e]);
-      }
+        for (int j = 0; j < 8; ++j) {
+          const float2 d = ffma2(make_float2(xa[j], xb[j]), make_float2(wv[e][j], wv[e][j]),
+                                 make_float2(acc[r][e], acc[r + 1][e]));
+          acc[r][e] = d.x;
+          acc[r + 1][e] = d.y;
+        }
     }
   }
   pdl_launch_dependents();
