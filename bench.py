@@ -388,13 +388,16 @@ def bench_ep(torch, dist, args, shape, dev, rank: int, world: int):
     torch.cuda.synchronize()
     dist.barrier()
     host_graphs = []
-    for step, inp, layer in zip(steps, inputs, copies):    # the same step with its host copies as graph nodes
+    for step, inp, layer in zip(steps, inputs, copies):    # the same step with its host transfers inside the graph
         side.wait_stream(torch.cuda.current_stream())
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g, stream=side):
-            inp.copy_(x_host, non_blocking=True)
-            step()
-            out_host.copy_(layer.out, non_blocking=True)
+            if args.ep_reduce == "peer":                   # kernels read the pinned rows and store the pinned result
+                layer.forward(x_host, out_host)
+            else:
+                inp.copy_(x_host, non_blocking=True)
+                step()
+                out_host.copy_(layer.out, non_blocking=True)
         host_graphs.append(g)
     torch.cuda.synchronize()
     dist.barrier()

@@ -312,6 +312,10 @@ class PeerWindow:
 
         st = self._stream()
         if x_local is not None:
+            if tuple(x_local.shape) != tuple(self.tokens.shape) or x_local.dtype != torch.bfloat16:
+                raise ValueError("x_local must be bf16 [rows_local, D]")
+            if not x_local.is_cuda and not x_local.is_pinned():
+                raise ValueError("host rows must be in pinned memory (a kernel reads them)")
             x_local = x_local.contiguous()
             _lib.call("tfb_peer_stage", x_local.data_ptr(), self.window.data_ptr(), self.x_offset, self.x_bytes, st)
         moe.router(self.tokens, self.router_rows, self.logits)
@@ -389,10 +393,17 @@ class PeerExpertParallel:
             self.launches += 2
             torch.cuda.synchronize(dev)
 
-    def forward(self, x_local: torch.Tensor | None = None) -> torch.Tensor:
-        """``x_local`` [rows_local, D] bf16, or None when the caller has written its rows into ``self.tokens``."""
+    def forward(self, x_local: torch.Tensor | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
+        """``x_local`` [rows_local, D] bf16 (device memory, or pinned host memory that the staging kernel reads over
+        PCIe), or None when the caller has written its rows into ``self.tokens``.  ``out`` [rows_local, D] bf16:
+        where the last kernel stores the result (device or pinned host memory); default ``self.out``."""
 
         g, w, k, d = self.grouped, self.win, self.top_k, self.win.dims
+        out = self.out if out is None else out
+        if tuple(out.shape) != tuple(self.out.shape) or out.dtype != self.out.dtype or not out.is_contiguous():
+            raise ValueError("out must be contiguous bf16 [rows_local, D]")
+        if not out.is_cuda and not out.is_pinned():
+            raise ValueError("a host result buffer must be pinned memory (a kernel stores into it)")
         plan = self.plan
         plan.tile = plan.decode_tile
         with torch.cuda.device(w.device):
@@ -412,8 +423,8 @@ class PeerExpertParallel:
             _lib.call("tfb_combine_push", self.y.data_ptr(), w.wts_all.data_ptr(), w.pick_all.data_ptr(), w.lo,
                       w.per_rank, w.windows.data_ptr(), w.p_offset, w.rank, self.rows_local, self.rows, w.slots, d,
                       w.step.data_ptr(), st)
-            w.sum(self.out, self.y_s if self.shared_ex is not None else None)
-        return self.out
+            w.sum(out, self.y_s if self.shared_ex is not None else None)
+        return out
 
 
 class PeerExl3ExpertParallel:

@@ -221,9 +221,11 @@ class Runner:
         self.x.copy_(x, non_blocking=True)
         return self.replay()
 
-    def bind_host(self, x_host: torch.Tensor, out_host: torch.Tensor) -> None:
-        """Capture the step together with its copies from ``x_host`` and to ``out_host`` (both pinned host memory, the
-        caller's staging buffers): ``replay_host()`` is then one graph launch a step, copies included."""
+    def bind_host(self, x_host: torch.Tensor, out_host: torch.Tensor, direct: bool = True) -> None:
+        """Capture the step together with its transfers from ``x_host`` and to ``out_host`` (both pinned host memory,
+        the caller's staging buffers): ``replay_host()`` is then one graph launch a step, transfers included.
+        ``direct``: the rows are pulled from the pinned buffer by a kernel and the combine kernel stores the result
+        rows straight into the pinned buffer (no copy-engine nodes in the graph); else two memcpy nodes."""
 
         want = (self.rows, self.layer.experts.dims)
         for t in (x_host, out_host):
@@ -235,9 +237,16 @@ class Runner:
             self._stream.wait_stream(torch.cuda.current_stream(device))
             self.host_graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(self.host_graph, stream=self._stream):
-                self.x.copy_(x_host, non_blocking=True)
-                self._step()
-                out_host.copy_(self.out, non_blocking=True)
+                if direct:
+                    m = self.layer
+                    _lib.call("tfb_peer_stage", x_host.data_ptr(), self.x.data_ptr(), 0,
+                              self.x.numel() * self.x.element_size(), self._stream.cuda_stream)
+                    moe(self.x, m.router, m.experts, self.buf, m.top_k, m.count)
+                    combine(self.buf.y[:self.rows], self.buf.wts[:self.rows], out_host)
+                else:
+                    self.x.copy_(x_host, non_blocking=True)
+                    self._step()
+                    out_host.copy_(self.out, non_blocking=True)
 
     def replay_host(self) -> torch.Tensor:
         """Tokens from the bound host buffer through the layer into the bound host buffer (asynchronous: synchronise

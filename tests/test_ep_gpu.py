@@ -110,6 +110,11 @@ def _peer_body(rank, world, port, out):
         flags.append(bool(torch.equal(peer.out, nccl.forward(x))))
     del graph
     torch.cuda.synchronize()
+    # rows read from and results stored to pinned host memory by the kernels themselves
+    x_pin, out_pin = xs[0].cpu().pin_memory(), torch.zeros((rows, shape.dims), dtype=torch.bfloat16).pin_memory()
+    peer.forward(x_pin, out_pin)
+    torch.cuda.synchronize()
+    flags.append(bool(torch.equal(out_pin, nccl.forward(xs[0]).cpu())))
 
     # a layer with a shared expert: replicated, run on the own rows, joined in the final sum
     sh = synthetic.SMALL_SHARED

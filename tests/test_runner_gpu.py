@@ -7,8 +7,9 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
+@pytest.mark.parametrize("direct", [True, False])
 @pytest.mark.parametrize("rows", [5, 32, 33, 70])
-def test_replay_equals_eager_and_host_bound(rows):
+def test_replay_equals_eager_and_host_bound(rows, direct):
     from tensorfold_b200 import experts, moe, synthetic
 
     dev = torch.device("cuda", 0)
@@ -19,7 +20,7 @@ def test_replay_equals_eager_and_host_bound(rows):
     runner = moe.Runner(layer, rows)
     x_host = torch.empty((rows, shape.dims), dtype=torch.bfloat16).pin_memory()
     out_host = torch.zeros((rows, shape.dims), dtype=torch.bfloat16).pin_memory()
-    runner.bind_host(x_host, out_host)
+    runner.bind_host(x_host, out_host, direct=direct)
     for index in (11, 12):                                  # the replays follow the new rows' experts
         x = synthetic.activations(shape, rows, dev, index=index)
         want = moe.run(x, layer)
