@@ -3,7 +3,8 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--rows T]
 
 Workload: BASELINE config 2 - one layer, hidden 2048, 128 experts of width 768, top-8 - at 64-token decode (the
-headline line), with 1-token decode and the 2048-token prompt reported beside it under "sweep".  One step = one pass of
+headline line), with 1-, 4- and 16-token decode, the 2048-token prompt and the EXL3 layer (config 3) beside it under
+"sweep"; `--gpus N` (torchrun) times the expert-parallel step, `--config c4` the large skewed layer.  One step = one pass of
 the whole layer (router, top-k, plan, gate/up + SiLU-gate, down, combine) over one batch of seeded synthetic tokens.
 Two independent weight copies (340 MB each, together far beyond the 126 MB L2) alternate step by step.
 
@@ -519,7 +520,7 @@ def run_ours(args) -> None:
     sweep = []
     if world == 1 and not args.no_sweep:
         del runners
-        for t_rows, pre in ((1, False), (2048, True)):
+        for t_rows, pre in ((1, False), (4, False), (16, False), (2048, True)):
             res, rr = bench_rows(torch, shape, layers, t_rows, max(5, args.steps // 2), args.warmup, hbm, pre, tflops)
             res.setdefault("form", "decode")
             sweep.append(res)
@@ -574,7 +575,7 @@ def main() -> None:
                     help="expert-parallel peer form: experts with at least this many pairs use the prompt-form kernel "
                          "(default 0: never)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--no-sweep", action="store_true", help="skip the 1-token and 2048-token lines")
+    ap.add_argument("--no-sweep", action="store_true", help="skip the 1-, 4-, 16- and 2048-token lines")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
