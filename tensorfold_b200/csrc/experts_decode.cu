@@ -4,8 +4,9 @@
 // blocks).  A column block's packed weights for one expert are one contiguous run of KG * M blocks in HBM.  The four
 // warps are KW K-slices times CBC = 4 / KW column blocks (KW is a function of the shape only); each warp pulls its run
 // through a private shared-memory ring with bulk async copies (one elected lane issues; a slot holds G groups fetched
-// by one copy a column block, an mbarrier a slot), so many kilobytes a warp are in flight while the lanes compute.  The weights are the mma A operand (16 columns x 16 inputs a fragment, read
-// from shared memory as one 128-bit word a lane), the pairs' inputs the B operand (8 pairs).  Nibbles become the
+// by one copy a column block, an mbarrier a slot), so many kilobytes a warp are in flight while the lanes compute.
+// The weights are the mma A operand (16 columns x 16 inputs a fragment, read from shared memory as one 128-bit word a
+// lane), the pairs' inputs the B operand (8 pairs).  Nibbles become the
 // exact bf16 values 128 + q with a shift and one lop3; the 128 is taken out again per group in fp32:
 // acc += s * sum((128 + q) x) + (b - 128 s) * sum(x), with sum(x) from an all-ones mma.  K-slices meet in shared
 // memory in slice order, so a pair's bits depend on nothing but its own row.

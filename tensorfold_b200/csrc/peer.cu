@@ -10,8 +10,9 @@
 // which every peer signals after its pull; peers overwrite a rank's result buffer only after they passed the next
 // tokens barrier, which the rank signals after its sum.  Barrier numbers come from a device-side step counter, so a
 // step can be replayed from a CUDA graph.  Every wait is bounded (about a second): on a time-out the device status
-// word is set and the kernel goes on (its output is then meaningless; the host reads the status).  (No counterpart in the reference, which has no expert parallelism:
-// src/tensorfold/cuda/comm.py is a 2-rank all-gather.)
+// word is set and the kernel goes on (its output is then meaningless; the host reads the status).
+// (No counterpart in the reference, which has no expert parallelism: src/tensorfold/cuda/comm.py is a 2-rank
+// all-gather.)
 
 #include "api.h"
 #include "common.cuh"
