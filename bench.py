@@ -155,6 +155,12 @@ def run_reference(args) -> None:
 
 
 def workload_config(shape, rows: int, gpus: int, config: str = "c2") -> dict:
+    if config == "c5":
+        return {"workload": f"BASELINE config 5: 8 MoE layers with bf16 residual adds, {rows * gpus} tokens over the "
+                            f"ranks, hidden {shape.dims}, {shape.experts} experts x FFN {shape.width}, "
+                            f"top-{shape.top_k}, EXL3 experts at a seeded 2..8 bits a tensor (3inst)",
+                "rows_per_gpu": rows, "l2": "the 8 layers' weights of a rank (15 GB / ranks) cycle every step",
+                "parallelism": f"ep{gpus}" if gpus > 1 else "single"}
     what = (f"BASELINE config 4: one MoE layer, {rows * gpus} tokens over the ranks, Zipf-skewed router, one replicated "
             "shared expert," if config == "c4" else f"BASELINE config 2: one MoE layer, {rows}-token decode,")
     return {"workload": f"{what} hidden {shape.dims}, {shape.experts} "
@@ -429,6 +435,91 @@ def bench_ep(torch, dist, args, shape, dev, rank: int, world: int):
     return ms, e2e_ms, layer.launches, nbytes
 
 
+def bench_c5(torch, dist, args, dev, rank: int, world: int):
+    """Config 5 on the expert-parallel EXL3 path: 8 layers (hidden 4096, 160 experts x FFN 1536, top-8, a seeded width
+    of 2..8 bits a tensor), 128 tokens split over the ranks, `h = bf16(h + moe(h))` between layers; one step = the
+    8-layer stack in one CUDA graph.  A rank holds only its experts (1.9 GB over the 8 layers at 8 ranks, so no layer's
+    weights survive in L2 from step to step).  Returns (ms a step, ms end to end, launches, rank-0 bytes, rows)."""
+
+    import random
+
+    from tensorfold_b200 import ep, synthetic
+    from tensorfold_b200.exl3 import experts as x3
+
+    shape, layers_n, tokens = synthetic.C5, 8, 128
+    rows, per = tokens // world, shape.experts // world
+    rng = random.Random(5005)
+    widths = {(li, e, m): rng.choice((2, 3, 4, 5, 6, 7, 8)) for li in range(layers_n) for e in range(shape.experts)
+              for m in range(3)}                                  # every rank draws all widths in the same order
+    router = synthetic.router_rows(shape, dev)
+    layers = []
+    for li in range(layers_n):
+        base = 1000 * shape.config + 10 + 1000003 * li
+        gate, up, down = [], [], []
+        for e in range(rank * per, (rank + 1) * per):
+            gate.append(synthetic.exl3_matrix(base + 3 * e, shape.dims, shape.width, widths[(li, e, 0)], dev))
+            up.append(synthetic.exl3_matrix(base + 3 * e + 1, shape.dims, shape.width, widths[(li, e, 1)], dev))
+            down.append(synthetic.exl3_matrix(base + 3 * e + 2, shape.width, shape.dims, widths[(li, e, 2)], dev))
+        ex = x3.prepare(gate, up, down, x3.CB_3INST, device=dev)
+        layers.append(ep.PeerExl3ExpertParallel(router, ex, shape.experts, shape.top_k, rows))
+    x = synthetic.activations(shape, rows, dev, index=100 + rank)
+    h_out = torch.zeros_like(x)
+
+    def step(src):
+        h = src
+        for li, layer in enumerate(layers):
+            y = layer.forward(h)                                  # fp32 [rows, D]
+            if li == 0:
+                h = layer.tokens                                  # the staged rows (src may be pinned host memory)
+            h = (h.float() + y).to(torch.bfloat16)                # the residual add between layers
+        h_out.copy_(h)
+
+    step(x)
+    torch.cuda.synchronize()
+    dist.barrier()
+    side = torch.cuda.Stream(dev)
+    side.wait_stream(torch.cuda.current_stream())
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        step(x)
+    x_host = x.cpu().pin_memory()
+    out_host = torch.empty((rows, shape.dims), dtype=torch.bfloat16).pin_memory()
+    side.wait_stream(torch.cuda.current_stream())
+    host_graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(host_graph, stream=side):
+        step(x_host)
+        out_host.copy_(h_out, non_blocking=True)
+    torch.cuda.synchronize()
+    dist.barrier()
+
+    def timed(g, sync_each):
+        for _ in range(args.warmup):
+            g.replay()
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(args.steps):
+            g.replay()
+            if sync_each:
+                torch.cuda.current_stream().synchronize()
+        b.record()
+        torch.cuda.synchronize()
+        dist.barrier()
+        return a.elapsed_time(b) / args.steps
+
+    ms, e2e_ms = timed(graph, False), timed(host_graph, True)
+    nbytes = layers_n * (router.numel() * 2) + 2 * rows * shape.dims * 2
+    for layer in layers:
+        w = layer.win
+        mine = w.pick_all.reshape(-1)
+        mine = torch.unique(mine[(mine >= w.lo) & (mine < w.lo + w.per_rank)]) - w.lo
+        nbytes += layer.local.nbytes_read(mine.cpu().tolist())
+    launches = sum(layer.launches for layer in layers) + 3 * layers_n + 1
+    return ms, e2e_ms, launches, nbytes, rows
+
+
 def run_ours(args) -> None:
     import torch
 
@@ -440,7 +531,7 @@ def run_ours(args) -> None:
         raise SystemExit("bench.py needs a GPU: there is no CPU fallback (use --impl reference for the CPU baseline)")
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
-    ep_path = world > 1 or args.config == "c4"        # config 4 always runs the expert-parallel code, also on one GPU
+    ep_path = world > 1 or args.config in ("c4", "c5")   # configs 4 and 5 always run the expert-parallel code
     if ep_path:
         import torch.distributed as dist
 
@@ -455,7 +546,10 @@ def run_ours(args) -> None:
     if args.exl3_only:
         print(json.dumps({"sweep": bench_exl3(torch, (1, 64), args.steps, args.warmup, hbm)}))
         return
-    shape, rows = (synthetic.C4 if args.config == "c4" else synthetic.C2), args.rows
+    shape, rows = (synthetic.C4 if args.config == "c4" else synthetic.C5 if args.config == "c5" else synthetic.C2), \
+        args.rows
+    if args.config == "c5" and args.ep_reduce != "peer":
+        raise SystemExit("--config c5 runs the peer-memory form")
     if args.config == "c4":
         if args.ep_reduce != "peer":
             raise SystemExit("--config c4 runs the peer-memory form")
@@ -474,7 +568,10 @@ def run_ours(args) -> None:
             raise SystemExit(f"{shape.experts} experts do not shard over {world} ranks")
         del layers
         with ClockSampler(local) as clocks:
-            ms, e2e_ms, launches, rank_bytes = bench_ep(torch, dist, args, shape, dev, rank, world)
+            if args.config == "c5":
+                ms, e2e_ms, launches, rank_bytes, rows = bench_c5(torch, dist, args, dev, rank, world)
+            else:
+                ms, e2e_ms, launches, rank_bytes = bench_ep(torch, dist, args, shape, dev, rank, world)
         t = torch.tensor([ms, e2e_ms], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms, e2e_ms = t.tolist()
@@ -485,10 +582,12 @@ def run_ours(args) -> None:
             nbytes = rows * shape.dims * 2 * world
             line = {"metric": METRIC, "value": world * rows / (ms * 1e-3), "unit": UNIT, "n_gpus": world,
                     "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
-                    "scaling": "strong" if args.config == "c4" else "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+                    "scaling": "weak" if args.config == "c2" else "strong", "vs_baseline": None,
+                    "dtype": "f16" if args.config == "c5" else "bf16", "data": "synthetic",
                     "config": {**workload_config(shape, rows, world, args.config),
-                               "l2": f"each rank rotates {ep_copies(args, world)} copies of its "
-                                     f"{shape.experts // world}-expert slice (inputs larger than the 126 MB L2)",
+                               **({} if args.config == "c5" else {
+                                   "l2": f"each rank rotates {ep_copies(args, world)} copies of its "
+                                         f"{shape.experts // world}-expert slice (inputs larger than the 126 MB L2)"}),
                                "collective": COLLECTIVE[args.ep_reduce] + "; the step is one CUDA graph",
                                "hot_pairs": hot_pairs(args)},
                     "clocks": clocks.summary(),
@@ -569,9 +668,10 @@ def main() -> None:
     ap.add_argument("--ep-reduce", default="peer", choices=["tokens", "rows", "peer"],
                     help="multi-GPU exchanges: own kernels over NVLink peer memory (default), or NCCL with per-token "
                          "partial sums / exact per-pair rows")
-    ap.add_argument("--config", default="c2", choices=["c2", "c4"],
+    ap.add_argument("--config", default="c2", choices=["c2", "c4", "c5"],
                     help="c2: the headline layer (default); c4: the 256-expert layer with a shared expert and skewed "
-                         "routing, 256 tokens split over the ranks (multi-GPU only)")
+                         "routing, 256 tokens split over the ranks; c5: the 8-layer mixed-width EXL3 stack, 128 tokens "
+                         "split over the ranks")
     ap.add_argument("--hot-pairs", type=int, default=-1,
                     help="expert-parallel peer form: experts with at least this many pairs use the prompt-form kernel "
                          "(default 0: never)")
