@@ -1,18 +1,20 @@
-"""Makes ``exl3_golden.npz`` from the REFERENCE's own decoder (run where the reference tree is mounted):
+"""Makes ``exl3_golden.npz`` from the REFERENCE's own decoder (run where the reference tree is mounted; its root is
+taken from ``TENSORFOLD_REFERENCE``, the same variable ``oracle/build_ref.py`` reads):
 
-    PYTHONPATH=/root/reference/src python tests/golden/make_exl3_golden.py
+    python tests/golden/make_exl3_golden.py
 
 For every codebook and every width the reference's format module accepts it stores a small random trellis and the
 W_q bits ``tensorfold.cuda.exl3.format.unpack`` returns for it, plus codebook spot values and one rotated forward.
 The tests compare the oracle restatement (and, on the GPU, the kernels) with these arrays.
 """
 
+import os
 import sys
 from pathlib import Path
 
 import numpy as np
 
-sys.path.insert(0, "/root/reference/src")
+sys.path.insert(0, os.path.join(os.environ.get("TENSORFOLD_REFERENCE", "/root/reference"), "src"))
 from tensorfold.cuda.exl3 import format as fmt  # noqa: E402
 
 out = {}
