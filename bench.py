@@ -347,9 +347,25 @@ def bench_ep(torch, dist, args, shape, dev, rank: int, world: int):
         local = cut(slice(rank * per, (rank + 1) * per))
         if args.ep_reduce == "peer":
             shared = cut(slice(shape.experts, shape.experts + 1)) if shape.shared else None
-            copies.append(ep.PeerExpertParallel(router, local, shape.experts, shape.top_k, rows,
-                                                shared_experts=shared, logit_bias=bias,
-                                                hot_pairs=hot_pairs(args)))
+            layer, why = None, ""
+            try:
+                layer = ep.PeerExpertParallel(router, local, shape.experts, shape.top_k, rows, shared_experts=shared,
+                                              logit_bias=bias, hot_pairs=hot_pairs(args))
+            except Exception as err:                       # e.g. peer mappings refused on this machine
+                why = repr(err)
+            failed = torch.tensor([0 if layer is not None else 1], device=dev)
+            dist.all_reduce(failed, op=dist.ReduceOp.MAX)
+            if int(failed.item()) and copy == 0 and args.config == "c2":
+                # said loudly and recorded in the line: the same data flow through NCCL, still this library's kernels
+                print(f"[bench] rank {rank}: peer windows unavailable ({why or 'on another rank'}); "
+                      "falling back to --ep-reduce tokens", file=sys.stderr)
+                args.ep_reduce = "tokens"
+                copies.append(ep.GatheredExpertParallel(router, local, shape.experts, shape.top_k, rows,
+                                                        reduce="tokens"))
+            elif int(failed.item()):
+                raise SystemExit(f"peer windows unavailable: {why or 'on another rank'}")
+            else:
+                copies.append(layer)
         else:
             copies.append(ep.GatheredExpertParallel(router, local, shape.experts, shape.top_k, rows,
                                                     reduce=args.ep_reduce))
