@@ -174,14 +174,17 @@ grouped_kernel(const __half* __restrict__ X0, const __half* __restrict__ X1, con
   __shared__ float red[GR_WARPS][GR_PAIRS][GR_NTB * 16 + 1];
   pdl_wait();
   const int u = blockIdx.x;
-  if (u >= ucount[0]) return;
   const int mtile = blockIdx.z % mtiles, mat = blockIdx.z / mtiles;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  // the count and the tile's members are read together (row u exists in the table for every u of the grid): most
+  // CTAs of a grid sized for the worst case find nothing and leave after one round trip, not two
+  const int n_u = ucount[0];
   if (threadIdx.x < GR_PAIRS) {
     const int m = mtile * GR_PAIRS + threadIdx.x;
     const int code = m < maxm ? members[(size_t)u * maxm + m] : -1;
     rows_sh[threadIdx.x] = code >= 0 ? (code >> 5) * slots + (code & 31) : -1;
   }
+  if (u >= n_u) return;
   __syncthreads();
   if (rows_sh[0] < 0) return;                         // members come first: this pair tile is empty
   const int e = uids[u];
