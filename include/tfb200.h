@@ -30,10 +30,19 @@ int tfb_version(void);
  * wait on the device before touching memory).  Returns the previous setting.  Off by default. */
 int tfb_set_pdl(int on);
 
-/* Reads and clears the current device's status word into *status (0: every bounded wait completed; 1: a wait ran out
- * and the kernel returned early).  Synchronises `stream`.  No reference counterpart: the reference traps instead
- * (src/tensorfold/cuda/exl3/experts_grouped.cuh:240,259). */
+/* Reads and clears the current device's status word into *status; synchronises `stream`.  0: every bounded wait
+ * completed.  Otherwise code | where << 8 | rank << 16: code 1 = a bounded wait ran out and the kernel returned early,
+ * 2 = a table held an index no kernel exists for; where (code 1) 0 = a kernel's own copy pipeline, 1 = the tokens
+ * barrier of an expert-parallel step, 2 = its results barrier; rank (where 1, 2) = the lowest rank that had not
+ * arrived.  After a barrier time-out the kernels of that step leave the peers' memory alone and its output is void.
+ * The trap's counterpart (src/tensorfold/cuda/exl3/experts_grouped.cuh:240,259) and, for the barriers, the named
+ * missing rank of NCCL.ready (src/tensorfold/cuda/comm.py:78-101). */
 int tfb_kernel_status(int* status, void* stream);
+
+/* Milliseconds an expert-parallel barrier waits for the other ranks before it gives up (1 .. 600000; 1000 unless
+ * set); returns the previous limit, or -1 with a message.  Read at launch (and at graph capture).  Counterpart of the
+ * `timeout` of NCCL.ready (src/tensorfold/cuda/comm.py:78). */
+int tfb_set_wait_limit_ms(int ms);
 
 /* ---- routing ------------------------------------------------------------------------------------------------- */
 
@@ -98,8 +107,10 @@ int tfb_combine_window(const void* y, int y_bf16, const float* wts, const int32_
  *   [tfb_peer_stage, or the caller writes its tokens into the window]  router and selection of the rank's own rows,
  *   written into the window   tfb_peer_gather (tokens barrier, then pull)   plan of the rank's experts   gate/up
  *   down   tfb_combine_push   tfb_peer_sum (results barrier, then sum in rank order).
- * A barrier's wait gives up after about a second and sets the device status word (tfb_kernel_status); it needs every
- * rank's kernel to be running at the same time, so the ranks must be separate GPUs. */
+ * A barrier's wait gives up after tfb_set_wait_limit_ms and records the barrier and the missing rank in the device
+ * status word; from then on the step's kernels touch no peer memory.  Read tfb_kernel_status after a step before its
+ * output is used.  A barrier needs every rank's kernel to be running at the same time, so the ranks must be separate
+ * GPUs. */
 int tfb_peer_stage(const void* x_local, void* window, int64_t x_offset, int64_t x_bytes, void* stream);
 /* nseg <= 4 regions (host arrays): seg_dst[s][r * seg_bytes[s] ...] <- rank r's window + seg_offset[s], every r. */
 int tfb_peer_gather(void* const* windows, int rank, int world, int nseg, const int64_t* seg_offset,

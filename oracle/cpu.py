@@ -15,6 +15,12 @@ class Matrix(Structure):
     _fields_ = [("words", c_void_p), ("scales", c_void_p), ("biases", c_void_p)]
 
 
+class Exl3Matrices(Structure):
+    """One projection of every expert: arrays of E pointers (trellis, suh, svh) and E half-bit widths."""
+
+    _fields_ = [("trellis", c_void_p), ("k2", c_void_p), ("suh", c_void_p), ("svh", c_void_p)]
+
+
 @lru_cache(maxsize=1)
 def lib() -> ctypes.CDLL:
     h = ctypes.CDLL(str(_build.build()))
@@ -36,6 +42,11 @@ def lib() -> ctypes.CDLL:
     h.tfo_moe_layer.restype = c_int
     h.tfo_threads.restype = c_int
     h.tfo_set_threads.argtypes = (c_int,)
+    h.tfo_exl3_unpack.argtypes = (c_void_p, c_int, c_int, c_int, c_int, c_void_p)
+    h.tfo_exl3_unpack.restype = None
+    h.tfo_exl3_routed.argtypes = (c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, Exl3Matrices,
+                                  Exl3Matrices, Exl3Matrices, c_int, c_void_p)
+    h.tfo_exl3_routed.restype = c_int
     return h
 
 
@@ -132,3 +143,47 @@ def moe_layer(x_bits, router_bits, experts: int, top_k: int, shared: bool, gate,
     if rc != 0:
         raise MemoryError("oracle moe_layer ran out of memory")
     return (out, pick, wts, act, y) if want_parts else out
+
+
+def exl3_unpack(trellis: np.ndarray, cb: int) -> np.ndarray:
+    """W_q [K, N] fp16 of a trellis int16 [K/16, N/16, 8 * k2] (the C twin of ``oracle.exl3.unpack``)."""
+
+    t = np.ascontiguousarray(trellis).view(np.uint16)
+    k, n, k2 = t.shape[0] * 16, t.shape[1] * 16, t.shape[2] // 8
+    out = np.empty((k, n), dtype=np.uint16)
+    lib().tfo_exl3_unpack(_p(t), k, n, k2, cb, _p(out))
+    return out.view(np.float16)
+
+
+def _exl3_table(mats, keep):
+    """mats: per expert (trellis int16, suh fp16, svh fp16), or None for an expert no row uses."""
+
+    e = len(mats)
+    ptrs = [np.zeros(e, dtype=np.uint64) for _ in range(3)]
+    k2 = np.zeros(e, dtype=np.int32)
+    for i, m in enumerate(mats):
+        if m is None:
+            continue
+        arrs = (np.ascontiguousarray(m[0]).view(np.uint16), np.ascontiguousarray(m[1]).view(np.uint16),
+                np.ascontiguousarray(m[2]).view(np.uint16))
+        keep.append(arrs)
+        for j in range(3):
+            ptrs[j][i] = arrs[j].ctypes.data
+        k2[i] = arrs[0].shape[-1] // 8
+    keep.extend(ptrs + [k2])
+    return Exl3Matrices(ptrs[0].ctypes.data, k2.ctypes.data, ptrs[1].ctypes.data, ptrs[2].ctypes.data)
+
+
+def exl3_routed(x: np.ndarray, pick: np.ndarray, wts: np.ndarray, gate, up, down, cb: int, dims: int,
+                width: int) -> np.ndarray:
+    """The routed EXL3 layer in fp32 on the host cores (the C twin of ``oracle.exl3.routed``): out [R, D]."""
+
+    xf, pk, w = _c(np.asarray(x, dtype=np.float32), np.float32), _c(pick, np.int32), _c(wts, np.float32)
+    r, slots = pk.shape
+    keep: list = []
+    out = np.empty((r, dims), dtype=np.float32)
+    rc = lib().tfo_exl3_routed(_p(xf), _p(pk), _p(w), r, slots, len(gate), dims, width, _exl3_table(gate, keep),
+                               _exl3_table(up, keep), _exl3_table(down, keep), cb, _p(out))
+    if rc != 0:
+        raise MemoryError("tfo_exl3_routed: out of memory")
+    return out

@@ -63,6 +63,8 @@ def lib() -> ctypes.CDLL:
     handle.tfb_version.restype = c_int
     handle.tfb_set_pdl.argtypes = (c_int,)
     handle.tfb_set_pdl.restype = c_int
+    handle.tfb_set_wait_limit_ms.argtypes = (c_int,)
+    handle.tfb_set_wait_limit_ms.restype = c_int
     handle.tfb_select_plan_max_rows.restype = c_int
     handle.tfb_select_plan_max_rows.argtypes = ()
     for name, args in SIGNATURES.items():
@@ -95,3 +97,46 @@ def kernel_status(stream: int = 0) -> int:
 
 def set_pdl(on: bool) -> bool:
     return bool(lib().tfb_set_pdl(1 if on else 0))
+
+
+def set_wait_limit_ms(ms: int) -> int:
+    """How long an expert-parallel barrier waits for the other ranks; returns the previous limit."""
+
+    was = lib().tfb_set_wait_limit_ms(int(ms))
+    if was < 0:
+        raise ValueError(lib().tfb_last_error().decode("utf-8", "replace"))
+    return was
+
+
+ST_WAIT_TIMEOUT, ST_BAD_INDEX = 1, 2
+_WHERE = {0: "a kernel's copy pipeline", 1: "the tokens barrier", 2: "the results barrier"}
+
+
+def describe_status(status: int) -> str:
+    """The status word in words: which wait ran out and, for a barrier between ranks, which rank never arrived."""
+
+    if status == 0:
+        return "ok"
+    code, where, rank = status & 0xFF, (status >> 8) & 0xFF, (status >> 16) & 0xFF
+    if code == ST_WAIT_TIMEOUT:
+        text = f"a bounded wait ran out at {_WHERE.get(where, f'site {where}')}"
+        return text + (f": rank {rank} had not arrived" if where in (1, 2) else "")
+    if code == ST_BAD_INDEX:
+        return "a table held an index no kernel exists for"
+    return f"unknown status word {status:#x}"
+
+
+class StepFailed(RuntimeError):
+    """A kernel recorded a failure on the device; ``status`` is the word ``describe_status`` reads."""
+
+    def __init__(self, status: int) -> None:
+        super().__init__(describe_status(status))
+        self.status = status
+
+
+def check_status(stream: int = 0) -> None:
+    """Raise ``StepFailed`` unless every kernel since the last read completed its waits."""
+
+    status = kernel_status(stream)
+    if status != 0:
+        raise StepFailed(status)

@@ -8,6 +8,9 @@
 namespace tfb {
 
 int g_use_pdl = 0;
+static int g_wait_limit_ms = 1000;
+
+uint64_t wait_limit_ns() { return (uint64_t)g_wait_limit_ms * 1000000ull; }
 
 static thread_local char g_error[512] = "";
 
@@ -30,6 +33,17 @@ extern "C" int tfb_version(void) { return 1; }
 extern "C" int tfb_set_pdl(int on) {
   const int was = g_use_pdl;
   g_use_pdl = on ? 1 : 0;
+  return was;
+}
+
+// Sets how long the barriers of an expert-parallel step (csrc/peer.cu) wait for the other ranks, in milliseconds
+// (1 .. 600000; one second unless set); returns the previous limit, or -1 for a value out of range.  The limit is read
+// when a step is launched or captured.  Long enough for the slowest rank's host to reach its launch (first calls,
+// graph instantiation), short enough that a rank that died is reported instead of waited for.
+extern "C" int tfb_set_wait_limit_ms(int ms) {
+  if (ms < 1 || ms > 600000) return fail(TFB_ERR_ARG, "set_wait_limit_ms: %d ms outside 1..600000", ms);
+  const int was = g_wait_limit_ms;
+  g_wait_limit_ms = ms;
   return was;
 }
 

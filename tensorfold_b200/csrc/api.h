@@ -30,6 +30,9 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 // one before it in the stream drains, and waits (griddepcontrol.wait) before it touches global memory.
 extern int g_use_pdl;
 
+// How long a barrier between expert-parallel ranks waits before it gives up (tfb_set_wait_limit_ms), in nanoseconds.
+uint64_t wait_limit_ns();
+
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
                           Args... args) {

@@ -91,8 +91,13 @@ __device__ __forceinline__ float2 sb_pair(uint32_t v) {
 }
 
 // ---- device status word -----------------------------------------------------------------------------------------
-// Kernels never trap: a wait that runs out records a code here and the kernel returns; the host reads it.
+// Kernels never trap: a wait that runs out records a word here and the kernel returns; the host reads it.
+// Word = code | where << 8 | rank << 16.  code: 1 a bounded wait ran out, 2 a table held an index no kernel exists
+// for.  where (time-outs): 0 a kernel's own copy pipeline (mbarrier), 1 the tokens barrier of an expert-parallel step,
+// 2 its results barrier.  rank (barriers): the lowest rank whose flag had not arrived.  The first failure stays until
+// the host reads the word (tfb_kernel_status), which clears it.
 enum KernelStatus : int { ST_OK = 0, ST_WAIT_TIMEOUT = 1, ST_BAD_INDEX = 2 };
+__host__ __device__ constexpr int status_word(int code, int where, int rank) { return code | (where << 8) | (rank << 16); }
 static __device__ int g_kernel_status = 0;   // one copy: the library is built as a single translation unit
 
 // ---- mbarrier / bulk copy (non-multicast) -----------------------------------------------------------------------
@@ -145,19 +150,31 @@ __device__ __forceinline__ uint64_t global_ns() {
   return t;
 }
 
-// Bounded wait: gives up after about a second, records ST_WAIT_TIMEOUT and returns false.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+// Bounded wait: false once `limit_ns` has passed (nothing is recorded).
+__device__ __forceinline__ bool mbar_wait_for(uint64_t* bar, uint32_t parity, uint64_t limit_ns) {
   uint64_t start = 0;
-  for (uint32_t spin = 0; spin < (1u << 26); ++spin) {
+  for (uint32_t spin = 0; spin < (1u << 30); ++spin) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((spin & 1023u) == 1023u) {
       const uint64_t now = global_ns();
       if (start == 0) start = now;
-      else if (now - start > 1000000000ull) break;
+      else if (now - start > limit_ns) break;
     }
   }
-  atomicExch(&g_kernel_status, ST_WAIT_TIMEOUT);
   return false;
+}
+
+// Bounded wait: gives up after about a second, records ST_WAIT_TIMEOUT and returns false.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+  if (mbar_wait_for(bar, parity, 1000000000ull)) return true;
+  atomicCAS(&g_kernel_status, 0, ST_WAIT_TIMEOUT);
+  return false;
+}
+
+// The same for a whole warp (every lane calls it): one answer for all lanes, so the branch on it never splits a warp
+// in front of a warp-wide instruction.
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity) {
+  return __all_sync(0xffffffffu, mbar_wait(bar, parity));
 }
 
 // global -> shared bulk copy of `bytes` (a multiple of 16, both addresses 16-byte aligned), completion on `bar`

@@ -208,7 +208,7 @@ grouped_kernel(const __half* __restrict__ X0, const __half* __restrict__ X1, con
     TFB_K2(13) TFB_K2(14) TFB_K2(15) TFB_K2(16)
 #undef TFB_K2
     default:
-      atomicExch(&g_kernel_status, ST_BAD_INDEX);     // a width the host should have refused
+      atomicCAS(&g_kernel_status, 0, ST_BAD_INDEX);    // a width the host should have refused
       break;
   }
   pdl_launch_dependents();

@@ -135,6 +135,7 @@ decode_kernel(const __nv_bfloat16* __restrict__ X, int64_t x_stride, int slots, 
       xn[pt][1] = ldg_nc(xrow[pt] + 8);
     }
   }
+  bool failed = false;
   for (int c = 0; c < ng; ++c) {
     const int fill = c / G, gi = c - fill * G, s = fill % STAGES;
     uint32_t xb[PT][8];
@@ -153,7 +154,13 @@ decode_kernel(const __nv_bfloat16* __restrict__ X, int64_t x_stride, int slots, 
 #pragma unroll
       for (int ks = 1; ks < 4; ++ks) mma_bf16(xs[pt], ONES, ONES, ONES, ONES, xb[pt][2 * ks], xb[pt][2 * ks + 1]);
     }
-    if (gi == 0 && !mbar_wait(bars + s, (fill / STAGES) & 1)) break;
+    if (gi == 0 && !mbar_wait_warp(bars + s, (fill / STAGES) & 1)) {
+      // the copy never landed (recorded in the status word): give the other copies this warp issued a short while to
+      // land, then the whole CTA leaves without storing anything
+      for (int f = fill + 1; f < nslot && f < fill + STAGES; ++f) mbar_wait_for(bars + f % STAGES, (f / STAGES) & 1, 10000000ull);
+      failed = true;
+      break;
+    }
     // group gi of the slot: matrices of a group are adjacent; column blocks are G groups apart
     const uint8_t* blk = ring + s * SM::STAGE_BYTES + gi * (M * BLOCK_BYTES);
 #pragma unroll
@@ -202,7 +209,7 @@ decode_kernel(const __nv_bfloat16* __restrict__ X, int64_t x_stride, int slots, 
   pdl_launch_dependents();
 
   // K-slices meet in slice order (the ring's memory is free once every warp is past its loop)
-  __syncthreads();
+  if (__syncthreads_or(failed ? 1 : 0)) return;
   float* red = reinterpret_cast<float*>(smem);
 #pragma unroll
   for (int m = 0; m < Q; ++m)

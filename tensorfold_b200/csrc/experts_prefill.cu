@@ -231,7 +231,7 @@ prefill_kernel(const __nv_bfloat16* __restrict__ X, int64_t x_stride, int slots,
     const uint32_t boff = (uint32_t)(r0 * 128 + ((c ^ (r0 & 7)) << 4));      // rows 16 apart share r & 7
     for (int g = 0; g < KG && ok; ++g) {
       const int s = g % SA, round = g / SA;
-      if (round > 0) ok = mbar_wait(ab_free + s, (round - 1) & 1);
+      if (round > 0) ok = mbar_wait_warp(ab_free + s, (round - 1) & 1);
       if (!ok) break;
       uint8_t* btile = smem + s * SM::AB_BYTES + M * SM::A_BYTES + boff;
 #pragma unroll
@@ -253,8 +253,8 @@ prefill_kernel(const __nv_bfloat16* __restrict__ X, int64_t x_stride, int slots,
     const int gq = lane >> 2, t = lane & 3, cbw = warp & 3, tt = warp >> 2;
     for (int g = 0; g < KG && ok; ++g) {
       const int sp = g % SP, sa = g % SA;
-      ok = mbar_wait(packed_full + sp, (g / SP) & 1);
-      if (ok && g >= SA) ok = mbar_wait(ab_free + sa, (g / SA - 1) & 1);
+      ok = mbar_wait_warp(packed_full + sp, (g / SP) & 1);
+      if (ok && g >= SA) ok = mbar_wait_warp(ab_free + sa, (g / SA - 1) & 1);
       if (!ok) break;
       if (cbw < ncb) {
         const uint8_t* blk = smem + SM::PACKED_OFFSET + sp * SM::PACKED_BYTES + cbw * (M * BLOCK_BYTES);
@@ -291,7 +291,7 @@ prefill_kernel(const __nv_bfloat16* __restrict__ X, int64_t x_stride, int slots,
   // TMEM lane quarter warp & 3 (output column (warp & 3) * 32 + lane of the unit); the three warps of a quarter take
   // a third of the pairs each, 16 pairs a load
   if (warp < PF_DQ_WARPS + PF_GA_WARPS) {
-    if (ok) ok = mbar_wait(acc_ready, 0);
+    if (ok) ok = mbar_wait_warp(acc_ready, 0);
     if (ok) {
       tc_fence_after();
       const int q = warp & 3, part = warp >> 2, col = ct * PF_COLS + q * 32 + lane;

@@ -9,8 +9,10 @@
 // The two barriers order every reuse: a rank overwrites its token buffer only after it passed the results barrier,
 // which every peer signals after its pull; peers overwrite a rank's result buffer only after they passed the next
 // tokens barrier, which the rank signals after its sum.  Barrier numbers come from a device-side step counter, so a
-// step can be replayed from a CUDA graph.  Every wait is bounded (about a second): on a time-out the device status
-// word is set and the kernel goes on (its output is then meaningless; the host reads the status).
+// step can be replayed from a CUDA graph.  Every wait is bounded (tfb_set_wait_limit_ms, one second unless set): on a
+// time-out the status word records WHICH barrier ran out and the lowest RANK that had not arrived, the kernel returns
+// without touching any peer's memory, and every later kernel of this file on that GPU does the same until the host has
+// read (and so cleared) the status word.  A step's output is valid only if the status read after it is 0.
 // (No counterpart in the reference, which has no expert parallelism: src/tensorfold/cuda/comm.py is a 2-rank
 // all-gather.)
 
@@ -39,36 +41,48 @@ __device__ __forceinline__ uint4 ld_relaxed_sys_v4(const void* p) {
 // Flag barrier folded into the kernel that needs it.  Block 0 tells every rank "rank `rank` reached barrier `target` of
 // kind `which`" (what this GPU wrote in earlier kernels is complete by stream order; the fence orders it before the
 // flag); then every block waits until all ranks said the same in THIS rank's window.  flags: [2][world] uint32 at the
-// start of a window.  Bounded: gives up after about a second and sets the status word.  All threads must call it.
-__device__ __forceinline__ void peer_barrier(uint8_t* const* __restrict__ windows, int rank, int world, int which,
-                                             uint32_t target) {
+// start of a window.  Bounded by `limit_ns`: a wait that runs out records (time-out, barrier kind, lowest missing rank)
+// in the status word and the call returns false to every thread of the block.  All threads must call it.
+__device__ __forceinline__ bool peer_barrier(uint8_t* const* __restrict__ windows, int rank, int world, int which,
+                                             uint32_t target, uint64_t limit_ns) {
+  __shared__ int arrived;
+  if (threadIdx.x == 0) arrived = 1;
+  __syncthreads();
   if (threadIdx.x < 32) {
     const int lane = threadIdx.x;
     if (blockIdx.x == 0 && blockIdx.y == 0) {
       __threadfence_system();
       if (lane < world) st_release_sys(reinterpret_cast<uint32_t*>(windows[lane]) + which * world + rank, target);
     }
+    bool ok = true;
     if (lane < world) {
       const uint32_t* mine = reinterpret_cast<const uint32_t*>(windows[rank]) + which * world + lane;
       uint64_t start = 0;
-      bool ok = false;
-      for (uint32_t spin = 0; spin < (1u << 28); ++spin) {
+      ok = false;
+      for (uint32_t spin = 0; spin < (1u << 30); ++spin) {
         if ((int32_t)(ld_acquire_sys(mine) - target) >= 0) {
           ok = true;
           break;
         }
-        if ((spin & 255u) == 255u) {
+        if ((spin & 63u) == 63u) {
           const uint64_t now = global_ns();
           if (start == 0) start = now;
-          else if (now - start > 1000000000ull) break;
+          else if (now - start > limit_ns) break;
         }
       }
-      if (!ok) atomicExch(&g_kernel_status, ST_WAIT_TIMEOUT);
     }
-    __syncwarp();
+    const unsigned late = __ballot_sync(0xffffffffu, !ok);
+    if (late != 0u && lane == 0) {
+      atomicCAS(&g_kernel_status, 0, status_word(ST_WAIT_TIMEOUT, which + 1, __ffs(late) - 1));
+      arrived = 0;
+    }
   }
   __syncthreads();
+  return arrived != 0;
 }
+
+// True when an earlier kernel recorded a failure that the host has not read yet: peers' memory is then left alone.
+__device__ __forceinline__ bool step_failed() { return *reinterpret_cast<volatile int*>(&g_kernel_status) != 0; }
 
 // x_local [rows, D] bf16 -> this rank's token buffer (for callers that do not write their tokens there themselves).
 __global__ void __launch_bounds__(256)
@@ -90,9 +104,9 @@ struct PeerSegs {
 
 __global__ void __launch_bounds__(256)
 peer_gather_kernel(uint8_t* const* __restrict__ windows, int rank, int world, PeerSegs segs,
-                   const uint32_t* __restrict__ step) {
+                   const uint32_t* __restrict__ step, uint64_t limit_ns) {
   pdl_wait();
-  peer_barrier(windows, rank, world, 0, step[0] + 1);
+  if (!peer_barrier(windows, rank, world, 0, step[0] + 1, limit_ns)) return;   // nothing is pulled
   int64_t per = 0;
   for (int s = 0; s < segs.n; ++s) per += segs.units[s];
   for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < per * world; i += (int64_t)gridDim.x * 256) {
@@ -115,6 +129,7 @@ combine_push_kernel(const float* __restrict__ y, const float* __restrict__ wts, 
   const int d = (blockIdx.y * 256 + threadIdx.x) * 4;
   pdl_wait();
   if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) step[0] += 1;     // read by the kernels before and after only
+  if (step_failed()) return;                          // a barrier of this step ran out: store nothing into the peers
   if (d < D) {
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
     for (int s = 0; s < S; ++s) {
@@ -142,6 +157,7 @@ peer_push_kernel(const float4* __restrict__ partial, uint8_t* const* __restrict_
   const int r = blockIdx.x;
   pdl_wait();
   if (blockIdx.x == 0 && threadIdx.x == 0) step[0] += 1;
+  if (step_failed()) return;                          // a barrier of this step ran out: store nothing into the peers
   const int home = r / rows, j = r - home * rows;
   float4* dst = reinterpret_cast<float4*>(windows[home] + p_offset) + ((size_t)rank * rows + j) * (D / 4);
   for (int i = threadIdx.x; i < D / 4; i += 256) dst[i] = partial[(size_t)r * (D / 4) + i];
@@ -170,9 +186,10 @@ template <typename TO>
 __global__ void __launch_bounds__(256)
 peer_sum_kernel(uint8_t* const* __restrict__ windows, int rank, int64_t p_offset, int world, int rows, int D,
                 TO* __restrict__ out, const float* __restrict__ extra, const float* __restrict__ extra_w,
-                int extra_w_stride, const uint32_t* __restrict__ step) {
+                int extra_w_stride, const uint32_t* __restrict__ step, uint64_t limit_ns) {
   pdl_wait();
-  peer_barrier(windows, rank, world, 1, step[0]);
+  if (step_failed()) return;                          // the tokens barrier ran out: out keeps what it held
+  if (!peer_barrier(windows, rank, world, 1, step[0], limit_ns)) return;
   const float* part = reinterpret_cast<const float*>(windows[rank] + p_offset);
   const int64_t n4 = (int64_t)rows * D / 4;
   for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < n4; i += (int64_t)gridDim.x * 256) {
@@ -242,7 +259,7 @@ extern "C" int tfb_peer_gather(void* const* windows, int rank, int world, int ns
   const int grid = (int)((n + 255) / 256 < 592 ? (n + 255) / 256 : 592);
   return check_cuda(launch(peer_gather_kernel, dim3(grid), dim3(256), 0, static_cast<cudaStream_t>(stream),
                            reinterpret_cast<uint8_t* const*>(windows), rank, world, segs,
-                           static_cast<const uint32_t*>(step)),
+                           static_cast<const uint32_t*>(step), wait_limit_ns()),
                     "peer_gather");
 }
 
@@ -297,9 +314,11 @@ extern "C" int tfb_peer_sum(void* const* windows, int rank, int64_t p_offset, in
   auto stp = static_cast<const uint32_t*>(step);
   if (out_f32)
     return check_cuda(launch(peer_sum_kernel<float>, dim3(grid), dim3(256), 0, st, wins, rank, p_offset, world,
-                             rows_local, D, static_cast<float*>(out), extra, extra_w, extra_w_stride, stp),
+                             rows_local, D, static_cast<float*>(out), extra, extra_w, extra_w_stride, stp,
+                             wait_limit_ns()),
                       "peer_sum");
   return check_cuda(launch(peer_sum_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, st, wins, rank, p_offset, world,
-                           rows_local, D, static_cast<__nv_bfloat16*>(out), extra, extra_w, extra_w_stride, stp),
+                           rows_local, D, static_cast<__nv_bfloat16*>(out), extra, extra_w, extra_w_stride, stp,
+                           wait_limit_ns()),
                     "peer_sum");
 }

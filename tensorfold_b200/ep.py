@@ -1,15 +1,21 @@
-"""Expert parallelism for the routed-expert layer: experts sharded over the ranks of a process group, tokens data
-parallel, one all-to-all each way (dispatch of token rows to the experts' owners, return of the per-pair outputs).
+"""Expert parallelism for the routed-expert layer: experts sharded over the ranks of a process group (expert ``e``
+lives on rank ``e // (E / world)``), router rows and a shared expert replicated, tokens data parallel.
 
 The reference has no expert parallelism (its only multi-GPU mode is 2-rank tensor parallelism with an all-gather of
-fp32 partials, ``src/tensorfold/cuda/comm.py:69-76``); this is the sharding the routed path admits on an NVSwitch
-node: expert ``e`` lives on rank ``e // (E / world)``, router rows and the shared expert are replicated, a token's
-pairs travel to their experts and come back as fp32 rows, and the home rank sums them in slot order - so a token's
-result does not depend on the world size.  Collectives are ``torch.distributed.all_to_all_single`` (NCCL over NVLink on
-GPUs; gloo in the CPU tests).  Rows are in the receiver's own memory before any kernel reads them.
+fp32 partials, ``src/tensorfold/cuda/comm.py:69-76``); this is the sharding the routed path admits on an NVSwitch node.
+Three forms of the two exchanges (tokens to the experts' owners, results back to the tokens' home ranks):
 
-The arithmetic is behind a small backend interface so the index logic can be exercised on CPU ranks with a stand-in;
-the product backend (``CudaBackend``) runs this package's CUDA operators and has no CPU path.
+* ``PeerExpertParallel`` / ``PeerExl3ExpertParallel`` (the default, and what the benchmark times): this library's own
+  kernels over NVLink peer memory (``csrc/peer.cu``) - every rank pulls all ranks' rows and selections after a flag
+  barrier, and the kernel that forms a rank's per-token partial sums stores them straight into the home ranks; no
+  collective-library call on the step, one CUDA graph a step.
+* ``GatheredExpertParallel``: the same data flow through NCCL (all-gather of the tokens, reduce-scatter of per-pair
+  rows - the exact one-GPU bits - or of per-token partial sums); the comparison arm.
+* ``ExpertParallel``: counted dispatch with ``all_to_all_single`` (bf16 rows and ids out, fp32 rows back) and one host
+  read of the counts a step; least link traffic, not graph-capturable.  Its index logic sits behind a small backend
+  interface so CPU ranks (gloo) can exercise it with a stand-in; the product backend (``CudaBackend``) has no CPU path.
+
+Rows are in the receiver's own memory before any expert kernel reads them.
 """
 
 from __future__ import annotations
@@ -245,10 +251,16 @@ class PeerWindow:
     after the tokens barrier, and the sum of the ranks' partial results after the results barrier.
 
     The windows are one ``torch.distributed._symmetric_memory`` allocation a rank (plain peer mappings; multicast is
-    not used).  Waits are bounded: a rank that never arrives shows up as a non-zero ``_lib.kernel_status()``."""
+    not used).  Waits are bounded (``_lib.set_wait_limit_ms``): when a rank never arrives the status word names the
+    barrier and that rank, the step's kernels leave the peers' memory alone, and the step's output is void - read
+    ``_lib.kernel_status()`` (or ``_lib.check_status()``) after a step before using its output."""
 
     def __init__(self, router_rows: torch.Tensor, experts: int, top_k: int, rows_local: int, dims: int, shared: bool,
-                 group=None, logit_bias: torch.Tensor | None = None) -> None:
+                 group=None, logit_bias: torch.Tensor | None = None, rows_active: int | None = None) -> None:
+        """``rows_active`` (default ``rows_local``): how many of this rank's rows hold tokens.  Every rank's window has
+        ``rows_local`` rows; a batch smaller than the rank count (one token on eight GPUs) leaves some ranks with
+        none.  The other rows are never routed: their slots carry an id no rank owns, so no expert runs for them."""
+
         import ctypes
         import os
 
@@ -266,6 +278,9 @@ class PeerWindow:
         self.router_rows, self.rows_local, self.dims = router_rows, rows_local, dims
         self.logit_bias = logit_bias                              # [experts] fp32 added to the routed logits, or None
         self.slots = slots = top_k + (1 if shared else 0)
+        self.rows_active = rows_local if rows_active is None else int(rows_active)
+        if not 0 <= self.rows_active <= rows_local:
+            raise ValueError(f"rows_active must lie in 0..{rows_local}")
         dev, d = router_rows.device, dims
         self.device = dev
         self.rows = rows = rows_local * self.world
@@ -291,6 +306,8 @@ class PeerWindow:
         self.tokens = win[self.x_offset:self.x_offset + x_bytes].view(torch.bfloat16).view(rows_local, d)
         self.pick_mine = win[self.pick_offset:self.pick_offset + s_bytes].view(torch.int32).view(rows_local, slots)
         self.wts_mine = win[self.wts_offset:self.wts_offset + s_bytes].view(torch.float32).view(rows_local, slots)
+        self.pick_mine[self.rows_active:] = experts + 1           # rows without a token: an id outside every window
+        torch.cuda.synchronize(dev)
         dist.barrier(self.group)                                  # every window is zeroed before any flag is written
         self.logits = torch.zeros((rows_local, router_rows.shape[0]), dtype=torch.float32, device=dev)
         self.x_all = torch.zeros((rows, d), dtype=torch.bfloat16, device=dev)
@@ -318,11 +335,14 @@ class PeerWindow:
                 raise ValueError("host rows must be in pinned memory (a kernel reads them)")
             x_local = x_local.contiguous()
             _lib.call("tfb_peer_stage", x_local.data_ptr(), self.window.data_ptr(), self.x_offset, self.x_bytes, st)
-        moe.router(self.tokens, self.router_rows, self.logits)
+        n = self.rows_active
+        if n == 0:
+            return
+        moe.router(self.tokens[:n], self.router_rows, self.logits[:n])
         if self.logit_bias is not None:
-            self.logits[:, :self.experts].add_(self.logit_bias)
+            self.logits[:n, :self.experts].add_(self.logit_bias)
         _lib.call("tfb_select_rows", self.logits.data_ptr(), self.logits.shape[1], self.pick_mine.data_ptr(),
-                  self.wts_mine.data_ptr(), self.rows_local, self.experts, self.top_k, 1 if self.shared else 0, st)
+                  self.wts_mine.data_ptr(), n, self.experts, self.top_k, 1 if self.shared else 0, st)
 
     def gather(self) -> None:
         """Tokens barrier, then all ranks' rows and selections into ``x_all``, ``pick_all``, ``wts_all``."""
@@ -358,7 +378,8 @@ class PeerExpertParallel:
     ``GatheredExpertParallel(reduce="tokens")`` up to fp32 summation order across ranks (here fixed: rank 0, 1, ...)."""
 
     def __init__(self, router_rows: torch.Tensor, local_experts, experts: int, top_k: int, rows_local: int,
-                 group=None, shared_experts=None, logit_bias: torch.Tensor | None = None, hot_pairs: int = 0) -> None:
+                 group=None, shared_experts=None, logit_bias: torch.Tensor | None = None, hot_pairs: int = 0,
+                 rows_active: int | None = None) -> None:
         """``hot_pairs`` > 0: a rank's experts with at least that many pairs run through the prompt-form kernel (one
         pass over the expert's weights for up to 192 pairs) instead of one decode item per 8 pairs - for skewed
         routing, where one rank's busiest experts otherwise set the step time.  Those pairs then carry the prompt
@@ -370,7 +391,7 @@ class PeerExpertParallel:
         self.moe, self.grouped = moe, grouped
         shared = shared_experts is not None
         self.win = w = PeerWindow(router_rows, experts, top_k, rows_local, local_experts.dims, shared, group,
-                                  logit_bias)
+                                  logit_bias, rows_active)
         self.local, self.shared_ex, self.rows_local, self.top_k = local_experts, shared_experts, rows_local, top_k
         self.world, self.rank, self.rows, self.tokens = w.world, w.rank, w.rows, w.tokens
         dev, d, rows, slots = w.device, w.dims, w.rows, w.slots
@@ -434,11 +455,12 @@ class PeerExl3ExpertParallel:
     call's output."""
 
     def __init__(self, router_rows: torch.Tensor, local_ex, experts: int, top_k: int, rows_local: int, group=None,
-                 limit: float = float("inf")) -> None:
+                 limit: float = float("inf"), rows_active: int | None = None) -> None:
         from .exl3 import experts as exl3
 
         self.exl3 = exl3
-        self.win = w = PeerWindow(router_rows, experts, top_k, rows_local, local_ex.dims, False, group)
+        self.win = w = PeerWindow(router_rows, experts, top_k, rows_local, local_ex.dims, False, group,
+                                  rows_active=rows_active)
         self.local, self.rows_local, self.top_k, self.limit = local_ex, rows_local, top_k, limit
         self.world, self.rank, self.rows, self.tokens = w.world, w.rank, w.rows, w.tokens
         dev, d, rows = w.device, w.dims, w.rows

@@ -21,3 +21,15 @@ def pytest_collection_modifyitems(config, items):
     for item in items:
         if "gpu" in item.keywords:
             item.add_marker(skip)
+
+
+@pytest.fixture(params=[False, True], ids=["plain", "pdl"])
+def pdl(request):
+    """Runs the test twice: with ordinary launches and with programmatic dependent launch (every kernel may start
+    while the one before it drains, and waits on the device before it reads) - the mode the benchmark times."""
+
+    from tensorfold_b200 import _lib
+
+    was = _lib.set_pdl(request.param)
+    yield request.param
+    _lib.set_pdl(was)

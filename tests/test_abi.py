@@ -31,7 +31,8 @@ def test_library_exports_every_declared_symbol():
 def test_binding_covers_the_header():
     from tensorfold_b200 import _lib
 
-    bound = set(_lib.SIGNATURES) | {"tfb_last_error", "tfb_version", "tfb_set_pdl", "tfb_select_plan_max_rows"}
+    bound = set(_lib.SIGNATURES) | {"tfb_last_error", "tfb_version", "tfb_set_pdl", "tfb_select_plan_max_rows",
+                                     "tfb_set_wait_limit_ms"}
     assert set(declared()) == bound
 
 

@@ -96,7 +96,7 @@ MIXED = [
 
 
 @pytest.mark.parametrize("cb,kfun", MIXED, ids=[f"cb{m[0]}_{i}" for i, m in enumerate(MIXED)])
-def test_mixed_width_rows_are_independent_and_match_float64(cb, kfun):
+def test_mixed_width_rows_are_independent_and_match_float64(cb, kfun, pdl):
     """A width per expert matrix: each row gives identical bits alone and inside windows of 1..128 rows, and the
     layer agrees with the float64 reference (the bar of tests/cuda/test_exl3_experts.py:181-205: 1e-2 of the max)."""
 
@@ -148,7 +148,7 @@ def test_per_slot_output_and_fused_combine_agree():
     assert torch.equal(s.y[:R * TOPK].view(R, TOPK, D), y)         # the fused launch stores the same per-slot y
 
 
-def test_graph_replay_equals_eager():
+def test_graph_replay_equals_eager(pdl):
     from tensorfold_b200.exl3 import experts
 
     E, D, I, TOPK = 16, 256, 128, 4

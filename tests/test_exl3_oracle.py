@@ -3,8 +3,10 @@
 from pathlib import Path
 
 import numpy as np
+import pytest
 
 from oracle import exl3
+from oracle import exl3 as ref
 
 GOLDEN = np.load(Path(__file__).parent / "golden" / "exl3_golden.npz")
 
@@ -47,3 +49,37 @@ def test_grouping_semantics():
     uids, members = exl3.group(pick, 8)
     assert uids.tolist() == [1, 2, 3, 7]
     assert members.tolist() == [[1, 32, -1], [66, -1, -1], [0, 34, -1], [2, 64, 65]]
+
+
+@pytest.mark.parametrize("cb", [0, 1, 2])
+def test_c_restatement_decodes_like_the_numpy_one(cb):
+    """``oracle/cpu_exl3.c`` (the timed CPU baseline of the EXL3 path) against the pinned numpy decoder, bit for bit,
+    at every width."""
+
+    from oracle import cpu
+
+    rng = np.random.default_rng(17 + cb)
+    for k2 in range(2, 17):
+        t = rng.integers(-32768, 32768, (3, 2, 8 * k2)).astype(np.int16)
+        assert np.array_equal(cpu.exl3_unpack(t, cb).view(np.uint16), ref.unpack(t, cb).view(np.uint16)), k2
+
+
+def test_c_restatement_of_the_routed_layer():
+    from oracle import cpu
+
+    rng = np.random.default_rng(3)
+    e_count, d, ni, rows, k = 6, 256, 128, 5, 3
+
+    def mat(kk, nn, bits):
+        return (rng.integers(-32768, 32768, (kk // 16, nn // 16, 16 * bits)).astype(np.int16),
+                (rng.standard_normal(kk) * 0.05).astype(np.float16), rng.standard_normal(nn).astype(np.float16))
+
+    gate = [mat(d, ni, 2 + e % 4) for e in range(e_count)]
+    up = [mat(d, ni, 3 + e % 3) for e in range(e_count)]
+    down = [mat(ni, d, 4) for e in range(e_count)]
+    x = rng.standard_normal((rows, d)).astype(np.float32)
+    pick = np.stack([rng.permutation(e_count + 1)[:k] for _ in range(rows)]).astype(np.int32)   # id 6 is skipped
+    wts = rng.random((rows, k)).astype(np.float32)
+    got = cpu.exl3_routed(x, pick, wts, gate, up, down, 0, d, ni)
+    want = ref.routed(x, pick, wts, gate, up, down, 0)
+    assert np.abs(got - want).max() <= 1e-5 * np.abs(want).max()

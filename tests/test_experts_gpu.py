@@ -125,7 +125,7 @@ def test_one_hot_rows_read_back_every_nibble():
 
 
 @pytest.mark.parametrize("case", CASES)
-def test_pairs_do_not_depend_on_the_window(case):
+def test_pairs_do_not_depend_on_the_window(case, pdl):
     ex, _, _ = build(case, 11)
     rows = 40
     x = (torch.randn((rows, ex.dims), device=DEV) * 0.5).to(torch.bfloat16)
@@ -185,7 +185,7 @@ def test_matches_fp64(case, dtype):
     assert (y.double() - yref).abs().max() <= 1e-5 * yref.abs().max()
 
 
-def test_graph_replay_follows_the_picks():
+def test_graph_replay_follows_the_picks(pdl):
     from tensorfold_b200 import experts
 
     case = CASES[1]
@@ -230,7 +230,7 @@ def test_many_units_keep_the_bits():
 
 @pytest.mark.parametrize("shared", [False, True])
 @pytest.mark.parametrize("rows", [1, 9, 64])
-def test_layer_against_the_cpu_oracle(rows, shared):
+def test_layer_against_the_cpu_oracle(rows, shared, pdl):
     """moe.run end to end on a small layer: picks bit exact, weights within a bf16 ulp, output rel-L2 <= 1e-2 against
     the fp64-accumulated reference and against the CPU restatement."""
 

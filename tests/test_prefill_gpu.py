@@ -81,7 +81,7 @@ def test_matches_fp64_over_bf16_weights(case, dtype):
 
 
 @pytest.mark.parametrize("case", CASES)
-def test_rows_do_not_depend_on_the_chunk_or_the_item(case):
+def test_rows_do_not_depend_on_the_chunk_or_the_item(case, pdl):
     ex, _, _ = build(case, 71)
     rows = 200
     x = (torch.randn((rows, ex.dims), device=DEV) * 0.5).to(torch.bfloat16)
@@ -106,7 +106,7 @@ def test_rows_do_not_depend_on_the_chunk_or_the_item(case):
 
 
 @pytest.mark.parametrize("shared", [False, True])
-def test_prefill_layer_against_the_oracle(shared):
+def test_prefill_layer_against_the_oracle(shared, pdl):
     from oracle import affine, cpu
     from tensorfold_b200 import _lib, experts, moe, synthetic
 

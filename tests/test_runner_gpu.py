@@ -9,7 +9,7 @@ pytestmark = pytest.mark.gpu
 
 @pytest.mark.parametrize("direct", [True, False])
 @pytest.mark.parametrize("rows", [5, 32, 33, 70])
-def test_replay_equals_eager_and_host_bound(rows, direct):
+def test_replay_equals_eager_and_host_bound(rows, direct, pdl):
     from tensorfold_b200 import experts, moe, synthetic
 
     dev = torch.device("cuda", 0)
