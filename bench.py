@@ -1,22 +1,32 @@
-"""Benchmark of the routed-expert MoE layer (affine 4-bit group-64 experts) on B200.
+"""Benchmark of the routed-expert MoE layer on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--rows T]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--rows T] [--config c2|c4|c5]
 
-Workload: BASELINE config 2 - one layer, hidden 2048, 128 experts of width 768, top-8 - at 64-token decode (the
-headline line), with 1-, 4- and 16-token decode, the 2048-token prompt and the EXL3 layer (config 3) beside it under
-"sweep"; `--gpus N` (torchrun) times the expert-parallel step, `--config c4` the large skewed layer.  One step = one pass of
-the whole layer (router, top-k, plan, gate/up + SiLU-gate, down, combine) over one batch of seeded synthetic tokens.
-Two independent weight copies (340 MB each, together far beyond the 126 MB L2) alternate step by step.
+Headline workload: BASELINE config 2 - one layer, hidden 2048, 128 experts of width 768, top-8, MLX affine 4-bit
+group-64 experts - at 64-token decode.  One step = one pass of the whole layer (router, top-k, plan, gate/up +
+SiLU-gate, down, combine) over one batch of seeded synthetic tokens.  Beside it, in the same JSON line:
 
-Prints ONE JSON line (rank 0).  ``--impl reference`` times the CPU restatement of the reference's path (oracle/) on
-the host cores instead.
+* "sweep": 1-, 4- and 16-token decode, the 2048-token prompt (tcgen05 form) and the EXL3 layer of config 3;
+* "c4": BASELINE config 4 (hidden 6144, 256 experts x FFN 2048 + a shared expert, Zipf-skewed router, 256 tokens
+  split over the ranks - strong scaling) and "c5": BASELINE config 5 (8 EXL3 layers of mixed width, 1..512 tokens
+  split over the ranks), both on the expert-parallel path at the run's rank count;
+* with `--gpus N` (torchrun) the headline is the expert-parallel step at 64 tokens a rank (weak scaling), and
+  "ep_check" records that every rank's output was compared with the one-GPU layer before the clock started.
+
+Timing: K steps between two CUDA events, repeated until at least 300 steps were timed; the median repeat is reported
+(every repeat times exactly K steps).  Weights and inputs rotate so that a step's weights are read from DRAM.
+Prints ONE JSON line (rank 0).  `--impl reference` times the CPU restatement of the reference's path (oracle/) on
+all host cores instead.
 """
 
 from __future__ import annotations
 
 import argparse
+import hashlib
 import json
+import math
 import os
+import re
 import statistics
 import subprocess
 import sys
@@ -28,12 +38,14 @@ ROOT = Path(__file__).resolve().parent
 if str(ROOT) not in sys.path:
     sys.path.insert(0, str(ROOT))
 
-TRAFFIC_GATE_UP_C2_64 = 225054208 + 4798464      # bytes, from the committed ncu capture of the same launch
 METRIC = "moe_layer_tokens_per_s"
 UNIT = "tokens/s"
 SMI_FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
               "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+C5_TOKENS = (1, 8, 32, 128, 512)
+C5_LAYERS = 8
+TOL = 1e-2                                         # relative L2 of a layer output against the one-GPU layer
 
 
 def peaks() -> tuple[float, float, str]:
@@ -44,6 +56,33 @@ def peaks() -> tuple[float, float, str]:
         d = json.loads(p.read_text())
         return float(d["hbm_gbs"]), float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), "measured"
     return 6650.0, 1590.0, "fallback"
+
+
+def kernel_source_sha() -> str:
+    """Hash of the decode kernel's sources: an ncu capture is quoted only while the kernel it measured is unchanged."""
+
+    h = hashlib.sha256()
+    for name in ("common.cuh", "experts_decode.cu"):
+        h.update((ROOT / "tensorfold_b200" / "csrc" / name).read_bytes())
+    return h.hexdigest()[:16]
+
+
+def captured_traffic() -> tuple[int | None, str]:
+    """DRAM bytes of one gate/up launch of the headline workload from the committed ncu summary, or None when that
+    summary was taken from other kernel sources than the ones in this tree."""
+
+    path = ROOT / "profiles" / "decode_kernel_c2_64tokens.md"
+    if not path.exists():
+        return None, "no ncu summary committed"
+    text = path.read_text()
+    nbytes = re.search(r"traffic_bytes_per_launch:\s*(\d+)", text)
+    sha = re.search(r"kernel_source_sha:\s*([0-9a-f]+)", text)
+    if not nbytes or not sha:
+        return None, "the ncu summary carries no traffic record"
+    if sha.group(1) != kernel_source_sha():
+        return None, "the committed ncu capture measured other kernel sources than this tree's (stale)"
+    return int(nbytes.group(1)), ("ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch of this workload "
+                                  "(profiles/decode_kernel_c2_64tokens.md, same kernel sources)")
 
 
 class ClockSampler:
@@ -106,15 +145,19 @@ def layer_bytes(shape, rows: int, distinct: int) -> dict:
             "layer": distinct * 3 * per_matrix + ne * d * 2 + 2 * rows * d * 2}
 
 
-def cpu_baseline(shape, rows: int, steps: int, warmup: int):
-    """The CPU restatement of the reference's path (oracle/cpu_moe.c, OpenMP over all host cores) on the same
-    synthetic workload; returns (tokens/s, seconds a step, cores)."""
+# ---- CPU legs (the only code here that touches oracle/) --------------------------------------------------------------
+
+def cpu_baseline(shape, rows: int, steps: int, warmup: int, threads: int | None = None):
+    """The CPU restatement of the reference's path (oracle/cpu_moe.c, OpenMP) on the same synthetic workload with
+    `threads` host threads (all cores unless given); returns (tokens/s, seconds a step, threads used)."""
 
     import numpy as np
     import torch
 
     from oracle import cpu
     from tensorfold_b200 import synthetic
+
+    cpu.set_threads(threads or os.cpu_count() or 1)      # torchrun exports OMP_NUM_THREADS=1: set it explicitly
 
     def b16(t):
         return t.contiguous().view(torch.int16).numpy().view(np.uint16)
@@ -135,8 +178,46 @@ def cpu_baseline(shape, rows: int, steps: int, warmup: int):
     return rows / sec, sec, cpu.threads()
 
 
+def cpu_baseline_exl3(rows: int, steps: int, threads: int | None = None):
+    """The EXL3 layer of config 3 (4.00 bits a weight) through oracle/cpu_exl3.c on the host cores: the routed experts
+    of `rows` seeded tokens (routing by the oracle's router and top-k).  Returns (tokens/s, seconds a step, threads)."""
+
+    import numpy as np
+    import torch
+
+    from oracle import cpu
+    from tensorfold_b200 import synthetic
+
+    cpu.set_threads(threads or os.cpu_count() or 1)
+    shape = synthetic.C3
+    x = synthetic.activations(shape, rows, "cpu")
+    rt = synthetic.router_rows(shape, "cpu")
+
+    def b16(t):
+        return t.contiguous().view(torch.int16).numpy().view(np.uint16)
+
+    logits = cpu.router_logits(b16(x), b16(rt))
+    pick, wts = cpu.topk_rows(logits, shape.experts, shape.top_k, False)
+    used = sorted(set(pick.reshape(-1).tolist()))
+    base = 1000 * shape.config + 10
+    mats = [[None] * shape.experts for _ in range(3)]
+    for e in used:                                          # only the experts the rows use are generated
+        for m, (k, n) in enumerate(((shape.dims, shape.width), (shape.dims, shape.width), (shape.width, shape.dims))):
+            t, suh, svh = synthetic.exl3_matrix(base + 3 * e + m, k, n, 4, "cpu")
+            mats[m][e] = (t.numpy(), suh.numpy(), svh.numpy())
+    xf = x.float().numpy()
+    times = []
+    for i in range(1 + steps):
+        t0 = time.perf_counter()
+        cpu.exl3_routed(xf, pick, wts, mats[0], mats[1], mats[2], 0, shape.dims, shape.width)
+        if i >= 1:
+            times.append(time.perf_counter() - t0)
+    sec = sum(times) / len(times)
+    return rows / sec, sec, cpu.threads()
+
+
 def run_reference(args) -> None:
-    """--impl reference: the reference's CPU path (restated in oracle/) on the host cores; rank 0 only."""
+    """--impl reference: the reference's CPU path (restated in oracle/) on all host cores; rank 0 only."""
 
     if int(os.environ.get("RANK", "0")) != 0:
         return
@@ -156,10 +237,10 @@ def run_reference(args) -> None:
 
 def workload_config(shape, rows: int, gpus: int, config: str = "c2") -> dict:
     if config == "c5":
-        return {"workload": f"BASELINE config 5: 8 MoE layers with bf16 residual adds, {rows * gpus} tokens over the "
+        return {"workload": f"BASELINE config 5: {C5_LAYERS} MoE layers with bf16 residual adds, {rows} tokens over the "
                             f"ranks, hidden {shape.dims}, {shape.experts} experts x FFN {shape.width}, "
                             f"top-{shape.top_k}, EXL3 experts at a seeded 2..8 bits a tensor (3inst)",
-                "rows_per_gpu": rows, "l2": "the 8 layers' weights of a rank (15 GB / ranks) cycle every step",
+                "tokens": rows, "l2": "16 seeded token batches rotate, so the experts (and weights) change every step",
                 "parallelism": f"ep{gpus}" if gpus > 1 else "single"}
     what = (f"BASELINE config 4: one MoE layer, {rows * gpus} tokens over the ranks, Zipf-skewed router, one replicated "
             "shared expert," if config == "c4" else f"BASELINE config 2: one MoE layer, {rows}-token decode,")
@@ -169,37 +250,87 @@ def workload_config(shape, rows: int, gpus: int, config: str = "c2") -> dict:
             "parallelism": f"ep{gpus}" if gpus > 1 else "single"}
 
 
-def time_graphs(torch, graphs, steps: int, warmup: int) -> float:
-    """Milliseconds a step: `steps` replays alternating over `graphs`, CUDA events on the current stream."""
+# ---- timing ---------------------------------------------------------------------------------------------------------
 
-    for i in range(warmup):
-        graphs[i % len(graphs)].replay()
-    torch.cuda.synchronize()
-    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    a.record()
-    for i in range(steps):
-        graphs[i % len(graphs)].replay()
-    b.record()
-    torch.cuda.synchronize()
-    return a.elapsed_time(b) / steps
+def repeats_for(steps: int) -> int:
+    """Repeats of `steps` timed steps so that at least 300 steps are timed in all (3 .. 25 repeats)."""
 
+    return max(3, min(25, math.ceil(300 / max(steps, 1))))
+
+
+def timed(torch, replay, steps: int, warmup: int, repeats: int, dist=None, sync_each: bool = False):
+    """`repeats` measurements, each of exactly `steps` calls `replay(i)` between two CUDA events on the current stream
+    (device time; with `dist` a barrier before each and the max over ranks of each).  Returns (median ms a step, all)."""
+
+    n = 0
+    for _ in range(warmup):
+        replay(n)
+        n += 1
+    torch.cuda.synchronize()
+    out = []
+    for _ in range(repeats):
+        if dist is not None:
+            dist.barrier()
+            torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(steps):
+            replay(n)
+            n += 1
+            if sync_each:
+                torch.cuda.current_stream().synchronize()
+        b.record()
+        torch.cuda.synchronize()
+        out.append(a.elapsed_time(b) / steps)
+    if dist is not None and dist.get_world_size() > 1:
+        t = torch.tensor(out, device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        out = t.tolist()
+    return statistics.median(out), out
+
+
+def spread(all_ms) -> dict:
+    return {"repeats": len(all_ms), "ms_min": min(all_ms), "ms_max": max(all_ms)}
+
+
+def rel_l2(torch, got, want) -> float:
+    return float((got.float() - want.float()).norm() / want.float().norm().clamp_min(1e-30))
+
+
+# ---- one GPU --------------------------------------------------------------------------------------------------------
 
 def bench_rows(torch, shape, layers, rows: int, steps: int, warmup: int, hbm: float, prefill: bool = False,
                tflops: float = 0.0):
-    """Device-resident timing of the whole layer at `rows` tokens plus the gate/up kernel alone."""
+    """Device-resident timing of the whole layer at `rows` tokens plus the gate/up kernel alone.  Enough runners
+    (weight copy x seeded token batch) rotate that the weights a step reads were not read by the steps just before
+    it: a few tokens touch only a few experts, so their batches - and with them the experts - change every step."""
 
-    from tensorfold_b200 import experts, moe, synthetic
+    from tensorfold_b200 import _lib, experts, moe, synthetic
 
     dev = layers[0].router.device
-    runners = [moe.Runner(m, rows, prefill=prefill, device=dev) for m in layers]
-    x = synthetic.activations(shape, rows, dev)
+    per_expert = layers[0].experts.bytes_per_expert()
+    touched = min(shape.experts, rows * shape.top_k) * per_expert
+    n_inputs = 1 if prefill else max(1, min(16, math.ceil(400e6 / (touched * len(layers)))))
+    runners = []
+    for i in range(n_inputs):
+        for m in layers:
+            r = moe.Runner(m, rows, prefill=prefill, device=dev)
+            r.x.copy_(synthetic.activations(shape, rows, dev, index=i))
+            runners.append(r)
+    # the timed mode (CUDA graph + programmatic dependent launch) against ordinary eager launches, once
+    was = _lib.set_pdl(False)
+    eager = moe.run(runners[0].x, runners[0].layer, prefill=prefill).clone()
+    _lib.set_pdl(was)
+    if not torch.equal(runners[0].replay(), eager):
+        raise SystemExit(f"graph replay of the {rows}-token layer differs from the eager layer")
+    ms, all_ms = timed(torch, lambda i: runners[i % len(runners)].graph.replay(), steps, warmup, repeats_for(steps))
+    distinct = statistics.mean(int(r.buf.plan.counts[1]) for r in runners)
+    nbytes = {k: 0 for k in ("gate_up", "down", "layer")}
     for r in runners:
-        r.x.copy_(x)
-    ms = time_graphs(torch, [r.graph for r in runners], steps, warmup)
-    distinct = int(runners[0].buf.plan.counts[1])
-    nbytes = layer_bytes(shape, rows, distinct)
-    # the dominant kernel alone: gate/up over the plan the layer just made, 4 launches a weight copy in one graph
-    reps = 4
+        for k, v in layer_bytes(shape, rows, int(r.buf.plan.counts[1])).items():
+            nbytes[k] += v / len(runners)
+    # the dominant kernel alone: gate/up over the plans the layers just made, one graph over every runner
+    reps = max(1, 8 // len(runners))
     g = torch.cuda.CUDAGraph()
     side = torch.cuda.Stream(dev)
     side.wait_stream(torch.cuda.current_stream())
@@ -207,7 +338,8 @@ def bench_rows(torch, shape, layers, rows: int, steps: int, warmup: int, hbm: fl
         for _ in range(reps):
             for r in runners:
                 experts.gate_up(r.x, r.layer.experts, r.buf.plan, r.buf.act.view(-1, shape.width), rows)
-    kms = time_graphs(torch, [g], max(3, steps // 4), 3) / (reps * len(runners))
+    kms, _ = timed(torch, lambda i: g.replay(), max(3, steps // 4), 3, 5)
+    kms /= reps * len(runners)
     gbs = nbytes["gate_up"] / (kms * 1e-3) / 1e9
     extra = {}
     if prefill:
@@ -217,16 +349,18 @@ def bench_rows(torch, shape, layers, rows: int, steps: int, warmup: int, hbm: fl
                  "gate_up_frac_of_bf16_peak": flops_gu / (kms * 1e-3) / 1e12 / tflops if tflops else None,
                  "layer_tflops": flops_all / (ms * 1e-3) / 1e12,
                  "layer_frac_of_bf16_peak": flops_all / (ms * 1e-3) / 1e12 / tflops if tflops else None}
-    return {**extra, "rows": rows, "ms_per_step": ms, "tokens_per_s": rows / (ms * 1e-3), "distinct_experts": distinct,
+    return {**extra, "rows": rows, "ms_per_step": ms, **spread(all_ms), "tokens_per_s": rows / (ms * 1e-3),
+            "distinct_experts": distinct, "rotation": f"{len(layers)} weight copies x {n_inputs} token batches",
             "layer_bytes": nbytes["layer"], "layer_gbs": nbytes["layer"] / (ms * 1e-3) / 1e9,
             "layer_frac_of_hbm": nbytes["layer"] / (ms * 1e-3) / 1e9 / hbm,
             "gate_up_us": kms * 1e3, "gate_up_bytes": nbytes["gate_up"], "gate_up_gbs": gbs,
-            "launches_per_step": runners[0].launches}, runners
+            "gate_up_frac_of_hbm": gbs / hbm, "launches_per_step": runners[0].launches}, runners
 
 
 def bench_exl3(torch, rows_list, steps: int, warmup: int, hbm: float):
     """Config 3: the same layer shape with EXL3 experts at 4.00 bits a weight (3inst), router and selection included;
-    two weight copies alternate.  Bytes = trellis + suh/svh of the distinct experts + router rows + tokens."""
+    two weight copies x enough seeded token batches rotate that a step's trellises come from DRAM.
+    Bytes = trellis + suh/svh of the distinct experts + router rows + tokens."""
 
     from tensorfold_b200 import moe, synthetic
     from tensorfold_b200.exl3 import experts as x3
@@ -234,6 +368,7 @@ def bench_exl3(torch, rows_list, steps: int, warmup: int, hbm: float):
     shape, dev = synthetic.C3, torch.device("cuda", torch.cuda.current_device())
     router = synthetic.router_rows(shape, dev)
     layers = [x3.prepare(*synthetic.exl3_layer(shape, dev, 4, copy=c), x3.CB_3INST, device=dev) for c in range(2)]
+    per_expert = 3 * shape.dims * shape.width // 2 + 2 * (2 * shape.dims + 2 * shape.width) + 2 * (shape.dims + shape.width)
 
     class _Cfg:
         num_experts_per_tok, num_experts = shape.top_k, shape.experts
@@ -241,35 +376,40 @@ def bench_exl3(torch, rows_list, steps: int, warmup: int, hbm: float):
 
     results = []
     for rows in rows_list:
-        x = synthetic.activations(shape, rows, dev)
-        graphs, bufs = [], []
-        for ex in layers:
-            buf = moe.MoEBuffers(rows, _Cfg, dev, shared=False)
-            scratch = x3.Scratch(ex, rows, shape.top_k, device=dev)
-            out = torch.empty((rows, shape.dims), dtype=torch.float32, device=dev)
+        touched = min(shape.experts, rows * shape.top_k) * per_expert
+        n_inputs = max(1, min(16, math.ceil(400e6 / (touched * len(layers)))))
+        graphs, counts, keep = [], [], []
+        for i in range(n_inputs):
+            x = synthetic.activations(shape, rows, dev, index=i)
+            for ex in layers:
+                buf = moe.MoEBuffers(rows, _Cfg, dev, shared=False)
+                scratch = x3.Scratch(ex, rows, shape.top_k, device=dev)
+                out = torch.empty((rows, shape.dims), dtype=torch.float32, device=dev)
 
-            def step(ex=ex, buf=buf, scratch=scratch, out=out):
-                moe.router(x, router, buf.logits)
-                moe.select_rows(buf.logits, buf, shape.top_k, shape.experts)
-                x3.routed(x, buf.pick, buf.wts, ex, scratch, out, rows)
+                def step(x=x, ex=ex, buf=buf, scratch=scratch, out=out):
+                    moe.router(x, router, buf.logits)
+                    moe.select_rows(buf.logits, buf, shape.top_k, shape.experts)
+                    x3.routed(x, buf.pick, buf.wts, ex, scratch, out, rows)
 
-            step()
-            torch.cuda.synchronize()
-            side = torch.cuda.Stream(dev)
-            side.wait_stream(torch.cuda.current_stream())
-            g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g, stream=side):
                 step()
-            graphs.append(g)
-            bufs.append((buf, scratch))
-        ms = time_graphs(torch, graphs, steps, warmup)
-        distinct = int(bufs[0][1].count[0])
-        per_expert = 3 * shape.dims * shape.width // 2 + 2 * (2 * shape.dims + 2 * shape.width) + 2 * (shape.dims + shape.width)
+                torch.cuda.synchronize()
+                side = torch.cuda.Stream(dev)
+                side.wait_stream(torch.cuda.current_stream())
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=side):
+                    step()
+                graphs.append(g)
+                counts.append(scratch.count)
+                keep.append((x, buf, scratch, out))
+        ms, all_ms = timed(torch, lambda i: graphs[i % len(graphs)].replay(), steps, warmup, repeats_for(steps))
+        distinct = statistics.mean(int(c[0]) for c in counts)
         nbytes = distinct * per_expert + shape.experts * shape.dims * 2 + rows * shape.dims * (2 + 4)
-        results.append({"form": "exl3 4.00 bpw (config 3)", "rows": rows, "ms_per_step": ms,
-                        "tokens_per_s": rows / (ms * 1e-3), "distinct_experts": distinct, "layer_bytes": nbytes,
+        results.append({"form": "exl3 4.00 bpw (config 3)", "rows": rows, "ms_per_step": ms, **spread(all_ms),
+                        "tokens_per_s": rows / (ms * 1e-3), "distinct_experts": distinct,
+                        "rotation": f"{len(layers)} weight copies x {n_inputs} token batches", "layer_bytes": nbytes,
                         "layer_gbs": nbytes / (ms * 1e-3) / 1e9, "layer_frac_of_hbm": nbytes / (ms * 1e-3) / 1e9 / hbm,
-                        "launches_per_step": 8})
+                        "launches_per_step": x3.LAUNCHES_PER_CALL + 2})
+        del graphs, keep
     return results
 
 
@@ -282,40 +422,14 @@ def bench_e2e(torch, runners, shape, rows: int, steps: int, warmup: int):
     out_host = torch.empty((rows, shape.dims), dtype=torch.bfloat16).pin_memory()
     for r in runners:
         r.bind_host(x_host, out_host)                           # the copies become nodes of the step's graph
-    for i in range(warmup):
-        runners[i % len(runners)].replay_host()
-        torch.cuda.synchronize()
-    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    a.record()
-    for i in range(steps):
-        runners[i % len(runners)].replay_host()
-        torch.cuda.current_stream().synchronize()               # the caller reads the result before the next step
-    b.record()
-    torch.cuda.synchronize()
-    ms = a.elapsed_time(b) / steps
+    ms, all_ms = timed(torch, lambda i: runners[i % len(runners)].replay_host(), steps, warmup, repeats_for(steps),
+                       sync_each=True)                          # the caller reads the result before the next step
     nbytes = rows * shape.dims * 2
-    return {"value": rows / (ms * 1e-3), "unit": UNIT, "ms_per_step": ms, "h2d_bytes_per_step": nbytes,
-            "d2h_bytes_per_step": nbytes}
+    return {"value": rows / (ms * 1e-3), "unit": UNIT, "ms_per_step": ms, **spread(all_ms),
+            "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": nbytes}
 
 
-def ep_rows(args, shape, world: int) -> int:
-    """Rows a rank: config 2 keeps `--rows` a GPU (weak scaling); config 4 splits its 256 tokens over the ranks."""
-
-    return 256 // world if args.config == "c4" else args.rows
-
-
-def hot_pairs(args) -> int:
-    """Pairs from which a rank's expert runs through the prompt-form kernel (off unless asked for: at config 4's sizes
-    one prompt-form item is a 70 us serial chain on 16 CTAs, which costs more than the decode items it replaces)."""
-
-    return max(args.hot_pairs, 0)
-
-
-def ep_copies(args, world: int) -> int:
-    """Independent weight copies a rank rotates so that a step's weights never sit in the 126 MB L2."""
-
-    return 2 if args.config == "c4" else 2 * world          # a config-4 slice is 5.4 GB / world
-
+# ---- expert parallelism ---------------------------------------------------------------------------------------------
 
 COLLECTIVE = {
     "tokens": "NCCL all-gather of the tokens, reduce-scatter of fp32 per-token partial sums",
@@ -325,18 +439,57 @@ COLLECTIVE = {
 }
 
 
-def bench_ep(torch, dist, args, shape, dev, rank: int, world: int):
-    """Expert-parallel step: this rank's `rows` tokens through the layer whose experts are sharded over the ranks
-    (NCCL all-to-all dispatch and return).  Each rank keeps 2 * world copies of its expert slice and rotates them, so a
-    step's weights (a slice is 340 / world MB) never sit in L2.  Returns (ms a step by CUDA events, launches a step)."""
+def ep_rows(config: str, rows: int, world: int) -> int:
+    """Rows a rank: config 2 keeps `--rows` a GPU (weak scaling); config 4 splits its 256 tokens over the ranks."""
 
-    from tensorfold_b200 import ep, experts, moe, synthetic
+    return 256 // world if config == "c4" else rows
 
-    rows, per = ep_rows(args, shape, world), shape.experts // world
+
+def ep_copies(config: str, world: int) -> int:
+    """Independent weight copies a rank rotates so that a step's weights never sit in the 126 MB L2."""
+
+    return 2 if config == "c4" else 2 * world              # a config-4 slice is 5.4 GB / world
+
+
+def all_ok(torch, dist, ok: bool, value: float):
+    """(every rank's ok, the largest value over the ranks)."""
+
+    t = torch.tensor([0.0 if ok else 1.0, value], device="cuda", dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return t[0].item() == 0.0, t[1].item()
+
+
+def one_gpu_layer(torch, x, router, full, shape, bias):
+    """The plain one-GPU layer on `x` (the same kernels, no exchange): (out bf16, pick)."""
+
+    from tensorfold_b200 import experts, moe
+
+    layer = moe.Routed(router, full, shape.top_k, shared=shape.shared)
+    rows = x.shape[0]
+    buf = moe.MoEBuffers(rows, moe._Shape(layer), x.device, shared=shape.shared)
+    moe.router(x, router, buf.logits[:rows])
+    if bias is not None:
+        buf.logits[:rows, :shape.experts] += bias
+    moe.select(buf.logits[:rows], buf, shape.top_k, shape.experts)
+    experts.gate_up(x, full, buf.plan, buf.act.view(-1, full.width), rows)
+    experts.down(buf.act.view(-1, full.width), full, buf.plan, buf.y.view(-1, full.dims), rows)
+    return moe.combine(buf.y[:rows], buf.wts[:rows]), buf.pick[:rows].clone()
+
+
+def bench_ep(torch, dist, args, config: str, shape, dev, rank: int, world: int) -> dict:
+    """Expert-parallel step of the affine layer: this rank's rows through the layer whose experts are sharded over the
+    ranks.  Each rank keeps several copies of its expert slice and rotates them, so a step's weights never sit in L2.
+    Before the clock starts every rank compares its output with the one-GPU layer on the same rows ("ep_check")."""
+
+    from tensorfold_b200 import _lib, ep, experts, synthetic
+
+    rows, per = ep_rows(config, args.rows, world), shape.experts // world
+    reduce = args.ep_reduce
     router = synthetic.router_rows(shape, dev)
-    bias = synthetic.zipf_bias(shape, 1.1, dev) if args.config == "c4" else None
-    copies, graphs = [], []
-    for copy in range(ep_copies(args, world)):
+    bias = synthetic.zipf_bias(shape, 1.1, dev) if config == "c4" else None
+    x = synthetic.activations(shape, rows, dev, index=100 + rank)
+    copies, graphs, check = [], [], None
+    for copy in range(ep_copies(config, world)):
         gate, up, down = synthetic.affine_layer(shape, dev, torch.float16 if args.scales == "fp16" else torch.bfloat16,
                                                 copy=copy)
 
@@ -345,42 +498,41 @@ def bench_ep(torch, dist, args, shape, dev, rank: int, world: int):
                                 tuple(t[which].contiguous() for t in down), 64)
 
         local = cut(slice(rank * per, (rank + 1) * per))
-        if args.ep_reduce == "peer":
+        if reduce == "peer":
             shared = cut(slice(shape.experts, shape.experts + 1)) if shape.shared else None
-            layer, why = None, ""
-            try:
-                layer = ep.PeerExpertParallel(router, local, shape.experts, shape.top_k, rows, shared_experts=shared,
-                                              logit_bias=bias, hot_pairs=hot_pairs(args))
-            except Exception as err:                       # e.g. peer mappings refused on this machine
-                why = repr(err)
-            failed = torch.tensor([0 if layer is not None else 1], device=dev)
-            dist.all_reduce(failed, op=dist.ReduceOp.MAX)
-            if int(failed.item()) and copy == 0 and args.config == "c2":
-                # said loudly and recorded in the line: the same data flow through NCCL, still this library's kernels
-                print(f"[bench] rank {rank}: peer windows unavailable ({why or 'on another rank'}); "
-                      "falling back to --ep-reduce tokens", file=sys.stderr)
-                args.ep_reduce = "tokens"
-                copies.append(ep.GatheredExpertParallel(router, local, shape.experts, shape.top_k, rows,
-                                                        reduce="tokens"))
-            elif int(failed.item()):
-                raise SystemExit(f"peer windows unavailable: {why or 'on another rank'}")
-            else:
-                copies.append(layer)
+            layer = ep.PeerExpertParallel(router, local, shape.experts, shape.top_k, rows, shared_experts=shared,
+                                          logit_bias=bias, hot_pairs=max(args.hot_pairs, 0))
         else:
-            copies.append(ep.GatheredExpertParallel(router, local, shape.experts, shape.top_k, rows,
-                                                    reduce=args.ep_reduce))
+            layer = ep.GatheredExpertParallel(router, local, shape.experts, shape.top_k, rows, reduce=reduce)
+        copies.append(layer)
+        if copy == 0:
+            # correctness before speed: this rank's rows through the expert-parallel step and through the whole layer
+            # on this GPU alone (every rank holds all experts of copy 0 for the moment)
+            full = experts.make([gate, up], down, 64)
+            got = layer.forward(x).clone()
+            want, pick = one_gpu_layer(torch, x, router, full, shape, bias)
+            mine = layer.win.pick_mine if reduce == "peer" else layer.buf.pick[rank * rows:(rank + 1) * rows]
+            same = bool(torch.equal(mine[:, :pick.shape[1]], pick))
+            err = rel_l2(torch, got, want)
+            torch.cuda.synchronize()
+            status = _lib.kernel_status()
+            ok, worst = all_ok(torch, dist, same and err <= TOL and status == 0, err)
+            check = {"picks_equal": ok or same, "rel_l2": worst, "tolerance": TOL, "rows_per_rank": rows,
+                     "against": "the one-GPU layer (same kernels, all experts on one GPU) on each rank's own rows",
+                     "passed": ok}
+            if not ok:
+                raise SystemExit(f"expert-parallel output differs from the one-GPU layer on rank {rank}: picks equal "
+                                 f"{same}, rel-L2 {err:.3e}, device status {_lib.describe_status(status)}")
+            del full, got, want
         del gate, up, down
-    x = synthetic.activations(shape, rows, dev, index=100 + rank)
     side = torch.cuda.Stream(dev)
-    if args.ep_reduce == "peer":                           # the tokens live in each copy's window; nothing to stage
-        inputs = [layer.tokens for layer in copies]
-        for t in inputs:
-            t.copy_(x)
+    if reduce == "peer":                                       # the tokens live in each copy's window; nothing to stage
+        for layer in copies:
+            layer.tokens.copy_(x)
         steps = [layer.forward for layer in copies]
     else:
-        inputs = [x] * len(copies)
         steps = [(lambda layer=layer: layer.forward(x)) for layer in copies]
-    for step in steps:                                     # warm up eagerly (NCCL set-up), then capture the step
+    for step in steps:                                         # warm up eagerly (NCCL set-up), then capture the step
         step()
     torch.cuda.synchronize()
     dist.barrier()
@@ -392,148 +544,249 @@ def bench_ep(torch, dist, args, shape, dev, rank: int, world: int):
         graphs.append(g)
     torch.cuda.synchronize()
     dist.barrier()
-    for i in range(args.warmup):
-        graphs[i % len(graphs)].replay()
-    torch.cuda.synchronize()
-    dist.barrier()
-    torch.cuda.synchronize()
-    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    a.record()
-    for i in range(args.steps):
-        graphs[i % len(graphs)].replay()
-    b.record()
-    torch.cuda.synchronize()
-    dist.barrier()
-    ms = a.elapsed_time(b) / args.steps
+    k = args.steps if config == "c2" else min(args.steps, 20)
+    ms, all_ms = timed(torch, lambda i: graphs[i % len(graphs)].replay(), k, args.warmup,
+                       repeats_for(k) if config == "c2" else 5, dist)
     # end to end: pinned host tokens in, result back, every step
     x_host = x.cpu().pin_memory()
     out_host = torch.empty((rows, shape.dims), dtype=torch.bfloat16).pin_memory()
     torch.cuda.synchronize()
     dist.barrier()
     host_graphs = []
-    for step, inp, layer in zip(steps, inputs, copies):    # the same step with its host transfers inside the graph
+    for step, layer in zip(steps, copies):                     # the same step with its host transfers inside the graph
         side.wait_stream(torch.cuda.current_stream())
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g, stream=side):
-            if args.ep_reduce == "peer":                   # kernels read the pinned rows and store the pinned result
+            if reduce == "peer":                               # kernels read the pinned rows and store the pinned result
                 layer.forward(x_host, out_host)
             else:
-                inp.copy_(x_host, non_blocking=True)
+                x.copy_(x_host, non_blocking=True)
                 step()
                 out_host.copy_(layer.out, non_blocking=True)
         host_graphs.append(g)
     torch.cuda.synchronize()
     dist.barrier()
-    for i in range(min(args.warmup, len(host_graphs))):
-        host_graphs[i].replay()
+    e2e_ms, e2e_all = timed(torch, lambda i: host_graphs[i % len(host_graphs)].replay(), k, min(args.warmup, 4),
+                            repeats_for(k) if config == "c2" else 5, dist, sync_each=True)
     torch.cuda.synchronize()
-    dist.barrier()
-    a.record()
-    for i in range(args.steps):
-        host_graphs[i % len(host_graphs)].replay()
-        torch.cuda.current_stream().synchronize()
-    b.record()
-    torch.cuda.synchronize()
-    dist.barrier()
-    e2e_ms = a.elapsed_time(b) / args.steps
+    status = _lib.kernel_status()
+    if status != 0:
+        raise SystemExit(f"a kernel recorded a failure on rank {rank}: {_lib.describe_status(status)}")
     # this rank's algorithmic bytes a step: its touched experts' packed weights, the router rows, its tokens in and out
     layer = copies[0]
     nbytes = router.numel() * 2 + 2 * rows * shape.dims * 2
-    if args.ep_reduce == "peer":
+    pairs = 0
+    if reduce == "peer":
         w = layer.win
         mine = w.pick_all[:, :shape.top_k].reshape(-1)
         mine = mine[(mine >= w.lo) & (mine < w.lo + w.per_rank)]
+        pairs = int(mine.numel())
         nbytes += int(torch.unique(mine).numel()) * local.bytes_per_expert()
         if shape.shared:
             nbytes += local.bytes_per_expert()
     else:
         nbytes += per * local.bytes_per_expert()
-    return ms, e2e_ms, layer.launches, nbytes
+    per_rank = torch.zeros((world, 2), device=dev, dtype=torch.float64)
+    per_rank[rank, 0], per_rank[rank, 1] = nbytes, pairs
+    dist.all_reduce(per_rank)
+    return {"ms": ms, "all_ms": all_ms, "e2e_ms": e2e_ms, "e2e_all": e2e_all, "launches": layer.launches, "rows": rows,
+            "rank_bytes": [int(v) for v in per_rank[:, 0].tolist()], "rank_pairs": [int(v) for v in per_rank[:, 1].tolist()],
+            "check": check, "steps": k, "reduce": reduce}
 
 
-def bench_c5(torch, dist, args, dev, rank: int, world: int):
-    """Config 5 on the expert-parallel EXL3 path: 8 layers (hidden 4096, 160 experts x FFN 1536, top-8, a seeded width
-    of 2..8 bits a tensor), 128 tokens split over the ranks, `h = bf16(h + moe(h))` between layers; one step = the
-    8-layer stack in one CUDA graph.  A rank holds only its experts (1.9 GB over the 8 layers at 8 ranks, so no layer's
-    weights survive in L2 from step to step).  Returns (ms a step, ms end to end, launches, rank-0 bytes, rows)."""
+def c5_widths() -> dict:
+    """Config 5's seeded width (2..8 bits) of every (layer, expert, matrix); every rank draws them in the same order."""
 
     import random
 
-    from tensorfold_b200 import ep, synthetic
+    from tensorfold_b200 import synthetic
+
+    rng = random.Random(5005)
+    return {(li, e, m): rng.choice((2, 3, 4, 5, 6, 7, 8)) for li in range(C5_LAYERS)
+            for e in range(synthetic.C5.experts) for m in range(3)}
+
+
+def c5_experts(torch, dev, li: int, ids, widths):
+    """The EXL3 experts `ids` of layer `li` (per-expert triples for gate, up, down)."""
+
+    from tensorfold_b200 import synthetic
+
+    shape = synthetic.C5
+    base = 1000 * shape.config + 10 + 1000003 * li
+    gate, up, down = [], [], []
+    for e in ids:
+        gate.append(synthetic.exl3_matrix(base + 3 * e, shape.dims, shape.width, widths[(li, e, 0)], dev))
+        up.append(synthetic.exl3_matrix(base + 3 * e + 1, shape.dims, shape.width, widths[(li, e, 1)], dev))
+        down.append(synthetic.exl3_matrix(base + 3 * e + 2, shape.width, shape.dims, widths[(li, e, 2)], dev))
+    return gate, up, down
+
+
+def bench_c5(torch, dist, args, dev, rank: int, world: int, hbm: float) -> dict:
+    """Config 5 on the expert-parallel EXL3 path: 8 layers (hidden 4096, 160 experts x FFN 1536, top-8, a seeded width
+    of 2..8 bits a tensor), `h = bf16(h + moe(h))` between layers, at 1, 8, 32, 128 and 512 tokens split over the ranks
+    (a batch smaller than the rank count leaves the last ranks without a token; they still serve their experts).
+    One step = the 8-layer stack in one CUDA graph; 16 seeded token batches rotate (a small copy in front of the graph)
+    so the experts change every step.  Before timing, every layer of the stack is compared with the one-GPU layer on
+    the same input ("ep_check")."""
+
+    from tensorfold_b200 import _lib, ep, moe, synthetic
     from tensorfold_b200.exl3 import experts as x3
 
-    shape, layers_n, tokens = synthetic.C5, 8, 128
-    rows, per = tokens // world, shape.experts // world
-    rng = random.Random(5005)
-    widths = {(li, e, m): rng.choice((2, 3, 4, 5, 6, 7, 8)) for li in range(layers_n) for e in range(shape.experts)
-              for m in range(3)}                                  # every rank draws all widths in the same order
+    shape = synthetic.C5
+    per = shape.experts // world
+    widths = c5_widths()
     router = synthetic.router_rows(shape, dev)
-    layers = []
-    for li in range(layers_n):
-        base = 1000 * shape.config + 10 + 1000003 * li
-        gate, up, down = [], [], []
-        for e in range(rank * per, (rank + 1) * per):
-            gate.append(synthetic.exl3_matrix(base + 3 * e, shape.dims, shape.width, widths[(li, e, 0)], dev))
-            up.append(synthetic.exl3_matrix(base + 3 * e + 1, shape.dims, shape.width, widths[(li, e, 1)], dev))
-            down.append(synthetic.exl3_matrix(base + 3 * e + 2, shape.width, shape.dims, widths[(li, e, 2)], dev))
-        ex = x3.prepare(gate, up, down, x3.CB_3INST, device=dev)
-        layers.append(ep.PeerExl3ExpertParallel(router, ex, shape.experts, shape.top_k, rows))
-    x = synthetic.activations(shape, rows, dev, index=100 + rank)
-    h_out = torch.zeros_like(x)
+    mine = list(range(rank * per, (rank + 1) * per))
+    local = [x3.prepare(*c5_experts(torch, dev, li, mine, widths), x3.CB_3INST, device=dev) for li in range(C5_LAYERS)]
 
-    def step(src):
+    class _Cfg:
+        num_experts_per_tok, num_experts = shape.top_k, shape.experts
+        moe_intermediate_size, hidden_size = shape.width, shape.dims
+
+    def build(tokens):
+        rows = max(1, math.ceil(tokens / world))
+        active = max(0, min(rows, tokens - rank * rows))
+        layers = [ep.PeerExl3ExpertParallel(router, ex, shape.experts, shape.top_k, rows, rows_active=active)
+                  for ex in local]
+        return rows, active, layers
+
+    def stack(layers, src, h_out, each=None):
         h = src
         for li, layer in enumerate(layers):
             y = layer.forward(h)                                  # fp32 [rows, D]
             if li == 0:
                 h = layer.tokens                                  # the staged rows (src may be pinned host memory)
+            if each is not None:
+                each(li, h, y)
             h = (h.float() + y).to(torch.bfloat16)                # the residual add between layers
         h_out.copy_(h)
 
-    step(x)
-    torch.cuda.synchronize()
-    dist.barrier()
-    side = torch.cuda.Stream(dev)
-    side.wait_stream(torch.cuda.current_stream())
-    graph = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(graph, stream=side):
-        step(x)
-    x_host = x.cpu().pin_memory()
-    out_host = torch.empty((rows, shape.dims), dtype=torch.bfloat16).pin_memory()
-    side.wait_stream(torch.cuda.current_stream())
-    host_graph = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(host_graph, stream=side):
-        step(x_host)
-        out_host.copy_(h_out, non_blocking=True)
-    torch.cuda.synchronize()
-    dist.barrier()
+    # ---- correctness first: 32 tokens, every layer against the one-GPU layer on the same input ----
+    rows, active, layers = build(32)
+    x = torch.zeros((rows, shape.dims), dtype=torch.bfloat16, device=dev)
+    x[:active] = synthetic.activations(shape, rows, dev, index=100 + rank)[:active]
+    worst, same = 0.0, True
 
-    def timed(g, sync_each):
-        for _ in range(args.warmup):
-            g.replay()
+    def compare(li, h, y):
+        nonlocal worst, same
+        if active == 0:
+            return
+        full = x3.prepare(*c5_experts(torch, dev, li, range(shape.experts), widths), x3.CB_3INST, device=dev)
+        buf = moe.MoEBuffers(rows, _Cfg, dev, shared=False)
+        moe.router(h[:active], router, buf.logits[:active])
+        moe.select_rows(buf.logits[:active], buf, shape.top_k, shape.experts)
+        want = x3.routed(h[:active], buf.pick[:active].contiguous(), buf.wts[:active].contiguous(), full,
+                         x3.Scratch(full, active, shape.top_k, device=dev), None, active)
+        same = same and bool(torch.equal(layers[li].win.pick_mine[:active], buf.pick[:active]))
+        worst = max(worst, rel_l2(torch, y[:active], want))
+        del full
+
+    h_chk = torch.zeros_like(x)
+    stack(layers, x, h_chk, compare)
+    torch.cuda.synchronize()
+    status = _lib.kernel_status()
+    ok, worst_all = all_ok(torch, dist, same and worst <= TOL and status == 0, worst)
+    check = {"picks_equal": ok or same, "rel_l2": worst_all, "tolerance": TOL, "tokens": 32, "layers": C5_LAYERS,
+             "against": "the one-GPU EXL3 layer on the same layer input, every layer of the stack", "passed": ok}
+    if not ok:
+        raise SystemExit(f"config 5: expert-parallel stack differs from the one-GPU layers on rank {rank}: picks "
+                         f"equal {same}, rel-L2 {worst:.3e}, device status {_lib.describe_status(status)}")
+    del layers
+    # ---- the sweep ----
+    lines = []
+    for tokens in C5_TOKENS:
+        rows, active, layers = build(tokens)
+        batches = []
+        for i in range(16):
+            xb = torch.zeros((rows, shape.dims), dtype=torch.bfloat16, device=dev)
+            xb[:active] = synthetic.activations(shape, rows, dev, index=200 + 16 * rank + i)[:active]
+            batches.append(xb)
+        x_in, h_out = batches[0].clone(), torch.zeros_like(batches[0])
+        stack(layers, x_in, h_out)
         torch.cuda.synchronize()
         dist.barrier()
-        torch.cuda.synchronize()
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
-        for _ in range(args.steps):
-            g.replay()
-            if sync_each:
-                torch.cuda.current_stream().synchronize()
-        b.record()
+        side = torch.cuda.Stream(dev)
+        side.wait_stream(torch.cuda.current_stream())
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            stack(layers, x_in, h_out)
+        x_host = [b.cpu().pin_memory() for b in batches[:4]]
+        x_pin = torch.empty_like(x_host[0]).pin_memory()
+        out_host = torch.empty((rows, shape.dims), dtype=torch.bfloat16).pin_memory()
+        side.wait_stream(torch.cuda.current_stream())
+        host_graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(host_graph, stream=side):
+            stack(layers, x_pin, h_out)
+            out_host.copy_(h_out, non_blocking=True)
         torch.cuda.synchronize()
         dist.barrier()
-        return a.elapsed_time(b) / args.steps
 
-    ms, e2e_ms = timed(graph, False), timed(host_graph, True)
-    nbytes = layers_n * (router.numel() * 2) + 2 * rows * shape.dims * 2
-    for layer in layers:
-        w = layer.win
-        mine = w.pick_all.reshape(-1)
-        mine = torch.unique(mine[(mine >= w.lo) & (mine < w.lo + w.per_rank)]) - w.lo
-        nbytes += layer.local.nbytes_read(mine.cpu().tolist())
-    launches = sum(layer.launches for layer in layers) + 3 * layers_n + 1
-    return ms, e2e_ms, launches, nbytes, rows
+        def step(i):
+            x_in.copy_(batches[i % len(batches)], non_blocking=True)
+            graph.replay()
+
+        def host_step(i):
+            x_pin.copy_(x_host[i % len(x_host)])                  # the caller fills its pinned buffer
+            host_graph.replay()
+
+        k = min(args.steps, 10)
+        ms, all_ms = timed(torch, step, k, 3, 5, dist)
+        e2e_ms, _ = timed(torch, host_step, k, 2, 3, dist, sync_each=True)
+        # bytes of the last step on this rank: trellises and scales of the experts its layers touched
+        nbytes = C5_LAYERS * router.numel() * 2 + 2 * active * shape.dims * 2
+        for layer in layers:
+            w = layer.win
+            sel = w.pick_all.reshape(-1)
+            sel = torch.unique(sel[(sel >= w.lo) & (sel < w.lo + w.per_rank)]) - w.lo
+            nbytes += layer.local.nbytes_read(sel.cpu().tolist())
+        per_rank = torch.zeros((world,), device=dev, dtype=torch.float64)
+        per_rank[rank] = nbytes
+        dist.all_reduce(per_rank)
+        rb = [int(v) for v in per_rank.tolist()]
+        launches = sum(layer.launches for layer in layers) + 3 * C5_LAYERS + 2
+        lines.append({"tokens": tokens, "rows_per_rank": rows, "ms_per_step": ms, **spread(all_ms),
+                      "tokens_per_s": tokens / (ms * 1e-3), "e2e_ms_per_step": e2e_ms,
+                      "e2e_tokens_per_s": tokens / (e2e_ms * 1e-3), "steps": k, "launches_per_step": launches,
+                      "rank_bytes_max": max(rb), "rank_bytes_sum": sum(rb),
+                      "slowest_rank_frac_of_hbm": max(rb) / (ms * 1e-3) / 1e9 / hbm,
+                      "all_ranks_frac_of_hbm": sum(rb) / world / (ms * 1e-3) / 1e9 / hbm})
+        status = _lib.kernel_status()
+        if status != 0:
+            raise SystemExit(f"config 5: a kernel recorded a failure on rank {rank}: {_lib.describe_status(status)}")
+        del layers, graph, host_graph
+        torch.cuda.empty_cache()
+    return {"config": workload_config(shape, 0, world, "c5") | {"tokens": list(C5_TOKENS)}, "dtype": "f16",
+            "scaling": "strong", "n_gpus": world, "sweep": lines, "ep_check": check}
+
+
+def ep_summary(res: dict, shape, config: str, world: int, hbm: float, which: str) -> dict:
+    """The fields of one expert-parallel affine run (configs 2 and 4) that go into the JSON line."""
+
+    ms, rows = res["ms"], res["rows"]
+    rb = res["rank_bytes"]
+    return {"config": {**workload_config(shape, rows, world, config),
+                       "l2": f"each rank rotates {ep_copies(config, world)} copies of its {shape.experts // world}-expert "
+                             "slice (inputs larger than the 126 MB L2)",
+                       "collective": COLLECTIVE[res["reduce"]] + "; the step is one CUDA graph"},
+            "scaling": "weak" if config == "c2" else "strong", "n_gpus": world, "steps": res["steps"],
+            "ms_per_step": ms, **spread(res["all_ms"]), "tokens_per_s": world * rows / (ms * 1e-3),
+            "e2e_ms_per_step": res["e2e_ms"], "e2e_tokens_per_s": world * rows / (res["e2e_ms"] * 1e-3),
+            "launches_per_step": res["launches"], "rank_bytes": rb, "rank_pairs": res["rank_pairs"],
+            "pairs_per_rank_min": min(res["rank_pairs"]), "pairs_per_rank_max": max(res["rank_pairs"]),
+            "rank0_frac_of_hbm": rb[0] / (ms * 1e-3) / 1e9 / hbm,
+            "slowest_rank_frac_of_hbm": max(rb) / (ms * 1e-3) / 1e9 / hbm,
+            "all_ranks_frac_of_hbm": sum(rb) / world / (ms * 1e-3) / 1e9 / hbm, "peak_source": f"of {which}",
+            "ep_check": res["check"]}
+
+
+def guarded(name: str, fn, torch, dist) -> dict:
+    """Run one of the extra workloads; a failure becomes an "error" entry instead of losing the headline line."""
+
+    try:
+        return fn()
+    except (Exception, SystemExit) as err:                     # noqa: BLE001
+        print(f"[bench] {name} failed: {err!r}", file=sys.stderr)
+        return {"error": repr(err)}
 
 
 def run_ours(args) -> None:
@@ -547,81 +800,103 @@ def run_ours(args) -> None:
         raise SystemExit("bench.py needs a GPU: there is no CPU fallback (use --impl reference for the CPU baseline)")
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
-    ep_path = world > 1 or args.config in ("c4", "c5")   # configs 4 and 5 always run the expert-parallel code
-    if ep_path:
-        import torch.distributed as dist
+    import datetime
 
-        if world == 1:                                 # not under torchrun: a group of one
-            os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-            os.environ.setdefault("MASTER_PORT", "29533")
-            dist.init_process_group("nccl", rank=0, world_size=1, device_id=dev)
-        else:
-            dist.init_process_group("nccl", device_id=dev)
+    import torch.distributed as dist
+
+    if world == 1:                                     # not under torchrun: a group of one
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29533")
+        dist.init_process_group("nccl", rank=0, world_size=1, device_id=dev, timeout=datetime.timedelta(seconds=180))
+    else:
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=180))
     hbm, tflops, which = peaks()
     _lib.set_pdl(bool(args.pdl))
     if args.exl3_only:
         print(json.dumps({"sweep": bench_exl3(torch, (1, 64), args.steps, args.warmup, hbm)}))
         return
-    shape, rows = (synthetic.C4 if args.config == "c4" else synthetic.C5 if args.config == "c5" else synthetic.C2), \
-        args.rows
-    if args.config == "c5" and args.ep_reduce != "peer":
-        raise SystemExit("--config c5 runs the peer-memory form")
-    if args.config == "c4":
-        if args.ep_reduce != "peer":
-            raise SystemExit("--config c4 runs the peer-memory form")
-        rows = ep_rows(args, shape, world)
+    shapes = {"c2": synthetic.C2, "c4": synthetic.C4, "c5": synthetic.C5}
+    if args.config != "c2" and args.ep_reduce != "peer":
+        raise SystemExit(f"--config {args.config} runs the peer-memory form")
+    for s in shapes.values():
+        if s.experts % world:
+            raise SystemExit(f"{s.experts} experts do not shard over {world} ranks")
+
+    extras = {}
+
+    def run_extras():
+        if args.no_extra:
+            return
+        torch.cuda.empty_cache()
+        extras["c4"] = guarded("config 4", lambda: ep_summary(
+            bench_ep(torch, dist, args, "c4", synthetic.C4, dev, rank, world), synthetic.C4, "c4", world, hbm, which),
+            torch, dist)
+        torch.cuda.empty_cache()
+        extras["c5"] = guarded("config 5", lambda: bench_c5(torch, dist, args, dev, rank, world, hbm), torch, dist)
+        torch.cuda.empty_cache()
+
+    if world > 1 or args.config in ("c4", "c5"):
+        # ---- the expert-parallel path is the headline ----
+        with ClockSampler(local) as clocks:
+            if args.config == "c5":
+                c5 = bench_c5(torch, dist, args, dev, rank, world, hbm)
+            else:
+                res = bench_ep(torch, dist, args, args.config, shapes[args.config], dev, rank, world)
+        if args.config == "c2":
+            run_extras()
+        if rank == 0:
+            if args.config == "c5":
+                top = next(l for l in c5["sweep"] if l["tokens"] == 128)
+                line = {"metric": METRIC, "value": top["tokens_per_s"], "unit": UNIT, "n_gpus": world,
+                        "steps": top["steps"], "warmup": 3, "ms_per_step": top["ms_per_step"],
+                        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16",
+                        "data": "synthetic", "config": workload_config(synthetic.C5, 128, world, "c5"),
+                        "clocks": clocks.summary(),
+                        "e2e": {"value": top["e2e_tokens_per_s"], "unit": UNIT, "ms_per_step": top["e2e_ms_per_step"],
+                                "h2d_bytes_per_step": 128 * synthetic.C5.dims * 2,
+                                "d2h_bytes_per_step": 128 * synthetic.C5.dims * 2},
+                        "gpu_launches": top["launches_per_step"] * top["steps"],
+                        "roofline": {"bound": "hbm", "kernel": "the 8-layer expert-parallel EXL3 step (slowest rank)",
+                                     "achieved": top["rank_bytes_max"] / (top["ms_per_step"] * 1e-3) / 1e9,
+                                     "peak": hbm, "unit": "GB/s", "frac": top["slowest_rank_frac_of_hbm"],
+                                     "peak_source": f"of {which}", "traffic": None},
+                        "cpu_baseline": None, "ep_check": c5["ep_check"], "c5": c5}
+            else:
+                shape = shapes[args.config]
+                s = ep_summary(res, shape, args.config, world, hbm, which)
+                nbytes = res["rows"] * shape.dims * 2 * world
+                line = {"metric": METRIC, "value": s["tokens_per_s"], "unit": UNIT, "n_gpus": world,
+                        "steps": res["steps"], "warmup": args.warmup, "ms_per_step": res["ms"],
+                        **spread(res["all_ms"]), "higher_is_better": True, "scaling": s["scaling"],
+                        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+                        "config": {**s["config"], "hot_pairs": max(args.hot_pairs, 0)}, "clocks": clocks.summary(),
+                        "e2e": {"value": s["e2e_tokens_per_s"], "unit": UNIT, "ms_per_step": res["e2e_ms"],
+                                "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": nbytes},
+                        "gpu_launches": res["launches"] * res["steps"],
+                        "roofline": {"bound": "hbm", "kernel": "the whole expert-parallel step on one GPU (rank 0)",
+                                     "achieved": res["rank_bytes"][0] / (res["ms"] * 1e-3) / 1e9, "peak": hbm,
+                                     "unit": "GB/s", "frac": s["rank0_frac_of_hbm"], "peak_source": f"of {which}",
+                                     "traffic": None, "bytes_per_step": res["rank_bytes"][0],
+                                     "slowest_rank_frac": s["slowest_rank_frac_of_hbm"],
+                                     "note": "algorithmic bytes of rank 0's step (its touched experts' packed weights, "
+                                             "router rows, tokens in and out) over the step time; the per-kernel "
+                                             "roofline with ncu traffic is the 1-GPU line's"},
+                        "rank_pairs": res["rank_pairs"], "cpu_baseline": None, "ep_check": res["check"], **extras}
+            print(json.dumps(line))
+        dist.barrier()
+        dist.destroy_process_group()
+        return
+
+    # ---- one GPU: the headline layer, its sweep, then configs 4 and 5 on the expert-parallel code with one rank ----
+    shape, rows = synthetic.C2, args.rows
     layers = []
-    for copy in range(0 if ep_path else 2):
+    for copy in range(2):
         gate, up, down = synthetic.affine_layer(shape, dev, torch.float16 if args.scales == "fp16" else torch.bfloat16,
                                                  copy=copy)
         layers.append(moe.Routed(synthetic.router_rows(shape, dev), experts.make([gate, up], down, 64), shape.top_k,
                                  shared=shape.shared))
         del gate, up, down
     torch.cuda.synchronize()
-
-    if ep_path:
-        if shape.experts % world:
-            raise SystemExit(f"{shape.experts} experts do not shard over {world} ranks")
-        del layers
-        with ClockSampler(local) as clocks:
-            if args.config == "c5":
-                ms, e2e_ms, launches, rank_bytes, rows = bench_c5(torch, dist, args, dev, rank, world)
-            else:
-                ms, e2e_ms, launches, rank_bytes = bench_ep(torch, dist, args, shape, dev, rank, world)
-        t = torch.tensor([ms, e2e_ms], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms, e2e_ms = t.tolist()
-        status = _lib.kernel_status()
-        if status != 0:
-            raise SystemExit(f"a kernel recorded device status {status}")
-        if rank == 0:
-            nbytes = rows * shape.dims * 2 * world
-            line = {"metric": METRIC, "value": world * rows / (ms * 1e-3), "unit": UNIT, "n_gpus": world,
-                    "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
-                    "scaling": "weak" if args.config == "c2" else "strong", "vs_baseline": None,
-                    "dtype": "f16" if args.config == "c5" else "bf16", "data": "synthetic",
-                    "config": {**workload_config(shape, rows, world, args.config),
-                               **({} if args.config == "c5" else {
-                                   "l2": f"each rank rotates {ep_copies(args, world)} copies of its "
-                                         f"{shape.experts // world}-expert slice (inputs larger than the 126 MB L2)"}),
-                               "collective": COLLECTIVE[args.ep_reduce] + "; the step is one CUDA graph",
-                               "hot_pairs": hot_pairs(args)},
-                    "clocks": clocks.summary(),
-                    "e2e": {"value": world * rows / (e2e_ms * 1e-3), "unit": UNIT, "ms_per_step": e2e_ms,
-                            "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": nbytes},
-                    "gpu_launches": launches * args.steps,
-                    "roofline": {"bound": "hbm", "kernel": "the whole expert-parallel step on one GPU (rank 0)",
-                                 "achieved": rank_bytes / (ms * 1e-3) / 1e9, "peak": hbm, "unit": "GB/s",
-                                 "frac": rank_bytes / (ms * 1e-3) / 1e9 / hbm, "peak_source": f"of {which}",
-                                 "traffic": None, "bytes_per_step": rank_bytes,
-                                 "note": "algorithmic bytes of rank 0's step (its touched experts' packed weights, "
-                                         "router rows, tokens in and out) over the step time; the per-kernel roofline "
-                                         "with ncu traffic is the 1-GPU line's"},
-                    "cpu_baseline": None}
-            print(json.dumps(line))
-        dist.barrier()
-        dist.destroy_process_group()
-        return
     with ClockSampler(local) as clocks:
         torch.cuda.synchronize()
         head, runners = bench_rows(torch, shape, layers, rows, args.steps, args.warmup, hbm, args.form == "prefill",
@@ -630,10 +905,10 @@ def run_ours(args) -> None:
     e2e = bench_e2e(torch, runners, shape, rows, args.steps, args.warmup)
     status = _lib.kernel_status()
     if status != 0:
-        raise SystemExit(f"a kernel recorded device status {status}")
+        raise SystemExit(f"a kernel recorded a failure: {_lib.describe_status(status)}")
     ms = head["ms_per_step"]
     sweep = []
-    if world == 1 and not args.no_sweep:
+    if not args.no_sweep:
         del runners
         for t_rows, pre in ((1, False), (4, False), (16, False), (2048, True)):
             res, rr = bench_rows(torch, shape, layers, t_rows, max(5, args.steps // 2), args.warmup, hbm, pre, tflops)
@@ -643,35 +918,44 @@ def run_ours(args) -> None:
         del layers
         torch.cuda.empty_cache()
         sweep += bench_exl3(torch, (1, 64), max(5, args.steps // 2), args.warmup, hbm)
-    if rank != 0:
-        return
-    value = world * rows / (ms * 1e-3)
-    cpu = None
+    else:
+        del layers
+    run_extras()
+    value = rows / (ms * 1e-3)
+    cpu = cpu_1 = cpu_x3 = None
     if not args.no_cpu:
         passes = 100                                      # about 10 s of host work at 0.1 s a pass
         v, sec, cores = cpu_baseline(shape, rows, passes, 2)
         cpu = {"value": v, "unit": UNIT, "cores": cores, "kind": "port",
                "sample": f"{passes} timed passes (2 warm-up) of the same {rows}-token layer call, {sec:.3f} s a pass"}
+        v1, sec1, _ = cpu_baseline(shape, rows, 4, 1, threads=1)
+        cpu_1 = {"value": v1, "unit": UNIT, "cores": 1, "kind": "port",
+                 "sample": f"4 timed passes (1 warm-up) of the same {rows}-token layer call, {sec1:.3f} s a pass"}
+        vx, secx, cx = cpu_baseline_exl3(rows, 3)
+        cpu_x3 = {"value": vx, "unit": UNIT, "cores": cx, "kind": "port",
+                  "sample": f"3 timed passes (1 warm-up) of the routed EXL3 experts of config 3 (4.00 bpw) on {rows} "
+                            f"tokens, {secx:.3f} s a pass"}
+    traffic, traffic_source = captured_traffic() if (rows, args.form) == (64, "decode") else (None, "not captured")
     line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "warmup": args.warmup, "ms_per_step": ms, **{k: head[k] for k in ("repeats", "ms_min", "ms_max")},
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic", "config": workload_config(shape, rows, world),
             "clocks": clocks.summary(), "e2e": e2e, "gpu_launches": head["launches_per_step"] * args.steps,
             "roofline": {"bound": "hbm", "kernel": "decode_kernel<M=2, SwiGLU> (gate/up)",
                          "achieved": head["gate_up_gbs"], "peak": hbm, "unit": "GB/s",
                          "frac": head["gate_up_gbs"] / hbm, "peak_source": f"of {which}",
-                         "traffic": TRAFFIC_GATE_UP_C2_64 if (rows, args.form) == (64, "decode") else None,
-                         "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch of this "
-                                           "workload (profiles/decode_kernel_c2_64tokens.md)",
+                         "traffic": traffic, "traffic_source": traffic_source,
                          "bytes_per_launch": head["gate_up_bytes"], "us_per_launch": head["gate_up_us"]},
             "layer": {k: head[k] for k in ("distinct_experts", "layer_bytes", "layer_gbs", "layer_frac_of_hbm")},
-            "cpu_baseline": cpu, "sweep": sweep}
+            "cpu_baseline": cpu, "cpu_baseline_1_thread": cpu_1, "cpu_baseline_exl3": cpu_x3, "sweep": sweep, **extras}
     print(json.dumps(line))
+    dist.destroy_process_group()
 
 
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--rows", type=int, default=64, help="tokens a step on each GPU")
@@ -685,18 +969,19 @@ def main() -> None:
                     help="multi-GPU exchanges: own kernels over NVLink peer memory (default), or NCCL with per-token "
                          "partial sums / exact per-pair rows")
     ap.add_argument("--config", default="c2", choices=["c2", "c4", "c5"],
-                    help="c2: the headline layer (default); c4: the 256-expert layer with a shared expert and skewed "
-                         "routing, 256 tokens split over the ranks; c5: the 8-layer mixed-width EXL3 stack, 128 tokens "
-                         "split over the ranks")
+                    help="c2: the headline layer, with configs 4 and 5 beside it under \"c4\" / \"c5\" (default); c4: "
+                         "only the 256-expert layer with a shared expert and skewed routing, 256 tokens split over the "
+                         "ranks; c5: only the 8-layer mixed-width EXL3 stack, 1..512 tokens split over the ranks")
     ap.add_argument("--hot-pairs", type=int, default=-1,
                     help="expert-parallel peer form: experts with at least this many pairs use the prompt-form kernel "
                          "(default 0: never)")
-    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--no-sweep", action="store_true", help="skip the 1-, 4-, 16- and 2048-token lines")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline legs")
+    ap.add_argument("--no-sweep", action="store_true", help="skip the 1-, 4-, 16- and 2048-token and EXL3 lines")
+    ap.add_argument("--no-extra", action="store_true", help="skip configs 4 and 5")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
-        args.steps = min(args.steps, 400)                        # a bounded CPU sample: a pass takes ~0.3 s
+        args.steps = min(args.steps, 400)                        # a bounded CPU sample: a pass takes ~0.1 s
         run_reference(args)
     else:
         run_ours(args)

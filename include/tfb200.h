@@ -217,7 +217,9 @@ int tfb_exl3_rot_in(const void* x, int64_t x_stride, int x_is_fp16, const int32_
                     const void* suh1, void* out0, void* out1, int R, int K, int slots, int E, void* stream);
 
 /* z [mats, P, N] fp32 = x_m [P, K] fp16 times W_q of each pair's expert, trellis decoded on the fly; tp*: int64 device
- * pointers [E], k2_*: int32 [E].  Replaces `grouped`: src/tensorfold/cuda/exl3/experts_grouped.cuh:190-284. */
+ * pointers [E], k2_*: int32 [E].  uids must hold maxu entries and members maxu * maxm words (the kernel reads row u
+ * of the table for every u of its grid, before it knows how many experts the step uses).
+ * Replaces `grouped`: src/tensorfold/cuda/exl3/experts_grouped.cuh:190-284. */
 int tfb_exl3_grouped(const void* x0, const void* x1, const int64_t* tp0, const int64_t* tp1, const int32_t* k2_0,
                      const int32_t* k2_1, const int32_t* uids, const int32_t* ucount, const int32_t* members, float* z,
                      int mats, int K, int N, int P, int slots, int cb, int maxm, int maxu, void* stream);

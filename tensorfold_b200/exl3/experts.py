@@ -19,6 +19,7 @@ from .. import _lib
 CB_3INST, CB_MCG, CB_MUL1 = 0, 1, 2
 ACT_BF16, ACT_F32 = 0, 1          # SwiGLU with the GLM family's bf16 roundings / in fp32
 K2_SUPPORTED = tuple(range(2, 17))   # half-bits a value: 1..8 bits and every half-integer rate between
+LAUNCHES_PER_CALL = 6             # kernels one ``routed`` call enqueues (grouping included)
 
 # (16-column tiles a block, K-slice warps, K splits across blocks, tiles in flight): this library's one setting.
 # The split is by shape only; partial sums meet in warp order inside the block, so there is one split.
