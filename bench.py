@@ -813,7 +813,8 @@ def run_ours(args) -> None:
     hbm, tflops, which = peaks()
     _lib.set_pdl(bool(args.pdl))
     if args.exl3_only:
-        print(json.dumps({"sweep": bench_exl3(torch, (1, 64), args.steps, args.warmup, hbm)}))
+        print(json.dumps({"sweep": bench_exl3(torch, args.exl3_rows, args.steps, args.warmup, hbm)}))
+        dist.destroy_process_group()
         return
     shapes = {"c2": synthetic.C2, "c4": synthetic.C4, "c5": synthetic.C5}
     if args.config != "c2" and args.ep_reduce != "peer":
@@ -958,7 +959,7 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--rows", type=int, default=64, help="tokens a step on each GPU")
+    ap.add_argument("--rows", type=int, default=None, help="tokens a step on each GPU (64 unless given)")
     ap.add_argument("--scales", default="fp16", choices=["fp16", "bf16"], help="dtype of the affine scales and biases")
     ap.add_argument("--pdl", type=int, default=1, help="1: programmatic dependent launch between the layer's kernels")
     ap.add_argument("--form", default="decode", choices=["decode", "prefill"],
@@ -979,6 +980,8 @@ def main() -> None:
     ap.add_argument("--no-sweep", action="store_true", help="skip the 1-, 4-, 16- and 2048-token and EXL3 lines")
     ap.add_argument("--no-extra", action="store_true", help="skip configs 4 and 5")
     args = ap.parse_args()
+    args.exl3_rows = (1, 64) if args.rows is None else (args.rows,)
+    args.rows = 64 if args.rows is None else args.rows
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
         args.steps = min(args.steps, 400)                        # a bounded CPU sample: a pass takes ~0.1 s

@@ -210,31 +210,36 @@ int tfb_exl3_group(const int32_t* pick, int32_t* uids, int32_t* ucount, int32_t*
 int tfb_exl3_group_static(const int32_t* pick, int32_t* uids, int32_t* ucount, int32_t* members, int R, int slots,
                           int E, int maxu, int maxm, void* stream);
 
-/* out0 / out1 [R * slots, K] fp16 = fp16(((x * suh) H) / sqrt(128)) for the two matrices of every routed pair; x is
- * bf16 (x_is_fp16 = 0) or fp16 rows with stride x_stride.
- * Replaces `rot_in`: src/tensorfold/cuda/exl3/experts.cu:93-111,312-330. */
-int tfb_exl3_rot_in(const void* x, int64_t x_stride, int x_is_fp16, const int32_t* pick, const void* suh0,
-                    const void* suh1, void* out0, void* out1, int R, int K, int slots, int E, void* stream);
+/* The first launch of a routed EXL3 call.  When `sort` != 0 one block sorts the (row, slot) pairs by expert:
+ * members [R * slots] = pair ids grouped by ascending expert (pair order kept), items [., 3] = (expert, first,
+ * count <= 16) with room for min(R * slots, E) + R * slots / 16 rows, counts [2] = (items, distinct experts),
+ * ucount [1] = distinct experts; ids outside [0, E) are left out.  The other blocks rotate the inputs:
+ * out0 / out1 [R * slots, K] fp16 = fp16(((x * suh_m[expert]) H) / sqrt(128)) for the two matrices of every routed pair
+ * (suh1 and out1 null: one matrix); x is bf16 (x_is_fp16 = 0) or fp16 rows with stride x_stride.
+ * Replaces `group` and `rot_in`: src/tensorfold/cuda/exl3/experts.cu:19-111,290-330. */
+int tfb_exl3_prologue(const void* x, int64_t x_stride, int x_is_fp16, const int32_t* pick, const void* suh0,
+                      const void* suh1, void* out0, void* out1, int R, int K, int slots, int E, int sort,
+                      int32_t* members, int32_t* items, int32_t* counts, int32_t* ucount, void* stream);
 
-/* z [mats, P, N] fp32 = x_m [P, K] fp16 times W_q of each pair's expert, trellis decoded on the fly; tp*: int64 device
- * pointers [E], k2_*: int32 [E].  uids must hold maxu entries and members maxu * maxm words (the kernel reads row u
- * of the table for every u of its grid, before it knows how many experts the step uses).
- * Replaces `grouped`: src/tensorfold/cuda/exl3/experts_grouped.cuh:190-284. */
-int tfb_exl3_grouped(const void* x0, const void* x1, const int64_t* tp0, const int64_t* tp1, const int32_t* k2_0,
-                     const int32_t* k2_1, const int32_t* uids, const int32_t* ucount, const int32_t* members, float* z,
-                     int mats, int K, int N, int P, int slots, int cb, int maxm, int maxu, void* stream);
+/* xd [P, N] fp16 = the down projection's rotated input of every routed pair, in one launch: gate and up (xg, xu
+ * [P, K] fp16 times W_q of each pair's expert, trellises decoded on the fly from 16-byte aligned tp_* [E] at widths
+ * k2_* [E]), output rotation, svh, SwiGLU (act_mode 0: bf16 roundings, 1: fp32; clipped at limit), suh_d, rotation.
+ * items / counts / members: the prologue's sort; z: fp32 scratch [2, P, N]; arrive: int32 scratch
+ * [max_items * N / 128], zero before the first call (a call leaves it zero); max_items >= the sort's item count.
+ * Replaces `grouped` + `gateup_epilogue`: src/tensorfold/cuda/exl3/experts_grouped.cuh:190-284,
+ * src/tensorfold/cuda/exl3/experts.cu:116-158. */
+int tfb_exl3_gateup(const void* xg, const void* xu, const int64_t* tp_g, const int64_t* tp_u, const int32_t* k2_g,
+                    const int32_t* k2_u, const int32_t* items, const int32_t* counts, const int32_t* members, float* z,
+                    int32_t* arrive, const void* svh_g, const void* svh_u, const void* suh_d, void* xd, int K, int N,
+                    int P, int cb, int max_items, float limit, int act_mode, void* stream);
 
-/* xd [P, N] fp16 = rotate(SwiGLU(rotate(z_gate) * svh_g, rotate(z_up) * svh_u) * suh_d); act_mode 0: bf16 roundings,
- * 1: fp32.  Replaces `gateup_epilogue`: src/tensorfold/cuda/exl3/experts.cu:116-158. */
-int tfb_exl3_gateup_epilogue(const float* z, const int32_t* pick, const void* svh_g, const void* svh_u,
-                             const void* suh_d, void* xd, int P, int N, int E, float limit, int act_mode,
-                             void* stream);
-
-/* y [R * slots, D] fp32 = rotate(z) * svh_d per routed pair; with wts and out (both or neither) also
- * out [R, D] fp32 = the slot-order fma chain of wts * y.
- * Replaces `down_epilogue`, `combine`, `down_combine`: src/tensorfold/cuda/exl3/experts.cu:161-237. */
-int tfb_exl3_down_epilogue(const float* z, const int32_t* pick, const void* svh_d, float* y, const float* wts,
-                           float* out, int R, int D, int E, int slots, void* stream);
+/* y [P, N] fp32 = rotate(x [P, K] fp16 times W_q of each pair's expert) * svh for every routed pair (other rows are
+ * left as they are), in one launch; z: fp32 scratch [P, N]; the other arguments as tfb_exl3_gateup.  The weighted
+ * slot-order sum over a row's slots is tfb_combine on y.
+ * Replaces `grouped` + `down_epilogue` (+ `combine`, `down_combine`): src/tensorfold/cuda/exl3/experts.cu:161-237. */
+int tfb_exl3_down(const void* x, const int64_t* tp, const int32_t* k2, const int32_t* items, const int32_t* counts,
+                  const int32_t* members, float* z, int32_t* arrive, const void* svh, float* y, int K, int N, int P,
+                  int cb, int max_items, void* stream);
 
 #ifdef __cplusplus
 }

@@ -4,8 +4,17 @@
 // E(p) = (p >> 1) K2 + (p odd ? K2 : K2 >> 1) (K2 = half-bits a value); a codebook turns a state into an fp16 value;
 // value p sits at row 2 (l % 4) + (j & 1) + 8 ((j >> 1) & 1), column l / 4 + 8 (j >> 2) of its tile (l = p / 8,
 // j = p % 8) - so lane l's eight values are exactly its mma.m16n8k16 fragment of the tile.  Here the tile
-// (transposed) is the A operand (16 output columns x 16 inputs) and eight pairs' rotated inputs the B operand.
+// (transposed) is the A operand (16 output columns x 16 inputs) and the pairs' rotated inputs the B operand.
 // The layer is y = (((x * suh) H) W_q) H * svh per 128-block, H = 128-point Hadamard / sqrt(128).
+//
+// Three launches a layer call (src/tensorfold/cuda/exl3/experts.py:173-202 needs seven):
+//   prologue  one block sorts the (row, slot) pairs by expert into items of <= 16 pairs (the affine plan's sort), the
+//             others rotate every routed pair's input for gate and up (x * suh, 128-point transform, fp16);
+//   gate/up   CTA = (item, 64 columns, matrix): the four warps split K, each pulls its rows of tiles through a private
+//             shared-memory ring with bulk async copies, decodes from shared memory and multiplies; the K slices meet
+//             in warp order; the LAST of the four CTAs that share (item, 128 columns) - counted with an atomic - runs
+//             the epilogue (rotate, svh, SwiGLU, suh_d, rotate) for the block and stores the down projection's input;
+//   down      the same kernel with the output rotation (and svh) as its epilogue; y fp32 per pair.
 // Fixed-order reductions everywhere: a pair's bits never depend on the other rows of the call.
 // (Replaces src/tensorfold/cuda/exl3/experts.cu and experts_grouped.cuh; the trellises are read in place.)
 
@@ -16,9 +25,15 @@ namespace tfb {
 namespace exl3 {
 
 constexpr float HAD_SCALE = 0.08838834764831845f;   // 1 / sqrt(128)
-constexpr int GR_WARPS = 4;                         // K slices a CTA of the grouped kernel (part of the arithmetic)
-constexpr int GR_NTB_MAX = 4;                       // 16-column tiles a CTA at most (no effect on the arithmetic)
-constexpr int GR_PAIRS = 8;                         // pairs a CTA (one mma B tile)
+constexpr int GR_WARPS = 4;                         // K slices a CTA (part of the arithmetic: they meet in warp order)
+constexpr int GR_NTB = 4;                           // 16-column tiles a CTA: 64 columns
+constexpr int GR_PT = 2;                            // mma tiles of 8 pairs an item: 16 pairs
+constexpr int GR_PAIRS = 8 * GR_PT;
+constexpr int GR_SLOT_BYTES = 2048;                 // a ring slot: whole rows of the CTA's four tiles
+constexpr int GR_STAGES = 3;
+constexpr int GR_RED_STRIDE = GR_NTB * 16 + 1;
+
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) { return __byte_perm(a, b, sel); }
 
 // ---- codebooks: two states -> two fp16 values (src/tensorfold/cuda/exl3/format.py:31-48) ------------------------
 template <int CB>
@@ -26,7 +41,7 @@ __device__ __forceinline__ uint32_t cb_pair(uint32_t s0, uint32_t s1) {
   if constexpr (CB == 2) {                            // mul1: fma(1024 + sum of the bytes of s * M, scale, bias) in fp16
     const uint32_t h0 = __dp4a(s0 * 0x83DCD12Du, 0x01010101u, 0x6400u);
     const uint32_t h1 = __dp4a(s1 * 0x83DCD12Du, 0x01010101u, 0x6400u);
-    const uint32_t hv = __byte_perm(h0, h1, 0x5410);
+    const uint32_t hv = prmt(h0, h1, 0x5410);
     const __half2 r = __hfma2(*reinterpret_cast<const __half2*>(&hv), __half2half2(__ushort_as_half(0x1EEE)),
                               __half2half2(__ushort_as_half(0xC931)));
     return *reinterpret_cast<const uint32_t*>(&r);
@@ -35,9 +50,18 @@ __device__ __forceinline__ uint32_t cb_pair(uint32_t s0, uint32_t s1) {
     uint32_t x1 = CB == 1 ? s1 * 0xCBAC1FEDu : s1 * 89226354u + 64248484u;
     asm("lop3.b32 %0, %1, %2, %3, 0x6A;\n" : "=r"(x0) : "r"(x0), "r"(0x8FFF8FFFu), "r"(0x3B603B60u));   // (x & M) ^ F
     asm("lop3.b32 %0, %1, %2, %3, 0x6A;\n" : "=r"(x1) : "r"(x1), "r"(0x8FFF8FFFu), "r"(0x3B603B60u));
-    const __half2 h0 = *reinterpret_cast<const __half2*>(&x0), h1 = *reinterpret_cast<const __half2*>(&x1);
-    const __half2 r = __halves2half2(__hadd(__low2half(h0), __high2half(h0)), __hadd(__low2half(h1), __high2half(h1)));
-    return *reinterpret_cast<const uint32_t*>(&r);
+    // each value = low half + high half of its own word: the fp16 adds take the halves straight from the register
+    // (no permute), one permute packs the two results
+    uint32_t r;
+    asm("{\n.reg .b16 a, b, c, d;\n"
+        "mov.b32 {a, b}, %1;\n"
+        "mov.b32 {c, d}, %2;\n"
+        "add.rn.f16 a, a, b;\n"
+        "add.rn.f16 c, c, d;\n"
+        "mov.b32 %0, {a, c};\n}\n"
+        : "=r"(r)
+        : "r"(x0), "r"(x1));
+    return r;
   }
 }
 
@@ -56,15 +80,16 @@ struct Win {
 };
 
 // The words of a tile a lane needs: NW consecutive words (cyclically) from the one holding the first bit of value
-// 8 lane's window.  4 bits a value (K2 = 8): exactly words lane - 1 and lane.
-template <int K2>
+// 8 lane's window.  4 bits a value (K2 = 8): exactly words lane - 1 and lane.  GLOBAL: the tile is in global memory
+// (read-only path); else in shared memory.
+template <int K2, bool GLOBAL>
 __device__ __forceinline__ void lane_words(const uint32_t* __restrict__ tile, int lane, uint32_t (&w)[Win<K2>::NW]) {
   constexpr int TW = Win<K2>::TW, NW = Win<K2>::NW;
   const int first = 4 * lane * K2 + (K2 >> 1) - 16 + 32 * TW;       // E(8 lane) - 16, made non-negative
   int wi = (first >> 5) % TW;
 #pragma unroll
   for (int i = 0; i < NW; ++i) {
-    w[i] = __ldg(tile + wi);
+    w[i] = GLOBAL ? __ldg(tile + wi) : tile[wi];
     wi = wi + 1 == TW ? 0 : wi + 1;
   }
 }
@@ -74,16 +99,19 @@ template <int K2>
 __device__ __forceinline__ void lane_states(const uint32_t (&w)[Win<K2>::NW], int lane, uint32_t (&st)[8]) {
   constexpr int NW = Win<K2>::NW, NV = Win<K2>::NV;
   if constexpr (K2 == 8) {
-    // windows of 16 bits ending at bit 4 (j + 1) of the lane's own word: three reach back into the word before
-    const uint32_t q = __funnelshift_r(w[1], w[0], 20);
-    st[0] = (q >> 8) & 0xFFFFu;
-    st[1] = (q >> 4) & 0xFFFFu;
-    st[2] = q & 0xFFFFu;
-    st[3] = w[1] >> 16;
-    st[4] = (w[1] >> 12) & 0xFFFFu;
-    st[5] = (w[1] >> 8) & 0xFFFFu;
-    st[6] = (w[1] >> 4) & 0xFFFFu;
-    st[7] = w[1] & 0xFFFFu;
+    // 16-bit windows ending 4 (j + 1) bits into the lane's own word w[1], the stream running on from w[0].  Three
+    // funnel shifts line the windows up on byte boundaries; a byte permute then cuts each one out, zero-extended.
+    const uint32_t q16 = __funnelshift_r(w[1], w[0], 16);           // stream bits -16 .. 16 of the own word
+    const uint32_t q20 = __funnelshift_r(w[1], w[0], 20);           // -20 .. 12
+    const uint32_t q4 = __funnelshift_r(w[1], w[0], 4);             // -4 .. 28
+    st[0] = prmt(q20, 0u, 0x4421);                                  // bits -12 .. 4
+    st[1] = prmt(q16, 0u, 0x4421);                                  // -8 .. 8
+    st[2] = prmt(q20, 0u, 0x4410);                                  // -4 .. 12
+    st[3] = prmt(q16, 0u, 0x4410);                                  // 0 .. 16
+    st[4] = prmt(q4, 0u, 0x4421);                                   // 4 .. 20
+    st[5] = prmt(w[1], 0u, 0x4421);                                 // 8 .. 24
+    st[6] = prmt(q4, 0u, 0x4410);                                   // 12 .. 28
+    st[7] = prmt(w[1], 0u, 0x4410);                                 // 16 .. 32
   } else {
     const int off = (4 * lane * K2 + (K2 >> 1) - 16 + 32 * Win<K2>::TW) & 31;
     uint32_t v[NV];                                   // v[i] = stream bits [first + 32 i, first + 32 i + 32)
@@ -114,13 +142,6 @@ __device__ __forceinline__ void decode_words(const uint32_t (&w)[Win<K2>::NW], i
   a[3] = cb_pair<CB>(st[6], st[7]);
 }
 
-template <int CB, int K2>
-__device__ __forceinline__ void decode_tile(const uint32_t* __restrict__ tile, int lane, uint32_t (&a)[4]) {
-  uint32_t w[Win<K2>::NW];
-  lane_words<K2>(tile, lane, w);
-  decode_words<CB, K2>(w, lane, a);
-}
-
 __device__ __forceinline__ void mma_f16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
   asm volatile(
       "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
@@ -129,115 +150,340 @@ __device__ __forceinline__ void mma_f16(float (&d)[4], const uint32_t (&a)[4], u
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-// One warp's k tiles [kt0, kt0 + nkt) of GR_NTB column tiles into acc; the next row of tiles' words and inputs are
-// loaded before this row is decoded.
-template <int CB, int K2, int GR_NTB>
-__device__ __forceinline__ void warp_tiles(const uint32_t* __restrict__ T, int ntiles, int kt0, int nkt, int nt0,
-                                           const __half* __restrict__ x, int lane, float (&acc)[GR_NTB][4]) {
+// One warp's k-tile rows [kt0, kt0 + nkt) of the CTA's four column tiles into acc.  The rows travel through the warp's
+// ring: a slot holds ROWS whole rows (one bulk copy a row: the four tiles of a row are contiguous in the trellis), the
+// elected lane refills a slot as soon as the warp has decoded it.  The rows of a slot are unrolled in blocks of up to
+// four, whose inputs are loaded before the block's tiles are decoded.  x[pt]: the lane's pair (B column lane / 4 of
+// tile pt) at input 16 kt0 + 2 (lane % 4).  TWO: the item holds more than eight pairs (the second mma tile is live).
+// Returns false when a copy never landed.
+template <int CB, int K2, bool TWO>
+__device__ __forceinline__ bool warp_rows(const uint8_t* __restrict__ T, int ntiles, int kt0, int nkt, int nt0,
+                                          const __half* const (&x)[GR_PT], uint8_t* ring, uint64_t* bars, int lane,
+                                          float (&acc)[GR_NTB][GR_PT][4]) {
   constexpr int TW = Win<K2>::TW, NW = Win<K2>::NW;
-  const int t = lane & 3;
-  uint32_t wn[GR_NTB][NW], bn0, bn1;
-  auto fetch = [&](int kt) {
-    bn0 = *reinterpret_cast<const uint32_t*>(x + kt * 16 + 2 * t);
-    bn1 = *reinterpret_cast<const uint32_t*>(x + kt * 16 + 2 * t + 8);
-    const uint32_t* row = T + ((size_t)kt * ntiles + nt0) * TW;
-#pragma unroll
-    for (int i = 0; i < GR_NTB; ++i) lane_words<K2>(row + i * TW, lane, wn[i]);
+  constexpr int TILE_B = 16 * K2, SEG = GR_NTB * TILE_B;              // bytes a tile / a row of the CTA's tiles
+  constexpr int ROWS = GR_SLOT_BYTES / SEG < 1 ? 1 : (GR_SLOT_BYTES / SEG > 16 ? 16 : GR_SLOT_BYTES / SEG);
+  constexpr int RB = ROWS < 4 ? ROWS : 4;                             // rows a block
+  constexpr int NPT = TWO ? GR_PT : 1;
+  static_assert(ROWS * SEG <= GR_SLOT_BYTES, "a slot holds whole rows");
+  const int nslot = (nkt + ROWS - 1) / ROWS;
+  const uint8_t* src = T + ((size_t)kt0 * ntiles + nt0) * TILE_B;
+  const size_t row_stride = (size_t)ntiles * TILE_B;
+  auto issue = [&](int f) {
+    const int rows = min(ROWS, nkt - f * ROWS);
+    uint64_t* bar = bars + f % GR_STAGES;
+    uint8_t* dst = ring + (f % GR_STAGES) * GR_SLOT_BYTES;
+    mbar_expect_tx(bar, (uint32_t)(rows * SEG));
+    for (int r = 0; r < rows; ++r) bulk_g2s(dst + r * SEG, src + (size_t)(f * ROWS + r) * row_stride, SEG, bar);
   };
-  if (nkt > 0) fetch(kt0);
-  for (int it = 0; it < nkt; ++it) {
-    uint32_t wc[GR_NTB][NW];
-    const uint32_t b0 = bn0, b1 = bn1;
+  if (lane == 0)
+    for (int f = 0; f < GR_STAGES && f < nslot; ++f) issue(f);
+  // where the lane's words sit inside a tile: NW consecutive words (cyclically) from the one that holds the first bit
+  // of value 8 lane's window
+  int word[NW];
+  {
+    int wi = ((4 * lane * K2 + (K2 >> 1) - 16 + 32 * TW) >> 5) % TW;
 #pragma unroll
-    for (int i = 0; i < GR_NTB; ++i)
-#pragma unroll
-      for (int j = 0; j < NW; ++j) wc[i][j] = wn[i][j];
-    if (it + 1 < nkt) fetch(kt0 + it + 1);
-#pragma unroll
-    for (int i = 0; i < GR_NTB; ++i) {
-      uint32_t a[4];
-      decode_words<CB, K2>(wc[i], lane, a);
-      mma_f16(acc[i], a, b0, b1);
+    for (int j = 0; j < NW; ++j) {
+      word[j] = wi;
+      wi = wi + 1 == TW ? 0 : wi + 1;
     }
   }
+  const __half* xp[GR_PT] = {x[0], x[1]};
+  int stage = 0;
+  uint32_t phase = 0;
+  for (int f = 0; f < nslot; ++f) {
+    const int rows = min(ROWS, nkt - f * ROWS);
+    const uint32_t* slot = reinterpret_cast<const uint32_t*>(ring + stage * GR_SLOT_BYTES);
+#pragma unroll
+    for (int r0 = 0; r0 < ROWS; r0 += RB) {
+      if (r0 < rows) {
+        uint32_t b[RB][NPT][2];
+#pragma unroll
+        for (int r = 0; r < RB; ++r)
+#pragma unroll
+          for (int pt = 0; pt < NPT; ++pt) {
+            b[r][pt][0] = b[r][pt][1] = 0u;
+            if (r0 + r < rows) {
+              b[r][pt][0] = *reinterpret_cast<const uint32_t*>(xp[pt] + (r0 + r) * 16);
+              b[r][pt][1] = *reinterpret_cast<const uint32_t*>(xp[pt] + (r0 + r) * 16 + 8);
+            }
+          }
+        if (r0 == 0 && !mbar_wait_warp(bars + stage, phase)) {
+          for (int g = f + 1; g < nslot && g < f + GR_STAGES; ++g)    // give the other copies in flight a while to land
+            mbar_wait_for(bars + g % GR_STAGES, (g / GR_STAGES) & 1, 10000000ull);
+          return false;
+        }
+#pragma unroll
+        for (int r = 0; r < RB; ++r) {
+          if (r0 + r < rows) {
+#pragma unroll
+            for (int i = 0; i < GR_NTB; ++i) {
+              const uint32_t* tile = slot + (r0 + r) * (SEG / 4) + i * TW;
+              uint32_t w[NW], a[4];
+#pragma unroll
+              for (int j = 0; j < NW; ++j) w[j] = tile[word[j]];
+              decode_words<CB, K2>(w, lane, a);
+              mma_f16(acc[i][0], a, b[r][0][0], b[r][0][1]);
+              if constexpr (TWO) mma_f16(acc[i][1], a, b[r][1][0], b[r][1][1]);   // one decode, both pair tiles
+            }
+          }
+        }
+      }
+    }
+    xp[0] += ROWS * 16;
+    xp[1] += ROWS * 16;
+    __syncwarp();
+    if (lane == 0 && f + GR_STAGES < nslot) issue(f + GR_STAGES);
+    if (++stage == GR_STAGES) {
+      stage = 0;
+      phase ^= 1u;
+    }
+  }
+  return true;
 }
 
-// Program (routed expert u, 64 columns, matrix x pair tile): up to 8 members times W_q; the four warps split K and
-// meet in warp order.  Z[mat][pair][n] fp32.
-template <int CB, int GR_NTB>
-__global__ void __launch_bounds__(GR_WARPS * 32)
-grouped_kernel(const __half* __restrict__ X0, const __half* __restrict__ X1, const int64_t* __restrict__ TP0,
-               const int64_t* __restrict__ TP1, const int* __restrict__ K2_0, const int* __restrict__ K2_1,
-               const int* __restrict__ uids, const int* __restrict__ ucount, const int* __restrict__ members,
-               float* __restrict__ Z, int K, int N, int P, int maxm, int slots, int mtiles) {
-  __shared__ int rows_sh[GR_PAIRS];
-  __shared__ float red[GR_WARPS][GR_PAIRS][GR_NTB * 16 + 1];
-  pdl_wait();
-  const int u = blockIdx.x;
-  const int mtile = blockIdx.z % mtiles, mat = blockIdx.z / mtiles;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-  // the count and the tile's members are read together (row u exists in the table for every u of the grid): most
-  // CTAs of a grid sized for the worst case find nothing and leave after one round trip, not two
-  const int n_u = ucount[0];
-  if (threadIdx.x < GR_PAIRS) {
-    const int m = mtile * GR_PAIRS + threadIdx.x;
-    const int code = m < maxm ? members[(size_t)u * maxm + m] : -1;
-    rows_sh[threadIdx.x] = code >= 0 ? (code >> 5) * slots + (code & 31) : -1;
-  }
-  if (u >= n_u) return;
-  __syncthreads();
-  if (rows_sh[0] < 0) return;                         // members come first: this pair tile is empty
-  const int e = uids[u];
-  const uint32_t* T = reinterpret_cast<const uint32_t*>(mat ? TP1[e] : TP0[e]);
-  const int k2 = mat ? K2_1[e] : K2_0[e];
-  const __half* X = mat ? X1 : X0;
-  // lanes past the last member read the first member's row: an mma column depends on its own inputs only
-  const int r = rows_sh[g] >= 0 ? rows_sh[g] : rows_sh[0];
-  const __half* x = X + (size_t)r * K;
-  const int KT = K >> 4, ntiles = N >> 4, per_warp = KT / GR_WARPS;
-  const int kt0 = warp * per_warp, nt0 = blockIdx.y * GR_NTB;
-  float acc[GR_NTB][4];
+// ---- 128-point Walsh-Hadamard transform by 16 lanes, 8 consecutive values a lane ---------------------------------
+// Strides 1, 2, 4 inside the lane, 8 .. 64 across the 16 lanes of a half warp (sub = lane % 16); a warp transforms two
+// blocks at once.  Not scaled.
+__device__ __forceinline__ void hadamard128(float (&v)[8], int sub) {
 #pragma unroll
-  for (int i = 0; i < GR_NTB; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+  for (int h = 1; h < 8; h <<= 1)
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      if ((i & h) == 0) {
+        const float a = v[i], b = v[i + h];
+        v[i] = a + b;
+        v[i + h] = a - b;
+      }
+#pragma unroll
+  for (int m = 1; m < 16; m <<= 1)
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float o = __shfl_xor_sync(0xffffffffu, v[i], m);
+      v[i] = (sub & m) ? o - v[i] : v[i] + o;
+    }
+}
+
+__device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&f)[8]) {
+  const uint4 u = *reinterpret_cast<const uint4*>(p);
+  f[0] = bf16_lo(u.x); f[1] = bf16_hi(u.x); f[2] = bf16_lo(u.y); f[3] = bf16_hi(u.y);
+  f[4] = bf16_lo(u.z); f[5] = bf16_hi(u.z); f[6] = bf16_lo(u.w); f[7] = bf16_hi(u.w);
+}
+__device__ __forceinline__ void load8(const __half* p, float (&f)[8]) {
+  const uint4 u = *reinterpret_cast<const uint4*>(p);
+  const __half2* h = reinterpret_cast<const __half2*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 t = __half22float2(h[i]);
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
+__device__ __forceinline__ void load8(const float* p, float (&f)[8]) {   // another CTA of this launch wrote it: L2
+  const float4 a = __ldcg(reinterpret_cast<const float4*>(p)), b = __ldcg(reinterpret_cast<const float4*>(p) + 1);
+  f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+}
+__device__ __forceinline__ void store8(__half* p, const float (&f)[8], float scale) {
+  uint4 u;
+  __half2* h = reinterpret_cast<__half2*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) h[i] = __floats2half2_rn(f[2 * i] * scale, f[2 * i + 1] * scale);
+  *reinterpret_cast<uint4*>(p) = u;
+}
+
+// ---- epilogues of one pair and one 128-block, by a half warp ------------------------------------------------------
+// gate/up: rotate both, * svh, SwiGLU (act_mode 0: the GLM family's bf16 roundings; 1: fp32), * suh_d, rotate, fp16.
+// (arithmetic of src/tensorfold/cuda/exl3/experts.cu:116-158)
+__device__ __forceinline__ void gateup_block(const float* zg, const float* zu, const __half* svh_g, const __half* svh_u,
+                                             const __half* suh_d, __half* xd, int sub, float limit, int act_mode,
+                                             bool store) {
+  float g[8], u[8], sg[8], su[8], sd[8];
+  load8(zg + 8 * sub, g);
+  load8(zu + 8 * sub, u);
+  load8(svh_g + 8 * sub, sg);
+  load8(svh_u + 8 * sub, su);
+  load8(suh_d + 8 * sub, sd);
+  hadamard128(g, sub);
+  hadamard128(u, sub);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    float act;
+    if (act_mode == 0) {
+      const float gv = fminf(round_bf16(g[i] * HAD_SCALE * sg[i]), limit);
+      const float uv = fminf(fmaxf(round_bf16(u[i] * HAD_SCALE * su[i]), -limit), limit);
+      act = round_bf16(round_bf16(gv / (1.f + expf(-gv))) * uv);
+    } else {
+      const float gv = fminf(g[i] * HAD_SCALE * sg[i], limit);
+      const float uv = fminf(fmaxf(u[i] * HAD_SCALE * su[i], -limit), limit);
+      act = gv / (1.f + expf(-gv)) * uv;
+    }
+    g[i] = act * sd[i];
+  }
+  hadamard128(g, sub);
+  if (store) store8(xd + 8 * sub, g, HAD_SCALE);
+}
+
+// down: y = rotate(z) * svh, fp32.  (src/tensorfold/cuda/exl3/experts.cu:161-180)
+__device__ __forceinline__ void down_block(const float* z, const __half* svh, float* y, int sub, bool store) {
+  float v[8], s[8];
+  load8(z + 8 * sub, v);
+  load8(svh + 8 * sub, s);
+  hadamard128(v, sub);
+  if (!store) return;
+  float4 a, b;
+  a.x = v[0] * HAD_SCALE * s[0]; a.y = v[1] * HAD_SCALE * s[1]; a.z = v[2] * HAD_SCALE * s[2]; a.w = v[3] * HAD_SCALE * s[3];
+  b.x = v[4] * HAD_SCALE * s[4]; b.y = v[5] * HAD_SCALE * s[5]; b.z = v[6] * HAD_SCALE * s[6]; b.w = v[7] * HAD_SCALE * s[7];
+  reinterpret_cast<float4*>(y + 8 * sub)[0] = a;
+  reinterpret_cast<float4*>(y + 8 * sub)[1] = b;
+}
+
+struct GroupedArgs {
+  const __half* x[2];            // rotated inputs [P, K] fp16 of matrix 0 / 1
+  const int64_t* tp[2];          // trellis pointers [E]
+  const int* k2[2];              // half-bit widths [E]
+  const int* items;              // [., 3] (expert, first, count <= 16)
+  const int* counts;             // [0] = items
+  const int* members;            // pair ids p = row * slots + slot, grouped by expert
+  float* z;                      // [mats, P, N] fp32
+  int* arrive;                   // [max items * N / 128] zero between launches
+  const __half* sv[2];           // svh [E, N] of matrix 0 / 1
+  const __half* suh_next;        // gate/up: suh of the down projection [E, N]
+  void* out;                     // gate/up: xd [P, N] fp16; down: y [P, N] fp32
+  int K, N, P, mats, epi, act_mode;
+  float limit;
+};
+
+enum GroupedEpilogue : int { GE_NONE = 0, GE_GATEUP = 1, GE_DOWN = 2 };
+
+// CTA (item, 64 columns, matrix).
+template <int CB>
+__global__ void __launch_bounds__(GR_WARPS * 32)
+grouped_kernel(const GroupedArgs a) {
+  __shared__ __align__(128) uint8_t ring[GR_WARPS * GR_STAGES * GR_SLOT_BYTES];
+  __shared__ uint64_t bars[GR_WARPS * GR_STAGES];
+  __shared__ int pair_sh[GR_PAIRS];
+  __shared__ int last_sh;
+  static_assert(GR_WARPS * GR_PAIRS * GR_RED_STRIDE * 4 <= GR_WARPS * GR_STAGES * GR_SLOT_BYTES,
+                "the K slices meet in the ring's memory");
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+  const int it = blockIdx.x, nt0 = blockIdx.y * GR_NTB, mat = blockIdx.z;
+  if (lane == 0) {
+#pragma unroll
+    for (int s = 0; s < GR_STAGES; ++s) mbar_init(bars + warp * GR_STAGES + s, 1);
+    mbar_fence_init();
+    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+  }
+  __syncwarp();
+  pdl_wait();
+  // the item is read together with the count that says whether it exists (its slot is always inside the table)
+  const int n_items = a.counts[0];
+  const int e = a.items[3 * it], first = a.items[3 * it + 1], cnt = min(a.items[3 * it + 2], GR_PAIRS);
+  if (it >= n_items) return;
+  if (tid < GR_PAIRS) pair_sh[tid] = tid < cnt ? a.members[first + tid] : -1;
+  const uint8_t* T = reinterpret_cast<const uint8_t*>(a.tp[mat][e]);
+  const int k2 = a.k2[mat][e];
+  const bool two = cnt > 8;
+  // lanes past the item's last pair read its first pair's row: an mma column depends on its own inputs only
+  const int KT = a.K >> 4, per_warp = (KT + GR_WARPS - 1) / GR_WARPS;
+  const int kt0 = min(KT, warp * per_warp), nkt = min(KT, kt0 + per_warp) - kt0;
+  const __half* x[GR_PT];
+#pragma unroll
+  for (int pt = 0; pt < GR_PT; ++pt) {
+    const int p = a.members[first + (8 * pt + g < cnt ? 8 * pt + g : 0)];
+    x[pt] = a.x[mat] + (size_t)p * a.K + kt0 * 16 + 2 * t;
+  }
+  float acc[GR_NTB][GR_PT][4];
+#pragma unroll
+  for (int i = 0; i < GR_NTB; ++i)
+#pragma unroll
+    for (int pt = 0; pt < GR_PT; ++pt) acc[i][pt][0] = acc[i][pt][1] = acc[i][pt][2] = acc[i][pt][3] = 0.f;
+  bool ok = true;
+  uint8_t* my_ring = ring + warp * (GR_STAGES * GR_SLOT_BYTES);
+  uint64_t* my_bars = bars + warp * GR_STAGES;
   switch (k2) {
-#define TFB_K2(K2_)                                                          \
-  case K2_:                                                                  \
-    warp_tiles<CB, K2_, GR_NTB>(T, ntiles, kt0, per_warp, nt0, x, lane, acc); \
+#define TFB_K2(K2_)                                                                                       \
+  case K2_:                                                                                               \
+    ok = two ? warp_rows<CB, K2_, true>(T, a.N >> 4, kt0, nkt, nt0, x, my_ring, my_bars, lane, acc)        \
+             : warp_rows<CB, K2_, false>(T, a.N >> 4, kt0, nkt, nt0, x, my_ring, my_bars, lane, acc);      \
     break;
     TFB_K2(2) TFB_K2(3) TFB_K2(4) TFB_K2(5) TFB_K2(6) TFB_K2(7) TFB_K2(8) TFB_K2(9) TFB_K2(10) TFB_K2(11) TFB_K2(12)
     TFB_K2(13) TFB_K2(14) TFB_K2(15) TFB_K2(16)
 #undef TFB_K2
     default:
-      atomicCAS(&g_kernel_status, 0, ST_BAD_INDEX);    // a width the host should have refused
+      atomicCAS(&g_kernel_status, 0, ST_BAD_INDEX);   // a width the host should have refused
+      ok = false;
       break;
   }
   pdl_launch_dependents();
-  // acc[i]: d0 = (col g, pair 2t), d1 = (col g, pair 2t + 1), d2 = (col g + 8, pair 2t), d3 = (col g + 8, pair 2t + 1)
+  if (__syncthreads_or(ok ? 0 : 1)) return;           // a copy never landed (recorded): store nothing
+  // the K slices meet in warp order (the ring's memory is free: every warp is past its loop)
+  // acc[i][pt]: d0 = (col g, pair 2t), d1 = (col g, pair 2t + 1), d2 = (col g + 8, pair 2t), d3 = (col g + 8, 2t + 1)
+  float* red = reinterpret_cast<float*>(ring);
 #pragma unroll
-  for (int i = 0; i < GR_NTB; ++i) {
-    red[warp][2 * t][i * 16 + g] = acc[i][0];
-    red[warp][2 * t + 1][i * 16 + g] = acc[i][1];
-    red[warp][2 * t][i * 16 + g + 8] = acc[i][2];
-    red[warp][2 * t + 1][i * 16 + g + 8] = acc[i][3];
+  for (int i = 0; i < GR_NTB; ++i)
+#pragma unroll
+    for (int pt = 0; pt < GR_PT; ++pt) {
+      float* base = red + (warp * GR_PAIRS + 8 * pt + 2 * t) * GR_RED_STRIDE + i * 16 + g;
+      base[0] = acc[i][pt][0];
+      base[GR_RED_STRIDE] = acc[i][pt][1];
+      base[8] = acc[i][pt][2];
+      base[GR_RED_STRIDE + 8] = acc[i][pt][3];
+    }
+  __syncthreads();
+  for (int o = tid; o < GR_PAIRS * GR_NTB * 16; o += GR_WARPS * 32) {
+    const int pi = o / (GR_NTB * 16), col = o % (GR_NTB * 16);
+    const int p = pair_sh[pi];
+    if (p < 0) continue;
+    float s = red[pi * GR_RED_STRIDE + col];
+#pragma unroll
+    for (int w = 1; w < GR_WARPS; ++w) s += red[(w * GR_PAIRS + pi) * GR_RED_STRIDE + col];
+    a.z[((size_t)mat * a.P + p) * a.N + nt0 * 16 + col] = s;
+  }
+  if (a.epi == GE_NONE) return;
+  // Whoever finishes last among the CTAs that share (item, 128 columns) - two column halves, times the matrices -
+  // finds every part of the block in z and runs the block's epilogue.
+  const int blk = blockIdx.y >> 1;
+  int* counter = a.arrive + (size_t)it * (a.N >> 7) + blk;
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    const int need = 2 * a.mats;
+    const int seen = atomicAdd(counter, 1);
+    last_sh = seen == need - 1;
+    if (seen == need - 1) *counter = 0;               // nobody else touches it before the next launch
   }
   __syncthreads();
-  for (int o = threadIdx.x; o < GR_PAIRS * GR_NTB * 16; o += GR_WARPS * 32) {
-    const int pi = o / (GR_NTB * 16), col = o % (GR_NTB * 16);
-    const int row = rows_sh[pi];
-    if (row < 0) continue;
-    float s = red[0][pi][col];
-#pragma unroll
-    for (int w = 1; w < GR_WARPS; ++w) s += red[w][pi][col];
-    Z[((size_t)mat * P + row) * N + nt0 * 16 + col] = s;
+  if (!last_sh) return;
+  __threadfence();
+  // a half warp a pair (the transform's shuffles need every lane of the warp: a half without a pair repeats the item's
+  // first pair and stores nothing); pairs fill an item from the front, so a warp whose first pair is missing is done
+  const int sub = lane & 15, half = lane >> 4;
+  for (int p0 = 2 * warp; p0 < GR_PAIRS && pair_sh[p0] >= 0; p0 += 2 * GR_WARPS) {
+    const int p = pair_sh[p0 + half];
+    const int q = p < 0 ? pair_sh[0] : p;
+    const size_t at = (size_t)q * a.N + blk * 128, sc = (size_t)e * a.N + blk * 128;
+    if (a.epi == GE_GATEUP)
+      gateup_block(a.z + at, a.z + (size_t)a.P * a.N + at, a.sv[0] + sc, a.sv[1] + sc, a.suh_next + sc,
+                   static_cast<__half*>(a.out) + at, sub, a.limit, a.act_mode, p >= 0);
+    else
+      down_block(a.z + at, a.sv[0] + sc, static_cast<float*>(a.out) + at, sub, p >= 0);
   }
 }
+
+}  // namespace exl3
+}  // namespace tfb
+
+namespace tfb {
+namespace exl3 {
 
 // W_q [K, N] fp16 of one matrix through the same lane decode (the bit-exactness hook).
 template <int CB, int K2>
 __global__ void dequant_kernel(const uint32_t* __restrict__ T, __half* __restrict__ out, int K, int N) {
   const int kt = blockIdx.x, nt = blockIdx.y, lane = threadIdx.x, g = lane >> 2, t = lane & 3;
-  uint32_t a[4];
-  decode_tile<CB, K2>(T + ((size_t)kt * (N >> 4) + nt) * Win<K2>::TW, lane, a);
+  uint32_t w[Win<K2>::NW], a[4];
+  lane_words<K2, true>(T + ((size_t)kt * (N >> 4) + nt) * Win<K2>::TW, lane, w);
+  decode_words<CB, K2>(w, lane, a);
   // a0 = (col g, k 2t, 2t+1), a1 = (col g + 8, ...), a2 = (col g, k 2t + 8, ..), a3 = (col g + 8, k 2t + 8, ..)
 #pragma unroll
   for (int q = 0; q < 4; ++q) {
@@ -248,142 +494,63 @@ __global__ void dequant_kernel(const uint32_t* __restrict__ T, __half* __restric
   }
 }
 
-// ---- 128-point Walsh-Hadamard transform, 4 values a lane: strides 1, 2 in registers, 4 .. 64 across lanes ---------
-__device__ __forceinline__ void fwht128(float (&v)[4], int lane) {
-  const float a = v[0] + v[1], b = v[0] - v[1], c = v[2] + v[3], d = v[2] - v[3];
-  v[0] = a + c;
-  v[1] = b + d;
-  v[2] = a - c;
-  v[3] = b - d;
-#pragma unroll
-  for (int m = 1; m < 32; m <<= 1)
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const float o = __shfl_xor_sync(0xffffffffu, v[j], m);
-      v[j] = (lane & m) ? o - v[j] : v[j] + o;
-    }
-}
-
-template <typename T>
-__device__ __forceinline__ float to_float(T v);
-template <>
-__device__ __forceinline__ float to_float<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
-template <>
-__device__ __forceinline__ float to_float<__half>(__half v) { return __half2float(v); }
-
-// Program (pair, 128-block of K, matrix): xh = fp16(((x * suh) H)) for gate and up of every routed slot.
-template <typename TIN>
-__global__ void __launch_bounds__(32)
-rot_in_kernel(const TIN* __restrict__ x, int64_t x_stride, const int* __restrict__ pick,
-              const __half* __restrict__ suh0, const __half* __restrict__ suh1, __half* __restrict__ out0,
-              __half* __restrict__ out1, int K, int slots, int E) {
-  pdl_wait();
-  const int p = blockIdx.x, blk = blockIdx.y, mat = blockIdx.z, lane = threadIdx.x;
-  const int e = pick[p];
-  if (e < 0 || e >= E) return;
-  const __half* suh = (mat ? suh1 : suh0) + (size_t)e * K + blk * 128 + 4 * lane;
-  const TIN* xr = x + (size_t)(p / slots) * x_stride + blk * 128 + 4 * lane;
-  float v[4];
-#pragma unroll
-  for (int j = 0; j < 4; ++j) v[j] = to_float<TIN>(xr[j]) * __half2float(suh[j]);
-  fwht128(v, lane);
-  __half* o = (mat ? out1 : out0) + (size_t)p * K + blk * 128 + 4 * lane;
-#pragma unroll
-  for (int j = 0; j < 4; ++j) o[j] = __float2half_rn(v[j] * HAD_SCALE);
-  pdl_launch_dependents();
-}
-
-// Program (pair, 128-block of the width): rotate gate and up, * svh, SwiGLU (act_mode 0: bf16 roundings as the GLM
-// family; 1: fp32), * suh_d, rotate, fp16.
-__global__ void __launch_bounds__(32)
-gateup_epilogue_kernel(const float* __restrict__ Z, const int* __restrict__ pick, const __half* __restrict__ svh_g,
-                       const __half* __restrict__ svh_u, const __half* __restrict__ suh_d, __half* __restrict__ xd,
-                       int P, int N, int E, float limit, int act_mode) {
-  pdl_wait();
-  const int p = blockIdx.x, blk = blockIdx.y, lane = threadIdx.x;
-  const int e = pick[p];
-  if (e < 0 || e >= E) return;
-  const int n = blk * 128 + 4 * lane;
-  float gv[4], uv[4], v[4];
-#pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    gv[j] = Z[(size_t)p * N + n + j];
-    uv[j] = Z[((size_t)P + p) * N + n + j];
-  }
-  fwht128(gv, lane);
-  fwht128(uv, lane);
-#pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    const float sg = __half2float(svh_g[(size_t)e * N + n + j]), su = __half2float(svh_u[(size_t)e * N + n + j]);
-    float act;
-    if (act_mode == 0) {
-      const float gg = fminf(round_bf16(gv[j] * HAD_SCALE * sg), limit);
-      const float uu = fminf(fmaxf(round_bf16(uv[j] * HAD_SCALE * su), -limit), limit);
-      act = round_bf16(round_bf16(gg / (1.f + expf(-gg))) * uu);
-    } else {
-      const float gg = fminf(gv[j] * HAD_SCALE * sg, limit);
-      const float uu = fminf(fmaxf(uv[j] * HAD_SCALE * su, -limit), limit);
-      act = gg / (1.f + expf(-gg)) * uu;
-    }
-    v[j] = act * __half2float(suh_d[(size_t)e * N + n + j]);
-  }
-  fwht128(v, lane);
-  __half* o = xd + (size_t)p * N + n;
-#pragma unroll
-  for (int j = 0; j < 4; ++j) o[j] = __float2half_rn(v[j] * HAD_SCALE);
-  pdl_launch_dependents();
-}
-
-// Program (row, 128-block of the model width), a warp a slot: y = (Z H) * svh_d per slot (fp32, also stored), then,
-// when `out` is given, out = sum over slots in slot order of wts * y (an fma chain from 0).  Slots that are not routed
-// experts keep the y the caller put there.
-__global__ void down_epilogue_kernel(const float* __restrict__ Z, const int* __restrict__ pick,
-                                     const __half* __restrict__ svh_d, float* __restrict__ y,
-                                     const float* __restrict__ wts, float* __restrict__ out, int D, int E,
-                                     int slots) {
-  __shared__ float4 part[32][32];                     // [slot][lane]
-  pdl_wait();
-  const int r = blockIdx.x, blk = blockIdx.y, k = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n = blk * 128 + 4 * lane, p = r * slots + k;
-  const int e = pick[p];
-  float o[4];
-  if (e >= 0 && e < E) {
-    float v[4];
-#pragma unroll
-    for (int j = 0; j < 4; ++j) v[j] = Z[(size_t)p * D + n + j];
-    fwht128(v, lane);
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      o[j] = v[j] * HAD_SCALE * __half2float(svh_d[(size_t)e * D + n + j]);
-      y[(size_t)p * D + n + j] = o[j];
-    }
-  } else if (out != nullptr) {
-#pragma unroll
-    for (int j = 0; j < 4; ++j) o[j] = y[(size_t)p * D + n + j];
-  }
-  if (out == nullptr) return;
-  part[k][lane] = make_float4(o[0], o[1], o[2], o[3]);
-  __syncthreads();
-  if (k != 0) return;
-  float acc[4] = {0.f, 0.f, 0.f, 0.f};
-  for (int q = 0; q < slots; ++q) {
-    const float w = wts[r * slots + q];
-    const float4 s = part[q][lane];
-    acc[0] = fmaf(w, s.x, acc[0]);
-    acc[1] = fmaf(w, s.y, acc[1]);
-    acc[2] = fmaf(w, s.z, acc[2]);
-    acc[3] = fmaf(w, s.w, acc[3]);
-  }
-#pragma unroll
-  for (int j = 0; j < 4; ++j) out[(size_t)r * D + n + j] = acc[j];
-  pdl_launch_dependents();
-}
-
 }  // namespace exl3
 
-// Grouping for the EXL3 kernels in one block: the plan's stable sort (one item an expert), then the reference's
-// tables: uids = distinct routed experts (< E) ascending, members[u][<= maxm] = row * 32 + slot in row order, -1 after
-// the last.  (src/tensorfold/cuda/exl3/experts.cu:19-72)
+// The first launch of a layer call.  Block 0 (when `sort`): the plan's stable sort of the pairs by expert, items of at
+// most 16 pairs (ids outside [0, E) are left out), and the number of distinct experts into ucount.  The other blocks:
+// out_m[p, :] = fp16(((x[row of p] * suh_m[expert of p]) H) / sqrt(128)) for every routed pair and 128-block, a half
+// warp a block, both matrices from one read of x.  suh1 == nullptr: one matrix.
+// (src/tensorfold/cuda/exl3/experts.cu:19-111: `group` and `rot_in`)
+template <typename TIN>
+__global__ void __launch_bounds__(PLAN_THREADS)
+exl3_prologue_kernel(const int* __restrict__ picks, int P, int E, int slots, int sort, int* __restrict__ members,
+                     int* __restrict__ items, int* __restrict__ counts, int* __restrict__ ucount,
+                     const TIN* __restrict__ x, int64_t x_stride, const __half* __restrict__ suh0,
+                     const __half* __restrict__ suh1, __half* __restrict__ out0, __half* __restrict__ out1, int K) {
+  extern __shared__ int whist[];
+  __shared__ int first[PLAN_EMAX];
+  __shared__ int wsum[4][32];
+  pdl_wait();
+  if (blockIdx.x == 0) {
+    if (sort) {
+      plan_block(picks, P, E, exl3::GR_PAIRS, members, items, counts, whist, first, wsum);
+      if (threadIdx.x == 0) ucount[0] = counts[1];    // written by this thread inside plan_block
+    }
+    pdl_launch_dependents();
+    return;
+  }
+  const int lane = threadIdx.x & 31, sub = lane & 15, half = lane >> 4;
+  const int nblk = K >> 7;
+  const int64_t units = (int64_t)P * nblk;
+  const int64_t warps = (int64_t)(gridDim.x - 1) * (PLAN_THREADS / 32);
+  for (int64_t u0 = 2 * ((int64_t)(blockIdx.x - 1) * (PLAN_THREADS / 32) + (threadIdx.x >> 5)); u0 < units;
+       u0 += 2 * warps) {
+    const bool have = u0 + half < units;              // the transform's shuffles need every lane: an idle half repeats u0
+    const int64_t u = have ? u0 + half : u0;
+    const int p = (int)(u / nblk), blk = (int)(u - (int64_t)p * nblk);
+    const int e = picks[p];
+    const bool routed = have && e >= 0 && e < E;
+    const int es = routed ? e : 0;
+    float xv[8];
+    exl3::load8(x + (size_t)(p / slots) * x_stride + blk * 128 + 8 * sub, xv);
+#pragma unroll
+    for (int m = 0; m < 2; ++m) {
+      const __half* suh = m ? suh1 : suh0;
+      if (suh == nullptr) continue;
+      float s[8], v[8];
+      exl3::load8(suh + (size_t)es * K + blk * 128 + 8 * sub, s);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] = xv[i] * s[i];
+      exl3::hadamard128(v, sub);
+      if (routed) exl3::store8((m ? out1 : out0) + (size_t)p * K + blk * 128 + 8 * sub, v, exl3::HAD_SCALE);
+    }
+  }
+  pdl_launch_dependents();
+}
+
+// Grouping for callers of the `group` operator, in one block: the plan's stable sort (one item an expert), then the
+// reference's tables: uids = distinct routed experts (< E) ascending, members[u][<= maxm] = row * 32 + slot in row
+// order, -1 after the last.  (src/tensorfold/cuda/exl3/experts.cu:19-72)
 __global__ void __launch_bounds__(PLAN_THREADS)
 exl3_group_kernel(const int* __restrict__ picks, int P, int E, int slots, int* __restrict__ tmp_members,
                   int* __restrict__ tmp_items, int* __restrict__ tmp_counts, int* __restrict__ uids,
@@ -446,6 +613,20 @@ extern "C" int tfb_exl3_dequant(const void* trellis, void* out, int K, int N, in
   return check_launch("exl3_dequant");
 }
 
+// Opts a plan-sized kernel into the dynamic shared memory of PLAN_EMAX experts, once a device.
+template <typename Kernel>
+static int plan_smem_opt_in(Kernel kernel, int* configured, const char* what) {
+  int dev = 0;
+  TFB_CUDA(cudaGetDevice(&dev), what);
+  if (dev >= 0 && dev < 64 && !configured[dev]) {
+    TFB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  (int)(sizeof(int) * 32 * PLAN_EMAX)),
+             what);
+    configured[dev] = 1;
+  }
+  return TFB_OK;
+}
+
 // pick [R, slots] -> uids [maxu], ucount [1], members [maxu, maxm]; tmp_members [R * slots], tmp_items
 // [3 * min(R * slots, E)], tmp_counts [2] are caller scratch.  (exl3/experts.cpp `group`)
 extern "C" int tfb_exl3_group(const int32_t* pick, int32_t* uids, int32_t* ucount, int32_t* members,
@@ -456,106 +637,11 @@ extern "C" int tfb_exl3_group(const int32_t* pick, int32_t* uids, int32_t* ucoun
   TFB_REQUIRE(slots >= 1 && slots <= 32, "exl3_group: 1..32 slots, not %d", slots);
   TFB_REQUIRE(R >= 0 && maxu >= 0 && maxm >= 0, "exl3_group: bad sizes");
   static int configured[64] = {0};
-  int dev = 0;
-  TFB_CUDA(cudaGetDevice(&dev), "exl3_group: cudaGetDevice");
-  if (dev >= 0 && dev < 64 && !configured[dev]) {
-    TFB_CUDA(cudaFuncSetAttribute(exl3_group_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                  (int)(sizeof(int) * 32 * PLAN_EMAX)),
-             "exl3_group: shared memory opt-in");
-    configured[dev] = 1;
-  }
+  if (int rc = plan_smem_opt_in(exl3_group_kernel, configured, "exl3_group: shared memory opt-in")) return rc;
   return check_cuda(launch(exl3_group_kernel, dim3(1), dim3(PLAN_THREADS), sizeof(int) * 32 * (size_t)E,
                            static_cast<cudaStream_t>(stream), pick, R * slots, E, slots, tmp_members, tmp_items,
                            tmp_counts, uids, ucount, members, maxm, maxu),
                     "exl3_group");
-}
-
-// xg / xu [R * slots, K] fp16 = rotated, suh-scaled inputs of every routed pair.  (exl3/experts.cpp `rot_in`)
-extern "C" int tfb_exl3_rot_in(const void* x, int64_t x_stride, int x_is_fp16, const int32_t* pick, const void* suh0,
-                               const void* suh1, void* out0, void* out1, int R, int K, int slots, int E,
-                               void* stream) {
-  TFB_REQUIRE(x && pick && suh0 && suh1 && out0 && out1, "exl3_rot_in: null pointer");
-  TFB_REQUIRE(K > 0 && K % 128 == 0, "exl3_rot_in: K must be a multiple of 128");
-  TFB_REQUIRE(slots >= 1 && slots <= 32 && x_stride >= K, "exl3_rot_in: bad slots or stride");
-  if (R <= 0) return TFB_OK;
-  const dim3 grid(R * slots, K / 128, 2);
-  auto st = static_cast<cudaStream_t>(stream);
-  cudaError_t e;
-  if (x_is_fp16)
-    e = launch(exl3::rot_in_kernel<__half>, grid, dim3(32), 0, st, static_cast<const __half*>(x), x_stride, pick,
-               static_cast<const __half*>(suh0), static_cast<const __half*>(suh1), static_cast<__half*>(out0),
-               static_cast<__half*>(out1), K, slots, E);
-  else
-    e = launch(exl3::rot_in_kernel<__nv_bfloat16>, grid, dim3(32), 0, st, static_cast<const __nv_bfloat16*>(x),
-               x_stride, pick, static_cast<const __half*>(suh0), static_cast<const __half*>(suh1),
-               static_cast<__half*>(out0), static_cast<__half*>(out1), K, slots, E);
-  return check_cuda(e, "exl3_rot_in");
-}
-
-// Z [mats, P, N] fp32 = rotated inputs times W_q for every routed pair.  tp*: int64 trellis pointers [E]; k2_*: int32
-// half-bit widths [E].  (exl3/experts.cpp `grouped`)
-extern "C" int tfb_exl3_grouped(const void* x0, const void* x1, const int64_t* tp0, const int64_t* tp1,
-                                const int32_t* k2_0, const int32_t* k2_1, const int32_t* uids, const int32_t* ucount,
-                                const int32_t* members, float* z, int mats, int K, int N, int P, int slots, int cb,
-                                int maxm, int maxu, void* stream) {
-  TFB_REQUIRE(x0 && x1 && tp0 && tp1 && k2_0 && k2_1 && uids && ucount && members && z, "exl3_grouped: null pointer");
-  TFB_REQUIRE(mats == 1 || mats == 2, "exl3_grouped: one or two matrices");
-  TFB_REQUIRE(K > 0 && N > 0 && K % (16 * exl3::GR_WARPS) == 0 && N % (16 * exl3::GR_NTB_MAX) == 0,
-              "exl3_grouped: K must be a multiple of %d and N of %d", 16 * exl3::GR_WARPS, 16 * exl3::GR_NTB_MAX);
-  TFB_REQUIRE(cb >= 0 && cb <= 2, "exl3_grouped: codebook must be 0 (3inst), 1 (mcg) or 2 (mul1)");
-  TFB_REQUIRE(slots >= 1 && slots <= 32 && maxm >= 0 && maxu >= 0, "exl3_grouped: bad sizes");
-  if (maxu == 0 || maxm == 0) return TFB_OK;
-  const int mtiles = (maxm + exl3::GR_PAIRS - 1) / exl3::GR_PAIRS;
-  TFB_REQUIRE((int64_t)mats * mtiles <= 65535, "exl3_grouped: too many pair tiles for one launch");
-  // column tiles a CTA: fewer when the call is small, so that every SM gets work (columns are independent: no effect
-  // on any result)
-  const int64_t units4 = (int64_t)maxu * (N / 64) * mats * mtiles;
-  const int ntb = units4 >= 1184 ? 4 : units4 >= 592 ? 2 : 1;
-  const dim3 grid(maxu, N / (16 * ntb), mats * mtiles);
-  auto st = static_cast<cudaStream_t>(stream);
-  auto* h0 = static_cast<const __half*>(x0);
-  auto* h1 = static_cast<const __half*>(x1);
-  cudaError_t e = cudaSuccess;
-#define TFB_GR(CB_, NTB_)                                                                                          \
-  e = launch(exl3::grouped_kernel<CB_, NTB_>, grid, dim3(exl3::GR_WARPS * 32), 0, st, h0, h1, tp0, tp1, k2_0, k2_1, \
-             uids, ucount, members, z, K, N, P, maxm, slots, mtiles)
-#define TFB_GR_CB(CB_)                  \
-  if (ntb == 4) TFB_GR(CB_, 4);         \
-  else if (ntb == 2) TFB_GR(CB_, 2);    \
-  else TFB_GR(CB_, 1)
-  if (cb == 0) { TFB_GR_CB(0); } else if (cb == 1) { TFB_GR_CB(1); } else { TFB_GR_CB(2); }
-#undef TFB_GR_CB
-#undef TFB_GR
-  return check_cuda(e, "exl3_grouped");
-}
-
-// xd [P, N] fp16 from Z [2, P, N].  (exl3/experts.cpp `gateup_epilogue`)
-extern "C" int tfb_exl3_gateup_epilogue(const float* z, const int32_t* pick, const void* svh_g, const void* svh_u,
-                                        const void* suh_d, void* xd, int P, int N, int E, float limit, int act_mode,
-                                        void* stream) {
-  TFB_REQUIRE(z && pick && svh_g && svh_u && suh_d && xd, "exl3_gateup_epilogue: null pointer");
-  TFB_REQUIRE(N > 0 && N % 128 == 0, "exl3_gateup_epilogue: N must be a multiple of 128");
-  TFB_REQUIRE(act_mode == 0 || act_mode == 1, "exl3_gateup_epilogue: act_mode 0 (bf16 roundings) or 1 (fp32)");
-  if (P <= 0) return TFB_OK;
-  return check_cuda(launch(exl3::gateup_epilogue_kernel, dim3(P, N / 128), dim3(32), 0,
-                           static_cast<cudaStream_t>(stream), z, pick, static_cast<const __half*>(svh_g),
-                           static_cast<const __half*>(svh_u), static_cast<const __half*>(suh_d),
-                           static_cast<__half*>(xd), P, N, E, limit, act_mode),
-                    "exl3_gateup_epilogue");
-}
-
-// y [R * slots, D] fp32 from Z [R * slots, D]; with wts and out also out [R, D] = the slot-order weighted sum.
-// (exl3/experts.cpp `down_epilogue`, `combine`, `down_combine`)
-extern "C" int tfb_exl3_down_epilogue(const float* z, const int32_t* pick, const void* svh_d, float* y,
-                                      const float* wts, float* out, int R, int D, int E, int slots, void* stream) {
-  TFB_REQUIRE(z && pick && svh_d && y, "exl3_down_epilogue: null pointer");
-  TFB_REQUIRE((wts == nullptr) == (out == nullptr), "exl3_down_epilogue: wts and out come together");
-  TFB_REQUIRE(D > 0 && D % 128 == 0 && slots >= 1 && slots <= 32, "exl3_down_epilogue: D % 128 == 0, 1..32 slots");
-  if (R <= 0) return TFB_OK;
-  return check_cuda(launch(exl3::down_epilogue_kernel, dim3(R, D / 128), dim3(32 * slots), 0,
-                           static_cast<cudaStream_t>(stream), z, pick, static_cast<const __half*>(svh_d), y, wts, out,
-                           D, E, slots),
-                    "exl3_down_epilogue");
 }
 
 // ---- grouping without caller scratch ---------------------------------------------------------------------------
@@ -603,4 +689,136 @@ extern "C" int tfb_exl3_group_static(const int32_t* pick, int32_t* uids, int32_t
                            static_cast<cudaStream_t>(stream), pick, R * slots, E, slots, tmp_members, tmp_items,
                            tmp_counts, uids, ucount, members, maxm, maxu),
                     "exl3_group_static");
+}
+
+// The first launch of a routed call: sorts the pairs by expert (when `sort`: members [R * slots], items
+// [(min(R * slots, E) + R * slots / 16), 3] = (expert, first, count <= 16), counts [2], ucount [1] = distinct experts)
+// and rotates the inputs: out0 / out1 [R * slots, K] fp16 for the two matrices (suh1 / out1 null: one matrix).
+extern "C" int tfb_exl3_prologue(const void* x, int64_t x_stride, int x_is_fp16, const int32_t* pick, const void* suh0,
+                                 const void* suh1, void* out0, void* out1, int R, int K, int slots, int E, int sort,
+                                 int32_t* members, int32_t* items, int32_t* counts, int32_t* ucount, void* stream) {
+  TFB_REQUIRE(x && pick && suh0 && out0, "exl3_prologue: null pointer");
+  TFB_REQUIRE((suh1 == nullptr) == (out1 == nullptr), "exl3_prologue: the second matrix's scales and output come together");
+  TFB_REQUIRE(!sort || (members && items && counts && ucount), "exl3_prologue: null sort table");
+  TFB_REQUIRE(K > 0 && K % 128 == 0, "exl3_prologue: K must be a multiple of 128");
+  TFB_REQUIRE(slots >= 1 && slots <= 32 && x_stride >= K && x_stride % 8 == 0, "exl3_prologue: bad slots or stride");
+  TFB_REQUIRE(aligned16(x) && aligned16(suh0) && aligned16(out0) && aligned16(suh1) && aligned16(out1),
+              "exl3_prologue: 16-byte aligned rows");
+  TFB_REQUIRE(E >= 1 && E <= PLAN_EMAX, "exl3_prologue: at most %d experts, not %d", PLAN_EMAX, E);
+  if (R <= 0) return TFB_OK;
+  const int64_t units = (int64_t)R * slots * (K / 128);
+  const int64_t want = (units + 2 * (PLAN_THREADS / 32) - 1) / (2 * (PLAN_THREADS / 32));
+  const int rot_blocks = (int)(want < 2 * sm_count() ? want : 2 * sm_count());
+  const dim3 grid(1 + rot_blocks);
+  const size_t smem = sort ? sizeof(int) * 32 * (size_t)E : 0;
+  auto st = static_cast<cudaStream_t>(stream);
+  cudaError_t e;
+  if (x_is_fp16) {
+    static int configured[64] = {0};
+    if (int rc = plan_smem_opt_in(exl3_prologue_kernel<__half>, configured, "exl3_prologue: shared memory opt-in")) return rc;
+    e = launch(exl3_prologue_kernel<__half>, grid, dim3(PLAN_THREADS), smem, st, pick, R * slots, E, slots, sort, members,
+               items, counts, ucount, static_cast<const __half*>(x), x_stride, static_cast<const __half*>(suh0),
+               static_cast<const __half*>(suh1), static_cast<__half*>(out0), static_cast<__half*>(out1), K);
+  } else {
+    static int configured[64] = {0};
+    if (int rc = plan_smem_opt_in(exl3_prologue_kernel<__nv_bfloat16>, configured, "exl3_prologue: shared memory opt-in"))
+      return rc;
+    e = launch(exl3_prologue_kernel<__nv_bfloat16>, grid, dim3(PLAN_THREADS), smem, st, pick, R * slots, E, slots, sort,
+               members, items, counts, ucount, static_cast<const __nv_bfloat16*>(x), x_stride,
+               static_cast<const __half*>(suh0), static_cast<const __half*>(suh1), static_cast<__half*>(out0),
+               static_cast<__half*>(out1), K);
+  }
+  return check_cuda(e, "exl3_prologue");
+}
+
+static int exl3_grouped_launch(const char* who, const exl3::GroupedArgs& a, int cb, int max_items, void* stream) {
+  TFB_REQUIRE(a.K > 0 && a.N > 0 && a.K % 128 == 0 && a.N % 128 == 0, "%s: K and N must be multiples of 128", who);
+  TFB_REQUIRE(cb >= 0 && cb <= 2, "%s: codebook must be 0 (3inst), 1 (mcg) or 2 (mul1)", who);
+  TFB_REQUIRE(max_items >= 0 && a.P >= 0, "%s: bad sizes", who);
+  if (max_items == 0 || a.P == 0) return TFB_OK;
+  TFB_REQUIRE(a.N / 64 <= 65535, "%s: too many columns for one launch", who);
+  const dim3 grid(max_items, a.N / (16 * exl3::GR_NTB), a.mats);
+  auto st = static_cast<cudaStream_t>(stream);
+  cudaError_t e;
+  if (cb == 0)
+    e = launch(exl3::grouped_kernel<0>, grid, dim3(exl3::GR_WARPS * 32), 0, st, a);
+  else if (cb == 1)
+    e = launch(exl3::grouped_kernel<1>, grid, dim3(exl3::GR_WARPS * 32), 0, st, a);
+  else
+    e = launch(exl3::grouped_kernel<2>, grid, dim3(exl3::GR_WARPS * 32), 0, st, a);
+  return check_cuda(e, who);
+}
+
+// xd [P, N] fp16 = the down projection's rotated input of every routed pair: gate and up (trellis GEMV over the rotated
+// inputs xg, xu [P, K] fp16), output rotation, svh, SwiGLU (act_mode 0: bf16 roundings, 1: fp32; clipped at limit),
+// suh_d, rotation - one launch.  tp_*: int64 trellis pointers [E] (16-byte aligned trellises), k2_*: int32 [E];
+// items / counts / members: the prologue's sort; z: fp32 scratch [2, P, N]; arrive: int scratch
+// [max_items * N / 128], zero before the first call (every call leaves it zero); max_items >= the sort's items.
+// (exl3/experts.cpp `grouped` + `gateup_epilogue`: src/tensorfold/cuda/exl3/experts_grouped.cuh:190-284,
+// src/tensorfold/cuda/exl3/experts.cu:116-158)
+extern "C" int tfb_exl3_gateup(const void* xg, const void* xu, const int64_t* tp_g, const int64_t* tp_u,
+                               const int32_t* k2_g, const int32_t* k2_u, const int32_t* items, const int32_t* counts,
+                               const int32_t* members, float* z, int32_t* arrive, const void* svh_g, const void* svh_u,
+                               const void* suh_d, void* xd, int K, int N, int P, int cb, int max_items, float limit,
+                               int act_mode, void* stream) {
+  TFB_REQUIRE(xg && xu && tp_g && tp_u && k2_g && k2_u && items && counts && members && z && arrive && svh_g && svh_u &&
+                  suh_d && xd,
+              "exl3_gateup: null pointer");
+  TFB_REQUIRE(act_mode == 0 || act_mode == 1, "exl3_gateup: act_mode 0 (bf16 roundings) or 1 (fp32)");
+  TFB_REQUIRE(aligned16(z) && aligned16(svh_g) && aligned16(svh_u) && aligned16(suh_d) && aligned16(xd),
+              "exl3_gateup: 16-byte aligned rows");
+  exl3::GroupedArgs a = {};
+  a.x[0] = static_cast<const __half*>(xg);
+  a.x[1] = static_cast<const __half*>(xu);
+  a.tp[0] = tp_g;
+  a.tp[1] = tp_u;
+  a.k2[0] = k2_g;
+  a.k2[1] = k2_u;
+  a.items = items;
+  a.counts = counts;
+  a.members = members;
+  a.z = z;
+  a.arrive = arrive;
+  a.sv[0] = static_cast<const __half*>(svh_g);
+  a.sv[1] = static_cast<const __half*>(svh_u);
+  a.suh_next = static_cast<const __half*>(suh_d);
+  a.out = xd;
+  a.K = K;
+  a.N = N;
+  a.P = P;
+  a.mats = 2;
+  a.epi = exl3::GE_GATEUP;
+  a.act_mode = act_mode;
+  a.limit = limit;
+  return exl3_grouped_launch("exl3_gateup", a, cb, max_items, stream);
+}
+
+// y [P, N] fp32 = rotate(x [P, K] fp16 times W_q of each pair's expert) * svh of every routed pair (rows of other
+// pairs are left as they are) - one launch; z: fp32 scratch [P, N]; the other arguments as tfb_exl3_gateup.
+// (exl3/experts.cpp `grouped` + `down_epilogue`: src/tensorfold/cuda/exl3/experts.cu:161-180)
+extern "C" int tfb_exl3_down(const void* x, const int64_t* tp, const int32_t* k2, const int32_t* items,
+                             const int32_t* counts, const int32_t* members, float* z, int32_t* arrive, const void* svh,
+                             float* y, int K, int N, int P, int cb, int max_items, void* stream) {
+  TFB_REQUIRE(x && tp && k2 && items && counts && members && z && arrive && svh && y, "exl3_down: null pointer");
+  TFB_REQUIRE(aligned16(z) && aligned16(svh) && aligned16(y), "exl3_down: 16-byte aligned rows");
+  exl3::GroupedArgs a = {};
+  a.x[0] = a.x[1] = static_cast<const __half*>(x);
+  a.tp[0] = a.tp[1] = tp;
+  a.k2[0] = a.k2[1] = k2;
+  a.items = items;
+  a.counts = counts;
+  a.members = members;
+  a.z = z;
+  a.arrive = arrive;
+  a.sv[0] = a.sv[1] = static_cast<const __half*>(svh);
+  a.suh_next = nullptr;
+  a.out = y;
+  a.K = K;
+  a.N = N;
+  a.P = P;
+  a.mats = 1;
+  a.epi = exl3::GE_DOWN;
+  a.act_mode = 1;
+  a.limit = 0.f;
+  return exl3_grouped_launch("exl3_down", a, cb, max_items, stream);
 }

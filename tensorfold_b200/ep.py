@@ -470,7 +470,7 @@ class PeerExl3ExpertParallel:
         self.wts_local = torch.zeros((rows, top_k), dtype=torch.float32, device=dev)
         self.partial = torch.zeros((rows, d), dtype=torch.float32, device=dev)
         self.out = torch.zeros((rows_local, d), dtype=torch.float32, device=dev)
-        self.launches = 13
+        self.launches = 7 + exl3.LAUNCHES_PER_CALL               # + 1 when forward() is given rows to stage
         torch.cuda.synchronize(dev)
 
     def forward(self, x_local: torch.Tensor | None = None) -> torch.Tensor:

@@ -4,6 +4,10 @@ Mirrors the operator surface of the reference's ``src/tensorfold/cuda/exl3/exper
 Exl3RoutedExperts, Scratch, routed, dequant, default_config, codebook_id, k2_of) over the C-ABI library.  The
 trellises are referenced in place by device pointer; the returned object keeps them alive.  ``routed`` allocates
 nothing (unless ``out`` is None) and never synchronises, so it can be captured in a CUDA graph.
+
+One ``routed`` call is three launches (``csrc/exl3.cu``): a prologue that sorts the pairs by expert and rotates the
+inputs, the gate/up projection with its epilogue fused in, the down projection with its output rotation fused in -
+plus the slot-order combine when weights are given.
 """
 
 from __future__ import annotations
@@ -19,11 +23,13 @@ from .. import _lib
 CB_3INST, CB_MCG, CB_MUL1 = 0, 1, 2
 ACT_BF16, ACT_F32 = 0, 1          # SwiGLU with the GLM family's bf16 roundings / in fp32
 K2_SUPPORTED = tuple(range(2, 17))   # half-bits a value: 1..8 bits and every half-integer rate between
-LAUNCHES_PER_CALL = 6             # kernels one ``routed`` call enqueues (grouping included)
+LAUNCHES_PER_CALL = 4             # kernels one ``routed`` call with weights enqueues (3 without)
+ITEM_PAIRS = 16                   # pairs an item of the sort holds: two mma tiles share one decoded weight tile
 
 # (16-column tiles a block, K-slice warps, K splits across blocks, tiles in flight): this library's one setting.
 # The split is by shape only; partial sums meet in warp order inside the block, so there is one split.
 CONFIG = (4, 4, 1, 1)
+_CODEBOOKS = {"3inst": CB_3INST, "mcg": CB_MCG, "mul1": CB_MUL1}
 
 
 def _stream(t: torch.Tensor) -> int:
@@ -31,19 +37,25 @@ def _stream(t: torch.Tensor) -> int:
 
 
 def codebook_id(name: str) -> int:
-    ids = {"3inst": CB_3INST, "mcg": CB_MCG, "mul1": CB_MUL1}
-    if name not in ids:
-        raise ValueError(f"unknown EXL3 codebook {name!r}")
-    return ids[name]
+    try:
+        return _CODEBOOKS[name]
+    except KeyError:
+        raise ValueError(f"unknown EXL3 codebook {name!r}") from None
+
+
+def _codebook(codebook: int | str) -> int:
+    cb = codebook_id(codebook) if isinstance(codebook, str) else int(codebook)
+    if cb not in _CODEBOOKS.values():
+        raise ValueError("codebook must be 0 (3inst), 1 (mcg) or 2 (mul1)")
+    return cb
 
 
 def k2_of(trellis: torch.Tensor) -> int:
     """Half-bits a value of a trellis int16 [K/16, N/16, 8 * K2]."""
 
-    w = trellis.shape[-1]
-    if w % 8:
-        raise ValueError(f"trellis last dim {w} is not a multiple of 8")
-    k2 = w // 8
+    k2, rest = divmod(trellis.shape[-1], 8)
+    if rest:
+        raise ValueError(f"trellis last dim {trellis.shape[-1]} is not a multiple of 8")
     if k2 not in K2_SUPPORTED:
         raise ValueError(f"unsupported EXL3 bit width {k2 / 2}")
     return k2
@@ -78,95 +90,103 @@ class Exl3RoutedExperts:
         return int(self.trellis_bytes[list(ids)].sum())
 
 
+class _Projection:
+    """The experts' matrices of one projection (K -> N): checked, then one pointer table, one width table and the two
+    scale vectors stacked - each made in a single pass over the experts."""
+
+    def __init__(self, mats: Sequence[tuple], k: int, n: int, device) -> None:
+        for t, _, _ in mats:
+            if t.dtype != torch.int16 or not t.is_contiguous() or t.device.type != "cuda":
+                raise ValueError("trellis must be a contiguous CUDA int16 tensor")
+            if (t.shape[0] * 16, t.shape[1] * 16) != (k, n):
+                raise ValueError(f"expert shape {tuple(t.shape)} does not match [{k // 16}, {n // 16}, *]")
+            if t.data_ptr() % 16:
+                raise ValueError("trellises must start on a 16-byte boundary (the kernels copy them in 16-byte units)")
+        self.trellises = [t for t, _, _ in mats]
+        self.widths = [k2_of(t) for t in self.trellises]
+        self.ptr = torch.tensor([t.data_ptr() for t in self.trellises], dtype=torch.int64).to(device)
+        self.k2 = torch.tensor(self.widths, dtype=torch.int32).to(device)
+        self.suh = torch.stack([m[1].reshape(k) for m in mats]).to(device=device, dtype=torch.float16).contiguous()
+        self.svh = torch.stack([m[2].reshape(n) for m in mats]).to(device=device, dtype=torch.float16).contiguous()
+
+
 def prepare(gate: Sequence[tuple], up: Sequence[tuple], down: Sequence[tuple], codebook: int | str,
             device="cuda") -> Exl3RoutedExperts:
     """A layer from per-expert (trellis, suh, svh) triples, trellises referenced in place, each at its own width."""
 
-    cb = codebook_id(codebook) if isinstance(codebook, str) else int(codebook)
-    if cb not in (CB_3INST, CB_MCG, CB_MUL1):
-        raise ValueError("codebook must be 0 (3inst), 1 (mcg) or 2 (mul1)")
-    e_count = len(gate)
-    if not (len(up) == len(down) == e_count) or e_count == 0:
+    cb = _codebook(codebook)
+    if len(gate) == 0 or len({len(gate), len(up), len(down)}) != 1:
         raise ValueError("gate, up and down need the same, non-zero number of experts")
-    d, i = gate[0][0].shape[0] * 16, gate[0][0].shape[1] * 16
-    if d % 128 or i % 128:
-        raise ValueError(f"EXL3 experts need K and N in multiples of 128, not {d} and {i}")
-    keep = []
-
-    def table(mats, k, n):
-        ptrs, k2s = [], []
-        for t, _, _ in mats:
-            if t.dtype != torch.int16 or not t.is_contiguous() or t.device.type != "cuda":
-                raise ValueError("trellis must be a contiguous CUDA int16 tensor")
-            if t.shape[0] * 16 != k or t.shape[1] * 16 != n:
-                raise ValueError(f"expert shape {tuple(t.shape)} does not match [{k // 16}, {n // 16}, *]")
-            k2s.append(k2_of(t))
-            ptrs.append(t.data_ptr())
-            keep.append(t)
-        return (torch.tensor(ptrs, dtype=torch.int64, device=device),
-                torch.tensor(k2s, dtype=torch.int32, device=device), k2s)
-
-    gp, gk, gks = table(gate, d, i)
-    upp, uk, uks = table(up, d, i)
-    dp, dk, dks = table(down, i, d)
-
-    def stack(mats, j, n):
-        out = torch.empty((e_count, n), dtype=torch.float16, device=device)
-        for e, m in enumerate(mats):
-            out[e].copy_(m[j].reshape(-1))
-        return out
-
-    tb = torch.tensor([(d * i // 256) * (gks[e] + uks[e] + dks[e]) * 16 for e in range(e_count)], dtype=torch.int64)
-    return Exl3RoutedExperts(gp, upp, dp, gk, uk, dk, stack(gate, 1, d), stack(up, 1, d), stack(gate, 2, i),
-                             stack(up, 2, i), stack(down, 1, i), stack(down, 2, d), e_count, d, i, cb,
-                             (min(gks + uks), max(gks + uks)), (min(dks), max(dks)), tb, keep)
+    dims, width = (16 * s for s in gate[0][0].shape[:2])
+    if dims % 128 or width % 128:
+        raise ValueError(f"EXL3 experts need K and N in multiples of 128, not {dims} and {width}")
+    g, u, d = _Projection(gate, dims, width, device), _Projection(up, dims, width, device), \
+        _Projection(down, width, dims, device)
+    # a tile of 256 values takes 16 * K2 bytes, so an expert's three trellises take (tiles a matrix) * 16 * sum(K2)
+    tile_bytes = (dims // 16) * (width // 16) * 16
+    trellis_bytes = ((g.k2 + u.k2 + d.k2).to(torch.int64) * tile_bytes).cpu()
+    return Exl3RoutedExperts(g.ptr, u.ptr, d.ptr, g.k2, u.k2, d.k2, g.suh, u.suh, g.svh, u.svh, d.suh, d.svh,
+                             len(gate), dims, width, cb, (min(g.widths + u.widths), max(g.widths + u.widths)),
+                             (min(d.widths), max(d.widths)), trellis_bytes, g.trellises + u.trellises + d.trellises)
 
 
 def prepare_stacked(gt, ut, dt, suh_g, suh_u, svh_g, svh_u, suh_d, svh_d, codebook: int | str) -> Exl3RoutedExperts:
     """A uniform-width layer stacked per projection: trellis [E, K/16, N/16, 16 bits] (int16, or int32 words)."""
 
-    def as16(t):
-        return t.view(torch.int16) if t.dtype == torch.int32 else t
+    def triples(t, suh, svh):
+        t16 = t.view(torch.int16) if t.dtype == torch.int32 else t      # 32-bit words are pairs of the same int16
+        return list(zip(t16.unbind(0), suh.unbind(0), svh.unbind(0)))
 
-    gt, ut, dt = as16(gt), as16(ut), as16(dt)
-    e_count = gt.shape[0]
-    return prepare([(gt[e], suh_g[e], svh_g[e]) for e in range(e_count)],
-                   [(ut[e], suh_u[e], svh_u[e]) for e in range(e_count)],
-                   [(dt[e], suh_d[e], svh_d[e]) for e in range(e_count)], codebook, device=gt.device)
+    return prepare(triples(gt, suh_g, svh_g), triples(ut, suh_u, svh_u), triples(dt, suh_d, svh_d), codebook,
+                   device=gt.device)
 
 
 def default_config(K: int, N: int, gateup: bool) -> tuple[int, int, int, int]:
     """The tile setting for a K -> N projection: one setting, the shape only decides whether it divides."""
 
-    nt, w, sk, pf = CONFIG
-    if K % (16 * sk * w) or N % (16 * nt):
+    tiles, warps, splits, _ = CONFIG
+    if K % (16 * splits * warps) or N % (16 * tiles):
         raise ValueError(f"no tile setting divides K={K}, N={N}")
     return CONFIG
+
+
+def max_items(pairs: int, experts: int) -> int:
+    """Items the sort of ``pairs`` pairs over ``experts`` experts can make: one an expert in use, one more for every
+    full ``ITEM_PAIRS`` pairs."""
+
+    return min(pairs, experts) + pairs // ITEM_PAIRS
 
 
 class Scratch:
     """Buffers for up to ``rows`` rows of ``slots`` slots; slots whose pick is not a routed expert are the caller's."""
 
     def __init__(self, ex: Exl3RoutedExperts, rows: int, slots: int, cfg_gu=None, cfg_d=None, device="cuda") -> None:
-        d, i = ex.dims, ex.width
-        self.cfg_gu = cfg_gu or default_config(d, i, True)
-        self.cfg_d = cfg_d or default_config(i, d, False)
         if slots > 32:
             raise ValueError("at most 32 slots")
-        p = rows * slots
-        self.xg = torch.zeros((p, d), dtype=torch.float16, device=device)
-        self.xu = torch.zeros((p, d), dtype=torch.float16, device=device)
-        self.xd = torch.zeros((p, i), dtype=torch.float16, device=device)
-        self.z = torch.zeros((max(2 * i, d) * p,), dtype=torch.float32, device=device)
-        self.y = torch.zeros((p, d), dtype=torch.float32, device=device)
-        maxu = min(p, ex.count)
-        self.ids = torch.zeros((maxu,), dtype=torch.int32, device=device)
-        self.count = torch.zeros((1,), dtype=torch.int32, device=device)
-        self.members_buf = torch.full((maxu * rows,), -1, dtype=torch.int32, device=device)
-        self.sort_members = torch.zeros((p,), dtype=torch.int32, device=device)
-        self.sort_items = torch.zeros((max(1, maxu), 3), dtype=torch.int32, device=device)
-        self.sort_counts = torch.zeros((2,), dtype=torch.int32, device=device)
+        self.cfg_gu = cfg_gu or default_config(ex.dims, ex.width, True)
+        self.cfg_d = cfg_d or default_config(ex.width, ex.dims, False)
         self.rows, self.slots, self.count_experts = rows, slots, ex.count
+        pairs, experts_seen = rows * slots, min(rows * slots, ex.count)
+
+        def buf(shape, dtype, fill=0):
+            return torch.full(shape, fill, dtype=dtype, device=device)
+
+        # rotated inputs of gate, up and down; partial sums (gate and up side by side, or down); per-pair outputs
+        self.xg, self.xu = buf((pairs, ex.dims), torch.float16), buf((pairs, ex.dims), torch.float16)
+        self.xd = buf((pairs, ex.width), torch.float16)
+        self.z = buf((pairs * max(2 * ex.width, ex.dims),), torch.float32)
+        self.y = buf((pairs, ex.dims), torch.float32)
+        # the `group` operator's tables (distinct experts, how many, their members) and its sort temporaries
+        self.ids, self.count = buf((experts_seen,), torch.int32), buf((1,), torch.int32)
+        self.members_buf = buf((experts_seen * rows,), torch.int32, -1)
+        self.tmp_members, self.tmp_items = buf((pairs,), torch.int32), buf((max(1, experts_seen), 3), torch.int32)
+        self.tmp_counts = buf((2,), torch.int32)
+        # what the kernels read: pairs sorted by expert, items of up to ITEM_PAIRS pairs, and the arrival counters of
+        # the fused epilogues (one a (item, 128 columns); the kernels leave them zero)
+        items = max_items(pairs, ex.count)
+        self.sort_members, self.sort_items = buf((pairs,), torch.int32), buf((max(1, items), 3), torch.int32)
+        self.sort_counts = buf((2,), torch.int32)
+        self.arrive = buf((max(1, items) * (max(ex.width, ex.dims) // 128),), torch.int32)
 
     def window(self, R: int):
         """(ids, members) sized for R rows: the grids only span what R rows can use."""
@@ -176,13 +196,17 @@ class Scratch:
 
 
 def group(pick: torch.Tensor, s: Scratch, R: int, experts: int) -> None:
-    """Distinct routed experts (< E) in id order into ``s.ids`` / ``s.count``, their members into ``s.members_buf``."""
+    """Distinct routed experts (< E) in id order into ``s.ids`` / ``s.count``, their members into ``s.members_buf``
+    (the reference's tables), and the sort the kernels read into ``s.sort_*`` - so a following
+    ``routed(..., group_first=False)`` finds its pairs grouped."""
 
     ids, members = s.window(R)
     with torch.cuda.device(pick.device):
         _lib.call("tfb_exl3_group", pick.data_ptr(), ids.data_ptr(), s.count.data_ptr(), members.data_ptr(),
-                  s.sort_members.data_ptr(), s.sort_items.data_ptr(), s.sort_counts.data_ptr(), R, s.slots, experts,
+                  s.tmp_members.data_ptr(), s.tmp_items.data_ptr(), s.tmp_counts.data_ptr(), R, s.slots, experts,
                   ids.shape[0], R, _stream(pick))
+        _lib.call("tfb_plan", pick.data_ptr(), R * s.slots, experts, ITEM_PAIRS, s.sort_members.data_ptr(),
+                  s.sort_items.data_ptr(), s.sort_counts.data_ptr(), _stream(pick))
 
 
 def routed(x: torch.Tensor, pick: torch.Tensor, wts: torch.Tensor | None, ex: Exl3RoutedExperts, s: Scratch,
@@ -191,49 +215,48 @@ def routed(x: torch.Tensor, pick: torch.Tensor, wts: torch.Tensor | None, ex: Ex
     """Routed experts of R rows (picks >= E skipped): y per slot [R * slots, D] fp32, or ``out`` [R, D] fp32 = the
     wts-weighted slot-order sum when ``wts`` is given; no host sync."""
 
-    d, i, e_count, slots = ex.dims, ex.width, ex.count, s.slots
-    p = R * slots
+    dims, width, slots = ex.dims, ex.width, s.slots
+    pairs = R * slots
     if R > s.rows:
         raise ValueError(f"{R} rows but the scratch holds {s.rows}")
-    if not x.is_cuda or x.dtype not in (torch.bfloat16, torch.float16) or x.stride(1) != 1 or x.shape[1] != d:
+    if not x.is_cuda or x.dtype not in (torch.bfloat16, torch.float16) or x.stride(1) != 1 or x.shape[1] != dims:
         raise ValueError("x must be CUDA bf16 or fp16 [R, D] with unit-stride rows")
     if pick.dtype != torch.int32 or not pick.is_contiguous() or pick.shape != (R, slots):
         raise ValueError(f"pick must be contiguous int32 [{R}, {slots}]")
-    ids, members = s.window(R)
-    st = _stream(x)
-    lim = float(min(limit, 3.0e38))
+    if act_mode not in (ACT_BF16, ACT_F32):
+        raise ValueError("act_mode is ACT_BF16 or ACT_F32")
+    st, items = _stream(x), max_items(pairs, ex.count)
+    sort = (s.sort_members.data_ptr(), s.sort_items.data_ptr(), s.sort_counts.data_ptr())
     with torch.cuda.device(x.device):
-        if group_first:
-            group(pick, s, R, e_count)
-        _lib.call("tfb_exl3_rot_in", x.data_ptr(), x.stride(0), 1 if x.dtype == torch.float16 else 0, pick.data_ptr(),
-                  ex.suh_g.data_ptr(), ex.suh_u.data_ptr(), s.xg.data_ptr(), s.xu.data_ptr(), R, d, slots, e_count, st)
-        _lib.call("tfb_exl3_grouped", s.xg.data_ptr(), s.xu.data_ptr(), ex.gate_ptr.data_ptr(), ex.up_ptr.data_ptr(),
-                  ex.gate_k2.data_ptr(), ex.up_k2.data_ptr(), ids.data_ptr(), s.count.data_ptr(), members.data_ptr(),
-                  s.z.data_ptr(), 2, d, i, p, slots, ex.cb, R, ids.shape[0], st)
-        _lib.call("tfb_exl3_gateup_epilogue", s.z.data_ptr(), pick.data_ptr(), ex.svh_g.data_ptr(),
-                  ex.svh_u.data_ptr(), ex.suh_d.data_ptr(), s.xd.data_ptr(), p, i, e_count, lim, act_mode, st)
-        _lib.call("tfb_exl3_grouped", s.xd.data_ptr(), s.xd.data_ptr(), ex.down_ptr.data_ptr(), ex.down_ptr.data_ptr(),
-                  ex.down_k2.data_ptr(), ex.down_k2.data_ptr(), ids.data_ptr(), s.count.data_ptr(),
-                  members.data_ptr(), s.z.data_ptr(), 1, i, d, p, slots, ex.cb, R, ids.shape[0], st)
+        _lib.call("tfb_exl3_prologue", x.data_ptr(), x.stride(0), int(x.dtype == torch.float16), pick.data_ptr(),
+                  ex.suh_g.data_ptr(), ex.suh_u.data_ptr(), s.xg.data_ptr(), s.xu.data_ptr(), R, dims, slots, ex.count,
+                  int(group_first), *sort, s.count.data_ptr(), st)
+        tables = (sort[1], sort[2], sort[0], s.z.data_ptr(), s.arrive.data_ptr())
+        _lib.call("tfb_exl3_gateup", s.xg.data_ptr(), s.xu.data_ptr(), ex.gate_ptr.data_ptr(), ex.up_ptr.data_ptr(),
+                  ex.gate_k2.data_ptr(), ex.up_k2.data_ptr(), *tables, ex.svh_g.data_ptr(), ex.svh_u.data_ptr(),
+                  ex.suh_d.data_ptr(), s.xd.data_ptr(), dims, width, pairs, ex.cb, items, float(min(limit, 3.0e38)),
+                  act_mode, st)
+        _lib.call("tfb_exl3_down", s.xd.data_ptr(), ex.down_ptr.data_ptr(), ex.down_k2.data_ptr(), *tables,
+                  ex.svh_d.data_ptr(), s.y.data_ptr(), width, dims, pairs, ex.cb, items, st)
         if wts is None:
-            _lib.call("tfb_exl3_down_epilogue", s.z.data_ptr(), pick.data_ptr(), ex.svh_d.data_ptr(), s.y.data_ptr(),
-                      0, 0, R, d, e_count, slots, st)
-            return s.y[:p]
+            return s.y[:pairs]
         if out is None:
-            out = torch.empty((R, d), dtype=torch.float32, device=x.device)
-        _lib.call("tfb_exl3_down_epilogue", s.z.data_ptr(), pick.data_ptr(), ex.svh_d.data_ptr(), s.y.data_ptr(),
-                  wts.data_ptr(), out.data_ptr(), R, d, e_count, slots, st)
+            out = torch.empty((R, dims), dtype=torch.float32, device=x.device)
+        if out.dtype != torch.float32 or not out.is_contiguous() or not wts.is_contiguous():
+            raise ValueError("out must be contiguous fp32 [R, D] and wts contiguous fp32 [R, slots]")
+        # slots that are not routed experts keep the y their owner put there and take part in the sum
+        _lib.call("tfb_combine", s.y.data_ptr(), 0, wts.data_ptr(), out.data_ptr(), 1, R, slots, dims, st)
     return out
 
 
 def dequant(trellis: torch.Tensor, codebook: int | str) -> torch.Tensor:
     """W_q [K, N] fp16 of one matrix through the kernels' own lane decode; for tests."""
 
-    cb = codebook_id(codebook) if isinstance(codebook, str) else int(codebook)
-    k2 = k2_of(trellis)
-    k, n = trellis.shape[0] * 16, trellis.shape[1] * 16
-    t = trellis.contiguous()
-    out = torch.empty((k, n), dtype=torch.float16, device=trellis.device)
+    cb = _codebook(codebook)
+    rows, cols = trellis.shape[0] * 16, trellis.shape[1] * 16
+    words = trellis.contiguous()
+    w_q = torch.empty((rows, cols), dtype=torch.float16, device=trellis.device)
     with torch.cuda.device(trellis.device):
-        _lib.call("tfb_exl3_dequant", t.data_ptr(), out.data_ptr(), k, n, k2, cb, _stream(trellis))
-    return out
+        _lib.call("tfb_exl3_dequant", words.data_ptr(), w_q.data_ptr(), rows, cols, k2_of(trellis), cb,
+                  _stream(trellis))
+    return w_q

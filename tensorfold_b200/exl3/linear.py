@@ -3,6 +3,8 @@ every input row one member, so the trellis decoder, the K split by shape and the
 
 Mirrors ``tensorfold.cuda.exl3.linear`` (``src/tensorfold/cuda/exl3/linear.py:58-203``): ``Exl3Linear.from_tensors``,
 ``__call__`` (y = x @ W + bias for 1..128 rows, any codebook and width), ``unpack``, ``unpack_cuda``, ``k2_of``.
+The input rotation is the experts' prologue with one matrix, the product and the output rotation their down
+projection.
 The trellis is read where the caller keeps it (the reference's "stored" layout; no strip copy is made).  No CPU path.
 """
 
@@ -74,33 +76,38 @@ class Exl3Linear:
     def nbytes(self) -> int:
         return self.trellis.numel() * 2
 
-    def _tables(self):
-        """Pointer / width tables of the one matrix, and per row count the members of "expert" 0 (never changes)."""
+    def _tables(self, m: int) -> dict:
+        """What the experts' kernels need to see the layer as one "expert" whose members are the m input rows: the
+        pointer and width of the one matrix, all-zero picks, and the sort of those picks (rows in order, items of 16)."""
 
         st = self._state
         if "ptr" not in st:
             dev = self.trellis.device
+            if self.trellis.data_ptr() % 16:
+                raise ValueError("the trellis must start on a 16-byte boundary")
             st["ptr"] = torch.tensor([self.trellis.data_ptr()], dtype=torch.int64, device=dev)
             st["k2"] = torch.tensor([self.k2], dtype=torch.int32, device=dev)
-            st["ids"] = torch.zeros((1,), dtype=torch.int32, device=dev)
-            st["count"] = torch.ones((1,), dtype=torch.int32, device=dev)
-            st["pick"] = torch.zeros((MAX_ROWS,), dtype=torch.int32, device=dev)
-            st["members"] = {}
-        return st
-
-    def _members(self, m: int) -> torch.Tensor:
-        st = self._tables()
-        mem = st["members"].get(m)
-        if mem is None:
-            # row * 32 + slot for slot 0 of every row, the table the grouping kernel would make for all-zero picks
-            mem = (torch.arange(m, dtype=torch.int32, device=self.trellis.device) * 32).contiguous()
-            st["members"][m] = mem
-        return mem
+            st["rows"] = {}
+        rows = st["rows"].get(m)
+        if rows is None:
+            dev = self.trellis.device
+            n_items = -(-m // routed.ITEM_PAIRS)
+            first = torch.arange(n_items, dtype=torch.int32) * routed.ITEM_PAIRS
+            items = torch.stack([torch.zeros_like(first), first, (m - first).clamp(max=routed.ITEM_PAIRS)], dim=1)
+            rows = st["rows"][m] = {
+                "pick": torch.zeros((m,), dtype=torch.int32, device=dev),
+                "members": torch.arange(m, dtype=torch.int32, device=dev),
+                "items": items.contiguous().to(dev),
+                "counts": torch.tensor([n_items, 1], dtype=torch.int32, device=dev),
+                "arrive": torch.zeros((n_items * (self.n // 128),), dtype=torch.int32, device=dev),
+                "n_items": n_items,
+            }
+        return {**st, **rows}
 
     def __call__(self, x: torch.Tensor, out: torch.Tensor | None = None, out_dtype: torch.dtype | None = None,
                  xh: torch.Tensor | None = None, z: torch.Tensor | None = None) -> torch.Tensor:
-        """y [M, N] = x [M, K] @ W + bias for M = 1..128; scratch ``xh`` fp16 [M, K] and ``z`` fp32 [M, N] are
-        allocated when not given."""
+        """y [M, N] = x [M, K] @ W + bias for M = 1 .. MAX_ROWS; scratch ``xh`` fp16 [M, K] and ``z`` fp32 [M, N] are
+        allocated when not given.  Every 16 rows decode the trellis once (the decode form of the experts)."""
 
         if not x.is_cuda or x.dim() != 2 or x.shape[1] != self.k or not 1 <= x.shape[0] <= MAX_ROWS:
             raise ValueError(f"x must be CUDA [1..{MAX_ROWS}, {self.k}], got {tuple(x.shape)}")
@@ -108,23 +115,20 @@ class Exl3Linear:
             raise ValueError("x must be bf16 or fp16")
         x = x.contiguous()
         m, dev = x.shape[0], x.device
-        st = self._tables()
+        t = self._tables(m)
         if xh is None:
             xh = torch.empty((m, self.k), dtype=torch.float16, device=dev)
         if z is None:
             z = torch.empty((m, self.n), dtype=torch.float32, device=dev)
         y = torch.empty((m, self.n), dtype=torch.float32, device=dev)
-        pick, mem, s = st["pick"], self._members(m), _stream(x)
-        cb = CODEBOOK_IDS[self.codebook]
+        s = _stream(x)
         with torch.cuda.device(dev):
-            _lib.call("tfb_exl3_rot_in", x.data_ptr(), x.stride(0), 1 if x.dtype == torch.float16 else 0,
-                      pick.data_ptr(), self.suh.data_ptr(), self.suh.data_ptr(), xh.data_ptr(), xh.data_ptr(), m,
-                      self.k, 1, 1, s)
-            _lib.call("tfb_exl3_grouped", xh.data_ptr(), xh.data_ptr(), st["ptr"].data_ptr(), st["ptr"].data_ptr(),
-                      st["k2"].data_ptr(), st["k2"].data_ptr(), st["ids"].data_ptr(), st["count"].data_ptr(),
-                      mem.data_ptr(), z.data_ptr(), 1, self.k, self.n, m, 1, cb, m, 1, s)
-            _lib.call("tfb_exl3_down_epilogue", z.data_ptr(), pick.data_ptr(), self.svh.data_ptr(), y.data_ptr(), 0, 0,
-                      m, self.n, 1, 1, s)
+            _lib.call("tfb_exl3_prologue", x.data_ptr(), x.stride(0), int(x.dtype == torch.float16),
+                      t["pick"].data_ptr(), self.suh.data_ptr(), 0, xh.data_ptr(), 0, m, self.k, 1, 1, 0, 0, 0, 0, 0, s)
+            _lib.call("tfb_exl3_down", xh.data_ptr(), t["ptr"].data_ptr(), t["k2"].data_ptr(), t["items"].data_ptr(),
+                      t["counts"].data_ptr(), t["members"].data_ptr(), z.data_ptr(), t["arrive"].data_ptr(),
+                      self.svh.data_ptr(), y.data_ptr(), self.k, self.n, m, CODEBOOK_IDS[self.codebook], t["n_items"],
+                      s)
         if self.bias is not None:
             y += self.bias.float()
         want = out_dtype or (out.dtype if out is not None else x.dtype)

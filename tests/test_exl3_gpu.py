@@ -148,6 +148,25 @@ def test_per_slot_output_and_fused_combine_agree():
     assert torch.equal(s.y[:R * TOPK].view(R, TOPK, D), y)         # the fused launch stores the same per-slot y
 
 
+def test_grouping_ahead_of_the_call_gives_the_same_rows():
+    """``group`` then ``routed(group_first=False)`` (the caller grouped already) equals the call that groups itself."""
+
+    from tensorfold_b200.exl3 import experts
+
+    E, D, I, TOPK, R = 10, 256, 128, 3, 37
+    ex, _ = _layer(E, D, I, [(6, 8, 4)] * E, 0, 27)
+    g = torch.Generator().manual_seed(12)
+    x = torch.randn((R, D), generator=g).to(torch.bfloat16).to(DEV)
+    sel, w = _picks(E, R, TOPK, g, shared=True)
+    s = experts.Scratch(ex, R, TOPK + 1)
+    want = experts.routed(x, sel, w, ex, s, None, R).clone()
+    s2 = experts.Scratch(ex, R, TOPK + 1)
+    experts.group(sel, s2, R, E)
+    got = experts.routed(x, sel, w, ex, s2, None, R, group_first=False)
+    assert torch.equal(got, want)
+    assert int(s2.count[0]) == int(s.count[0]) == len(set(sel[:, :TOPK].reshape(-1).tolist()))
+
+
 def test_graph_replay_equals_eager(pdl):
     from tensorfold_b200.exl3 import experts
 
