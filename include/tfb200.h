@@ -94,6 +94,17 @@ int tfb_plan_split(const int32_t* picks, int64_t pairs, int lo, int experts, int
 int tfb_select_plan_window(const float* logits, int NL, int32_t* pick, float* wts, int T, int E, int top_k, int shared,
                            int tile, int plan_lo, int plan_n, int32_t* members, int32_t* items, int32_t* counts,
                            void* stream);
+
+/* tfb_router, tfb_select_rows and tfb_plan_window of a few rows in ONE launch, with the same bits: logits [T, NE] fp32
+ * from x [T, D] and rows [NE, D] (NE = E + 1 with the shared expert's gate row), pick / wts [T, slots], and the plan of
+ * the ids in [plan_lo, plan_lo + plan_n).  The CTA that finishes a group of eight rows selects them; the one that
+ * finishes the last group plans.  arrive: int32 scratch [1 + (T + 7) / 8], zero before the first call (a call leaves it
+ * zero).  T <= tfb_route_max_rows(NE).  Replaces the three launches of moe.moe's routing:
+ * src/tensorfold/cuda/moe.py:41-55,103-116 and src/tensorfold/cuda/experts.py:101-125. */
+int tfb_route_max_rows(int NE);
+int tfb_route(const void* x, int64_t x_stride, const void* rows, float* logits, int T, int D, int NE, int E, int top_k,
+              int shared, int32_t* pick, float* wts, int tile, int plan_lo, int plan_n, int32_t* members,
+              int32_t* items, int32_t* counts, int32_t* arrive, void* stream);
 int tfb_combine_window(const void* y, int y_bf16, const float* wts, const int32_t* pick, int lo, int n, void* out,
                        int out_f32, int T, int slots, int D, void* stream);
 
@@ -177,6 +188,17 @@ int tfb_experts_run(int gs, int epi, const void* x, int64_t x_stride, int slots,
 int tfb_experts_run_tile(int gs, int epi, const void* x, int64_t x_stride, int slots, const void* w, int kg, int nb,
                          const int32_t* items, const int32_t* counts, const int32_t* members, void* out, int n,
                          float limit, int64_t max_units, int sb_type, int tile, void* stream);
+
+/* The down projection and the weighted combine in one launch: y [P, n] fp32 per pair exactly as tfb_experts_run_tile
+ * with epilogue 0 (x = act [P, K] bf16, one row a pair), and out [T, n] (bf16, or fp32 when out_f32) = the sum over a
+ * token's slots in slot order of wts[t, s] * y[t * slots + s, :] (an fp32 fma chain from 0, rounded once), formed by
+ * the CTA that stores the token's last row.  Every pair t * slots + s of the call's tokens must be in the plan.
+ * arrive: int32 scratch [T, nb], zero before the first call (a call leaves it zero).
+ * Replaces `down` followed by `combine`: src/tensorfold/cuda/experts.py:141-150, src/tensorfold/cuda/moe.py:131-151. */
+int tfb_experts_down_combine(int gs, const void* x, int64_t x_stride, const void* w, int kg, int nb,
+                             const int32_t* items, const int32_t* counts, const int32_t* members, float* y, int n,
+                             int64_t max_units, int sb_type, int tile, const float* wts, int slots, void* out,
+                             int out_f32, int32_t* arrive, void* stream);
 
 /* Grouped 4-bit expert matmul, prefill form (tcgen05 tensor cores, weights dequantised to bf16 with one rounding,
  * one fp32 chain over K).  Arguments as tfb_experts_run, but items may hold up to 192 pairs (plan with tile <= 192) and

@@ -22,6 +22,8 @@ SIGNATURES: dict[str, tuple] = {
     "tfb_select_plan": (P, I, P, P, I, I, I, I, I, P, P, P, P),
     "tfb_select_plan_window": (P, I, P, P, I, I, I, I, I, I, I, P, P, P, P),
     "tfb_plan_window": (P, L, I, I, I, P, P, P, P),
+    "tfb_route": (P, L, P, P, I, I, I, I, I, I, P, P, I, I, I, P, P, P, P, P),
+    "tfb_experts_down_combine": (I, P, L, P, I, I, P, P, P, P, I, L, I, I, P, I, P, I, P, P),
     "tfb_plan_split": (P, L, I, I, I, I, I, P, P, P, P, P, P),
     "tfb_combine_window": (P, I, P, P, I, I, P, I, I, I, I, P),
     "tfb_combine": (P, I, P, P, I, I, I, I, P),
@@ -64,6 +66,8 @@ def lib() -> ctypes.CDLL:
     handle.tfb_set_pdl.restype = c_int
     handle.tfb_set_wait_limit_ms.argtypes = (c_int,)
     handle.tfb_set_wait_limit_ms.restype = c_int
+    handle.tfb_route_max_rows.argtypes = (c_int,)
+    handle.tfb_route_max_rows.restype = c_int
     handle.tfb_select_plan_max_rows.restype = c_int
     handle.tfb_select_plan_max_rows.argtypes = ()
     for name, args in SIGNATURES.items():

@@ -207,7 +207,42 @@ __device__ __forceinline__ uint32_t comp(const uint4& v, int c) {
 // Programmatic dependent launch: a kernel launched with the attribute may start early and must wait here before it
 // reads what the previous kernel in the stream wrote; without the attribute both are no-ops.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+
+// pdl_wait for a kernel's inputs: every pointer through which the kernel reads what earlier kernels wrote is passed
+// through an empty volatile asm right behind the wait, so no load through it can be scheduled ahead of the wait (a
+// const __restrict__ pointer otherwise invites the read-only path, whose loads count as invariant and may be hoisted
+// over the wait - where they would read what the previous step left behind).
+template <typename P>
+__device__ __forceinline__ void after_wait(P& p) {     // P: a pointer type, restrict-qualified or not
+  asm volatile("" : "+l"(p)::"memory");
+}
+template <typename P, typename... Rest>
+__device__ __forceinline__ void after_wait(P& p, Rest&... rest) {
+  after_wait(p);
+  after_wait(rest...);
+}
+
+// A word that the kernel before this one in the stream wrote (a plan table, a count): loaded by a volatile asm, which
+// the compiler keeps behind the volatile asm of pdl_wait.  The read-only path (__ldg, or a const __restrict__ pointer)
+// must not be used for such data: those loads count as invariant and may be moved ahead of the wait, where they read
+// what the previous step left behind.
+__device__ __forceinline__ int ld_dep(const int* p) {
+  int v;
+  asm volatile("ld.global.s32 %0, [%1];\n" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::); }
+
+// ---- "whoever comes last finishes the work" -----------------------------------------------------------------------
+// A CTA that has stored its part calls __syncthreads() and then ONE thread counts the CTA in with this atomic: the
+// release half publishes, at GPU scope, everything the CTA's threads stored before the barrier (release is cumulative
+// over what the barrier ordered before it); the acquire half lets the CTA that sees the last count read the other
+// CTAs' parts after its next __syncthreads().  No per-thread fence is needed.
+__device__ __forceinline__ int arrive_count(int* counter) {
+  int seen;
+  asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], 1;\n" : "=r"(seen) : "l"(counter) : "memory");
+  return seen;
+}
 
 // ---- activation epilogues (src/tensorfold/cuda/experts.cuh:57-75 states the roundings) -------------------------
 // SwiGLU on bf16-rounded gate and up: bf16(silu(g)) * u, clipped first when limit > 0; the caller rounds to bf16.

@@ -376,11 +376,14 @@ grouped_kernel(const GroupedArgs a) {
   }
   __syncwarp();
   pdl_wait();
+  const int *items = a.items, *counts = a.counts, *members = a.members;
+  const __half* xin = a.x[mat];
+  after_wait(items, counts, members, xin);
   // the item is read together with the count that says whether it exists (its slot is always inside the table)
-  const int n_items = a.counts[0];
-  const int e = a.items[3 * it], first = a.items[3 * it + 1], cnt = min(a.items[3 * it + 2], GR_PAIRS);
+  const int n_items = ld_dep(counts);
+  const int e = ld_dep(items + 3 * it), first = ld_dep(items + 3 * it + 1), cnt = min(ld_dep(items + 3 * it + 2), GR_PAIRS);
   if (it >= n_items) return;
-  if (tid < GR_PAIRS) pair_sh[tid] = tid < cnt ? a.members[first + tid] : -1;
+  if (tid < GR_PAIRS) pair_sh[tid] = tid < cnt ? ld_dep(members + first + tid) : -1;
   const uint8_t* T = reinterpret_cast<const uint8_t*>(a.tp[mat][e]);
   const int k2 = a.k2[mat][e];
   const bool two = cnt > 8;
@@ -390,8 +393,8 @@ grouped_kernel(const GroupedArgs a) {
   const __half* x[GR_PT];
 #pragma unroll
   for (int pt = 0; pt < GR_PT; ++pt) {
-    const int p = a.members[first + (8 * pt + g < cnt ? 8 * pt + g : 0)];
-    x[pt] = a.x[mat] + (size_t)p * a.K + kt0 * 16 + 2 * t;
+    const int p = ld_dep(members + first + (8 * pt + g < cnt ? 8 * pt + g : 0));
+    x[pt] = xin + (size_t)p * a.K + kt0 * 16 + 2 * t;
   }
   float acc[GR_NTB][GR_PT][4];
 #pragma unroll
@@ -445,17 +448,15 @@ grouped_kernel(const GroupedArgs a) {
   // finds every part of the block in z and runs the block's epilogue.
   const int blk = blockIdx.y >> 1;
   int* counter = a.arrive + (size_t)it * (a.N >> 7) + blk;
-  __threadfence();
   __syncthreads();
   if (tid == 0) {
     const int need = 2 * a.mats;
-    const int seen = atomicAdd(counter, 1);
+    const int seen = arrive_count(counter);
     last_sh = seen == need - 1;
     if (seen == need - 1) *counter = 0;               // nobody else touches it before the next launch
   }
   __syncthreads();
   if (!last_sh) return;
-  __threadfence();
   // a half warp a pair (the transform's shuffles need every lane of the warp: a half without a pair repeats the item's
   // first pair and stores nothing); pairs fill an item from the front, so a warp whose first pair is missing is done
   const int sub = lane & 15, half = lane >> 4;
@@ -509,11 +510,12 @@ exl3_prologue_kernel(const int* __restrict__ picks, int P, int E, int slots, int
                      const __half* __restrict__ suh1, __half* __restrict__ out0, __half* __restrict__ out1, int K) {
   extern __shared__ int whist[];
   __shared__ int first[PLAN_EMAX];
-  __shared__ int wsum[4][32];
+  __shared__ uint64_t tot2[2][PLAN_THREADS / 32];
   pdl_wait();
+  after_wait(picks, x);
   if (blockIdx.x == 0) {
     if (sort) {
-      plan_block(picks, P, E, exl3::GR_PAIRS, members, items, counts, whist, first, wsum);
+      plan_block<PLAN_THREADS>(picks, P, E, exl3::GR_PAIRS, members, items, counts, whist, first, tot2);
       if (threadIdx.x == 0) ucount[0] = counts[1];    // written by this thread inside plan_block
     }
     pdl_launch_dependents();
@@ -557,9 +559,10 @@ exl3_group_kernel(const int* __restrict__ picks, int P, int E, int slots, int* _
                   int* __restrict__ ucount, int* __restrict__ members, int maxm, int maxu) {
   extern __shared__ int whist[];
   __shared__ int first[PLAN_EMAX];
-  __shared__ int wsum[4][32];
+  __shared__ uint64_t tot2[2][PLAN_THREADS / 32];
   pdl_wait();
-  plan_block(picks, P, E, P + 1, tmp_members, tmp_items, tmp_counts, whist, first, wsum);
+  after_wait(picks);
+  plan_block<PLAN_THREADS>(picks, P, E, P + 1, tmp_members, tmp_items, tmp_counts, whist, first, tot2);
   __threadfence_block();
   __syncthreads();
   const int n = min(tmp_counts[0], maxu);

@@ -44,11 +44,22 @@ __device__ __forceinline__ void mma_bf16_zero(float (&d)[4], uint32_t a0, uint32
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.f));
 }
 
-template <int M, int NCB, int EPI, int SB, int KW, int G, int STAGES, int PT>
+// The weighted combine folded into the down projection (COMBINE): every pair p = token * slots + slot of the call is
+// in the plan; after a CTA has stored its pairs' fp32 rows it counts, per (token, column group), the slots that are
+// done; the CTA that completes a token's last slot adds that token's rows in slot order (an fp32 fma chain from 0,
+// the combine kernel's arithmetic) and stores the result row - so the layer needs no combine launch.
+struct CombineArgs {
+  const float* wts;      // [T, slots] fp32
+  void* out;             // [T, N] bf16, or fp32 when out_f32
+  int* arrive;           // [T, NB] ints, zero between launches (the kernel leaves them zero)
+  int slots, out_f32;
+};
+
+template <int M, int NCB, int EPI, int SB, int KW, int G, int STAGES, int PT, bool COMBINE = false>
 __global__ void __launch_bounds__(DEC_WARPS * 32, PT == 2 ? (M == 2 ? 4 : 1) : 5)
 decode_kernel(const __nv_bfloat16* __restrict__ X, int64_t x_stride, int slots, const uint8_t* __restrict__ W, int KG,
               int NB, const int* __restrict__ items, const int* __restrict__ counts, const int* __restrict__ members,
-              void* __restrict__ out, int N, float limit) {
+              void* __restrict__ out, int N, float limit, CombineArgs cmb) {
   static_assert(M == 1 || NCB == 1, "a warp takes two matrices of one column block, or column blocks of one matrix");
   constexpr int Q = M * NCB;
   using SM = DecodeSmem<Q, G, STAGES>;
@@ -71,11 +82,12 @@ decode_kernel(const __nv_bfloat16* __restrict__ X, int64_t x_stride, int slots, 
   __syncwarp();
 
   pdl_wait();                                         // the plan (and the inputs) come from the kernels before
+  after_wait(X, items, counts, members);
   // the item is read together with the count that says whether it exists (its slot is always inside the table)
-  const int n_items = __ldg(counts);
-  const int e = __ldg(items + 3 * it), first = __ldg(items + 3 * it + 1);
+  const int n_items = ld_dep(counts);
+  const int e = ld_dep(items + 3 * it), first = ld_dep(items + 3 * it + 1);
   constexpr int PAIRS = 8 * PT;
-  const int cnt = min(__ldg(items + 3 * it + 2), PAIRS);
+  const int cnt = min(ld_dep(items + 3 * it + 2), PAIRS);
   if (it >= n_items) return;
 
   // this warp's K run: groups [g0, g1) of column block cb
@@ -100,7 +112,7 @@ decode_kernel(const __nv_bfloat16* __restrict__ X, int64_t x_stride, int slots, 
   if (lane == 0)
     for (int c = 0; c < STAGES && c < nslot; ++c) issue(c);
 
-  if (tid < DEC_PAIRS) pair_id[tid] = tid < cnt ? __ldg(members + first + tid) : -1;
+  if (tid < DEC_PAIRS) pair_id[tid] = tid < cnt ? ld_dep(members + first + tid) : -1;
 
   // the lane's pairs (B operand column gq of each tile of 8) and their input rows
   // (lanes past the item's last pair read its first pair's row: an mma column depends on its own inputs only, and
@@ -108,7 +120,7 @@ decode_kernel(const __nv_bfloat16* __restrict__ X, int64_t x_stride, int slots, 
   const __nv_bfloat16* xrow[PT];
 #pragma unroll
   for (int pt = 0; pt < PT; ++pt) {
-    const int pr = __ldg(members + first + (8 * pt + gq < cnt ? 8 * pt + gq : 0));
+    const int pr = ld_dep(members + first + (8 * pt + gq < cnt ? 8 * pt + gq : 0));
     xrow[pt] = X + (size_t)(slots ? pr / slots : pr) * x_stride + 16 * t + (size_t)g0 * GS;
   }
 
@@ -249,6 +261,48 @@ decode_kernel(const __nv_bfloat16* __restrict__ X, int64_t x_stride, int slots, 
       static_cast<__nv_bfloat16*>(out)[at] = __float2bfloat16_rn(v[0]);
     }
   }
+  if constexpr (COMBINE) {
+    static_assert(EPI == EPI_F32 && M == 1, "the combine follows the fp32 down projection");
+    __shared__ int done[DEC_PAIRS];
+    __syncthreads();                                  // this CTA's rows before its counts
+    if (tid < PAIRS) {
+      int mine = 0;
+      if (tid < cnt) {
+        int* ctr = cmb.arrive + (size_t)(pair_id[tid] / cmb.slots) * NB + cbt;
+        const int seen = arrive_count(ctr);
+        if (seen == cmb.slots - 1) {
+          *ctr = 0;                                   // nobody else touches it before the next launch
+          mine = 1;
+        }
+      }
+      done[tid] = mine;
+    }
+    __syncthreads();
+    const float* y = static_cast<const float*>(out);
+    for (int pi = 0; pi < cnt; ++pi) {
+      if (!done[pi]) continue;                        // the same for every thread of the CTA
+      const int token = pair_id[pi] / cmb.slots;
+      for (int o = tid; o < CBC * COLS; o += DEC_WARPS * 32) {
+        const int col = cbt * (CBC * COLS) + o;
+        if (col >= N) continue;
+        const float* rows = y + (size_t)token * cmb.slots * N + col;
+        const float* w = cmb.wts + (size_t)token * cmb.slots;
+        float acc = 0.f;
+        for (int s0 = 0; s0 < cmb.slots; s0 += 8) {   // eight rows in flight, then their fma chain in slot order
+          float v[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) v[j] = s0 + j < cmb.slots ? __ldcg(rows + (size_t)(s0 + j) * N) : 0.f;
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            if (s0 + j < cmb.slots) acc = fmaf(w[s0 + j], v[j], acc);
+        }
+        if (cmb.out_f32)
+          static_cast<float*>(cmb.out)[(size_t)token * N + col] = acc;
+        else
+          static_cast<__nv_bfloat16*>(cmb.out)[(size_t)token * N + col] = __float2bfloat16_rn(acc);
+      }
+    }
+  }
 }
 
 // SMs of the current device (looked up once a device)
@@ -269,17 +323,17 @@ __host__ __device__ inline int decode_kslices(int kg) { return kg >= 32 ? 4 : kg
 
 // DEEP: a grid of at most three CTAs an SM (a few tokens) is bound by the latency of a warp's own stream, not by how
 // many CTAs share an SM: four slots put a K slice of eight groups in flight at once.
-template <int M, int EPI, int SB, int KW, int PT, bool DEEP>
+template <int M, int EPI, int SB, int KW, int PT, bool DEEP, bool COMBINE>
 int launch_decode_kw(const void* x, int64_t x_stride, int slots, const void* w, int kg, int nb, const int* items,
                      const int* counts, const int* members, void* out, int n, float limit, int64_t max_items,
-                     cudaStream_t stream) {
+                     cudaStream_t stream, CombineArgs cmb) {
   // two groups a slot, two slots a warp (9.2 KB); gate/up items of 16 pairs keep more registers a thread, so fewer
   // CTAs share an SM (4, by the launch bounds) and each gets a third slot
   constexpr int G = 2;
   constexpr int STAGES = DEEP ? 4 : M == 2 && PT == 2 ? 3 : 2;
   constexpr int NCB = M == 1 ? 2 : 1;                 // one matrix: a warp shares its inputs between two column blocks
   using SM = DecodeSmem<M * NCB, G, STAGES>;
-  auto* kern = decode_kernel<M, NCB, EPI, SB, KW, G, STAGES, PT>;
+  auto* kern = decode_kernel<M, NCB, EPI, SB, KW, G, STAGES, PT, COMBINE>;
   static_assert(SM::TOTAL <= (DEEP ? 75 : M == 2 && PT == 2 ? 56 : 48) * 1024, "the decode kernel's shared memory lets 3, 4 or 5 CTAs share an SM");
   if constexpr (SM::TOTAL > 48 * 1024) {
     static bool configured[64] = {false};
@@ -297,41 +351,41 @@ int launch_decode_kw(const void* x, int64_t x_stride, int slots, const void* w, 
   if (grid >= (int64_t(1) << 31)) return fail(TFB_ERR_ARG, "experts_run: too many units");
   return check_cuda(launch(kern, dim3((unsigned)grid), dim3(DEC_WARPS * 32), (size_t)SM::TOTAL, stream,
                            static_cast<const __nv_bfloat16*>(x), x_stride, slots, static_cast<const uint8_t*>(w), kg,
-                           nb, items, counts, members, out, n, limit),
+                           nb, items, counts, members, out, n, limit, cmb),
                     "experts_run");
 }
 
-template <int M, int EPI, int SB, int PT>
+template <int M, int EPI, int SB, int PT, bool COMBINE = false>
 int launch_decode(const void* x, int64_t x_stride, int slots, const void* w, int kg, int nb, const int* items,
                   const int* counts, const int* members, void* out, int n, float limit, int64_t max_items,
-                  cudaStream_t stream) {
+                  cudaStream_t stream, CombineArgs cmb = CombineArgs{nullptr, nullptr, nullptr, 0, 0}) {
   const int kw = decode_kslices(kg);
   if constexpr (PT == 1) {
     const int cbc = DEC_WARPS / kw * (M == 1 ? 2 : 1);
     if (max_items * ((nb + cbc - 1) / cbc) <= 3 * sm_count()) {
       switch (kw) {
         case 4:
-          return launch_decode_kw<M, EPI, SB, 4, PT, true>(x, x_stride, slots, w, kg, nb, items, counts, members, out,
-                                                           n, limit, max_items, stream);
+          return launch_decode_kw<M, EPI, SB, 4, PT, true, COMBINE>(x, x_stride, slots, w, kg, nb, items, counts, members, out,
+                                                           n, limit, max_items, stream, cmb);
         case 2:
-          return launch_decode_kw<M, EPI, SB, 2, PT, true>(x, x_stride, slots, w, kg, nb, items, counts, members, out,
-                                                           n, limit, max_items, stream);
+          return launch_decode_kw<M, EPI, SB, 2, PT, true, COMBINE>(x, x_stride, slots, w, kg, nb, items, counts, members, out,
+                                                           n, limit, max_items, stream, cmb);
         default:
-          return launch_decode_kw<M, EPI, SB, 1, PT, true>(x, x_stride, slots, w, kg, nb, items, counts, members, out,
-                                                           n, limit, max_items, stream);
+          return launch_decode_kw<M, EPI, SB, 1, PT, true, COMBINE>(x, x_stride, slots, w, kg, nb, items, counts, members, out,
+                                                           n, limit, max_items, stream, cmb);
       }
     }
   }
   switch (kw) {
     case 4:
-      return launch_decode_kw<M, EPI, SB, 4, PT, false>(x, x_stride, slots, w, kg, nb, items, counts, members, out, n,
-                                                        limit, max_items, stream);
+      return launch_decode_kw<M, EPI, SB, 4, PT, false, COMBINE>(x, x_stride, slots, w, kg, nb, items, counts, members, out, n,
+                                                        limit, max_items, stream, cmb);
     case 2:
-      return launch_decode_kw<M, EPI, SB, 2, PT, false>(x, x_stride, slots, w, kg, nb, items, counts, members, out, n,
-                                                        limit, max_items, stream);
+      return launch_decode_kw<M, EPI, SB, 2, PT, false, COMBINE>(x, x_stride, slots, w, kg, nb, items, counts, members, out, n,
+                                                        limit, max_items, stream, cmb);
     default:
-      return launch_decode_kw<M, EPI, SB, 1, PT, false>(x, x_stride, slots, w, kg, nb, items, counts, members, out, n,
-                                                        limit, max_items, stream);
+      return launch_decode_kw<M, EPI, SB, 1, PT, false, COMBINE>(x, x_stride, slots, w, kg, nb, items, counts, members, out, n,
+                                                        limit, max_items, stream, cmb);
   }
 }
 
@@ -389,4 +443,37 @@ extern "C" int tfb_experts_run_tile(int gs, int epi, const void* x, int64_t x_st
                                     void* stream) {
   return experts_run(gs, epi, x, x_stride, slots, w, kg, nb, items, counts, members, out, n, limit, max_units, sb_type,
                      tile, stream);
+}
+
+// The down projection and the weighted combine in one launch: y [P, n] fp32 per pair as tfb_experts_run_tile with
+// epilogue 0 (x = act [P, K] bf16, one row a pair), and out [T, n] (bf16, or fp32 when out_f32) = sum over a token's
+// slots in slot order of wts[t, s] * y[t * slots + s, :], formed by the CTA that stores the token's last row.  Every
+// pair t * slots + s of the T tokens must be in the plan.  arrive: int scratch [T, nb], zero before the first call (a
+// call leaves it zero).  (src/tensorfold/cuda/experts.py:141-150 `down` then src/tensorfold/cuda/moe.py:131-151 `combine`)
+extern "C" int tfb_experts_down_combine(int gs, const void* x, int64_t x_stride, const void* w, int kg, int nb,
+                                        const int32_t* items, const int32_t* counts, const int32_t* members, float* y,
+                                        int n, int64_t max_units, int sb_type, int tile, const float* wts, int slots,
+                                        void* out, int out_f32, int32_t* arrive, void* stream) {
+  TFB_REQUIRE(gs == GS, "experts_down_combine: groups of %d inputs only, not %d", GS, gs);
+  TFB_REQUIRE(x && w && items && counts && members && y && wts && out && arrive, "experts_down_combine: null pointer");
+  TFB_REQUIRE(kg >= 1 && nb >= 1 && n == nb * COLS, "experts_down_combine: n must be the column blocks times %d", COLS);
+  TFB_REQUIRE(aligned16(x) && x_stride % 8 == 0 && x_stride >= (int64_t)kg * GS,
+              "experts_down_combine: x rows of K = groups * group size inputs, 16-byte aligned");
+  TFB_REQUIRE(aligned16(w), "experts_down_combine: w must be 16-byte aligned");
+  TFB_REQUIRE(slots >= 1 && max_units >= 0 && max_units < (int64_t(1) << 31), "experts_down_combine: bad slots or unit count");
+  TFB_REQUIRE(sb_type == SB_BF16 || sb_type == SB_FP16, "experts_down_combine: scales are bf16 (0) or fp16 (1), not %d",
+              sb_type);
+  TFB_REQUIRE(tile == 8 || tile == 16, "experts_down_combine: items of 8 or 16 pairs, not %d", tile);
+  const int64_t max_items = (max_units + nb - 1) / nb;
+  if (max_items == 0) return TFB_OK;
+  auto st = static_cast<cudaStream_t>(stream);
+  const CombineArgs cmb{wts, out, arrive, slots, out_f32 ? 1 : 0};
+#define TFB_DC(SB_)                                                                                                  \
+  return tile == 8 ? launch_decode<1, EPI_F32, SB_, 1, true>(x, x_stride, 0, w, kg, nb, items, counts, members, y, n, \
+                                                             0.f, max_items, st, cmb)                                \
+                   : launch_decode<1, EPI_F32, SB_, 2, true>(x, x_stride, 0, w, kg, nb, items, counts, members, y, n, \
+                                                             0.f, max_items, st, cmb)
+  if (sb_type == SB_BF16) TFB_DC(SB_BF16);
+  TFB_DC(SB_FP16);
+#undef TFB_DC
 }

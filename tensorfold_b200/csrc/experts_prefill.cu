@@ -160,15 +160,16 @@ prefill_kernel(const __nv_bfloat16* __restrict__ X, int64_t x_stride, int slots,
     fence_async_smem();
   }
   pdl_wait();
-  const bool live = it < __ldg(counts);          // uniform over the CTA
+  after_wait(X, items, counts, members);
+  const bool live = it < ld_dep(counts);          // uniform over the CTA
   constexpr uint32_t TMEM_COLS = 512;
   if (live && warp == PF_MMA_WARP) tmem_alloc(tmem_slot, TMEM_COLS);
   int e = 0, first = 0, cnt = 0;
   if (live) {
-    e = __ldg(items + 3 * it);
-    first = __ldg(items + 3 * it + 1);
-    cnt = min(__ldg(items + 3 * it + 2), PF_MAXP);
-    for (int i = tid; i < PF_MAXP; i += PF_THREADS) out_row[i] = i < cnt ? __ldg(members + first + i) : -1;
+    e = ld_dep(items + 3 * it);
+    first = ld_dep(items + 3 * it + 1);
+    cnt = min(ld_dep(items + 3 * it + 2), PF_MAXP);
+    for (int i = tid; i < PF_MAXP; i += PF_THREADS) out_row[i] = i < cnt ? ld_dep(members + first + i) : -1;
   }
   tc_fence_before();
   __syncthreads();

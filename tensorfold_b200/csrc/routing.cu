@@ -35,6 +35,7 @@ router_kernel(const __nv_bfloat16* __restrict__ X, int64_t x_stride, const __nv_
 #pragma unroll
     for (int e = 0; e < R_ET; ++e) acc[r][e] = 0.f;
   pdl_wait();
+  after_wait(X);
   // the next chunk's twelve 16-byte loads travel while this chunk's 256 fmas run
   const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
   uint4 wn[R_ET], xn[R_RT];
@@ -98,6 +99,7 @@ router_rows_kernel(const __nv_bfloat16* __restrict__ X, int64_t x_stride, const 
   for (int i = 0; i < RPW; ++i) acc[i] = 0.f;
   const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
   pdl_wait();
+  after_wait(X);
   for (int kb = 0; kb < D; kb += 256 * RR_CH) {
     float wv[RR_CH][8];
 #pragma unroll
@@ -163,7 +165,7 @@ __device__ __forceinline__ int select_row(const float* __restrict__ Lr, int E, i
 #pragma unroll
   for (int i = 0; i < VPL; ++i) {
     const int e = i * 32 + lane;
-    key[i] = e < E ? order_key(Lr[e]) : 0u;
+    key[i] = e < E ? order_key(__ldcg(Lr + e)) : 0u;      // L2: another CTA of this launch may have written it
   }
   float top = 0.f, total = 0.f, my_ex = 0.f;
   int my_pick = -1;
@@ -194,7 +196,7 @@ __device__ __forceinline__ int select_row(const float* __restrict__ Lr, int E, i
     pick_row[lane] = my_pick;
     wts_row[lane] = round_bf16(my_ex / total);
   } else if (lane == top_k && shared) {
-    const float sg = round_bf16(Lr[E]);
+    const float sg = round_bf16(__ldcg(Lr + E));
     my_pick = E;
     pick_row[lane] = E;
     wts_row[lane] = round_bf16(1.f / (1.f + expf(-sg)));
@@ -210,6 +212,7 @@ select_kernel(const float* __restrict__ L, int NL, int* __restrict__ pick, float
   const int r = blockIdx.x * S_WARPS + (threadIdx.x >> 5);
   if (r >= T) return;
   pdl_wait();
+  after_wait(L);
   const int slots = top_k + (shared ? 1 : 0);
   select_row<VPL>(L + (size_t)r * NL, E, top_k, shared, lane, pick + (size_t)r * slots, wts + (size_t)r * slots);
   pdl_launch_dependents();
@@ -227,6 +230,7 @@ select_sigmoid_kernel(const float* __restrict__ L, int NL, const float* __restri
   const int r = blockIdx.x * S_WARPS + (threadIdx.x >> 5);
   if (r >= T) return;
   pdl_wait();
+  after_wait(L);
   const int slots = top_k + shared;
   const float* Lr = L + (size_t)r * NL;
   uint32_t key[VPL];
@@ -294,67 +298,48 @@ struct PlanSplit {
   int* counts;       // [2]: its items, its distinct experts
 };
 
-__device__ int place_items(int c, int E, int T, int* __restrict__ items, int* __restrict__ counts,
-                           int (*wsum)[32], PlanSplit sp) {
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const bool big = c >= sp.hot;
-  const int tiles = big ? 0 : (c + T - 1) / T;
-  const int btiles = big ? (c + sp.Tb - 1) / sp.Tb : 0;
-  int a = c, b = tiles, u = (c > 0 && !big) ? 1 : 0, bb = btiles | ((big ? 1 : 0) << 20);   // items and experts in one scan
+// Exclusive prefix over the NT threads of a block, of two packed 64-bit values a thread; sum_* = the block's totals.
+// tot: [2][NT / 32] in shared memory.  Every thread of the block calls it.
+template <int NT>
+__device__ __forceinline__ void block_prefix2(uint64_t& a, uint64_t& b, uint64_t (*tot)[NT / 32], uint64_t& sum_a,
+                                              uint64_t& sum_b) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  uint64_t ia = a, ib = b;
 #pragma unroll
   for (int o = 1; o < 32; o <<= 1) {
-    const int ua = __shfl_up_sync(0xffffffffu, a, o), ub = __shfl_up_sync(0xffffffffu, b, o);
-    const int uu = __shfl_up_sync(0xffffffffu, u, o), ubb = __shfl_up_sync(0xffffffffu, bb, o);
+    const uint64_t ua = __shfl_up_sync(0xffffffffu, ia, o), ub = __shfl_up_sync(0xffffffffu, ib, o);
     if (lane >= o) {
-      a += ua;
-      b += ub;
-      u += uu;
-      bb += ubb;
+      ia += ua;
+      ib += ub;
     }
   }
   if (lane == 31) {
-    wsum[0][warp] = a;
-    wsum[1][warp] = b;
-    wsum[2][warp] = u;
-    wsum[3][warp] = bb;
+    tot[0][warp] = ia;
+    tot[1][warp] = ib;
   }
   __syncthreads();
-  if (warp < 4) {
-    int vv = wsum[warp][lane];
+  if (warp == 0) {                                   // the warps' totals become their inclusive prefix, in place
+    uint64_t ta = lane < NT / 32 ? tot[0][lane] : 0, tb = lane < NT / 32 ? tot[1][lane] : 0;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
-      const int w = __shfl_up_sync(0xffffffffu, vv, o);
-      if (lane >= o) vv += w;
+      const uint64_t ua = __shfl_up_sync(0xffffffffu, ta, o), ub = __shfl_up_sync(0xffffffffu, tb, o);
+      if (lane >= o) {
+        ta += ua;
+        tb += ub;
+      }
     }
-    wsum[warp][lane] = vv;
+    if (lane < NT / 32) {
+      tot[0][lane] = ta;
+      tot[1][lane] = tb;
+    }
   }
   __syncthreads();
-  const int off = (warp ? wsum[0][warp - 1] : 0) + a - c;
-  const int ioff = (warp ? wsum[1][warp - 1] : 0) + b - tiles;
-  const int boff = (((warp ? wsum[3][warp - 1] : 0) + bb) & 0xFFFFF) - btiles;
-  if (tid == 0) {
-    counts[0] = wsum[1][31];
-    counts[1] = wsum[2][31];
-    if (sp.counts != nullptr) {
-      sp.counts[0] = wsum[3][31] & 0xFFFFF;
-      sp.counts[1] = wsum[3][31] >> 20;
-    }
-  }
-  if (tid < E) {
-    for (int j = 0; j < tiles; ++j) {
-      int* it = items + 3 * (ioff + j);
-      it[0] = tid;
-      it[1] = off + T * j;
-      it[2] = min(T, c - T * j);
-    }
-    for (int j = 0; j < btiles; ++j) {
-      int* it = sp.items + 3 * (boff + j);
-      it[0] = tid;
-      it[1] = off + sp.Tb * j;
-      it[2] = min(sp.Tb, c - sp.Tb * j);
-    }
-  }
-  return off;
+  const uint64_t base_a = warp ? tot[0][warp - 1] : 0, base_b = warp ? tot[1][warp - 1] : 0;
+  sum_a = tot[0][NT / 32 - 1];
+  sum_b = tot[1][NT / 32 - 1];
+  a = base_a + ia - a;
+  b = base_b + ib - b;
+  __syncthreads();                                   // tot is free again
 }
 
 // The lanes of the warp whose key equals this lane's (keys < 2^nbits; lanes with ok == false match nobody): one ballot
@@ -369,19 +354,30 @@ __device__ __forceinline__ unsigned same_key_lanes(int e, bool ok, int nbits) {
   return ok ? m : 0u;
 }
 
-// The whole block: `picks` may live in global or shared memory.
-// With `tot` (a cluster launch: `nparts` blocks, this one `part`) the pairs are cut into nparts * 32 runs; each block
-// counts its runs, the blocks read one another's per-expert totals through distributed shared memory, and each
-// scatters its own runs.  The tables are the same as one block's.
+template <bool CG>
+__device__ __forceinline__ int load_pick(const int* p) {
+  if constexpr (CG) return __ldcg(p);                // written by other CTAs of this launch: read it in L2
+  else return *p;
+}
+
+// The whole block of NT threads: `picks` may live in global or shared memory (CG: global, written earlier in the same
+// launch).  Each of the NT / 32 warps owns a contiguous run of pairs, counts them per expert (whist [NT / 32][E]), a
+// prefix over the warps and over the experts (in turns of NT experts) gives every (warp, expert) its first slot, and
+// a second walk scatters.  first: [E]; tot2: [2][NT / 32]; all in shared memory.
+// With `ctot` (a cluster launch: `nparts` blocks, this one `part`; E <= NT) the pairs are cut into nparts * NT / 32
+// runs; each block counts its runs, the blocks read one another's per-expert totals through distributed shared memory,
+// and each scatters its own runs.  The tables are the same as one block's.
+template <int NT, bool CG = false>
 __device__ void plan_block(const int* picks, int P, int E, int T, int* __restrict__ members, int* __restrict__ items,
-                           int* __restrict__ counts, int* whist, int* first, int (*wsum)[32], int lo = 0,
-                           PlanSplit sp = PlanSplit{0x7FFFFFFF, 1, nullptr, nullptr}, int* tot = nullptr,
+                           int* __restrict__ counts, int* whist, int* first, uint64_t (*tot2)[NT / 32], int lo = 0,
+                           PlanSplit sp = PlanSplit{0x7FFFFFFF, 1, nullptr, nullptr}, int* ctot = nullptr,
                            int part = 0, int nparts = 1) {
+  constexpr int NWARP = NT / 32;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  for (int i = tid; i < 32 * E; i += PLAN_THREADS) whist[i] = 0;
-  const int runs = 32 * nparts;
+  for (int i = tid; i < NWARP * E; i += NT) whist[i] = 0;
+  const int runs = NWARP * nparts;
   const int seg = (((P + runs - 1) / runs + 31) / 32) * 32;
-  const int p0 = (int)min((int64_t)P, (int64_t)(part * 32 + warp) * seg), p1 = min(P, p0 + seg);
+  const int p0 = (int)min((int64_t)P, (int64_t)(part * NWARP + warp) * seg), p1 = min(P, p0 + seg);
   int* mine = whist + warp * E;
   const int nbits = 32 - __clz(max(E - 1, 0));
   __syncthreads();
@@ -390,7 +386,7 @@ __device__ void plan_block(const int* picks, int P, int E, int T, int* __restric
 #pragma unroll
     for (int i = 0; i < PLAN_BATCH; ++i) {
       const int p = base0 + 32 * i + lane;
-      ev[i] = p < p1 ? picks[p] - lo : -1;
+      ev[i] = p < p1 ? load_pick<CG>(picks + p) - lo : -1;
     }
 #pragma unroll
     for (int i = 0; i < PLAN_BATCH; ++i) {
@@ -403,37 +399,77 @@ __device__ void plan_block(const int* picks, int P, int E, int T, int* __restric
     }
   }
   __syncthreads();
-  int c = 0;
-  if (tid < E)
-    for (int w = 0; w < 32; ++w) {
-      const int v = whist[w * E + tid];
-      whist[w * E + tid] = c;
-      c += v;
-    }
-  int before = 0;                                    // pairs of this expert in the blocks before this one
-  if (tot != nullptr) {
-    namespace cg = cooperative_groups;
-    cg::cluster_group cluster = cg::this_cluster();
-    if (tid < E) tot[tid] = c;
-    cluster.sync();
-    if (tid < E) {
-      c = 0;
-      for (int r = 0; r < nparts; ++r) {
-        const int v = cluster.map_shared_rank(tot, r)[tid];
-        if (r < part) before += v;
+  // experts in turns of NT: an expert's pairs, items and (for a split plan) hot items get their first slots from a
+  // prefix over the experts; two packed words: A = pairs | items << 32, B = experts in use | hot items << 16 | hot
+  // experts << 48
+  uint64_t carry_a = 0, carry_b = 0;
+  for (int e0 = 0; e0 < E; e0 += NT) {
+    const int e = e0 + tid;
+    const bool live = e < E;
+    int c = 0;
+    if (live)
+      for (int w = 0; w < NWARP; ++w) {
+        const int v = whist[w * E + e];
+        whist[w * E + e] = c;
         c += v;
       }
+    int before = 0;                                  // pairs of this expert in the blocks before this one
+    if (ctot != nullptr) {
+      namespace cg = cooperative_groups;
+      cg::cluster_group cluster = cg::this_cluster();
+      if (live) ctot[e] = c;
+      cluster.sync();
+      if (live) {
+        c = 0;
+        for (int r = 0; r < nparts; ++r) {
+          const int v = cluster.map_shared_rank(ctot, r)[e];
+          if (r < part) before += v;
+          c += v;
+        }
+      }
+    }
+    const bool hot = c >= sp.hot;
+    const int n_items = hot ? 0 : (c + T - 1) / T, n_hot = hot ? (c + sp.Tb - 1) / sp.Tb : 0;
+    uint64_t a = (uint64_t)(uint32_t)c | ((uint64_t)(uint32_t)n_items << 32);
+    uint64_t b = (uint64_t)(c > 0 && !hot ? 1u : 0u) | ((uint64_t)(uint32_t)n_hot << 16) | ((uint64_t)(hot ? 1u : 0u) << 48);
+    uint64_t sum_a, sum_b;
+    block_prefix2<NT>(a, b, tot2, sum_a, sum_b);
+    a += carry_a;
+    b += carry_b;
+    if (live) {
+      const int at = (int)(uint32_t)a, item0 = (int)(a >> 32), hot0 = (int)((b >> 16) & 0xFFFFFFFFu);
+      first[e] = at + before;                        // every block of a cluster writes the same tables
+      for (int j = 0; j < n_items; ++j) {
+        int* it = items + 3 * (item0 + j);
+        it[0] = e;
+        it[1] = at + T * j;
+        it[2] = min(T, c - T * j);
+      }
+      for (int j = 0; j < n_hot; ++j) {
+        int* it = sp.items + 3 * (hot0 + j);
+        it[0] = e;
+        it[1] = at + sp.Tb * j;
+        it[2] = min(sp.Tb, c - sp.Tb * j);
+      }
+    }
+    carry_a += sum_a;
+    carry_b += sum_b;
+  }
+  if (tid == 0) {
+    counts[0] = (int)(carry_a >> 32);
+    counts[1] = (int)(carry_b & 0xFFFFu);
+    if (sp.counts != nullptr) {
+      sp.counts[0] = (int)((carry_b >> 16) & 0xFFFFFFFFu);
+      sp.counts[1] = (int)(carry_b >> 48);
     }
   }
-  const int off = place_items(c, E, T, items, counts, wsum, sp);      // every block writes the same tables
-  if (tid < E) first[tid] = off + before;
   __syncthreads();
   for (int base0 = p0; base0 < p1; base0 += 32 * PLAN_BATCH) {
     int ev[PLAN_BATCH];
 #pragma unroll
     for (int i = 0; i < PLAN_BATCH; ++i) {
       const int p = base0 + 32 * i + lane;
-      ev[i] = p < p1 ? picks[p] - lo : -1;
+      ev[i] = p < p1 ? load_pick<CG>(picks + p) - lo : -1;
     }
 #pragma unroll
     for (int i = 0; i < PLAN_BATCH; ++i) {
@@ -456,9 +492,10 @@ plan_kernel(const int* __restrict__ picks, int P, int E, int T, int* __restrict_
             int* __restrict__ counts, int lo, PlanSplit sp) {
   extern __shared__ int whist[];                 // [32][E]: pairs of expert e in warp w's run, then their first slot
   __shared__ int first[PLAN_EMAX];
-  __shared__ int wsum[4][32];
+  __shared__ uint64_t tot2[2][PLAN_THREADS / 32];
   pdl_wait();
-  plan_block(picks, P, E, T, members, items, counts, whist, first, wsum, lo, sp);
+  after_wait(picks);
+  plan_block<PLAN_THREADS>(picks, P, E, T, members, items, counts, whist, first, tot2, lo, sp);
   pdl_launch_dependents();
 }
 
@@ -471,9 +508,11 @@ plan_cluster_kernel(const int* __restrict__ picks, int P, int E, int T, int* __r
   extern __shared__ int whist[];
   __shared__ int first[PLAN_EMAX];
   __shared__ int tot[PLAN_EMAX];
-  __shared__ int wsum[4][32];
+  __shared__ uint64_t tot2[2][PLAN_THREADS / 32];
   pdl_wait();
-  plan_block(picks, P, E, T, members, items, counts, whist, first, wsum, lo, sp, tot, (int)blockIdx.x, PLAN_CLUSTER);
+  after_wait(picks);
+  plan_block<PLAN_THREADS>(picks, P, E, T, members, items, counts, whist, first, tot2, lo, sp, tot, (int)blockIdx.x,
+                           PLAN_CLUSTER);
   cooperative_groups::this_cluster().sync();          // no block leaves while another may still read its totals
   pdl_launch_dependents();
 }
@@ -487,19 +526,91 @@ select_plan_kernel(const float* __restrict__ L, int NL, int* __restrict__ pick, 
                    int* __restrict__ counts, int plan_lo, int plan_n) {
   extern __shared__ int dyn[];                   // whist [32][NP], then the picks [T * slots]
   __shared__ int first[PLAN_EMAX];
-  __shared__ int wsum[4][32];
+  __shared__ uint64_t tot2[2][PLAN_THREADS / 32];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int slots = top_k + (shared ? 1 : 0);
   int* picks_sh = dyn + 32 * plan_n;
   pdl_wait();
+  after_wait(L);
   for (int r = warp; r < T; r += PLAN_THREADS / 32) {
     const int mine = select_row<VPL>(L + (size_t)r * NL, E, top_k, shared, lane, pick + (size_t)r * slots,
                                      wts + (size_t)r * slots);
     if (lane < slots) picks_sh[r * slots + lane] = mine;
   }
   __syncthreads();
-  plan_block(picks_sh, T * slots, plan_n, tile, members, items, counts, dyn, first, wsum, plan_lo);
+  plan_block<PLAN_THREADS>(picks_sh, T * slots, plan_n, tile, members, items, counts, dyn, first, tot2, plan_lo);
   pdl_launch_dependents();
+}
+
+// ================================================================================================================
+// A few rows: router, selection and plan in ONE launch.  CTA (expert, eight rows) computes its logits exactly as
+// router_rows_kernel does; the CTA that completes a group of eight rows (counted with an atomic) selects those rows,
+// a warp a row; the CTA that completes the last group makes the plan.  Results equal the three kernels' bit for bit.
+// arrive: [1 + row groups] ints, zero between launches (the kernel leaves them zero).
+// ================================================================================================================
+constexpr int ROUTE_THREADS = RR_WARPS * 32;
+
+template <int VPL>
+__global__ void __launch_bounds__(ROUTE_THREADS)
+route_kernel(const __nv_bfloat16* __restrict__ X, int64_t x_stride, const __nv_bfloat16* __restrict__ W,
+             float* __restrict__ logits, int T, int D, int NE, int E, int top_k, int shared, int* __restrict__ pick,
+             float* __restrict__ wts, int tile, int* __restrict__ members, int* __restrict__ items,
+             int* __restrict__ counts, int plan_lo, int plan_n, int* __restrict__ arrive) {
+  static_assert(RR_ROWS == RR_WARPS, "a warp a row, in the router and in the selection");
+  extern __shared__ int dyn[];                       // the plan's: whist [RR_WARPS][plan_n], first [plan_n]
+  __shared__ uint64_t tot2[2][ROUTE_THREADS / 32];
+  __shared__ int last;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int e = blockIdx.x, group = blockIdx.y, r = group * RR_ROWS + warp;
+  const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+  pdl_wait();
+  after_wait(X);
+  float acc = 0.f;
+  for (int kb = 0; kb < D; kb += 256 * RR_CH) {
+    float wv[RR_CH][8];
+    uint4 xv[RR_CH];
+#pragma unroll
+    for (int c = 0; c < RR_CH; ++c) {
+      const int k = kb + 256 * c + 8 * lane;
+      unpack8(k < D ? ldg_nc(W + (size_t)e * D + k) : zero, wv[c]);
+      xv[c] = (k < D && r < T) ? ldg_nc(X + (size_t)r * x_stride + k) : zero;
+    }
+#pragma unroll
+    for (int c = 0; c < RR_CH; ++c) {
+      if (kb + 256 * c + 8 * lane < D) {
+        float xf[8];
+        unpack8(xv[c], xf);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc = fmaf(xf[j], wv[c][j], acc);
+      }
+    }
+  }
+  pdl_launch_dependents();
+#pragma unroll
+  for (int m = 16; m >= 1; m >>= 1) acc = acc + __shfl_xor_sync(0xffffffffu, acc, m);
+  if (lane == 0 && r < T) logits[(size_t)r * NE + e] = acc;
+  // ---- the CTA that finishes a row group selects its rows ----
+  __syncthreads();
+  if (tid == 0) {
+    const int seen = arrive_count(arrive + 1 + group);
+    last = seen == NE - 1;
+    if (seen == NE - 1) arrive[1 + group] = 0;
+  }
+  __syncthreads();
+  if (!last) return;
+  const int slots = top_k + (shared ? 1 : 0);
+  if (r < T) select_row<VPL>(logits + (size_t)r * NE, E, top_k, shared, lane, pick + (size_t)r * slots, wts + (size_t)r * slots);
+  // ---- the CTA that finishes the last row group plans ----
+  __syncthreads();
+  if (tid == 0) {
+    const int seen = arrive_count(arrive);
+    last = seen == (int)gridDim.y - 1;
+    if (seen == (int)gridDim.y - 1) arrive[0] = 0;
+  }
+  __syncthreads();
+  if (!last) return;
+  plan_block<ROUTE_THREADS, true>(pick, T * slots, plan_n, tile, members, items, counts, dyn, dyn + RR_WARPS * plan_n,
+                                  tot2, plan_lo);
 }
 
 // ================================================================================================================
@@ -515,6 +626,7 @@ combine_kernel(const TY* __restrict__ y, const float* __restrict__ wts, TO* __re
   const int d = (blockIdx.y * 256 + threadIdx.x) * 4;
   if (d >= D) return;
   pdl_wait();
+  after_wait(y, wts);
   float acc[4] = {0.f, 0.f, 0.f, 0.f};
   for (int s = 0; s < S; ++s) {
     if (pick != nullptr) {
@@ -748,6 +860,45 @@ extern "C" int tfb_select_plan_window(const float* logits, int NL, int32_t* pick
                                       int32_t* counts, void* stream) {
   return select_plan_launch(logits, NL, pick, wts, T, E, top_k, shared, tile, plan_lo, plan_n, members, items, counts,
                             stream);
+}
+
+// Rows the one-launch router + selection + plan takes: the row-form router's range (rows x router rows <= 8704).
+extern "C" int tfb_route_max_rows(int NE) { return NE >= 1 ? (8704 / NE < 256 ? 8704 / NE : 256) : 0; }
+
+// tfb_router, tfb_select_rows and tfb_plan_window of a few rows in one launch (the same bits): logits [T, NE] fp32 from
+// x [T, D] and rows [NE, D] (NE = E + 1 with the shared expert's gate row), pick / wts [T, slots], and the plan of the
+// ids in [plan_lo, plan_lo + plan_n).  arrive: int scratch [1 + (T + 7) / 8], zero before the first call (a call leaves
+// it zero).  T <= tfb_route_max_rows(NE).
+extern "C" int tfb_route(const void* x, int64_t x_stride, const void* rows, float* logits, int T, int D, int NE, int E,
+                         int top_k, int shared, int32_t* pick, float* wts, int tile, int plan_lo, int plan_n,
+                         int32_t* members, int32_t* items, int32_t* counts, int32_t* arrive, void* stream) {
+  TFB_REQUIRE(x && rows && logits && pick && wts && members && items && counts && arrive, "route: null pointer");
+  TFB_REQUIRE(D > 0 && D % 8 == 0 && x_stride % 8 == 0 && x_stride >= D, "route: D and the row stride must be multiples of 8");
+  TFB_REQUIRE(aligned16(x) && aligned16(rows), "route: x and rows must be 16-byte aligned");
+  const int NP = E + (shared ? 1 : 0);
+  TFB_REQUIRE(E >= 1 && NP <= PLAN_EMAX && NE >= NP, "route: %d router rows cannot hold %d experts%s", NE, E,
+              shared ? " and the shared gate" : "");
+  TFB_REQUIRE(top_k >= 1 && top_k <= E && top_k <= 31, "route: top_k=%d must be 1..min(E, 31)", top_k);
+  TFB_REQUIRE(plan_lo >= 0 && plan_n >= 1 && plan_lo + plan_n <= NP, "route: the plan window [%d, %d) leaves the %d experts",
+              plan_lo, plan_lo + plan_n, NP);
+  TFB_REQUIRE(tile >= 1, "route: items hold at least one pair");
+  TFB_REQUIRE(T >= 0 && T <= tfb_route_max_rows(NE), "route: at most %d rows of %d router rows, not %d",
+              tfb_route_max_rows(NE), NE, T);
+  if (T == 0) return TFB_OK;
+  const dim3 grid(NE, (T + RR_ROWS - 1) / RR_ROWS);
+  const size_t smem = sizeof(int) * (size_t)(RR_WARPS + 1) * plan_n;
+  auto st = static_cast<cudaStream_t>(stream);
+  const int vpl = (E + 31) / 32;
+#define TFB_ROUTE(V)                                                                                              \
+  return check_cuda(launch(route_kernel<V>, grid, dim3(ROUTE_THREADS), smem, st, static_cast<const __nv_bfloat16*>(x), \
+                           x_stride, static_cast<const __nv_bfloat16*>(rows), logits, T, D, NE, E, top_k,           \
+                           shared ? 1 : 0, pick, wts, tile, members, items, counts, plan_lo, plan_n, arrive),     \
+                    "route")
+  if (vpl <= 4) TFB_ROUTE(4);
+  if (vpl <= 8) TFB_ROUTE(8);
+  if (vpl <= 16) TFB_ROUTE(16);
+  TFB_ROUTE(32);
+#undef TFB_ROUTE
 }
 
 static int combine_launch(const void* y, int y_bf16, const float* wts, void* out, int out_f32, int T, int slots, int D,

@@ -254,3 +254,32 @@ def down(act: torch.Tensor, ex: Experts, plan: Plan, out: torch.Tensor, rows: in
     if plan.hot:
         big = max_items(rows * plan.slots, plan.experts, PREFILL_TILE)
         _run(epi, act, 0, ex.down, ex.width // ex.gs, ex.dims // COLS, _BigPart(plan), out, ex.dims, 0.0, big, ex, True)
+
+
+def down_combine(act: torch.Tensor, ex: Experts, plan: Plan, y: torch.Tensor, rows: int, wts: torch.Tensor,
+                 out: torch.Tensor, arrive: torch.Tensor) -> None:
+    """``down`` (decode form) and the slot-order weighted combine in one launch: y [R * slots, D] fp32 per pair as
+    ``down`` stores it, and out [R, D] (bf16 or fp32) = the sum over each row's slots of wts * y, formed by whichever
+    block stores a row's last slot.  Every (row, slot) pair must be in the plan; ``arrive`` is int32 scratch
+    [R, D / 32], zero before the first call (a call leaves it zero)."""
+
+    if plan.prefill or plan.hot:
+        raise ValueError("the fused combine follows the decode form of a plain plan")
+    if y.dtype != torch.float32 or not y.is_contiguous() or y.shape[-1] != ex.dims:
+        raise ValueError("y: contiguous fp32 rows of D columns")
+    if out.dtype not in (torch.bfloat16, torch.float32) or not out.is_contiguous() or out.shape[-1] != ex.dims:
+        raise ValueError("out: contiguous bf16 or fp32 rows of D columns")
+    if wts.dtype != torch.float32 or not wts.is_contiguous() or wts.shape[-1] != plan.slots:
+        raise ValueError("wts: contiguous fp32 [R, slots]")
+    nb = ex.dims // COLS
+    if arrive.dtype != torch.int32 or arrive.numel() < rows * nb:
+        raise ValueError(f"arrive: int32 scratch of at least {rows * nb} entries")
+    _check_x(act, ex.width)
+    if not ex.down.is_contiguous():
+        raise ValueError("w must be contiguous")
+    items = max_items(rows * plan.slots, plan.experts, plan.tile)
+    with torch.cuda.device(act.device):
+        _lib.call("tfb_experts_down_combine", ex.gs, act.data_ptr(), act.stride(0), ex.down.data_ptr(),
+                  ex.width // ex.gs, nb, plan.items.data_ptr(), plan.counts.data_ptr(), plan.members.data_ptr(),
+                  y.data_ptr(), ex.dims, items * nb, _SB[ex.scale_dtype], plan.tile, wts.data_ptr(), plan.slots,
+                  out.data_ptr(), 1 if out.dtype == torch.float32 else 0, arrive.data_ptr(), _stream(act))

@@ -55,6 +55,10 @@ class MoEBuffers:
         self.act = torch.empty((rows, slots, cfg.moe_intermediate_size), dtype=torch.bfloat16, device=device)
         self.y = torch.empty((rows, slots, cfg.hidden_size), dtype=torch.bfloat16 if prefill else torch.float32,
                              device=device)
+        # arrival counters of the kernels that finish their work in whichever block comes last (zero between calls):
+        # the one-launch routing (one a group of eight rows, plus one) and the combine folded into the down projection
+        self.arrive_route = torch.zeros((2 + rows // 8,), dtype=torch.int32, device=device)
+        self.arrive_combine = torch.zeros((rows * (cfg.hidden_size // grouped.COLS),), dtype=torch.int32, device=device)
 
 
 def select_rows(logits: torch.Tensor, buf: MoEBuffers, top_k: int, experts: int) -> None:
@@ -120,16 +124,84 @@ def select(logits: torch.Tensor, buf: MoEBuffers, top_k: int, experts: int,
     grouped.route(buf.pick[:rows], plan, tile)
 
 
+# Rows up to which the layer uses the one-launch routing (``route``) and the combine folded into the down projection
+# (``experts.down_combine``).  Both give the separate launches' bits.  Off unless set: measured on config 2 inside a
+# CUDA graph with programmatic dependent launch, a launch boundary costs about what the hand-over inside a kernel
+# costs (a block's release of its results, about a microsecond), so neither makes the layer faster - one-launch
+# routing: 26.5 -> 28.2 us at 1 row, 40.0 -> 39.5 at 4, 69.5 -> 69.1 at 16, 98.7 -> 99.0 at 64; folded combine:
+# 26.5 -> 26.7, 40.0 -> 40.1, 69.5 -> 71.6, 98.7 -> 106.2.
+FUSED_ROUTE_ROWS = 0
+FUSED_COMBINE_ROWS = 0
+
+
+def route_rows(router_rows: torch.Tensor) -> int:
+    """Up to this many rows the router, the selection and the plan can be one launch (``route``)."""
+
+    return _lib.lib().tfb_route_max_rows(router_rows.shape[0])
+
+
+def route(x: torch.Tensor, router_rows: torch.Tensor, buf: MoEBuffers, top_k: int, experts: int,
+          tile: int = grouped.PREFILL_TILE) -> None:
+    """``router`` then ``select`` for a few rows in ONE launch (the same logits, picks, weights and plan): the block
+    that completes a group of eight rows selects them, the block that completes the last group plans."""
+
+    rows, d = x.shape
+    ne, plan = router_rows.shape[0], buf.plan
+    shared = buf.slots == top_k + 1
+    if not x.is_cuda or x.dtype != torch.bfloat16 or router_rows.dtype != torch.bfloat16 or x.stride(1) != 1 \
+            or router_rows.shape[1] != d or not router_rows.is_contiguous():
+        raise ValueError("route: x [R, D] bf16 with unit-stride rows, rows [NE, D] contiguous bf16")
+    if buf.slots not in (top_k, top_k + 1) or rows > buf.rows or plan.slots != buf.slots or buf.logits.shape[1] != ne:
+        raise ValueError(f"{rows} rows of top-{top_k} do not fit buffers of {buf.rows} x {buf.slots}")
+    if rows > route_rows(router_rows):
+        raise ValueError(f"route: at most {route_rows(router_rows)} rows in one launch")
+    plan.tile = tile if plan.prefill else plan.decode_tile
+    with torch.cuda.device(x.device):
+        _lib.call("tfb_route", x.data_ptr(), x.stride(0), router_rows.data_ptr(), buf.logits.data_ptr(), rows, d, ne,
+                  experts, top_k, 1 if shared else 0, buf.pick.data_ptr(), buf.wts.data_ptr(), plan.tile, 0,
+                  plan.experts, plan.members.data_ptr(), plan.items.data_ptr(), plan.counts.data_ptr(),
+                  buf.arrive_route.data_ptr(), _stream(x))
+
+
+def _route_any(x: torch.Tensor, router_rows: torch.Tensor, buf: MoEBuffers, top_k: int, experts: int) -> int:
+    """The routing stage by the fewest launches available; returns how many it took."""
+
+    rows = x.shape[0]
+    if rows <= min(FUSED_ROUTE_ROWS, route_rows(router_rows)) and x.stride(1) == 1 \
+            and buf.plan.experts == router_rows.shape[0]:
+        route(x, router_rows, buf, top_k, experts)
+        return 1
+    router(x, router_rows, buf.logits[:rows])
+    select(buf.logits[:rows], buf, top_k, experts)
+    return 2 if rows <= fused_select_rows() else 3
+
+
 def moe(x: torch.Tensor, router_rows: torch.Tensor, ex: grouped.Experts, buf: MoEBuffers, top_k: int,
         experts: int) -> MoEBuffers:
     """Route x [R, D] and run its experts into buf.y [R, slots, D] (bf16 in prefill)."""
 
     rows = x.shape[0]
-    router(x, router_rows, buf.logits[:rows])
-    select(buf.logits[:rows], buf, top_k, experts)
+    _route_any(x, router_rows, buf, top_k, experts)
     grouped.gate_up(x, ex, buf.plan, buf.act.view(-1, ex.width), rows)
     grouped.down(buf.act.view(-1, ex.width), ex, buf.plan, buf.y.view(-1, ex.dims), rows)
     return buf
+
+
+def layer(x: torch.Tensor, m: "Routed", buf: MoEBuffers, out: torch.Tensor) -> int:
+    """The whole layer on x [R, D] into ``out`` [R, D] (bf16 or fp32; device or pinned host memory): ``moe`` and
+    ``combine`` with the combine folded into the down projection in the decode form - three launches for a few rows,
+    five for a decode batch, six for a prompt.  buf.y still holds every slot's row.  Returns the launches made."""
+
+    rows, ex = x.shape[0], m.experts
+    launches = _route_any(x, m.router, buf, m.top_k, m.count)
+    grouped.gate_up(x, ex, buf.plan, buf.act.view(-1, ex.width), rows)
+    if buf.plan.prefill or buf.plan.hot or rows > FUSED_COMBINE_ROWS:
+        grouped.down(buf.act.view(-1, ex.width), ex, buf.plan, buf.y.view(-1, ex.dims), rows)
+        combine(buf.y[:rows], buf.wts[:rows], out)
+        return launches + 3
+    grouped.down_combine(buf.act.view(-1, ex.width), ex, buf.plan, buf.y.view(-1, ex.dims), rows, buf.wts, out,
+                         buf.arrive_combine)
+    return launches + 2
 
 
 def combine(y: torch.Tensor, wts: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
@@ -178,8 +250,9 @@ def run(x: torch.Tensor, m: Routed, *, prefill: bool = False) -> torch.Tensor:
     buf = _scratch.get(key)
     if buf is None:
         buf = _scratch[key] = MoEBuffers(size, _Shape(m), x.device, prefill=prefill, shared=m.shared)
-    moe(x.contiguous(), m.router, m.experts, buf, m.top_k, m.count)
-    return combine(buf.y[:rows], buf.wts[:rows])
+    out = torch.empty((rows, m.experts.dims), dtype=torch.bfloat16, device=x.device)
+    layer(x.contiguous(), m, buf, out)
+    return out
 
 
 class Runner:
@@ -196,22 +269,19 @@ class Runner:
         self.x = torch.zeros((rows, m.experts.dims), dtype=torch.bfloat16, device=device)
         self.buf = MoEBuffers(rows, _Shape(m), device, prefill=prefill, shared=m.shared)
         self.out = torch.zeros((rows, m.experts.dims), dtype=torch.bfloat16, device=device)
-        self.launches = 5 if rows <= fused_select_rows() else 6
         self._stream = torch.cuda.Stream(device)
         with torch.cuda.device(device):
             self._stream.wait_stream(torch.cuda.current_stream(device))
             with torch.cuda.stream(self._stream):
-                self._step()                                       # warm up outside the capture
+                self.launches = self._step()                       # warm up outside the capture
             torch.cuda.current_stream(device).wait_stream(self._stream)
             torch.cuda.synchronize(device)
             self.graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(self.graph, stream=self._stream):
                 self._step()
 
-    def _step(self) -> None:
-        m = self.layer
-        moe(self.x, m.router, m.experts, self.buf, m.top_k, m.count)
-        combine(self.buf.y[:self.rows], self.buf.wts[:self.rows], self.out)
+    def _step(self) -> int:
+        return layer(self.x, self.layer, self.buf, self.out)
 
     def replay(self) -> torch.Tensor:
         self.graph.replay()
@@ -238,11 +308,9 @@ class Runner:
             self.host_graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(self.host_graph, stream=self._stream):
                 if direct:
-                    m = self.layer
                     _lib.call("tfb_peer_stage", x_host.data_ptr(), self.x.data_ptr(), 0,
                               self.x.numel() * self.x.element_size(), self._stream.cuda_stream)
-                    moe(self.x, m.router, m.experts, self.buf, m.top_k, m.count)
-                    combine(self.buf.y[:self.rows], self.buf.wts[:self.rows], out_host)
+                    layer(self.x, self.layer, self.buf, out_host)
                 else:
                     self.x.copy_(x_host, non_blocking=True)
                     self._step()

@@ -255,6 +255,38 @@ def test_layer_against_the_cpu_oracle(rows, shared, pdl):
     assert rel_l2(out.float().cpu().numpy(), affine.bf16_value(o_cpu)) <= 1e-2
 
 
+@pytest.mark.parametrize("shared", [False, True])
+@pytest.mark.parametrize("rows", [1, 5, 9, 64])
+def test_fewer_launches_give_the_same_bits(rows, shared, pdl):
+    """The layer with the one-launch routing and with the combine folded into the down projection (three launches)
+    against the default six: the same output bits, per-slot rows and plan, eagerly and from a CUDA graph, twice in a
+    row (the kernels' arrival counters return to zero)."""
+
+    from tensorfold_b200 import experts, moe, synthetic
+
+    shape = synthetic.SMALL_SHARED if shared else synthetic.SMALL
+    gate, up, down = synthetic.affine_layer(shape, DEV)
+    layer = moe.Routed(synthetic.router_rows(shape, DEV), experts.make([gate, up], down, 64), shape.top_k, shared=shared)
+    xs = [synthetic.activations(shape, rows, DEV, index=30 + i) for i in range(2)]
+    want = [moe.run(x, layer).clone() for x in xs]
+    was = moe.FUSED_ROUTE_ROWS, moe.FUSED_COMBINE_ROWS
+    try:
+        moe.FUSED_ROUTE_ROWS, moe.FUSED_COMBINE_ROWS = 256, 256
+        buf = moe.MoEBuffers(rows, moe._Shape(layer), DEV, shared=shared)
+        out = torch.zeros((rows, shape.dims), dtype=torch.bfloat16, device=DEV)
+        for x, w in zip(xs, want):
+            assert moe.layer(x, layer, buf, out) == 3
+            assert torch.equal(out, w)
+            assert torch.equal(moe.combine(buf.y[:rows], buf.wts[:rows]), w)      # every slot's row is still stored
+            assert int(buf.arrive_route.abs().sum()) == 0 and int(buf.arrive_combine.abs().sum()) == 0
+        runner = moe.Runner(layer, rows)
+        assert runner.launches == 3
+        for x, w in zip(xs, want):
+            assert torch.equal(runner(x), w)
+    finally:
+        moe.FUSED_ROUTE_ROWS, moe.FUSED_COMBINE_ROWS = was
+
+
 @pytest.mark.parametrize("reduce", ["rows", "tokens"])
 def test_gathered_expert_parallel_on_one_rank_is_the_layer(reduce):
     """World size 1: the expert-parallel step (windowed plan and combine included) gives moe.run's output."""

@@ -157,6 +157,40 @@ def test_fused_select_plan_equals_the_two_kernels(t, e, k, shared):
     assert torch.equal(a.plan.members, b.plan.members)
 
 
+@pytest.mark.parametrize("t,d,e,k,shared", [(1, 2048, 128, 8, False), (5, 768, 13, 4, True), (8, 256, 50, 7, False),
+                                            (9, 2048, 128, 8, False), (64, 2048, 128, 8, False),
+                                            (33, 6144, 256, 8, True), (3, 512, 1000, 6, True)])
+def test_one_launch_routing_equals_the_three_kernels(t, d, e, k, shared, pdl):
+    """``moe.route`` (router, selection and plan finished by whichever block comes last) against ``router``,
+    ``select_rows`` and ``route`` as separate launches: logits, picks, weights and the plan bit for bit, on two calls
+    in a row (the arrival counters return to zero) with different rows."""
+
+    from tensorfold_b200 import experts, moe
+
+    ne = e + (1 if shared else 0)
+    g = torch.Generator().manual_seed(500 + t)
+    rows_w = (torch.randn((ne, d), generator=g) * 0.02).to(torch.bfloat16).to(DEV)
+    a = moe.MoEBuffers(t, _Cfg(e, k), DEV, shared=shared)
+    b = moe.MoEBuffers(t, _Cfg(e, k), DEV, shared=shared)
+    assert t <= moe.route_rows(rows_w)
+    for call in range(2):
+        x = torch.randn((t, d), generator=g).to(torch.bfloat16).to(DEV)
+        moe.route(x, rows_w, a, k, e)                                           # one launch
+        moe.router(x, rows_w, b.logits[:t])
+        moe.select_rows(b.logits[:t], b, k, e)
+        experts.route(b.pick[:t], b.plan)
+        torch.cuda.synchronize()
+        assert torch.equal(a.logits[:t], b.logits[:t]), call
+        assert torch.equal(a.pick[:t], b.pick[:t]) and torch.equal(a.wts[:t], b.wts[:t]), call
+        n = int(b.plan.counts[0])
+        assert torch.equal(a.plan.counts, b.plan.counts) and torch.equal(a.plan.items[:n], b.plan.items[:n])
+        assert torch.equal(a.plan.members[:t * a.slots], b.plan.members[:t * a.slots])
+        assert int(a.arrive_route.abs().sum()) == 0
+    with pytest.raises(ValueError):
+        moe.route(torch.zeros((moe.route_rows(rows_w) + 1, d), dtype=torch.bfloat16, device=DEV), rows_w,
+                  moe.MoEBuffers(moe.route_rows(rows_w) + 1, _Cfg(e, k), DEV, shared=shared), k, e)
+
+
 def test_windowed_plan_and_combine():
     """The expert-parallel forms: a plan of the ids in [lo, lo + n) renumbered from 0, selection + that plan in one
     launch, and a combine over those slots only."""
