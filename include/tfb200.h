@@ -50,6 +50,12 @@ int tfb_set_wait_limit_ms(int ms);
  * Replaces moe.router / the Triton kernel _router: src/tensorfold/cuda/moe.py:23-55. */
 int tfb_router(const void* x, int64_t x_stride, const void* rows, float* logits, int T, int D, int NE, void* stream);
 
+/* The same logits for prompts, on the tensor cores (bf16 mma, fp32 accumulate, a fixed summation order of its own: the
+ * last bits differ from tfb_router's; a row's bits do not depend on the call's other rows).  D a multiple of 32.
+ * The reference's router changes its blocking with the row count in the same way: src/tensorfold/cuda/moe.py:23-55. */
+int tfb_router_prompt(const void* x, int64_t x_stride, const void* rows, float* logits, int T, int D, int NE,
+                      void* stream);
+
 /* Per row: the top_k experts among the first E logits (largest first, ties to the lower id), weights
  * bf16(exp(l_k - l_0) / sum) stored as fp32; when `shared` != 0 one more slot holds id E with weight
  * bf16(sigmoid(bf16(logits[r, E]))).  pick / wts are [T, top_k + (shared != 0)], NL is the logits' row length.

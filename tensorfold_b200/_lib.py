@@ -16,6 +16,7 @@ P, I, L, F = c_void_p, c_int, c_int64, c_float
 # name -> argument types (every entry point returns int status, except tfb_last_error / tfb_version / tfb_set_pdl)
 SIGNATURES: dict[str, tuple] = {
     "tfb_router": (P, L, P, P, I, I, I, P),
+    "tfb_router_prompt": (P, L, P, P, I, I, I, P),
     "tfb_select_rows": (P, I, P, P, I, I, I, I, P),
     "tfb_select_sigmoid": (P, I, P, P, P, I, I, I, I, F, I, P),
     "tfb_plan": (P, L, I, I, P, P, P, P),

@@ -140,6 +140,102 @@ router_rows_kernel(const __nv_bfloat16* __restrict__ X, int64_t x_stride, const 
 }
 
 // ================================================================================================================
+// The router for prompts, on the tensor cores (mma.sync m16n8k16, bf16 in, fp32 accumulate).  A CTA of eight warps owns
+// 64 rows x 32 experts: four row tiles times two halves of the inputs, the halves added in order (first + second).
+// Per block of 32 inputs a lane loads 8 consecutive inputs of its rows and of its experts' rows as one 16-byte word
+// each; the two mma steps of a block take inputs (0, 1 | 2, 3) and (4, 5 | 6, 7) of every lane's word - A and B are
+// permuted alike, so the products pair up correctly.  Two blocks are in flight while two are multiplied.  The order
+// of the sum is fixed: a row's logits do not depend on the other rows of the call.  The last bits differ from the
+// fp32-fma router's (the reference's Triton router changes its blocking with the row count in the same way,
+// src/tensorfold/cuda/moe.py:23-55).
+// ================================================================================================================
+constexpr int RT_ROWT = 4, RT_KH = 2, RT_NT = 4;     // row tiles and input halves a CTA; n-tiles of 8 experts a warp
+
+__global__ void __launch_bounds__(RT_ROWT * RT_KH * 32)
+router_mma_kernel(const __nv_bfloat16* __restrict__ X, int64_t x_stride, const __nv_bfloat16* __restrict__ W,
+                  float* __restrict__ out, int T, int D, int NE) {
+  __shared__ float part[RT_ROWT][RT_NT * 4][32];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
+  const int rt = warp % RT_ROWT, kh = warp / RT_ROWT;
+  const int r0 = (blockIdx.x * RT_ROWT + rt) * 16, e0 = blockIdx.y * (8 * RT_NT);
+  pdl_wait();
+  after_wait(X);
+  const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+  // rows past the last and experts past the last are read as zeros and never stored
+  const bool row_lo = r0 + g < T, row_hi = r0 + g + 8 < T;
+  const int blocks = D / 32, half = (blocks + RT_KH - 1) / RT_KH;
+  const int kb0 = min(blocks, kh * half), kb1 = min(blocks, kb0 + half);
+  const __nv_bfloat16* xa = X + (size_t)(row_lo ? r0 + g : 0) * x_stride + 8 * t;
+  const __nv_bfloat16* xb = X + (size_t)(row_hi ? r0 + g + 8 : 0) * x_stride + 8 * t;
+  const __nv_bfloat16* wr[RT_NT];
+  bool live[RT_NT];
+#pragma unroll
+  for (int j = 0; j < RT_NT; ++j) {
+    live[j] = e0 + 8 * j + g < NE;
+    wr[j] = W + (size_t)(live[j] ? e0 + 8 * j + g : 0) * D + 8 * t;
+  }
+  float acc[RT_NT][4];
+#pragma unroll
+  for (int j = 0; j < RT_NT; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+  uint4 an[2][2], bn[2][RT_NT];                       // the two blocks in flight
+  auto fetch = [&](int kb) {
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      const bool in = kb + u < kb1;
+      const int k = (kb + u) * 32;
+      an[u][0] = in && row_lo ? ldg_nc(xa + k) : zero;
+      an[u][1] = in && row_hi ? ldg_nc(xb + k) : zero;
+#pragma unroll
+      for (int j = 0; j < RT_NT; ++j) bn[u][j] = in && live[j] ? ldg_nc(wr[j] + k) : zero;
+    }
+  };
+  fetch(kb0);
+  for (int kb = kb0; kb < kb1; kb += 2) {
+    uint4 a[2][2], b[2][RT_NT];
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      a[u][0] = an[u][0];
+      a[u][1] = an[u][1];
+#pragma unroll
+      for (int j = 0; j < RT_NT; ++j) b[u][j] = bn[u][j];
+    }
+    fetch(kb + 2);                                    // past the end: zeros, no loads
+#pragma unroll
+    for (int u = 0; u < 2; ++u)
+#pragma unroll
+      for (int j = 0; j < RT_NT; ++j) {
+        mma_bf16(acc[j], a[u][0].x, a[u][1].x, a[u][0].y, a[u][1].y, b[u][j].x, b[u][j].y);
+        mma_bf16(acc[j], a[u][0].z, a[u][1].z, a[u][0].w, a[u][1].w, b[u][j].z, b[u][j].w);
+      }
+  }
+  pdl_launch_dependents();
+  if (kh == 1) {
+#pragma unroll
+    for (int j = 0; j < RT_NT; ++j)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) part[rt][4 * j + i][lane] = acc[j][i];
+  }
+  __syncthreads();
+  if (kh != 0) return;
+  // acc[j]: (row g, expert 2t), (row g, 2t + 1), (row g + 8, 2t), (row g + 8, 2t + 1) of n-tile j
+#pragma unroll
+  for (int j = 0; j < RT_NT; ++j) {
+    const int e = e0 + 8 * j + 2 * t;
+    float v[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) v[i] = acc[j][i] + part[rt][4 * j + i][lane];
+    if (row_lo) {
+      if (e < NE) out[(size_t)(r0 + g) * NE + e] = v[0];
+      if (e + 1 < NE) out[(size_t)(r0 + g) * NE + e + 1] = v[1];
+    }
+    if (row_hi) {
+      if (e < NE) out[(size_t)(r0 + g + 8) * NE + e] = v[2];
+      if (e + 1 < NE) out[(size_t)(r0 + g + 8) * NE + e + 1] = v[3];
+    }
+  }
+}
+
+// ================================================================================================================
 // Selection: a warp a row.  TOPK rounds of (largest fp32 logit, the lower id among equals), weight
 // bf16(exp(l_k - l_0) / sum_k exp(l_k - l_0)); with a shared expert, slot TOPK = id E with weight
 // bf16(sigmoid(bf16(logit E))).  (src/tensorfold/cuda/moe.py:58-85)
@@ -684,6 +780,23 @@ extern "C" int tfb_router(const void* x, int64_t x_stride, const void* rows, flo
                            static_cast<const __nv_bfloat16*>(x), x_stride, static_cast<const __nv_bfloat16*>(rows),
                            logits, T, D, NE),
                     "router");
+}
+
+// tfb_router for prompts: the same logits up to the last bits, on the tensor cores (a fixed summation order of its
+// own; a row's bits do not depend on the call's other rows).  D a multiple of 32.
+extern "C" int tfb_router_prompt(const void* x, int64_t x_stride, const void* rows, float* logits, int T, int D, int NE,
+                                 void* stream) {
+  TFB_REQUIRE(x && rows && logits, "router_prompt: null pointer");
+  TFB_REQUIRE(T >= 0 && D > 0 && NE > 0, "router_prompt: bad sizes T=%d D=%d NE=%d", T, D, NE);
+  TFB_REQUIRE(D % 32 == 0 && x_stride % 8 == 0 && x_stride >= D,
+              "router_prompt: D must be a multiple of 32 and the row stride of 8");
+  TFB_REQUIRE(aligned16(x) && aligned16(rows), "router_prompt: x and rows must be 16-byte aligned");
+  if (T == 0) return TFB_OK;
+  const dim3 grid((T + 16 * RT_ROWT - 1) / (16 * RT_ROWT), (NE + 8 * RT_NT - 1) / (8 * RT_NT));
+  return check_cuda(launch(router_mma_kernel, grid, dim3(RT_ROWT * RT_KH * 32), 0, static_cast<cudaStream_t>(stream),
+                           static_cast<const __nv_bfloat16*>(x), x_stride, static_cast<const __nv_bfloat16*>(rows),
+                           logits, T, D, NE),
+                    "router_prompt");
 }
 
 extern "C" int tfb_select_rows(const float* logits, int NL, int32_t* pick, float* wts, int T, int E, int top_k,

@@ -159,6 +159,9 @@ class Plan:
             big = max_items(pairs, experts, PREFILL_TILE)
             self.big_items = torch.zeros((big, 3), dtype=torch.int32, device=device)
             self.big_counts = torch.zeros((2,), dtype=torch.int32, device=device)
+            # the hot experts' prompt-form launches run beside the decode-form launch, on a stream of their own
+            self.side = torch.cuda.Stream(device)
+            self.forked, self.joined = torch.cuda.Event(), torch.cuda.Event()
         self.rank = torch.zeros((1,), dtype=torch.int32, device=device)     # unused here; kept for the surface
         self.hist = torch.zeros((1,), dtype=torch.int32, device=device)
 
@@ -205,6 +208,36 @@ class _BigPart:
         self.tile, self.slots, self.experts, self.prefill = PREFILL_TILE, plan.slots, plan.experts, True
 
 
+class _beside:
+    """The launches inside the block go to the plan's side stream, which first waits for everything enqueued on the
+    current stream (the plan, the inputs); ``_rejoin`` makes the current stream wait for them.  A split plan's
+    hot experts (one prompt-form pass over an expert's weights for up to 192 pairs, a long chain on few SMs) thereby
+    run beside the other experts' decode-form launch instead of after it.  Captured in a CUDA graph the two become
+    parallel branches.  For a plan without hot experts the block is skipped (``as hot`` is False)."""
+
+    def __init__(self, plan, device) -> None:
+        self.plan, self.device, self.ctx = plan, device, None
+
+    def __enter__(self) -> bool:
+        if not self.plan.hot:
+            return False
+        self.plan.forked.record(torch.cuda.current_stream(self.device))
+        self.plan.side.wait_event(self.plan.forked)
+        self.ctx = torch.cuda.stream(self.plan.side)
+        self.ctx.__enter__()
+        return True
+
+    def __exit__(self, *exc) -> None:
+        if self.ctx is not None:
+            self.plan.joined.record(self.plan.side)
+            self.ctx.__exit__(*exc)
+
+
+def _rejoin(plan, device) -> None:
+    if plan.hot:
+        torch.cuda.current_stream(device).wait_event(plan.joined)
+
+
 def _check_x(x: torch.Tensor, k: int) -> None:
     _need_cuda(x, "x")
     if x.dtype != torch.bfloat16 or x.dim() != 2 or x.stride(1) != 1 or x.stride(0) % 8 or x.shape[1] != k:
@@ -237,12 +270,14 @@ def gate_up(x: torch.Tensor, ex: Experts, plan: Plan, out: torch.Tensor, rows: i
 
     items = max_items(rows * plan.slots, plan.experts, plan.tile)
     epi = 2 if ex.swiglu else 1
+    with _beside(plan, x.device) as hot:                     # the hot experts' pairs: other rows of the same output
+        if hot:
+            big = max_items(rows * plan.slots, plan.experts, PREFILL_TILE)
+            _run(epi, x, plan.slots, ex.up, ex.dims // ex.gs, ex.width // COLS, _BigPart(plan), out, ex.width,
+                 ex.limit, big, ex, True)
     _run(epi, x, plan.slots, ex.up, ex.dims // ex.gs, ex.width // COLS, plan, out, ex.width, ex.limit, items, ex,
          plan.prefill)
-    if plan.hot:                                             # the hot experts' pairs: other rows of the same output
-        big = max_items(rows * plan.slots, plan.experts, PREFILL_TILE)
-        _run(epi, x, plan.slots, ex.up, ex.dims // ex.gs, ex.width // COLS, _BigPart(plan), out, ex.width, ex.limit,
-             big, ex, True)
+    _rejoin(plan, x.device)
 
 
 def down(act: torch.Tensor, ex: Experts, plan: Plan, out: torch.Tensor, rows: int) -> None:
@@ -250,10 +285,13 @@ def down(act: torch.Tensor, ex: Experts, plan: Plan, out: torch.Tensor, rows: in
 
     items = max_items(rows * plan.slots, plan.experts, plan.tile)
     epi = 3 if plan.prefill and out.dtype == torch.bfloat16 else 0
+    with _beside(plan, act.device) as hot:
+        if hot:
+            big = max_items(rows * plan.slots, plan.experts, PREFILL_TILE)
+            _run(epi, act, 0, ex.down, ex.width // ex.gs, ex.dims // COLS, _BigPart(plan), out, ex.dims, 0.0, big, ex,
+                 True)
     _run(epi, act, 0, ex.down, ex.width // ex.gs, ex.dims // COLS, plan, out, ex.dims, 0.0, items, ex, plan.prefill)
-    if plan.hot:
-        big = max_items(rows * plan.slots, plan.experts, PREFILL_TILE)
-        _run(epi, act, 0, ex.down, ex.width // ex.gs, ex.dims // COLS, _BigPart(plan), out, ex.dims, 0.0, big, ex, True)
+    _rejoin(plan, act.device)
 
 
 def down_combine(act: torch.Tensor, ex: Experts, plan: Plan, y: torch.Tensor, rows: int, wts: torch.Tensor,

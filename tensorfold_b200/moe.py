@@ -20,8 +20,10 @@ def _stream(t: torch.Tensor) -> int:
     return torch.cuda.current_stream(t.device).cuda_stream
 
 
-def router(x: torch.Tensor, rows: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
-    """x [R, D] bf16, rows [NE, D] bf16 (router rows, then the shared expert's gate row if any) -> [R, NE] fp32."""
+def router(x: torch.Tensor, rows: torch.Tensor, out: torch.Tensor | None = None, *, prompt: bool = False) -> torch.Tensor:
+    """x [R, D] bf16, rows [NE, D] bf16 (router rows, then the shared expert's gate row if any) -> [R, NE] fp32.
+    ``prompt``: the tensor-core form (the prefill arithmetic's router: its own fixed summation order, so the last bits
+    differ from the decode form's; a row's bits still do not depend on the other rows)."""
 
     if not x.is_cuda:
         raise ValueError("x must be a CUDA tensor (this library has no CPU path)")
@@ -36,7 +38,8 @@ def router(x: torch.Tensor, rows: torch.Tensor, out: torch.Tensor | None = None)
     elif out.shape != (m, ne) or out.dtype != torch.float32 or not out.is_contiguous():
         raise ValueError("router: out must be contiguous fp32 [R, NE]")
     with torch.cuda.device(x.device):
-        _lib.call("tfb_router", x.data_ptr(), x.stride(0), rows.data_ptr(), out.data_ptr(), m, d, ne, _stream(x))
+        _lib.call("tfb_router_prompt" if prompt and d % 32 == 0 else "tfb_router", x.data_ptr(), x.stride(0),
+                  rows.data_ptr(), out.data_ptr(), m, d, ne, _stream(x))
     return out
 
 
@@ -171,7 +174,7 @@ def _route_any(x: torch.Tensor, router_rows: torch.Tensor, buf: MoEBuffers, top_
             and buf.plan.experts == router_rows.shape[0]:
         route(x, router_rows, buf, top_k, experts)
         return 1
-    router(x, router_rows, buf.logits[:rows])
+    router(x, router_rows, buf.logits[:rows], prompt=buf.plan.prefill)
     select(buf.logits[:rows], buf, top_k, experts)
     return 2 if rows <= fused_select_rows() else 3
 

@@ -27,6 +27,31 @@ def test_router_logits_bit_exact(t, d, ne):
     assert np.array_equal(got, cpu.router_logits(bits(x), bits(w)))
 
 
+@pytest.mark.parametrize("t,d,ne", [(1, 2048, 128), (300, 256, 50), (17, 6144, 257), (2048, 2048, 129), (70, 96, 9)])
+def test_prompt_router_on_the_tensor_cores(t, d, ne):
+    """The prompt form's router: the fp32-fma router's logits up to summation order (1e-5 of the largest), the same
+    top-8 wherever the eighth and ninth logits are further apart than that, and a row's bits independent of the rows
+    it is computed with."""
+
+    from tensorfold_b200 import moe
+
+    g = torch.Generator().manual_seed(700 + t)
+    x = torch.randn((t, d), generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn((ne, d), generator=g) * 0.02).to(torch.bfloat16).to(DEV)
+    want = moe.router(x, w)
+    got = moe.router(x, w, prompt=True)
+    tol = 1e-5 * float(want.abs().max())
+    assert float((got - want).abs().max()) <= tol
+    k = min(8, ne - 1)
+    a, b = got.cpu().numpy(), want.cpu().numpy()
+    for r in range(0, t, max(1, t // 40)):
+        order = sorted(range(ne), key=lambda i: (-b[r, i], i))
+        if b[r, order[k - 1]] - b[r, order[k]] > 4 * tol:
+            assert sorted(range(ne), key=lambda i: (-a[r, i], i))[:k] == order[:k]
+    for lo, hi in ((0, 1), (t // 2, t // 2 + 1), (max(0, t - 19), t)):
+        assert torch.equal(moe.router(x[lo:hi], w, prompt=True), got[lo:hi])
+
+
 def test_router_rows_do_not_depend_on_the_window():
     from tensorfold_b200 import moe
 
