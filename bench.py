@@ -413,6 +413,96 @@ def bench_exl3(torch, rows_list, steps: int, warmup: int, hbm: float):
     return results
 
 
+def bench_reference_cuda(torch, rows_list, steps: int, warmup: int):
+    """The reference's OWN CUDA kernels for the grouped experts (its experts.cu / experts_prefill.cu / experts_pack.cu
+    compiled unmodified for sm_100 by oracle/build_ref_cuda.py) beside this library's, on this GPU, with the same
+    method: plan + gate/up + down of config 2's layer (bf16 scales, the reference's convention) in a CUDA graph, two
+    weight copies alternating.  Router, top-k and combine are left out on both sides (the reference's are Triton
+    kernels of its Python package, which does not travel).  None when the module was never built."""
+
+    from oracle import build_ref_cuda
+    from tensorfold_b200 import experts, moe, synthetic
+
+    ref = build_ref_cuda.load()
+    if ref is None:
+        return None
+    shape, dev = synthetic.C2, torch.device("cuda", torch.cuda.current_device())
+    kg_up, nb_up, kg_dn, nb_dn = shape.dims // 64, shape.width // 32, shape.width // 64, shape.dims // 32
+    ours, theirs = [], []
+    for copy in range(2):
+        gate, up, down = synthetic.affine_layer(shape, dev, torch.bfloat16, copy=copy)
+
+        def ref_pack(m):
+            e, n, k8 = m[0].shape
+            out = torch.empty((e, n // 32, k8 * 8 // 64, 288), dtype=torch.int32, device=dev)
+            ref.pack(m[0].contiguous(), m[1].contiguous(), m[2].contiguous(), 64, out)
+            return out
+
+        theirs.append((torch.stack([ref_pack(gate), ref_pack(up)], dim=3).contiguous(),
+                       ref_pack(down).unsqueeze(3).contiguous()))
+        ours.append(experts.make([gate, up], down, 64))
+        del gate, up, down
+    router = synthetic.router_rows(shape, dev)
+    layer = moe.Routed(router, ours[0], shape.top_k, shared=False)
+    out = []
+    for rows in rows_list:
+        prefill = rows >= 1024
+        x = synthetic.activations(shape, rows, dev)
+        buf = moe.MoEBuffers(rows, moe._Shape(layer), dev, shared=False, prefill=prefill)
+        moe.router(x, router, buf.logits[:rows])
+        moe.select_rows(buf.logits[:rows], buf, shape.top_k, shape.experts)
+        picks, pairs = buf.pick[:rows].contiguous(), rows * shape.top_k
+        tile = 64 if prefill else 16
+        r_members = torch.zeros((pairs,), dtype=torch.int32, device=dev)
+        r_items = torch.zeros((min(pairs, shape.experts) + pairs // 16, 3), dtype=torch.int32, device=dev)
+        r_counts = torch.zeros((2,), dtype=torch.int32, device=dev)
+        r_rank = torch.zeros((pairs,), dtype=torch.int32, device=dev)
+        r_hist = torch.zeros((-(-pairs // 1024) * shape.experts,), dtype=torch.int32, device=dev)
+        r_items_n = min(pairs, shape.experts) + pairs // tile
+        act = torch.zeros((pairs, shape.width), dtype=torch.bfloat16, device=dev)
+        y = torch.zeros((pairs, shape.dims), dtype=torch.bfloat16 if prefill else torch.float32, device=dev)
+        plan = experts.Plan(rows, shape.top_k, shape.experts, dev, prefill=prefill)
+
+        def step_ref(w):
+            ref.plan(picks, pairs, shape.experts, tile, r_members, r_items, r_counts, r_rank, r_hist)
+            if prefill:
+                ref.prefill(64, 2, x, shape.top_k, w[0], kg_up, nb_up, r_items, r_counts, r_members, act, shape.width,
+                            0.0, r_items_n)
+                ref.prefill(64, 3, act, 0, w[1], kg_dn, nb_dn, r_items, r_counts, r_members, y, shape.dims, 0.0,
+                            r_items_n)
+            else:
+                ref.run(64, 2, x, shape.top_k, w[0], kg_up, nb_up, r_items, r_counts, r_members, act, shape.width, 0.0,
+                        r_items_n * nb_up)
+                ref.run(64, 0, act, 0, w[1], kg_dn, nb_dn, r_items, r_counts, r_members, y, shape.dims, 0.0,
+                        r_items_n * nb_dn)
+
+        def step_ours(ex):
+            experts.route(picks, plan)
+            experts.gate_up(x, ex, plan, act, rows)
+            experts.down(act, ex, plan, y, rows)
+
+        times = {}
+        for name, step, sets in (("reference", step_ref, theirs), ("ours", step_ours, ours)):
+            graphs = []
+            for w in sets:
+                step(w)
+                torch.cuda.synchronize()
+                side = torch.cuda.Stream(dev)
+                side.wait_stream(torch.cuda.current_stream())
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=side):
+                    step(w)
+                graphs.append(g)
+            ms, _ = timed(torch, lambda i: graphs[i % len(graphs)].replay(), steps, warmup, 5)
+            times[name] = ms * 1e3
+        out.append({"rows": rows, "form": "prefill" if prefill else "decode",
+                    "reference_kernels_us": times["reference"], "these_kernels_us": times["ours"],
+                    "speedup": times["reference"] / times["ours"]})
+    return {"what": "plan + gate/up + down of config 2's layer with bf16 scales, CUDA graph, two weight copies; the "
+                    "reference's experts.cu / experts_prefill.cu compiled unmodified for sm_100 against this library",
+            "lines": out}
+
+
 def bench_e2e(torch, runners, shape, rows: int, steps: int, warmup: int):
     """The same step through the public API with HOST buffers: pinned tokens in, layer, result back, every step."""
 
@@ -921,6 +1011,9 @@ def run_ours(args) -> None:
         sweep += bench_exl3(torch, (1, 64), max(5, args.steps // 2), args.warmup, hbm)
     else:
         del layers
+    ref_cuda = None if args.no_sweep else guarded("reference kernels", lambda: bench_reference_cuda(
+        torch, (1, 64, 2048), max(5, args.steps // 4), 3), torch, dist)
+    torch.cuda.empty_cache()
     run_extras()
     value = rows / (ms * 1e-3)
     cpu = cpu_1 = cpu_x3 = None
@@ -948,7 +1041,7 @@ def run_ours(args) -> None:
                          "traffic": traffic, "traffic_source": traffic_source,
                          "bytes_per_launch": head["gate_up_bytes"], "us_per_launch": head["gate_up_us"]},
             "layer": {k: head[k] for k in ("distinct_experts", "layer_bytes", "layer_gbs", "layer_frac_of_hbm")},
-            "cpu_baseline": cpu, "cpu_baseline_1_thread": cpu_1, "cpu_baseline_exl3": cpu_x3, "sweep": sweep, **extras}
+            "cpu_baseline": cpu, "cpu_baseline_1_thread": cpu_1, "cpu_baseline_exl3": cpu_x3, "reference_cuda": ref_cuda, "sweep": sweep, **extras}
     print(json.dumps(line))
     dist.destroy_process_group()
 
