@@ -498,9 +498,65 @@ def bench_reference_cuda(torch, rows_list, steps: int, warmup: int):
         out.append({"rows": rows, "form": "prefill" if prefill else "decode",
                     "reference_kernels_us": times["reference"], "these_kernels_us": times["ours"],
                     "speedup": times["reference"] / times["ours"]})
+    del ours, theirs
+    torch.cuda.empty_cache()
     return {"what": "plan + gate/up + down of config 2's layer with bf16 scales, CUDA graph, two weight copies; the "
                     "reference's experts.cu / experts_prefill.cu compiled unmodified for sm_100 against this library",
-            "lines": out}
+            "lines": out, "exl3": bench_reference_exl3(torch, (1, 64), steps, warmup)}
+
+
+def bench_reference_exl3(torch, rows_list, steps: int, warmup: int):
+    """The reference's own EXL3 expert kernels (its exl3/experts*.cu compiled unmodified for sm_100) beside this
+    library's on config 3's layer (4.00 bits a weight): the whole ``routed`` call with the weighted combine, in a CUDA
+    graph, two weight copies alternating, the same picks on both sides.  None when the module was never built."""
+
+    from oracle import build_ref_cuda
+    from oracle import ref_exl3 as drive
+    from tensorfold_b200 import moe, synthetic
+    from tensorfold_b200.exl3 import experts as x3
+
+    ext = build_ref_cuda.load("exl3")
+    if ext is None:
+        return None
+    shape, dev = synthetic.C3, torch.device("cuda", torch.cuda.current_device())
+    router = synthetic.router_rows(shape, dev)
+    layers = [x3.prepare(*synthetic.exl3_layer(shape, dev, 4, copy=c), x3.CB_3INST, device=dev) for c in range(2)]
+
+    class _Cfg:
+        num_experts_per_tok, num_experts = shape.top_k, shape.experts
+        moe_intermediate_size, hidden_size = shape.width, shape.dims
+
+    out = []
+    for rows in rows_list:
+        x = synthetic.activations(shape, rows, dev)
+        buf = moe.MoEBuffers(rows, _Cfg, dev, shared=False)
+        moe.router(x, router, buf.logits[:rows])
+        moe.select_rows(buf.logits[:rows], buf, shape.top_k, shape.experts)
+        pick, wts = buf.pick[:rows].contiguous(), buf.wts[:rows].contiguous()
+        res = torch.zeros((rows, shape.dims), dtype=torch.float32, device=dev)
+        times = {}
+        for name in ("reference", "ours"):
+            graphs, keep = [], []
+            for ex in layers:
+                s = drive.Scratch(ex, rows, shape.top_k, dev) if name == "reference" else x3.Scratch(ex, rows, shape.top_k,
+                                                                                                   device=dev)
+                step = ((lambda ex=ex, s=s: drive.routed(ext, x, pick, wts, ex, s, res)) if name == "reference" else
+                        (lambda ex=ex, s=s: x3.routed(x, pick, wts, ex, s, res, rows)))
+                step()
+                torch.cuda.synchronize()
+                side = torch.cuda.Stream(dev)
+                side.wait_stream(torch.cuda.current_stream())
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=side):
+                    step()
+                graphs.append(g)
+                keep.append(s)
+            ms, _ = timed(torch, lambda i: graphs[i % len(graphs)].replay(), steps, warmup, 5)
+            times[name] = ms * 1e3
+        out.append({"rows": rows, "reference_kernels_us": times["reference"], "these_kernels_us": times["ours"],
+                    "speedup": times["reference"] / times["ours"]})
+    return {"what": "the routed EXL3 call (grouping, rotations, both projections, weighted combine) of config 3's "
+                    "layer at 4.00 bits a weight, CUDA graph, two weight copies", "lines": out}
 
 
 def bench_e2e(torch, runners, shape, rows: int, steps: int, warmup: int):

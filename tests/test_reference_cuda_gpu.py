@@ -96,3 +96,60 @@ def test_gate_up_and_down_against_the_reference_kernels(ref, rows):
     assert np.abs(a - b).max() <= 2 * 2.0 ** -6 * np.abs(b).max()
     assert np.abs(y.cpu().numpy() - y_r.cpu().numpy()).max() <= 2e-5 * np.abs(y_r.cpu().numpy()).max()
     assert np.isfinite(a).all() and np.abs(b).max() > 0
+
+
+@pytest.fixture(scope="module")
+def ref_exl3():
+    from oracle import build_ref_cuda
+
+    mod = build_ref_cuda.load("exl3")
+    if mod is None:
+        pytest.skip("the reference's EXL3 extension was not built (oracle/build_ref_cuda.py needs the reference tree)")
+    return mod
+
+
+@pytest.mark.parametrize("cb", [0, 1, 2])
+def test_trellis_decode_equals_the_reference_kernels(ref_exl3, cb):
+    """W_q of every width through this library's lane decode and through the reference's kernel: the same fp16 bits."""
+
+    from tensorfold_b200.exl3 import experts as x3
+
+    g = torch.Generator().manual_seed(40 + cb)
+    for k2 in range(2, 17):
+        t = torch.randint(-32768, 32768, (8, 16, 8 * k2), dtype=torch.int32, generator=g).to(torch.int16).to(DEV)
+        want = torch.empty((128, 256), dtype=torch.float16, device=DEV)
+        ref_exl3.dequant(t.contiguous(), want, k2, cb)
+        got = x3.dequant(t, cb)
+        assert torch.equal(got.view(torch.int16), want.view(torch.int16)), k2
+
+
+@pytest.mark.parametrize("rows,weighted", [(1, True), (9, False), (64, True)])
+def test_routed_exl3_layer_against_the_reference_kernels(ref_exl3, rows, weighted):
+    """A mixed-width layer through both libraries' launches: per-slot rows (or the weighted sum) agree to 2e-3 of the
+    largest output (each side is within the reference's 1e-2 bar of float64; the roundings differ only in the order of
+    fp32 sums)."""
+
+    from oracle import ref_exl3 as drive
+    from tensorfold_b200 import synthetic
+    from tensorfold_b200.exl3 import experts as x3
+
+    shape = synthetic.LayerShape("ref_x3", 12, 512, 16, 256, 4)
+    bits = lambda e, m: (2, 3, 4, 5, 6, 8)[(e + m) % 6]                             # noqa: E731
+    gate, up, down = synthetic.exl3_layer(shape, DEV, bits)
+    ex = x3.prepare(gate, up, down, x3.CB_3INST, device=DEV)
+    x = synthetic.activations(shape, rows, DEV)
+    g = torch.Generator().manual_seed(rows)
+    pick = torch.stack([torch.randperm(shape.experts + 1, generator=g)[:shape.top_k] for _ in range(rows)])
+    pick = pick.to(torch.int32).to(DEV).contiguous()                               # id 16 is not a routed expert
+    wts = (torch.rand((rows, shape.top_k), generator=g) * 0.3 + 0.05).to(DEV) if weighted else None
+    s_ref = drive.Scratch(ex, rows, shape.top_k)
+    out_ref = torch.zeros((rows, shape.dims), dtype=torch.float32, device=DEV)
+    want = drive.routed(ref_exl3, x, pick, wts, ex, s_ref, out_ref).clone()
+    s = x3.Scratch(ex, rows, shape.top_k)
+    got = x3.routed(x, pick, wts, ex, s, None, rows)
+    torch.cuda.synchronize()
+    if not weighted:                                                               # skipped slots keep what they held: 0
+        want, got = want.view(rows, shape.top_k, -1), got.view(rows, shape.top_k, -1)
+    assert torch.isfinite(got).all() and float(want.abs().max()) > 0
+    assert float((got - want).abs().max()) <= 2e-3 * float(want.abs().max())
+    assert int(s.count[0]) == int(s_ref.count[0])
