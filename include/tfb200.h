@@ -114,6 +114,14 @@ int tfb_route(const void* x, int64_t x_stride, const void* rows, float* logits, 
 int tfb_combine_window(const void* y, int y_bf16, const float* wts, const int32_t* pick, int lo, int n, void* out,
                        int out_f32, int T, int slots, int D, void* stream);
 
+/* The combine, the residual add and the RMSNorm behind a MoE block in one pass over each row: delta = bf16(sum over
+ * the first `routed` slots of wt * y, an fp32 fma chain in slot order, + the other (shared) slots' y); hn = bf16(h +
+ * delta); out = bf16(hn * rsqrt(mean(hn^2) + eps) * w); xs [R, D / 64] fp32 = the sums of out over groups of 64 (what
+ * the next 4-bit projection wants).  y [R, slots, D] fp32, or bf16 when y_bf16; D a multiple of 64, at most 8192.
+ * Replaces `add_moe_norm`: src/tensorfold/families/nemotron_h/cuda/glue.py:104-141. */
+int tfb_add_moe_norm(const void* h, const void* y, int y_bf16, const float* wt, const void* w, void* hn, void* out,
+                     float* xs, int R, int D, int slots, int routed, float eps, void* stream);
+
 /* Expert parallelism over NVLink peer memory (no reference counterpart, as above): the token exchange and the return of
  * the results done by this library's kernels with plain loads and stores to the peers' windows, no collective library
  * on the path.  `windows` is a DEVICE array of `world` pointers: entry i is rank i's window as mapped into this process

@@ -28,6 +28,7 @@ SIGNATURES: dict[str, tuple] = {
     "tfb_plan_split": (P, L, I, I, I, I, I, P, P, P, P, P, P),
     "tfb_combine_window": (P, I, P, P, I, I, P, I, I, I, I, P),
     "tfb_combine": (P, I, P, P, I, I, I, I, P),
+    "tfb_add_moe_norm": (P, P, I, P, P, P, P, P, I, I, I, I, F, P),
     "tfb_pack": (P, P, P, I, P, I, I, I, P),
     "tfb_unpack": (P, I, P, P, P, I, I, I, P),
     "tfb_dequant": (P, I, I, I, P, I, I, I, P),

@@ -755,6 +755,97 @@ combine_kernel(const TY* __restrict__ y, const float* __restrict__ wts, TO* __re
   }
 }
 
+// ================================================================================================================
+// Combine, residual add and RMSNorm in one pass over a row (the Nemotron family's step behind its MoE block):
+// delta = bf16(sum over the routed slots of wt * y, an fp32 fma chain in slot order, + the shared slots' y in slot
+// order); hn = bf16(h + delta); out = bf16(hn * rsqrt(mean(hn^2) + eps) * w); xs = the sums of out over groups of 64.
+// (src/tensorfold/families/nemotron_h/cuda/glue.py:104-141: _add_moe_norm, add_moe_norm)
+// ================================================================================================================
+constexpr int AMN_THREADS = 256, AMN_MAX_PER_THREAD = 8;   // rows of up to 256 * 4 * 8 = 8192 columns
+
+template <typename TY>
+__global__ void __launch_bounds__(AMN_THREADS)
+add_moe_norm_kernel(const __nv_bfloat16* __restrict__ h, const TY* __restrict__ y, const float* __restrict__ wt,
+                    const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ hn, __nv_bfloat16* __restrict__ out,
+                    float* __restrict__ xs, int D, int slots, int routed, float eps) {
+  __shared__ float warp_sq[AMN_THREADS / 32];
+  const int r = blockIdx.x, tid = threadIdx.x, lane = tid & 31;
+  pdl_wait();
+  after_wait(h, y, wt);
+  float hv[AMN_MAX_PER_THREAD][4];
+  float sq = 0.f;
+#pragma unroll
+  for (int i = 0; i < AMN_MAX_PER_THREAD; ++i) {
+    const int d = (i * AMN_THREADS + tid) * 4;
+    if (d >= D) break;
+    float acc[4] = {0.f, 0.f, 0.f, 0.f}, sh[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int s = 0; s < slots; ++s) {
+      const TY* src = y + ((size_t)r * slots + s) * D + d;
+      float v[4];
+      if constexpr (sizeof(TY) == 4) {
+        const float4 f = *reinterpret_cast<const float4*>(src);
+        v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w;
+      } else {
+        const uint2 u = *reinterpret_cast<const uint2*>(src);
+        v[0] = bf16_lo(u.x); v[1] = bf16_hi(u.x); v[2] = bf16_lo(u.y); v[3] = bf16_hi(u.y);
+      }
+      if (s < routed) {
+        const float ws = wt[(size_t)r * slots + s];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[j] = fmaf(ws, v[j], acc[j]);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) sh[j] += v[j];
+      }
+    }
+    const uint2 hx = *reinterpret_cast<const uint2*>(h + (size_t)r * D + d);
+    const float x4[4] = {bf16_lo(hx.x), bf16_hi(hx.x), bf16_lo(hx.y), bf16_hi(hx.y)};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      hv[i][j] = round_bf16(x4[j] + round_bf16(acc[j] + sh[j]));
+      sq = fmaf(hv[i][j], hv[i][j], sq);
+    }
+    __nv_bfloat162 a = __floats2bfloat162_rn(hv[i][0], hv[i][1]), b = __floats2bfloat162_rn(hv[i][2], hv[i][3]);
+    uint2 o;
+    o.x = *reinterpret_cast<uint32_t*>(&a);
+    o.y = *reinterpret_cast<uint32_t*>(&b);
+    *reinterpret_cast<uint2*>(hn + (size_t)r * D + d) = o;
+  }
+  pdl_launch_dependents();
+  // the row's sum of squares: lanes (butterfly), then the warps in warp order
+#pragma unroll
+  for (int m = 16; m >= 1; m >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, m);
+  if (lane == 0) warp_sq[tid >> 5] = sq;
+  __syncthreads();
+  float total = 0.f;
+#pragma unroll
+  for (int i = 0; i < AMN_THREADS / 32; ++i) total += warp_sq[i];
+  const float inv = 1.f / sqrtf(total / (float)D + eps);
+#pragma unroll
+  for (int i = 0; i < AMN_MAX_PER_THREAD; ++i) {
+    const int d = (i * AMN_THREADS + tid) * 4;
+    if (d >= D) break;                                 // D is a multiple of 64: a warp's lanes leave in groups of 16
+    const uint2 wx = *reinterpret_cast<const uint2*>(w + d);
+    const float w4[4] = {bf16_lo(wx.x), bf16_hi(wx.x), bf16_lo(wx.y), bf16_hi(wx.y)};
+    float o4[4], gs = 0.f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      o4[j] = round_bf16(hv[i][j] * inv * w4[j]);
+      gs += o4[j];
+    }
+    __nv_bfloat162 a = __floats2bfloat162_rn(o4[0], o4[1]), b = __floats2bfloat162_rn(o4[2], o4[3]);
+    uint2 o;
+    o.x = *reinterpret_cast<uint32_t*>(&a);
+    o.y = *reinterpret_cast<uint32_t*>(&b);
+    *reinterpret_cast<uint2*>(out + (size_t)r * D + d) = o;
+    // 16 lanes hold a group of 64 columns
+    const unsigned half_mask = 0xFFFFu << (lane & 16);
+#pragma unroll
+    for (int m = 8; m >= 1; m >>= 1) gs += __shfl_xor_sync(half_mask, gs, m);
+    if ((lane & 15) == 0) xs[(size_t)r * (D / 64) + d / 64] = gs;
+  }
+}
+
 }  // namespace tfb
 
 using namespace tfb;
@@ -1050,4 +1141,32 @@ extern "C" int tfb_combine_window(const void* y, int y_bf16, const float* wts, c
   TFB_REQUIRE(pick, "combine_window: null pointer");
   TFB_REQUIRE(lo >= 0 && n >= 1, "combine_window: bad window");
   return combine_launch(y, y_bf16, wts, out, out_f32, T, slots, D, pick, lo, n, stream);
+}
+
+// hn [R, D] bf16 = h + the layer's combined output, out [R, D] bf16 = its RMSNorm times w, xs [R, D / 64] fp32 = the
+// sums of out over groups of 64: the combine (routed slots weighted, shared slots added), the residual add and the norm
+// in one pass.  y [R, slots, D] fp32 (or bf16: the prompt form), wt [R, slots] fp32; the first `routed` slots are the
+// routed ones.  D a multiple of 64, at most 8192.
+// (src/tensorfold/families/nemotron_h/cuda/glue.py:128-141 `add_moe_norm`)
+extern "C" int tfb_add_moe_norm(const void* h, const void* y, int y_bf16, const float* wt, const void* w, void* hn,
+                                void* out, float* xs, int R, int D, int slots, int routed, float eps, void* stream) {
+  TFB_REQUIRE(h && y && wt && w && hn && out && xs, "add_moe_norm: null pointer");
+  TFB_REQUIRE(D > 0 && D % 64 == 0 && D <= AMN_THREADS * 4 * AMN_MAX_PER_THREAD,
+              "add_moe_norm: D must be a multiple of 64, at most %d", AMN_THREADS * 4 * AMN_MAX_PER_THREAD);
+  TFB_REQUIRE(slots >= 1 && routed >= 0 && routed <= slots, "add_moe_norm: %d routed of %d slots", routed, slots);
+  TFB_REQUIRE(aligned16(h) && aligned16(y) && aligned16(w) && aligned16(hn) && aligned16(out),
+              "add_moe_norm: rows must be 16-byte aligned");
+  if (R <= 0) return TFB_OK;
+  auto st = static_cast<cudaStream_t>(stream);
+  auto* hb = static_cast<const __nv_bfloat16*>(h);
+  auto* wb = static_cast<const __nv_bfloat16*>(w);
+  cudaError_t e;
+  if (y_bf16)
+    e = launch(add_moe_norm_kernel<__nv_bfloat16>, dim3(R), dim3(AMN_THREADS), 0, st, hb,
+               static_cast<const __nv_bfloat16*>(y), wt, wb, static_cast<__nv_bfloat16*>(hn),
+               static_cast<__nv_bfloat16*>(out), xs, D, slots, routed, eps);
+  else
+    e = launch(add_moe_norm_kernel<float>, dim3(R), dim3(AMN_THREADS), 0, st, hb, static_cast<const float*>(y), wt, wb,
+               static_cast<__nv_bfloat16*>(hn), static_cast<__nv_bfloat16*>(out), xs, D, slots, routed, eps);
+  return check_cuda(e, "add_moe_norm");
 }

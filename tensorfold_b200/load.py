@@ -27,8 +27,8 @@ PROJS = ("gate_proj", "up_proj", "down_proj")
 
 
 class Checkpoint:
-    """The tensors of one ``.safetensors`` file or of a folder of them (an ``model.safetensors.index.json`` is used
-    when present, else every file's header is read)."""
+    """The tensors of one ``.safetensors`` file or of a folder of them: every file's header is read (an index file
+    beside them is not needed and not looked at)."""
 
     def __init__(self, path: str | Path) -> None:
         root = Path(path)
@@ -135,14 +135,64 @@ def affine_routed(ck: Checkpoint, prefix: str, top_k: int, device="cuda", gs: in
     return moe.Routed(router, ex, int(top_k), shared=shared)
 
 
-def exl3_group(ck: Checkpoint, prefix: str, device="cuda"):
-    """(trellis int16, suh fp16 [K], svh fp16 [N], codebook name, bias or None) of the EXL3 group ``prefix``."""
+EXL3_BITS = (1.0, 1.5, 2.0, 2.5, 3.0, 3.5, 4.0, 4.5, 5.0, 5.5, 6.0, 6.5, 7.0, 7.5, 8.0)
+EXL3_PARTS = ("trellis", "suh", "su", "svh", "sv", "mcg", "mul1", "bias")
+HADAMARD = 128
 
-    if not ck.has(prefix + ".trellis"):
-        raise KeyError(f"{prefix}: no .trellis")
+
+def parse_group(ck: Checkpoint, prefix: str) -> tuple[float, str, int, int, str, str, bool]:
+    """(bits, codebook, K, N, input-scale part, output-scale part, has bias) of the EXL3 group ``prefix`` from the
+    header entries alone; ValueError, saying why, for a group the kernels cannot take.  The refusals are those of
+    ``src/tensorfold/cuda/exl3/format.py:226-267``: no trellis, a trellis that is not int16 [K/16, N/16, 16 * bits]
+    at a width of 1..8 bits in half steps, both codebook markers, a fractional width without the mul1 codebook,
+    missing or mis-shaped scales (fp16 [K] / [N], or packed signs int16 [K/16] / [N/16]), K or N not a multiple of
+    the 128-point rotation."""
+
+    def fail(why: str) -> ValueError:
+        return ValueError(f"{prefix}: {why}")
+
+    parts = {}
+    for part in EXL3_PARTS:
+        if ck.has(f"{prefix}.{part}"):
+            _, _, _, dtype, shape = ck.entry(f"{prefix}.{part}")
+            parts[part] = (dtype, shape)
+    if "trellis" not in parts:
+        raise fail("no .trellis")
+    dtype, shape = parts["trellis"]
+    if dtype != "I16" or len(shape) != 3:
+        raise fail(f"trellis must be int16 [K/16, N/16, 16 * bits], got {dtype} {shape}")
+    bits = shape[2] / 16
+    if shape[2] % 8 or bits not in EXL3_BITS:
+        raise fail(f"a trellis row of {shape[2]} words is {bits} bits; EXL3 widths are 1..8 in half steps")
+    marks = [m for m in ("mcg", "mul1") if m in parts]
+    if len(marks) > 1:
+        raise fail("both mcg and mul1 markers")
+    cb = marks[0] if marks else "3inst"
+    if not float(bits).is_integer() and cb != "mul1":
+        raise fail(f"{bits}-bit tiles need the mul1 codebook, found {cb}")
+    k, n = 16 * shape[0], 16 * shape[1]
+    chosen = []
+    for full, packed, size, what in (("suh", "su", k, "input"), ("svh", "sv", n, "output")):
+        if full in parts:
+            name, want = full, ("F16", [size])
+        elif packed in parts:
+            name, want = packed, ("I16", [size // 16])
+        else:
+            raise fail(f"no {what} scales (.{full} or .{packed})")
+        if (parts[name][0], list(parts[name][1])) != want:
+            raise fail(f".{name} must be {want[0]} {want[1]}, got {parts[name][0]} {parts[name][1]}")
+        chosen.append(name)
+    if k % HADAMARD or n % HADAMARD:
+        raise fail(f"K={k} and N={n} must be multiples of {HADAMARD} (the rotation's blocks)")
+    return float(bits), cb, k, n, chosen[0], chosen[1], "bias" in parts
+
+
+def exl3_group(ck: Checkpoint, prefix: str, device="cuda"):
+    """(trellis int16, suh fp16 [K], svh fp16 [N], codebook name, bias or None) of the EXL3 group ``prefix``; the
+    group's header entries are checked (``parse_group``) before any bytes are read."""
+
+    parse_group(ck, prefix)
     trellis = ck.get(prefix + ".trellis", device)
-    if trellis.dtype != torch.int16 or trellis.dim() != 3:
-        raise ValueError(f"{prefix}: trellis must be int16 [K/16, N/16, 16 * bits]")
 
     def scales(full: str, packed: str, size: int) -> torch.Tensor:
         if ck.has(f"{prefix}.{full}"):

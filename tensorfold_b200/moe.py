@@ -221,6 +221,29 @@ def combine(y: torch.Tensor, wts: torch.Tensor, out: torch.Tensor | None = None)
     return out
 
 
+def add_moe_norm(h: torch.Tensor, y: torch.Tensor, wt: torch.Tensor, w: torch.Tensor, eps: float, top_k: int):
+    """The step behind a MoE block in one launch: h [R, D] bf16, y [R * NS, D] (fp32, or bf16 in prefill), wt [R, NS]
+    fp32, w [D] bf16 -> (h + delta, its RMSNorm times w, the norm's sums over groups of 64), delta = the first ``top_k``
+    slots weighted plus the shared slots, summed in slot order and rounded to bf16.  Mirrors the Nemotron family's
+    ``glue.add_moe_norm`` (``src/tensorfold/families/nemotron_h/cuda/glue.py:128-141``)."""
+
+    rows, d = h.shape
+    slots = wt.shape[1]
+    if not h.is_cuda or h.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or not h.is_contiguous() or w.numel() != d:
+        raise ValueError("add_moe_norm: h [R, D] and w [D] must be contiguous CUDA bf16")
+    if y.dtype not in (torch.float32, torch.bfloat16) or not y.is_contiguous() or y.numel() != rows * slots * d:
+        raise ValueError("add_moe_norm: y must be contiguous fp32 or bf16 [R * NS, D]")
+    if wt.dtype != torch.float32 or not wt.is_contiguous() or wt.shape[0] != rows or not 0 <= top_k <= slots:
+        raise ValueError("add_moe_norm: wt must be contiguous fp32 [R, NS] with top_k <= NS")
+    hn, out = torch.empty_like(h), torch.empty_like(h)
+    xs = torch.empty((rows, d // 64), dtype=torch.float32, device=h.device)
+    with torch.cuda.device(h.device):
+        _lib.call("tfb_add_moe_norm", h.data_ptr(), y.data_ptr(), 1 if y.dtype == torch.bfloat16 else 0, wt.data_ptr(),
+                  w.contiguous().data_ptr(), hn.data_ptr(), out.data_ptr(), xs.data_ptr(), rows, d, slots, top_k,
+                  float(eps), _stream(h))
+    return hn, out, xs
+
+
 @dataclass
 class Routed:
     """A layer's router rows ([E + 1, D] bf16 with the shared expert's gate row last, or [E, D]) and its experts."""

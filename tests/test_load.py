@@ -128,3 +128,51 @@ def test_exl3_groups_from_a_checkpoint(tmp_path):
     signs = load.unpack_signs(tensors["x.q_proj.su"]).to(dev)
     direct = linear.Exl3Linear.from_tensors(t, signs, svh, "mcg")
     assert torch.equal(lin(x), direct(x))
+
+
+def test_exl3_groups_the_kernels_cannot_take_are_refused_by_name(tmp_path):
+    """The header checks of ``src/tensorfold/cuda/exl3/format.py:226-267``, one bad group each; a good group parses to
+    its width, codebook and sizes."""
+
+    from tensorfold_b200 import load
+
+    def group(k=128, n=256, words=40, **extra):
+        g = {"trellis": torch.zeros((k // 16, n // 16, words), dtype=torch.int16),
+             "suh": torch.ones((k,), dtype=torch.float16), "svh": torch.ones((n,), dtype=torch.float16)}
+        g.update(extra)
+        return {name: t for name, t in g.items() if t is not None}
+
+    mark = torch.zeros((1,), dtype=torch.int32)
+    cases = {
+        "good": (group(mul1=mark), None),
+        "signs": (group(words=48, suh=None, svh=None, su=torch.zeros((8,), dtype=torch.int16),
+                        sv=torch.zeros((16,), dtype=torch.int16), bias=torch.zeros((256,), dtype=torch.float16)), None),
+        "notrellis": ({"suh": torch.ones((128,), dtype=torch.float16)}, "no .trellis"),
+        "dtype": (group(trellis=torch.zeros((8, 16, 40), dtype=torch.int32), mul1=mark), "trellis must be int16"),
+        "rank": (group(trellis=torch.zeros((8, 640), dtype=torch.int16)), "trellis must be int16"),
+        "width": (group(words=36, mul1=mark), "EXL3 widths"),
+        "wide": (group(words=144), "EXL3 widths"),
+        "both": (group(mul1=mark, mcg=mark), "both mcg and mul1"),
+        "half": (group(mcg=mark), "need the mul1 codebook"),
+        "half3": (group(), "need the mul1 codebook"),
+        "noin": (group(words=32, suh=None), "no input scales"),
+        "noout": (group(words=32, svh=None), "no output scales"),
+        "inshape": (group(words=32, suh=torch.ones((64,), dtype=torch.float16)), ".suh must be F16 [128]"),
+        "outtype": (group(words=32, svh=torch.ones((256,), dtype=torch.float32)), ".svh must be F16 [256]"),
+        "sushape": (group(words=32, suh=None, su=torch.zeros((128,), dtype=torch.int16)), ".su must be I16 [8]"),
+        "k64": (group(k=64, words=32), "multiples of 128"),
+        "n192": (group(n=192, words=32), "multiples of 128"),
+    }
+    tensors = {f"{name}.{part}": t.clone() for name, (g, _) in cases.items() for part, t in g.items()}
+    _save(tmp_path / "model.safetensors", tensors)
+    ck = load.Checkpoint(tmp_path)
+    assert load.parse_group(ck, "good") == (2.5, "mul1", 128, 256, "suh", "svh", False)
+    assert load.parse_group(ck, "signs") == (3.0, "3inst", 128, 256, "su", "sv", True)
+    for name, (_, why) in cases.items():
+        if why is None:
+            continue
+        with pytest.raises(ValueError) as err:
+            load.parse_group(ck, name)
+        assert why in str(err.value) and str(err.value).startswith(name + ":"), (name, str(err.value))
+        with pytest.raises(ValueError):
+            load.exl3_group(ck, name, "cpu")

@@ -286,3 +286,32 @@ def test_sigmoid_bias_selection_matches_the_sorted_order(experts, top_k, shared,
     choice = (np.float32(score) + bias.cpu().numpy()).astype(np.float32)
     order = sorted(range(experts), key=lambda i: (-choice[i], i))[:top_k]
     assert got_pick[5, :top_k].tolist() == order
+
+
+@pytest.mark.parametrize("ydtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("rows,d,slots,top_k", [(5, 2688, 8, 6), (64, 2048, 9, 8), (3, 8192, 4, 4), (2, 64, 3, 1)])
+def test_add_moe_norm_against_float64(rows, d, slots, top_k, ydtype):
+    """Combine + residual add + RMSNorm in one launch (the Nemotron family's ``add_moe_norm``): the new hidden state
+    within one bf16 ulp of the float64 result, the normed row within 2^-7, the group sums equal to the sums of the
+    stored values."""
+
+    from tensorfold_b200 import moe
+
+    g = torch.Generator().manual_seed(rows + d)
+    h = torch.randn((rows, d), generator=g).to(torch.bfloat16).to(DEV)
+    y = (torch.randn((rows * slots, d), generator=g) * 0.5).to(ydtype).to(DEV)
+    wt = torch.rand((rows, slots), generator=g).float().to(DEV)
+    w = (torch.rand((d,), generator=g) + 0.5).to(torch.bfloat16).to(DEV)
+    eps = 1e-5
+    hn, out, xs = moe.add_moe_norm(h, y, wt, w, eps, top_k)
+    y64 = y.double().view(rows, slots, d)
+    routed = (wt.double()[:, :top_k, None] * y64[:, :top_k]).sum(1)
+    delta = (routed + y64[:, top_k:].sum(1)).to(torch.bfloat16).double()
+    want_h = (h.double() + delta)
+    ulp = torch.maximum(want_h.abs(), torch.tensor(1e-30, device=DEV, dtype=torch.float64)) * 2.0 ** -7
+    assert bool(((hn.double() - want_h).abs() <= ulp + 1e-6).all())
+    hf = hn.double()
+    want_out = hf / torch.sqrt((hf * hf).mean(1, keepdim=True) + eps) * w.double()
+    assert float((out.double() - want_out).abs().max()) <= 2.0 ** -7 * float(want_out.abs().max())
+    sums = out.float().view(rows, d // 64, 64).sum(2)
+    assert torch.allclose(xs, sums, rtol=1e-5, atol=1e-5)
