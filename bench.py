@@ -237,7 +237,8 @@ def run_reference(args) -> None:
 
 def workload_config(shape, rows: int, gpus: int, config: str = "c2") -> dict:
     if config == "c5":
-        return {"workload": f"BASELINE config 5: {C5_LAYERS} MoE layers with bf16 residual adds, {rows} tokens over the "
+        batch = f"{rows} tokens" if rows else "batches of " + ", ".join(str(t) for t in C5_TOKENS) + " tokens"
+        return {"workload": f"BASELINE config 5: {C5_LAYERS} MoE layers with bf16 residual adds, {batch} over the "
                             f"ranks, hidden {shape.dims}, {shape.experts} experts x FFN {shape.width}, "
                             f"top-{shape.top_k}, EXL3 experts at a seeded 2..8 bits a tensor (3inst)",
                 "tokens": rows, "l2": "16 seeded token batches rotate, so the experts (and weights) change every step",

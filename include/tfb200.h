@@ -203,6 +203,16 @@ int tfb_experts_run_tile(int gs, int epi, const void* x, int64_t x_stride, int s
                          const int32_t* items, const int32_t* counts, const int32_t* members, void* out, int n,
                          float limit, int64_t max_units, int sb_type, int tile, void* stream);
 
+/* The decode form with its K slices left apart: part [tfb_decode_kslices(kg), rows, n] fp32, slice k of pair p at
+ * part[k, p, :]; adding the slices in order k = 0, 1, .. gives epilogue 0's bits.  For a caller that folds the sum into
+ * its next kernel.  Replaces `matmul(reduce=False, part=)`: src/tensorfold/cuda/kernels/qmm.py:156-177. */
+int tfb_experts_run_slices(int gs, const void* x, int64_t x_stride, int slots, const void* w, int kg, int nb,
+                           const int32_t* items, const int32_t* counts, const int32_t* members, float* part, int n,
+                           int rows, int64_t max_units, int sb_type, int tile, void* stream);
+
+/* K slices the decode form cuts a projection of kg groups of 64 inputs into: a function of the shape alone. */
+int tfb_decode_kslices(int kg);
+
 /* The down projection and the weighted combine in one launch: y [P, n] fp32 per pair exactly as tfb_experts_run_tile
  * with epilogue 0 (x = act [P, K] bf16, one row a pair), and out [T, n] (bf16, or fp32 when out_f32) = the sum over a
  * token's slots in slot order of wts[t, s] * y[t * slots + s, :] (an fp32 fma chain from 0, rounded once), formed by

@@ -20,7 +20,8 @@ from pathlib import Path
 
 HERE = Path(__file__).resolve().parent
 OUT = HERE / "_ref" / "libaffine_header.so"
-REFERENCE = Path(os.environ.get("TENSORFOLD_REFERENCE", "/root/reference"))
+# the reference checkout: $TENSORFOLD_REFERENCE, else a folder named "reference" beside this repository
+REFERENCE = Path(os.environ.get("TENSORFOLD_REFERENCE") or HERE.parents[1] / "reference")
 SOURCE = REFERENCE / "src/tensorfold/kernels/qwen/dense/v1/affine_rows.py"
 BITS = (2, 3, 4, 5, 6, 8)
 

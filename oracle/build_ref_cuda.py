@@ -21,7 +21,8 @@ import sys
 from pathlib import Path
 
 HERE = Path(__file__).resolve().parent
-REFERENCE = Path(os.environ.get("TENSORFOLD_REFERENCE", "/root/reference"))
+# the reference checkout: $TENSORFOLD_REFERENCE, else a folder named "reference" beside this repository
+REFERENCE = Path(os.environ.get("TENSORFOLD_REFERENCE") or HERE.parents[1] / "reference")
 CUDA = REFERENCE / "src/tensorfold/cuda"
 # target -> (module name, build directory, sources)
 TARGETS = {

@@ -35,6 +35,7 @@ SIGNATURES: dict[str, tuple] = {
     "tfb_group_sums": (P, L, P, I, I, I, P),
     "tfb_experts_run": (I, I, P, L, I, P, I, I, P, P, P, P, I, F, L, I, P),
     "tfb_experts_run_tile": (I, I, P, L, I, P, I, I, P, P, P, P, I, F, L, I, I, P),
+    "tfb_experts_run_slices": (I, P, L, I, P, I, I, P, P, P, P, I, I, L, I, I, P),
     "tfb_experts_prefill": (I, I, P, L, I, P, I, I, P, P, P, P, I, F, L, I, P),
     "tfb_exl3_dequant": (P, P, I, I, I, I, P),
     "tfb_exl3_group": (P, P, P, P, P, P, P, I, I, I, I, I, P),
@@ -70,6 +71,8 @@ def lib() -> ctypes.CDLL:
     handle.tfb_set_wait_limit_ms.restype = c_int
     handle.tfb_route_max_rows.argtypes = (c_int,)
     handle.tfb_route_max_rows.restype = c_int
+    handle.tfb_decode_kslices.argtypes = (c_int,)
+    handle.tfb_decode_kslices.restype = c_int
     handle.tfb_select_plan_max_rows.restype = c_int
     handle.tfb_select_plan_max_rows.argtypes = ()
     for name, args in SIGNATURES.items():

@@ -271,6 +271,6 @@ __device__ __forceinline__ float relu2(float a) {
   return u * u;
 }
 
-enum Epilogue : int { EPI_F32 = 0, EPI_RELU2 = 1, EPI_SWIGLU = 2, EPI_BF16 = 3 };
+enum Epilogue : int { EPI_F32 = 0, EPI_RELU2 = 1, EPI_SWIGLU = 2, EPI_BF16 = 3, EPI_SLICES = 4 };
 
 }  // namespace tfb

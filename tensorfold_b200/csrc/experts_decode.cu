@@ -13,6 +13,8 @@
 // (Replaces src/tensorfold/cuda/experts.cu:13-155,287-351: expert_kernel and its launch.)
 
 #include "api.h"
+#include <cstring>
+
 #include "common.cuh"
 
 namespace tfb {
@@ -242,6 +244,14 @@ decode_kernel(const __nv_bfloat16* __restrict__ X, int64_t x_stride, int slots, 
     const int cbi = cbt * CBC + cbo;
     if (pi >= cnt || cbi >= NB) continue;
     const int w0 = (cbo / NCB) * KW, q0 = (cbo % NCB) * M;      // first K-slice warp and block of this column block
+    if constexpr (EPI == EPI_SLICES) {                 // the K slices as they are: [KW, rows, N], `limit` holds rows
+      const size_t rows = (size_t)__float_as_int(limit);
+#pragma unroll
+      for (int k = 0; k < KW; ++k)
+        static_cast<float*>(out)[(k * rows + pair_id[pi]) * N + cbi * COLS + col] =
+            red[(((w0 + k) * Q + q0) * DEC_PAIRS + pi) * RED_STRIDE + col];
+      continue;
+    }
     float v[M];
 #pragma unroll
     for (int m = 0; m < M; ++m) {
@@ -251,7 +261,7 @@ decode_kernel(const __nv_bfloat16* __restrict__ X, int64_t x_stride, int slots, 
       v[m] = sum;
     }
     const size_t at = (size_t)pair_id[pi] * N + cbi * COLS + col;
-    if constexpr (EPI == EPI_F32) {
+    if constexpr (EPI == EPI_F32 || EPI == EPI_SLICES) {
       static_cast<float*>(out)[at] = v[0];
     } else if constexpr (EPI == EPI_RELU2) {
       static_cast<__nv_bfloat16*>(out)[at] = __float2bfloat16_rn(relu2(v[0]));
@@ -418,7 +428,7 @@ static int experts_run(int gs, int epi, const void* x, int64_t x_stride, int slo
     if (sb_type == SB_BF16) TFB_RUN3(EPI_, M_, SB_BF16); \
     TFB_RUN3(EPI_, M_, SB_FP16);                       \
   }
-  TFB_RUN(EPI_F32, 1) TFB_RUN(EPI_RELU2, 1) TFB_RUN(EPI_SWIGLU, 2) TFB_RUN(EPI_BF16, 1)
+  TFB_RUN(EPI_F32, 1) TFB_RUN(EPI_RELU2, 1) TFB_RUN(EPI_SWIGLU, 2) TFB_RUN(EPI_BF16, 1) TFB_RUN(EPI_SLICES, 1)
 #undef TFB_RUN
 #undef TFB_RUN3
   return fail(TFB_ERR_ARG, "experts_run: no kernel for epilogue %d", epi);
@@ -430,6 +440,7 @@ static int experts_run(int gs, int epi, const void* x, int64_t x_stride, int slo
 extern "C" int tfb_experts_run(int gs, int epi, const void* x, int64_t x_stride, int slots, const void* w, int kg,
                                int nb, const int32_t* items, const int32_t* counts, const int32_t* members, void* out,
                                int n, float limit, int64_t max_units, int sb_type, void* stream) {
+  TFB_REQUIRE(epi >= EPI_F32 && epi <= EPI_BF16, "experts_run: no kernel for epilogue %d", epi);
   return experts_run(gs, epi, x, x_stride, slots, w, kg, nb, items, counts, members, out, n, limit, max_units, sb_type,
                      8, stream);
 }
@@ -441,9 +452,27 @@ extern "C" int tfb_experts_run_tile(int gs, int epi, const void* x, int64_t x_st
                                     int nb, const int32_t* items, const int32_t* counts, const int32_t* members,
                                     void* out, int n, float limit, int64_t max_units, int sb_type, int tile,
                                     void* stream) {
+  TFB_REQUIRE(epi >= EPI_F32 && epi <= EPI_BF16, "experts_run: no kernel for epilogue %d", epi);
   return experts_run(gs, epi, x, x_stride, slots, w, kg, nb, items, counts, members, out, n, limit, max_units, sb_type,
                      tile, stream);
 }
+
+// The decode form with its K slices left apart: part [tfb_decode_kslices(kg), rows, n] fp32, slice k of pair p at
+// part[k, p, :]; adding the slices in order k = 0, 1, .. gives epilogue 0's bits.  For a caller that folds the sum into
+// its next kernel.  (src/tensorfold/cuda/kernels/qmm.py:156-177 `matmul(reduce=False, part=)`)
+extern "C" int tfb_experts_run_slices(int gs, const void* x, int64_t x_stride, int slots, const void* w, int kg, int nb,
+                                      const int32_t* items, const int32_t* counts, const int32_t* members, float* part,
+                                      int n, int rows, int64_t max_units, int sb_type, int tile, void* stream) {
+  TFB_REQUIRE(rows >= 0, "experts_run_slices: bad row count %d", rows);
+  float carried;
+  static_assert(sizeof(carried) == sizeof(rows), "the row count rides in the limit's four bytes");
+  memcpy(&carried, &rows, sizeof(carried));
+  return experts_run(gs, EPI_SLICES, x, x_stride, slots, w, kg, nb, items, counts, members, part, n, carried, max_units,
+                     sb_type, tile, stream);
+}
+
+// K slices the decode form cuts a projection of kg groups into (a function of the shape alone).
+extern "C" int tfb_decode_kslices(int kg) { return decode_kslices(kg); }
 
 // The down projection and the weighted combine in one launch: y [P, n] fp32 per pair as tfb_experts_run_tile with
 // epilogue 0 (x = act [P, K] bf16, one row a pair), and out [T, n] (bf16, or fp32 when out_f32) = sum over a token's

@@ -5,8 +5,9 @@ experts' - a row's bits never depend on how many rows run with it.
 Mirrors ``tensorfold.cuda.kernels.qmm`` (``src/tensorfold/cuda/kernels/qmm.py:41-219``): ``Q4``, ``pack`` / ``unpack``,
 ``matmul``, ``prefill_matmul``, ``group_sums``, ``split_k``, ``bucket``.  Differences a caller can see: the packed words
 use this library's block order (``unpack`` inverts it bit for bit), n is padded to 32 (the reference pads to 128),
-``matmul`` adds its K slices inside the kernel in slice order (``reduce=False`` is refused), and the group sums the
-reference passes in (``xs``) are formed inside the kernel from the same inputs, so ``xs`` is accepted and not read.
+``matmul`` adds its K slices inside the kernel in slice order (``reduce=False`` hands them out apart, as the reference
+does), the slicing is the shape's and cannot be chosen per call, and the group sums the reference passes in (``xs``)
+are formed inside the kernel from the same inputs, so ``xs`` is accepted and not read.
 No CPU path.
 """
 
@@ -67,8 +68,7 @@ def unpack(q: Q4) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
 def split_k(n: int, k: int, gs: int = 64, target: int = 192) -> int:
     """K slices the kernel adds in order for an (n, k) weight: a function of the shape only, never of the rows."""
 
-    kg = k // gs
-    return 4 if kg >= 32 else 2 if kg >= 8 else 1
+    return _lib.lib().tfb_decode_kslices(k // gs)
 
 
 def bucket(m: int) -> int:
@@ -136,13 +136,42 @@ def _run(x: torch.Tensor, q: Q4, f32: bool, out: torch.Tensor | None, prefill: b
 def matmul(x: torch.Tensor, q: Q4, xs: torch.Tensor | None = None, *, sk: int | None = None, f32: bool = False,
            out: torch.Tensor | None = None, part: torch.Tensor | None = None, reduce: bool = True) -> torch.Tensor:
     """x @ q.T as (M, n) bf16, or unrounded fp32 with ``f32``: exact integer products per group, then
-    ``acc = fma(xs, b, fma(p, s, acc))`` in fp32 (the decode arithmetic)."""
+    ``acc = fma(xs, b, fma(p, s, acc))`` in fp32 (the decode arithmetic).  ``reduce=False`` returns the K slices apart,
+    fp32 (split_k, M, n) (in ``part`` when given), for a caller that adds them in slice order inside its next kernel;
+    with one slice it returns the product itself, as the reference does
+    (``src/tensorfold/cuda/kernels/qmm.py:156-177``)."""
 
-    if not reduce or part is not None:
-        raise ValueError("matmul: the K slices are added inside the kernel (slice order); reduce=False is not offered")
-    if sk is not None and sk != split_k(q.n, q.k, q.gs):
+    slices = split_k(q.n, q.k, q.gs)
+    if sk is not None and sk != slices:
         raise ValueError("matmul: the K slicing is the shape's (split_k), it cannot be chosen per call")
-    return _run(_check(x, q, "matmul"), q, f32, out, False)
+    x = _check(x, q, "matmul")
+    if reduce or slices == 1:
+        return _run(x, q, f32, out, False)
+    return _slices(x, q, slices, part)
+
+
+def _slices(x: torch.Tensor, q: Q4, slices: int, part: torch.Tensor | None) -> torch.Tensor:
+    m = x.shape[0]
+    need = slices * m * q.n
+    padded = q.n_pad != q.n
+    if part is not None and (part.dtype != torch.float32 or not part.is_contiguous() or part.numel() < need
+                             or part.device != x.device):
+        raise ValueError(f"part must be contiguous fp32 with at least {need} elements on x's device")
+    dst = part.reshape(-1)[:need].view(slices, m, q.n) if part is not None and not padded else \
+        torch.empty((slices, m, q.n_pad), dtype=torch.float32, device=x.device)
+    plan = _plan(m, x.device, False)
+    with torch.cuda.device(x.device):
+        _lib.call("tfb_experts_run_slices", q.gs, x.data_ptr(), x.stride(0), 0, q.weight.data_ptr(), q.k // q.gs,
+                  q.n_pad // grouped.COLS, plan.items.data_ptr(), plan.counts.data_ptr(), plan.members.data_ptr(),
+                  dst.data_ptr(), q.n_pad, m, grouped.max_items(m, 1, plan.tile) * (q.n_pad // grouped.COLS),
+                  0 if q.scale_dtype == torch.bfloat16 else 1, plan.tile, torch.cuda.current_stream(x.device).cuda_stream)
+    if not padded:
+        return dst
+    if part is None:
+        return dst[:, :, :q.n].contiguous()
+    view = part.reshape(-1)[:need].view(slices, m, q.n)
+    view.copy_(dst[:, :, :q.n])
+    return view
 
 
 def prefill_matmul(x: torch.Tensor, q: Q4, *, f32: bool = False, tile: int = 0,

@@ -14,7 +14,8 @@ from pathlib import Path
 
 import numpy as np
 
-sys.path.insert(0, os.path.join(os.environ.get("TENSORFOLD_REFERENCE", "/root/reference"), "src"))
+# the reference checkout: $TENSORFOLD_REFERENCE, else a folder named "reference" beside this repository
+sys.path.insert(0, str(Path(os.environ.get("TENSORFOLD_REFERENCE") or Path(__file__).resolve().parents[3] / "reference") / "src"))
 from tensorfold.cuda.exl3 import format as fmt  # noqa: E402
 
 out = {}

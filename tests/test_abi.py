@@ -32,7 +32,7 @@ def test_binding_covers_the_header():
     from tensorfold_b200 import _lib
 
     bound = set(_lib.SIGNATURES) | {"tfb_last_error", "tfb_version", "tfb_set_pdl", "tfb_select_plan_max_rows",
-                                     "tfb_set_wait_limit_ms", "tfb_route_max_rows"}
+                                     "tfb_set_wait_limit_ms", "tfb_route_max_rows", "tfb_decode_kslices"}
     assert set(declared()) == bound
 
 

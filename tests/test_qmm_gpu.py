@@ -93,5 +93,35 @@ def test_group_sums_and_argument_errors():
     with pytest.raises(ValueError):
         qmm.matmul(x.float(), q)
     with pytest.raises(ValueError):
-        qmm.matmul(x, q, reduce=False)
+        qmm.matmul(x, q, sk=1)                                         # 10 groups are two slices: not the caller's choice
+    with pytest.raises(ValueError):
+        qmm.matmul(x, q, reduce=False, part=torch.empty(10, device=DEV))
     assert qmm.split_k(64, 2048) == 4 and qmm.split_k(64, 768) == 2 and qmm.bucket(3) == 8 and qmm.bucket(300) == 16
+
+
+@pytest.mark.parametrize("n,k,m", [(96, 512, 1), (200, 2048, 5), (1024, 768, 19), (64, 256, 3)])
+def test_k_slices_apart_add_up_to_the_reduced_bits(n, k, m):
+    """``matmul(reduce=False)``: fp32 (split_k, M, n) slices whose sum in slice order is ``matmul(f32=True)`` bit for
+    bit; ``part=`` is filled in place; one slice returns the product itself (the reference's contract,
+    src/tensorfold/cuda/kernels/qmm.py:156-177)."""
+
+    from tensorfold_b200 import qmm
+
+    w, s, b = mlx(n, k, n + k)
+    q = qmm.pack(w, s, b, 64)
+    x = rows(m, k, m)
+    whole = qmm.matmul(x, q, f32=True)
+    sk = qmm.split_k(n, k)
+    got = qmm.matmul(x, q, reduce=False)
+    if sk == 1:
+        assert got.shape == (m, n) and torch.equal(got.float(), qmm.matmul(x, q).float())
+        return
+    assert got.shape == (sk, m, n) and got.dtype == torch.float32 and got.is_contiguous()
+    total = got[0].clone()
+    for i in range(1, sk):
+        total += got[i]
+    assert torch.equal(total, whole)
+    assert float(got[sk - 1].abs().max()) > 0
+    part = torch.full((sk * m * n + 7,), 3.0, device=DEV)
+    again = qmm.matmul(x, q, reduce=False, part=part)
+    assert again.data_ptr() == part.data_ptr() and torch.equal(again, got) and bool((part[sk * m * n:] == 3.0).all())
