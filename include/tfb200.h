@@ -262,30 +262,38 @@ int tfb_exl3_group_static(const int32_t* pick, int32_t* uids, int32_t* ucount, i
  * ucount [1] = distinct experts; ids outside [0, E) are left out.  The other blocks rotate the inputs:
  * out0 / out1 [R * slots, K] fp16 = fp16(((x * suh_m[expert]) H) / sqrt(128)) for the two matrices of every routed pair
  * (suh1 and out1 null: one matrix); x is bf16 (x_is_fp16 = 0) or fp16 rows with stride x_stride.
+ * sorted (or null; needs `sort`): int32 [3, sorted_stride, 4], 16-byte aligned, filled with the items as (expert,
+ * first, count, index) once in the order of each projection's widths k2_g / k2_u / k2_d [E], widest first - hand the
+ * three tables to tfb_exl3_gateup / tfb_exl3_down when a layer's tensors differ in width, so that blocks that run
+ * together decode one width; sorted_stride >= the sort's item count.
  * Replaces `group` and `rot_in`: src/tensorfold/cuda/exl3/experts.cu:19-111,290-330. */
 int tfb_exl3_prologue(const void* x, int64_t x_stride, int x_is_fp16, const int32_t* pick, const void* suh0,
                       const void* suh1, void* out0, void* out1, int R, int K, int slots, int E, int sort,
-                      int32_t* members, int32_t* items, int32_t* counts, int32_t* ucount, void* stream);
+                      int32_t* members, int32_t* items, int32_t* counts, int32_t* ucount, const int32_t* k2_g,
+                      const int32_t* k2_u, const int32_t* k2_d, int32_t* sorted, int sorted_stride, void* stream);
 
 /* xd [P, N] fp16 = the down projection's rotated input of every routed pair, in one launch: gate and up (xg, xu
  * [P, K] fp16 times W_q of each pair's expert, trellises decoded on the fly from 16-byte aligned tp_* [E] at widths
  * k2_* [E]), output rotation, svh, SwiGLU (act_mode 0: bf16 roundings, 1: fp32; clipped at limit), suh_d, rotation.
  * items / counts / members: the prologue's sort; z: fp32 scratch [2, P, N]; arrive: int32 scratch
  * [max_items * N / 128], zero before the first call (a call leaves it zero); max_items >= the sort's item count.
+ * sorted_g / sorted_u (both or neither): the prologue's width-ordered items of the two matrices, [., 4] each.
  * Replaces `grouped` + `gateup_epilogue`: src/tensorfold/cuda/exl3/experts_grouped.cuh:190-284,
  * src/tensorfold/cuda/exl3/experts.cu:116-158. */
 int tfb_exl3_gateup(const void* xg, const void* xu, const int64_t* tp_g, const int64_t* tp_u, const int32_t* k2_g,
                     const int32_t* k2_u, const int32_t* items, const int32_t* counts, const int32_t* members, float* z,
                     int32_t* arrive, const void* svh_g, const void* svh_u, const void* suh_d, void* xd, int K, int N,
-                    int P, int cb, int max_items, float limit, int act_mode, void* stream);
+                    int P, int cb, int max_items, float limit, int act_mode, const int32_t* sorted_g,
+                    const int32_t* sorted_u, void* stream);
 
 /* y [P, N] fp32 = rotate(x [P, K] fp16 times W_q of each pair's expert) * svh for every routed pair (other rows are
- * left as they are), in one launch; z: fp32 scratch [P, N]; the other arguments as tfb_exl3_gateup.  The weighted
+ * left as they are), in one launch; z: fp32 scratch [P, N]; the other arguments as tfb_exl3_gateup (sorted: the
+ * prologue's width-ordered items of the down matrices, or null).  The weighted
  * slot-order sum over a row's slots is tfb_combine on y.
  * Replaces `grouped` + `down_epilogue` (+ `combine`, `down_combine`): src/tensorfold/cuda/exl3/experts.cu:161-237. */
 int tfb_exl3_down(const void* x, const int64_t* tp, const int32_t* k2, const int32_t* items, const int32_t* counts,
                   const int32_t* members, float* z, int32_t* arrive, const void* svh, float* y, int K, int N, int P,
-                  int cb, int max_items, void* stream);
+                  int cb, int max_items, const int32_t* sorted, void* stream);
 
 #ifdef __cplusplus
 }

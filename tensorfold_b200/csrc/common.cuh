@@ -238,6 +238,11 @@ __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepc
 // release half publishes, at GPU scope, everything the CTA's threads stored before the barrier (release is cumulative
 // over what the barrier ordered before it); the acquire half lets the CTA that sees the last count read the other
 // CTAs' parts after its next __syncthreads().  No per-thread fence is needed.
+__device__ __forceinline__ int4 ld_dep4(const int* p) {   // 16-byte aligned
+  int4 v;
+  asm volatile("ld.global.v4.s32 {%0, %1, %2, %3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
 __device__ __forceinline__ int arrive_count(int* counter) {
   int seen;
   asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], 1;\n" : "=r"(seen) : "l"(counter) : "memory");

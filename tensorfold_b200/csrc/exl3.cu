@@ -338,11 +338,20 @@ __device__ __forceinline__ void down_block(const float* z, const __half* svh, fl
   reinterpret_cast<float4*>(y + 8 * sub)[1] = b;
 }
 
+// What the prologue needs to lay the items out by width: the three matrices' width tables [E] and the table it fills,
+// [3, stride, 4] (gate, up, down order).
+struct WidthOrder {
+  const int* k2[3];
+  int* sorted;
+  int stride;
+};
+
 struct GroupedArgs {
   const __half* x[2];            // rotated inputs [P, K] fp16 of matrix 0 / 1
   const int64_t* tp[2];          // trellis pointers [E]
   const int* k2[2];              // half-bit widths [E]
   const int* items;              // [., 3] (expert, first, count <= 16)
+  const int* sorted[2];          // or null: the items in the order their CTAs should run, [., 4] = (expert, first, count, index)
   const int* counts;             // [0] = items
   const int* members;            // pair ids p = row * slots + slot, grouped by expert
   float* z;                      // [mats, P, N] fp32
@@ -367,7 +376,7 @@ grouped_kernel(const GroupedArgs a) {
   static_assert(GR_WARPS * GR_PAIRS * GR_RED_STRIDE * 4 <= GR_WARPS * GR_STAGES * GR_SLOT_BYTES,
                 "the K slices meet in the ring's memory");
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
-  const int it = blockIdx.x, nt0 = blockIdx.y * GR_NTB, mat = blockIdx.z;
+  const int nt0 = blockIdx.x * GR_NTB, mat = blockIdx.z;
   if (lane == 0) {
 #pragma unroll
     for (int s = 0; s < GR_STAGES; ++s) mbar_init(bars + warp * GR_STAGES + s, 1);
@@ -376,13 +385,19 @@ grouped_kernel(const GroupedArgs a) {
   }
   __syncwarp();
   pdl_wait();
-  const int *items = a.items, *counts = a.counts, *members = a.members;
+  const int *items = a.items, *counts = a.counts, *members = a.members, *sorted = a.sorted[mat];
   const __half* xin = a.x[mat];
-  after_wait(items, counts, members, xin);
+  after_wait(items, counts, members, xin, sorted);
   // the item is read together with the count that says whether it exists (its slot is always inside the table)
   const int n_items = ld_dep(counts);
-  const int e = ld_dep(items + 3 * it), first = ld_dep(items + 3 * it + 1), cnt = min(ld_dep(items + 3 * it + 2), GR_PAIRS);
-  if (it >= n_items) return;
+  int it = blockIdx.y, e, first, cnt;
+  if (sorted != nullptr) {                            // the CTA's place in the launch is not the item's index
+    const int4 s4 = ld_dep4(sorted + 4 * blockIdx.y);
+    e = s4.x, first = s4.y, cnt = min(s4.z, GR_PAIRS), it = s4.w;
+  } else {
+    e = ld_dep(items + 3 * it), first = ld_dep(items + 3 * it + 1), cnt = min(ld_dep(items + 3 * it + 2), GR_PAIRS);
+  }
+  if ((int)blockIdx.y >= n_items) return;
   if (tid < GR_PAIRS) pair_sh[tid] = tid < cnt ? ld_dep(members + first + tid) : -1;
   const uint8_t* T = reinterpret_cast<const uint8_t*>(a.tp[mat][e]);
   const int k2 = a.k2[mat][e];
@@ -446,7 +461,7 @@ grouped_kernel(const GroupedArgs a) {
   if (a.epi == GE_NONE) return;
   // Whoever finishes last among the CTAs that share (item, 128 columns) - two column halves, times the matrices -
   // finds every part of the block in z and runs the block's epilogue.
-  const int blk = blockIdx.y >> 1;
+  const int blk = blockIdx.x >> 1;
   int* counter = a.arrive + (size_t)it * (a.N >> 7) + blk;
   __syncthreads();
   if (tid == 0) {
@@ -507,16 +522,51 @@ __global__ void __launch_bounds__(PLAN_THREADS)
 exl3_prologue_kernel(const int* __restrict__ picks, int P, int E, int slots, int sort, int* __restrict__ members,
                      int* __restrict__ items, int* __restrict__ counts, int* __restrict__ ucount,
                      const TIN* __restrict__ x, int64_t x_stride, const __half* __restrict__ suh0,
-                     const __half* __restrict__ suh1, __half* __restrict__ out0, __half* __restrict__ out1, int K) {
+                     const __half* __restrict__ suh1, __half* __restrict__ out0, __half* __restrict__ out1, int K,
+                     exl3::WidthOrder wo) {
   extern __shared__ int whist[];
   __shared__ int first[PLAN_EMAX];
   __shared__ uint64_t tot2[2][PLAN_THREADS / 32];
+  __shared__ int bucket[3][16];
   pdl_wait();
   after_wait(picks, x);
   if (blockIdx.x == 0) {
     if (sort) {
       plan_block<PLAN_THREADS>(picks, P, E, exl3::GR_PAIRS, members, items, counts, whist, first, tot2);
       if (threadIdx.x == 0) ucount[0] = counts[1];    // written by this thread inside plan_block
+      if (wo.sorted != nullptr) {
+        // The items once more for each matrix, widest trellis first: blocks that run at the same time then decode the
+        // same width, i.e. run the same code (every width is its own unrolled loop; seven of them at once on an SM
+        // miss the instruction cache all the time).  The order inside a width is whatever the atomics give: no
+        // result depends on it.
+        if (threadIdx.x < 48) bucket[threadIdx.x / 16][threadIdx.x % 16] = 0;
+        __threadfence_block();
+        __syncthreads();
+        const int n = counts[0];
+        for (int i = threadIdx.x; i < n; i += PLAN_THREADS) {
+          const int e = items[3 * i];
+#pragma unroll
+          for (int m = 0; m < 3; ++m) atomicAdd(&bucket[m][16 - min(max(wo.k2[m][e], 1), 16)], 1);
+        }
+        __syncthreads();
+        if (threadIdx.x < 3) {
+          int run = 0;
+          for (int b = 0; b < 16; ++b) {
+            const int c = bucket[threadIdx.x][b];
+            bucket[threadIdx.x][b] = run;
+            run += c;
+          }
+        }
+        __syncthreads();
+        for (int i = threadIdx.x; i < n; i += PLAN_THREADS) {
+          const int4 item = make_int4(items[3 * i], items[3 * i + 1], items[3 * i + 2], i);
+#pragma unroll
+          for (int m = 0; m < 3; ++m) {
+            const int at = atomicAdd(&bucket[m][16 - min(max(wo.k2[m][item.x], 1), 16)], 1);
+            reinterpret_cast<int4*>(wo.sorted + (size_t)m * wo.stride * 4)[at] = item;
+          }
+        }
+      }
     }
     pdl_launch_dependents();
     return;
@@ -697,10 +747,18 @@ extern "C" int tfb_exl3_group_static(const int32_t* pick, int32_t* uids, int32_t
 // The first launch of a routed call: sorts the pairs by expert (when `sort`: members [R * slots], items
 // [(min(R * slots, E) + R * slots / 16), 3] = (expert, first, count <= 16), counts [2], ucount [1] = distinct experts)
 // and rotates the inputs: out0 / out1 [R * slots, K] fp16 for the two matrices (suh1 / out1 null: one matrix).
+// sorted (or null): int32 [3, sorted_stride, 4], filled with the items as (expert, first, count, index), once in the
+// order of each matrix's widths k2_g / k2_u / k2_d [E] (widest first), for tfb_exl3_gateup / tfb_exl3_down of a layer
+// whose tensors differ in width; sorted_stride >= the sort's items.
 extern "C" int tfb_exl3_prologue(const void* x, int64_t x_stride, int x_is_fp16, const int32_t* pick, const void* suh0,
                                  const void* suh1, void* out0, void* out1, int R, int K, int slots, int E, int sort,
-                                 int32_t* members, int32_t* items, int32_t* counts, int32_t* ucount, void* stream) {
+                                 int32_t* members, int32_t* items, int32_t* counts, int32_t* ucount,
+                                 const int32_t* k2_g, const int32_t* k2_u, const int32_t* k2_d, int32_t* sorted,
+                                 int sorted_stride, void* stream) {
   TFB_REQUIRE(x && pick && suh0 && out0, "exl3_prologue: null pointer");
+  TFB_REQUIRE(sorted == nullptr || (sort && k2_g && k2_u && k2_d && sorted_stride >= 1 && aligned16(sorted)),
+              "exl3_prologue: the width order needs the sort, the three width tables and a 16-byte aligned table");
+  const exl3::WidthOrder wo = {{k2_g, k2_u, k2_d}, sorted, sorted_stride};
   TFB_REQUIRE((suh1 == nullptr) == (out1 == nullptr), "exl3_prologue: the second matrix's scales and output come together");
   TFB_REQUIRE(!sort || (members && items && counts && ucount), "exl3_prologue: null sort table");
   TFB_REQUIRE(K > 0 && K % 128 == 0, "exl3_prologue: K must be a multiple of 128");
@@ -721,7 +779,7 @@ extern "C" int tfb_exl3_prologue(const void* x, int64_t x_stride, int x_is_fp16,
     if (int rc = plan_smem_opt_in(exl3_prologue_kernel<__half>, configured, "exl3_prologue: shared memory opt-in")) return rc;
     e = launch(exl3_prologue_kernel<__half>, grid, dim3(PLAN_THREADS), smem, st, pick, R * slots, E, slots, sort, members,
                items, counts, ucount, static_cast<const __half*>(x), x_stride, static_cast<const __half*>(suh0),
-               static_cast<const __half*>(suh1), static_cast<__half*>(out0), static_cast<__half*>(out1), K);
+               static_cast<const __half*>(suh1), static_cast<__half*>(out0), static_cast<__half*>(out1), K, wo);
   } else {
     static int configured[64] = {0};
     if (int rc = plan_smem_opt_in(exl3_prologue_kernel<__nv_bfloat16>, configured, "exl3_prologue: shared memory opt-in"))
@@ -729,7 +787,7 @@ extern "C" int tfb_exl3_prologue(const void* x, int64_t x_stride, int x_is_fp16,
     e = launch(exl3_prologue_kernel<__nv_bfloat16>, grid, dim3(PLAN_THREADS), smem, st, pick, R * slots, E, slots, sort,
                members, items, counts, ucount, static_cast<const __nv_bfloat16*>(x), x_stride,
                static_cast<const __half*>(suh0), static_cast<const __half*>(suh1), static_cast<__half*>(out0),
-               static_cast<__half*>(out1), K);
+               static_cast<__half*>(out1), K, wo);
   }
   return check_cuda(e, "exl3_prologue");
 }
@@ -739,8 +797,8 @@ static int exl3_grouped_launch(const char* who, const exl3::GroupedArgs& a, int 
   TFB_REQUIRE(cb >= 0 && cb <= 2, "%s: codebook must be 0 (3inst), 1 (mcg) or 2 (mul1)", who);
   TFB_REQUIRE(max_items >= 0 && a.P >= 0, "%s: bad sizes", who);
   if (max_items == 0 || a.P == 0) return TFB_OK;
-  TFB_REQUIRE(a.N / 64 <= 65535, "%s: too many columns for one launch", who);
-  const dim3 grid(max_items, a.N / (16 * exl3::GR_NTB), a.mats);
+  TFB_REQUIRE(max_items <= 65535, "%s: too many items for one launch", who);
+  const dim3 grid(a.N / (16 * exl3::GR_NTB), max_items, a.mats);       // an item's column blocks run together
   auto st = static_cast<cudaStream_t>(stream);
   cudaError_t e;
   if (cb == 0)
@@ -757,13 +815,16 @@ static int exl3_grouped_launch(const char* who, const exl3::GroupedArgs& a, int 
 // suh_d, rotation - one launch.  tp_*: int64 trellis pointers [E] (16-byte aligned trellises), k2_*: int32 [E];
 // items / counts / members: the prologue's sort; z: fp32 scratch [2, P, N]; arrive: int scratch
 // [max_items * N / 128], zero before the first call (every call leaves it zero); max_items >= the sort's items.
+// sorted_g / sorted_u (or null): the prologue's width orders of the two matrices ([., 4] each).
 // (exl3/experts.cpp `grouped` + `gateup_epilogue`: src/tensorfold/cuda/exl3/experts_grouped.cuh:190-284,
 // src/tensorfold/cuda/exl3/experts.cu:116-158)
 extern "C" int tfb_exl3_gateup(const void* xg, const void* xu, const int64_t* tp_g, const int64_t* tp_u,
                                const int32_t* k2_g, const int32_t* k2_u, const int32_t* items, const int32_t* counts,
                                const int32_t* members, float* z, int32_t* arrive, const void* svh_g, const void* svh_u,
                                const void* suh_d, void* xd, int K, int N, int P, int cb, int max_items, float limit,
-                               int act_mode, void* stream) {
+                               int act_mode, const int32_t* sorted_g, const int32_t* sorted_u, void* stream) {
+  TFB_REQUIRE((sorted_g == nullptr) == (sorted_u == nullptr) && aligned16(sorted_g) && aligned16(sorted_u),
+              "exl3_gateup: the two width orders come together, 16-byte aligned");
   TFB_REQUIRE(xg && xu && tp_g && tp_u && k2_g && k2_u && items && counts && members && z && arrive && svh_g && svh_u &&
                   suh_d && xd,
               "exl3_gateup: null pointer");
@@ -778,6 +839,8 @@ extern "C" int tfb_exl3_gateup(const void* xg, const void* xu, const int64_t* tp
   a.k2[0] = k2_g;
   a.k2[1] = k2_u;
   a.items = items;
+  a.sorted[0] = sorted_g;
+  a.sorted[1] = sorted_u;
   a.counts = counts;
   a.members = members;
   a.z = z;
@@ -797,18 +860,22 @@ extern "C" int tfb_exl3_gateup(const void* xg, const void* xu, const int64_t* tp
 }
 
 // y [P, N] fp32 = rotate(x [P, K] fp16 times W_q of each pair's expert) * svh of every routed pair (rows of other
-// pairs are left as they are) - one launch; z: fp32 scratch [P, N]; the other arguments as tfb_exl3_gateup.
+// pairs are left as they are) - one launch; z: fp32 scratch [P, N]; the other arguments as tfb_exl3_gateup
+// (sorted: the prologue's width order of the down matrices, or null).
 // (exl3/experts.cpp `grouped` + `down_epilogue`: src/tensorfold/cuda/exl3/experts.cu:161-180)
 extern "C" int tfb_exl3_down(const void* x, const int64_t* tp, const int32_t* k2, const int32_t* items,
                              const int32_t* counts, const int32_t* members, float* z, int32_t* arrive, const void* svh,
-                             float* y, int K, int N, int P, int cb, int max_items, void* stream) {
+                             float* y, int K, int N, int P, int cb, int max_items, const int32_t* sorted,
+                             void* stream) {
   TFB_REQUIRE(x && tp && k2 && items && counts && members && z && arrive && svh && y, "exl3_down: null pointer");
+  TFB_REQUIRE(aligned16(sorted), "exl3_down: the width order must be 16-byte aligned");
   TFB_REQUIRE(aligned16(z) && aligned16(svh) && aligned16(y), "exl3_down: 16-byte aligned rows");
   exl3::GroupedArgs a = {};
   a.x[0] = a.x[1] = static_cast<const __half*>(x);
   a.tp[0] = a.tp[1] = tp;
   a.k2[0] = a.k2[1] = k2;
   a.items = items;
+  a.sorted[0] = a.sorted[1] = sorted;
   a.counts = counts;
   a.members = members;
   a.z = z;

@@ -89,6 +89,12 @@ class Exl3RoutedExperts:
     def nbytes_read(self, ids: Sequence[int]) -> int:
         return int(self.trellis_bytes[list(ids)].sum())
 
+    @property
+    def mixed(self) -> bool:
+        """The tensors of a projection differ in width: the kernels then run the items width by width."""
+
+        return self.k2_gu[0] != self.k2_gu[1] or self.k2_d[0] != self.k2_d[1]
+
 
 class _Projection:
     """The experts' matrices of one projection (K -> N): checked, then one pointer table, one width table and the two
@@ -187,6 +193,8 @@ class Scratch:
         self.sort_members, self.sort_items = buf((pairs,), torch.int32), buf((max(1, items), 3), torch.int32)
         self.sort_counts = buf((2,), torch.int32)
         self.arrive = buf((max(1, items) * (max(ex.width, ex.dims) // 128),), torch.int32)
+        # the items once more in the order of each projection's widths (gate, up, down), for layers of mixed widths
+        self.by_width = buf((3, max(1, items), 4), torch.int32)
 
     def window(self, R: int):
         """(ids, members) sized for R rows: the grids only span what R rows can use."""
@@ -227,17 +235,20 @@ def routed(x: torch.Tensor, pick: torch.Tensor, wts: torch.Tensor | None, ex: Ex
         raise ValueError("act_mode is ACT_BF16 or ACT_F32")
     st, items = _stream(x), max_items(pairs, ex.count)
     sort = (s.sort_members.data_ptr(), s.sort_items.data_ptr(), s.sort_counts.data_ptr())
+    # a layer of mixed widths: the prologue lays the items out width by width, once a projection
+    order = [s.by_width[m].data_ptr() for m in range(3)] if ex.mixed and group_first else [0, 0, 0]
     with torch.cuda.device(x.device):
         _lib.call("tfb_exl3_prologue", x.data_ptr(), x.stride(0), int(x.dtype == torch.float16), pick.data_ptr(),
                   ex.suh_g.data_ptr(), ex.suh_u.data_ptr(), s.xg.data_ptr(), s.xu.data_ptr(), R, dims, slots, ex.count,
-                  int(group_first), *sort, s.count.data_ptr(), st)
+                  int(group_first), *sort, s.count.data_ptr(), ex.gate_k2.data_ptr(), ex.up_k2.data_ptr(),
+                  ex.down_k2.data_ptr(), order[0], s.by_width.shape[1], st)
         tables = (sort[1], sort[2], sort[0], s.z.data_ptr(), s.arrive.data_ptr())
         _lib.call("tfb_exl3_gateup", s.xg.data_ptr(), s.xu.data_ptr(), ex.gate_ptr.data_ptr(), ex.up_ptr.data_ptr(),
                   ex.gate_k2.data_ptr(), ex.up_k2.data_ptr(), *tables, ex.svh_g.data_ptr(), ex.svh_u.data_ptr(),
                   ex.suh_d.data_ptr(), s.xd.data_ptr(), dims, width, pairs, ex.cb, items, float(min(limit, 3.0e38)),
-                  act_mode, st)
+                  act_mode, order[0], order[1], st)
         _lib.call("tfb_exl3_down", s.xd.data_ptr(), ex.down_ptr.data_ptr(), ex.down_k2.data_ptr(), *tables,
-                  ex.svh_d.data_ptr(), s.y.data_ptr(), width, dims, pairs, ex.cb, items, st)
+                  ex.svh_d.data_ptr(), s.y.data_ptr(), width, dims, pairs, ex.cb, items, order[2], st)
         if wts is None:
             return s.y[:pairs]
         if out is None:

@@ -124,11 +124,12 @@ class Exl3Linear:
         s = _stream(x)
         with torch.cuda.device(dev):
             _lib.call("tfb_exl3_prologue", x.data_ptr(), x.stride(0), int(x.dtype == torch.float16),
-                      t["pick"].data_ptr(), self.suh.data_ptr(), 0, xh.data_ptr(), 0, m, self.k, 1, 1, 0, 0, 0, 0, 0, s)
+                      t["pick"].data_ptr(), self.suh.data_ptr(), 0, xh.data_ptr(), 0, m, self.k, 1, 1, 0, 0, 0, 0, 0,
+                      0, 0, 0, 0, 0, s)
             _lib.call("tfb_exl3_down", xh.data_ptr(), t["ptr"].data_ptr(), t["k2"].data_ptr(), t["items"].data_ptr(),
                       t["counts"].data_ptr(), t["members"].data_ptr(), z.data_ptr(), t["arrive"].data_ptr(),
                       self.svh.data_ptr(), y.data_ptr(), self.k, self.n, m, CODEBOOK_IDS[self.codebook], t["n_items"],
-                      s)
+                      0, s)
         if self.bias is not None:
             y += self.bias.float()
         want = out_dtype or (out.dtype if out is not None else x.dtype)

@@ -148,13 +148,18 @@ def test_per_slot_output_and_fused_combine_agree():
     assert torch.equal(s.y[:R * TOPK].view(R, TOPK, D), y)         # the fused launch stores the same per-slot y
 
 
-def test_grouping_ahead_of_the_call_gives_the_same_rows():
-    """``group`` then ``routed(group_first=False)`` (the caller grouped already) equals the call that groups itself."""
+@pytest.mark.parametrize("widths", [lambda e: (8, 8, 4), lambda e: ((4, 16, 7)[e % 3], (5, 8)[e % 2], (2, 9, 12, 6)[e % 4])],
+                         ids=["one_width", "mixed_widths"])
+def test_grouping_ahead_of_the_call_gives_the_same_rows(widths):
+    """``group`` then ``routed(group_first=False)`` (the caller grouped already) equals the call that groups itself.
+    With mixed widths the self-grouping call also runs its items width by width (the other does not): same bits, and
+    the three width-ordered tables are the items, each once, widest first."""
 
     from tensorfold_b200.exl3 import experts
 
     E, D, I, TOPK, R = 10, 256, 128, 3, 37
-    ex, _ = _layer(E, D, I, [(6, 8, 4)] * E, 0, 27)
+    ex, _ = _layer(E, D, I, [widths(e) for e in range(E)], 0, 27)
+    assert ex.mixed == (widths(0) != widths(1))
     g = torch.Generator().manual_seed(12)
     x = torch.randn((R, D), generator=g).to(torch.bfloat16).to(DEV)
     sel, w = _picks(E, R, TOPK, g, shared=True)
@@ -165,6 +170,15 @@ def test_grouping_ahead_of_the_call_gives_the_same_rows():
     got = experts.routed(x, sel, w, ex, s2, None, R, group_first=False)
     assert torch.equal(got, want)
     assert int(s2.count[0]) == int(s.count[0]) == len(set(sel[:, :TOPK].reshape(-1).tolist()))
+    if ex.mixed:
+        n = int(s.sort_counts[0])
+        items = s.sort_items[:n].cpu()
+        for m, k2 in enumerate((ex.gate_k2, ex.up_k2, ex.down_k2)):
+            table = s.by_width[m, :n].cpu()
+            assert sorted(table[:, 3].tolist()) == list(range(n))                  # every item once
+            assert torch.equal(table[:, :3], items[table[:, 3].long()])             # with its own three fields
+            seen = k2.cpu()[table[:, 0].long()].tolist()
+            assert seen == sorted(seen, reverse=True)                               # widest first
 
 
 def test_graph_replay_equals_eager(pdl):
