@@ -623,6 +623,75 @@ def one_gpu_layer(torch, x, router, full, shape, bias):
     return moe.combine(buf.y[:rows], buf.wts[:rows]), buf.pick[:rows].clone()
 
 
+def bench_rank_slice(torch, args, shape, dev, hbm: float) -> dict:
+    """One GPU doing what one rank of an `--as-rank-of N` group does between its two exchanges, for profiling that
+    regime under ncu (never wrap a multi-rank run in ncu): the rank's 128 / N experts, the 64 * N tokens of all ranks
+    routed over all experts, the plan over the rank's expert window, gate/up and down.  The slice's weight copies
+    rotate so every step reads DRAM.  Times the two expert launches together and gate/up alone."""
+
+    from tensorfold_b200 import _lib, experts, moe, synthetic
+
+    n = args.as_rank_of
+    rows, per = (args.rows or 64) * n, shape.experts // n
+    router = synthetic.router_rows(shape, dev)
+    x = synthetic.activations(shape, rows, dev, index=100)
+
+    class _Cfg:
+        num_experts_per_tok, num_experts = shape.top_k, shape.experts
+        moe_intermediate_size, hidden_size = shape.width, shape.dims
+
+    buf = moe.MoEBuffers(rows, _Cfg, dev, shared=False)
+    moe.router(x, router, buf.logits)
+    moe.select_rows(buf.logits, buf, shape.top_k, shape.experts)
+    wide = rows * shape.top_k >= 24 * shape.experts              # the expert-parallel step's own rule for items of 16
+    plan = experts.Plan(rows, shape.top_k, per, dev, decode_tile=experts.WIDE_TILE if wide else experts.TILE)
+    plan.tile = plan.decode_tile
+    st = torch.cuda.current_stream(dev).cuda_stream
+    _lib.call("tfb_plan_window", buf.pick.data_ptr(), rows * shape.top_k, 0, per, plan.tile, plan.members.data_ptr(),
+              plan.items.data_ptr(), plan.counts.data_ptr(), st)
+    torch.cuda.synchronize()
+    pairs = int((buf.pick < per).sum())
+    slices = []
+    for copy in range(2 * n):                                     # as a rank of the group does: 2 N copies of its slice
+        gate, up, down = synthetic.affine_layer(shape, dev, torch.float16 if args.scales == "fp16" else torch.bfloat16,
+                                                copy=copy)
+        cut = slice(0, per)
+        slices.append(experts.make([tuple(t[cut].contiguous() for t in gate), tuple(t[cut].contiguous() for t in up)],
+                                   tuple(t[cut].contiguous() for t in down), 64))
+        del gate, up, down
+    act = torch.zeros((rows * shape.top_k, shape.width), dtype=torch.bfloat16, device=dev)
+    y = torch.zeros((rows * shape.top_k, shape.dims), dtype=torch.float32, device=dev)
+
+    def graph_of(body):
+        side = torch.cuda.Stream(dev)
+        side.wait_stream(torch.cuda.current_stream())
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=side):
+            body()
+        return g
+
+    def both():
+        for ex in slices:
+            experts.gate_up(x, ex, plan, act, rows)
+            experts.down(act, ex, plan, y, rows)
+
+    def first():
+        for ex in slices:
+            experts.gate_up(x, ex, plan, act, rows)
+
+    both()
+    torch.cuda.synchronize()
+    g_both, g_first = graph_of(both), graph_of(first)
+    k = len(slices)
+    ms_both, _ = timed(torch, lambda i: g_both.replay(), max(args.steps // k, 3), args.warmup, 5)
+    ms_first, _ = timed(torch, lambda i: g_first.replay(), max(args.steps // k, 3), args.warmup, 5)
+    nbytes = per * slices[0].bytes_per_expert()
+    return {"as_rank_of": n, "experts": per, "tokens": rows, "pairs_in_window": pairs, "items_of": plan.tile,
+            "weight_copies": k, "slice_bytes": nbytes, "gate_up_plus_down_us": ms_both / k * 1e3,
+            "gate_up_us": ms_first / k * 1e3, "frac_of_hbm": nbytes / (ms_both / k * 1e-3) / 1e9 / hbm,
+            "gate_up_frac_of_hbm": nbytes * 2 / 3 / (ms_first / k * 1e-3) / 1e9 / hbm}
+
+
 def bench_ep(torch, dist, args, config: str, shape, dev, rank: int, world: int) -> dict:
     """Expert-parallel step of the affine layer: this rank's rows through the layer whose experts are sharded over the
     ranks.  Each rank keeps several copies of its expert slice and rotates them, so a step's weights never sit in L2.
@@ -963,6 +1032,12 @@ def run_ours(args) -> None:
         print(json.dumps({"sweep": bench_exl3(torch, args.exl3_rows, args.steps, args.warmup, hbm)}))
         dist.destroy_process_group()
         return
+    if args.as_rank_of:
+        if world != 1 or synthetic.C2.experts % args.as_rank_of:
+            raise SystemExit("--as-rank-of N runs on one GPU, N a divisor of the expert count")
+        print(json.dumps(bench_rank_slice(torch, args, synthetic.C2, dev, hbm)))
+        dist.destroy_process_group()
+        return
     shapes = {"c2": synthetic.C2, "c4": synthetic.C4, "c5": synthetic.C5}
     if args.config != "c2" and args.ep_reduce != "peer":
         raise SystemExit(f"--config {args.config} runs the peer-memory form")
@@ -1126,6 +1201,8 @@ def main() -> None:
     ap.add_argument("--hot-pairs", type=int, default=-1,
                     help="expert-parallel peer form: experts with at least this many pairs use the prompt-form kernel "
                          "(default 0: never)")
+    ap.add_argument("--as-rank-of", type=int, default=0,
+                    help="one GPU runs the expert launches of one rank of an N-rank config-2 group (for profiling)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline legs")
     ap.add_argument("--no-sweep", action="store_true", help="skip the 1-, 4-, 16- and 2048-token and EXL3 lines")
     ap.add_argument("--no-extra", action="store_true", help="skip configs 4 and 5")
