@@ -256,9 +256,10 @@ int tfb_exl3_group(const int32_t* pick, int32_t* uids, int32_t* ucount, int32_t*
 int tfb_exl3_group_static(const int32_t* pick, int32_t* uids, int32_t* ucount, int32_t* members, int R, int slots,
                           int E, int maxu, int maxm, void* stream);
 
-/* The first launch of a routed EXL3 call.  When `sort` != 0 one block sorts the (row, slot) pairs by expert:
- * members [R * slots] = pair ids grouped by ascending expert (pair order kept), items [., 3] = (expert, first,
- * count <= 16) with room for min(R * slots, E) + R * slots / 16 rows, counts [2] = (items, distinct experts),
+/* The first launch of a routed EXL3 call.  When `sort` != 0 (then 16 or 32: the pairs an item holds) one block sorts
+ * the (row, slot) pairs by expert: members [R * slots] = pair ids grouped by ascending expert (pair order kept),
+ * items [., 3] = (expert, first, count <= sort) with room for min(R * slots, E) + R * slots / sort rows, counts [2] =
+ * (items, distinct experts),
  * ucount [1] = distinct experts; ids outside [0, E) are left out.  The other blocks rotate the inputs:
  * out0 / out1 [R * slots, K] fp16 = fp16(((x * suh_m[expert]) H) / sqrt(128)) for the two matrices of every routed pair
  * (suh1 and out1 null: one matrix); x is bf16 (x_is_fp16 = 0) or fp16 rows with stride x_stride.
@@ -278,13 +279,15 @@ int tfb_exl3_prologue(const void* x, int64_t x_stride, int x_is_fp16, const int3
  * items / counts / members: the prologue's sort; z: fp32 scratch [2, P, N]; arrive: int32 scratch
  * [max_items * N / 128], zero before the first call (a call leaves it zero); max_items >= the sort's item count.
  * sorted_g / sorted_u (both or neither): the prologue's width-ordered items of the two matrices, [., 4] each.
+ * item_pairs: 16 or 32, the most pairs an item holds (with 32 one decode of a weight tile serves up to 32 pairs, at
+ * more registers a thread: for calls with many pairs an expert); a pair's bits do not depend on it.
  * Replaces `grouped` + `gateup_epilogue`: src/tensorfold/cuda/exl3/experts_grouped.cuh:190-284,
  * src/tensorfold/cuda/exl3/experts.cu:116-158. */
 int tfb_exl3_gateup(const void* xg, const void* xu, const int64_t* tp_g, const int64_t* tp_u, const int32_t* k2_g,
                     const int32_t* k2_u, const int32_t* items, const int32_t* counts, const int32_t* members, float* z,
                     int32_t* arrive, const void* svh_g, const void* svh_u, const void* suh_d, void* xd, int K, int N,
                     int P, int cb, int max_items, float limit, int act_mode, const int32_t* sorted_g,
-                    const int32_t* sorted_u, void* stream);
+                    const int32_t* sorted_u, int item_pairs, void* stream);
 
 /* y [P, N] fp32 = rotate(x [P, K] fp16 times W_q of each pair's expert) * svh for every routed pair (other rows are
  * left as they are), in one launch; z: fp32 scratch [P, N]; the other arguments as tfb_exl3_gateup (sorted: the
@@ -293,7 +296,14 @@ int tfb_exl3_gateup(const void* xg, const void* xu, const int64_t* tp_g, const i
  * Replaces `grouped` + `down_epilogue` (+ `combine`, `down_combine`): src/tensorfold/cuda/exl3/experts.cu:161-237. */
 int tfb_exl3_down(const void* x, const int64_t* tp, const int32_t* k2, const int32_t* items, const int32_t* counts,
                   const int32_t* members, float* z, int32_t* arrive, const void* svh, float* y, int K, int N, int P,
-                  int cb, int max_items, const int32_t* sorted, void* stream);
+                  int cb, int max_items, const int32_t* sorted, int item_pairs, void* stream);
+
+/* The output side of an EXL3 product formed elsewhere (prompts: a dense fp16 GEMM over the decoded W_q):
+ * out [M, N] (out_type 0 fp32, 1 fp16, 2 bf16; rows out_stride elements apart) = rotate(z) / sqrt(128) * svh + bias
+ * for every 128-column block of z [M, N] fp32; bias fp16 [N] or null.
+ * Replaces the epilogue of `_gemm`: src/tensorfold/cuda/exl3/prefill.py:15-44. */
+int tfb_exl3_rot_out(const float* z, const void* svh, const void* bias, void* out, int64_t out_stride, int out_type,
+                     int M, int N, void* stream);
 
 #ifdef __cplusplus
 }

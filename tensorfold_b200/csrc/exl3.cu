@@ -18,6 +18,8 @@
 // Fixed-order reductions everywhere: a pair's bits never depend on the other rows of the call.
 // (Replaces src/tensorfold/cuda/exl3/experts.cu and experts_grouped.cuh; the trellises are read in place.)
 
+#include <type_traits>
+
 #include "api.h"
 #include "common.cuh"
 
@@ -27,8 +29,9 @@ namespace exl3 {
 constexpr float HAD_SCALE = 0.08838834764831845f;   // 1 / sqrt(128)
 constexpr int GR_WARPS = 4;                         // K slices a CTA (part of the arithmetic: they meet in warp order)
 constexpr int GR_NTB = 4;                           // 16-column tiles a CTA: 64 columns
-constexpr int GR_PT = 2;                            // mma tiles of 8 pairs an item: 16 pairs
+constexpr int GR_PT = 2;                            // mma tiles of 8 pairs an item: 16 pairs (4: the wide items, 32 pairs)
 constexpr int GR_PAIRS = 8 * GR_PT;
+constexpr int GR_WIDE_PT = 4;
 constexpr int GR_SLOT_BYTES = 2048;                 // a ring slot: whole rows of the CTA's four tiles
 constexpr int GR_STAGES = 3;
 constexpr int GR_RED_STRIDE = GR_NTB * 16 + 1;
@@ -154,17 +157,17 @@ __device__ __forceinline__ void mma_f16(float (&d)[4], const uint32_t (&a)[4], u
 // ring: a slot holds ROWS whole rows (one bulk copy a row: the four tiles of a row are contiguous in the trellis), the
 // elected lane refills a slot as soon as the warp has decoded it.  The rows of a slot are unrolled in blocks of up to
 // four, whose inputs are loaded before the block's tiles are decoded.  x[pt]: the lane's pair (B column lane / 4 of
-// tile pt) at input 16 kt0 + 2 (lane % 4).  TWO: the item holds more than eight pairs (the second mma tile is live).
+// tile pt) at input 16 kt0 + 2 (lane % 4).  NPT: the mma tiles of eight pairs that are live (one decode feeds them all).
 // Returns false when a copy never landed.
-template <int CB, int K2, bool TWO>
+template <int CB, int K2, int PT, int NPT>
 __device__ __forceinline__ bool warp_rows(const uint8_t* __restrict__ T, int ntiles, int kt0, int nkt, int nt0,
-                                          const __half* const (&x)[GR_PT], uint8_t* ring, uint64_t* bars, int lane,
-                                          float (&acc)[GR_NTB][GR_PT][4]) {
+                                          const __half* const (&x)[PT], uint8_t* ring, uint64_t* bars, int lane,
+                                          float (&acc)[GR_NTB][PT][4]) {
   constexpr int TW = Win<K2>::TW, NW = Win<K2>::NW;
   constexpr int TILE_B = 16 * K2, SEG = GR_NTB * TILE_B;              // bytes a tile / a row of the CTA's tiles
   constexpr int ROWS = GR_SLOT_BYTES / SEG < 1 ? 1 : (GR_SLOT_BYTES / SEG > 16 ? 16 : GR_SLOT_BYTES / SEG);
-  constexpr int RB = ROWS < 4 ? ROWS : 4;                             // rows a block
-  constexpr int NPT = TWO ? GR_PT : 1;
+  constexpr int RBMAX = NPT > 2 ? 2 : 4;                              // rows a block (their inputs sit in registers)
+  constexpr int RB = ROWS < RBMAX ? ROWS : RBMAX;
   static_assert(ROWS * SEG <= GR_SLOT_BYTES, "a slot holds whole rows");
   const int nslot = (nkt + ROWS - 1) / ROWS;
   const uint8_t* src = T + ((size_t)kt0 * ntiles + nt0) * TILE_B;
@@ -189,7 +192,9 @@ __device__ __forceinline__ bool warp_rows(const uint8_t* __restrict__ T, int nti
       wi = wi + 1 == TW ? 0 : wi + 1;
     }
   }
-  const __half* xp[GR_PT] = {x[0], x[1]};
+  const __half* xp[PT];
+#pragma unroll
+  for (int pt = 0; pt < PT; ++pt) xp[pt] = x[pt];
   int stage = 0;
   uint32_t phase = 0;
   for (int f = 0; f < nslot; ++f) {
@@ -224,15 +229,15 @@ __device__ __forceinline__ bool warp_rows(const uint8_t* __restrict__ T, int nti
 #pragma unroll
               for (int j = 0; j < NW; ++j) w[j] = tile[word[j]];
               decode_words<CB, K2>(w, lane, a);
-              mma_f16(acc[i][0], a, b[r][0][0], b[r][0][1]);
-              if constexpr (TWO) mma_f16(acc[i][1], a, b[r][1][0], b[r][1][1]);   // one decode, both pair tiles
+#pragma unroll
+              for (int pt = 0; pt < NPT; ++pt) mma_f16(acc[i][pt], a, b[r][pt][0], b[r][pt][1]);   // one decode, every pair tile
             }
           }
         }
       }
     }
-    xp[0] += ROWS * 16;
-    xp[1] += ROWS * 16;
+#pragma unroll
+    for (int pt = 0; pt < PT; ++pt) xp[pt] += ROWS * 16;
     __syncwarp();
     if (lane == 0 && f + GR_STAGES < nslot) issue(f + GR_STAGES);
     if (++stage == GR_STAGES) {
@@ -365,16 +370,18 @@ struct GroupedArgs {
 
 enum GroupedEpilogue : int { GE_NONE = 0, GE_GATEUP = 1, GE_DOWN = 2 };
 
-// CTA (item, 64 columns, matrix).
-template <int CB>
+// CTA (item, 64 columns, matrix).  PT: mma tiles of eight pairs an item may hold (2: items of 16 pairs; 4: items of 32,
+// for calls with many pairs an expert - every weight tile is then decoded once for up to 32 pairs).
+template <int CB, int PT>
 __global__ void __launch_bounds__(GR_WARPS * 32)
 grouped_kernel(const GroupedArgs a) {
-  __shared__ __align__(128) uint8_t ring[GR_WARPS * GR_STAGES * GR_SLOT_BYTES];
+  constexpr int PAIRS = 8 * PT;
+  constexpr int RING_BYTES = GR_WARPS * GR_STAGES * GR_SLOT_BYTES, RED_BYTES = GR_WARPS * PAIRS * GR_RED_STRIDE * 4;
+  // the K slices meet in the ring's memory (free by then)
+  __shared__ __align__(128) uint8_t ring[RING_BYTES > RED_BYTES ? RING_BYTES : RED_BYTES];
   __shared__ uint64_t bars[GR_WARPS * GR_STAGES];
-  __shared__ int pair_sh[GR_PAIRS];
+  __shared__ int pair_sh[PAIRS];
   __shared__ int last_sh;
-  static_assert(GR_WARPS * GR_PAIRS * GR_RED_STRIDE * 4 <= GR_WARPS * GR_STAGES * GR_SLOT_BYTES,
-                "the K slices meet in the ring's memory");
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
   const int nt0 = blockIdx.x * GR_NTB, mat = blockIdx.z;
   if (lane == 0) {
@@ -393,37 +400,41 @@ grouped_kernel(const GroupedArgs a) {
   int it = blockIdx.y, e, first, cnt;
   if (sorted != nullptr) {                            // the CTA's place in the launch is not the item's index
     const int4 s4 = ld_dep4(sorted + 4 * blockIdx.y);
-    e = s4.x, first = s4.y, cnt = min(s4.z, GR_PAIRS), it = s4.w;
+    e = s4.x, first = s4.y, cnt = min(s4.z, PAIRS), it = s4.w;
   } else {
-    e = ld_dep(items + 3 * it), first = ld_dep(items + 3 * it + 1), cnt = min(ld_dep(items + 3 * it + 2), GR_PAIRS);
+    e = ld_dep(items + 3 * it), first = ld_dep(items + 3 * it + 1), cnt = min(ld_dep(items + 3 * it + 2), PAIRS);
   }
   if ((int)blockIdx.y >= n_items) return;
-  if (tid < GR_PAIRS) pair_sh[tid] = tid < cnt ? ld_dep(members + first + tid) : -1;
+  if (tid < PAIRS) pair_sh[tid] = tid < cnt ? ld_dep(members + first + tid) : -1;
   const uint8_t* T = reinterpret_cast<const uint8_t*>(a.tp[mat][e]);
   const int k2 = a.k2[mat][e];
-  const bool two = cnt > 8;
+  const int live = (cnt + 7) >> 3;                   // mma tiles of pairs in use
   // lanes past the item's last pair read its first pair's row: an mma column depends on its own inputs only
   const int KT = a.K >> 4, per_warp = (KT + GR_WARPS - 1) / GR_WARPS;
   const int kt0 = min(KT, warp * per_warp), nkt = min(KT, kt0 + per_warp) - kt0;
-  const __half* x[GR_PT];
+  const __half* x[PT];
 #pragma unroll
-  for (int pt = 0; pt < GR_PT; ++pt) {
+  for (int pt = 0; pt < PT; ++pt) {
     const int p = ld_dep(members + first + (8 * pt + g < cnt ? 8 * pt + g : 0));
     x[pt] = xin + (size_t)p * a.K + kt0 * 16 + 2 * t;
   }
-  float acc[GR_NTB][GR_PT][4];
+  float acc[GR_NTB][PT][4];
 #pragma unroll
   for (int i = 0; i < GR_NTB; ++i)
 #pragma unroll
-    for (int pt = 0; pt < GR_PT; ++pt) acc[i][pt][0] = acc[i][pt][1] = acc[i][pt][2] = acc[i][pt][3] = 0.f;
+    for (int pt = 0; pt < PT; ++pt) acc[i][pt][0] = acc[i][pt][1] = acc[i][pt][2] = acc[i][pt][3] = 0.f;
   bool ok = true;
   uint8_t* my_ring = ring + warp * (GR_STAGES * GR_SLOT_BYTES);
   uint64_t* my_bars = bars + warp * GR_STAGES;
   switch (k2) {
 #define TFB_K2(K2_)                                                                                       \
   case K2_:                                                                                               \
-    ok = two ? warp_rows<CB, K2_, true>(T, a.N >> 4, kt0, nkt, nt0, x, my_ring, my_bars, lane, acc)        \
-             : warp_rows<CB, K2_, false>(T, a.N >> 4, kt0, nkt, nt0, x, my_ring, my_bars, lane, acc);      \
+    if constexpr (PT == 2)                                                                                \
+      ok = live > 1 ? warp_rows<CB, K2_, 2, 2>(T, a.N >> 4, kt0, nkt, nt0, x, my_ring, my_bars, lane, acc)  \
+                    : warp_rows<CB, K2_, 2, 1>(T, a.N >> 4, kt0, nkt, nt0, x, my_ring, my_bars, lane, acc); \
+    else                                                                                                  \
+      ok = live > 2 ? warp_rows<CB, K2_, 4, 4>(T, a.N >> 4, kt0, nkt, nt0, x, my_ring, my_bars, lane, acc)  \
+                    : warp_rows<CB, K2_, 4, 2>(T, a.N >> 4, kt0, nkt, nt0, x, my_ring, my_bars, lane, acc); \
     break;
     TFB_K2(2) TFB_K2(3) TFB_K2(4) TFB_K2(5) TFB_K2(6) TFB_K2(7) TFB_K2(8) TFB_K2(9) TFB_K2(10) TFB_K2(11) TFB_K2(12)
     TFB_K2(13) TFB_K2(14) TFB_K2(15) TFB_K2(16)
@@ -441,21 +452,21 @@ grouped_kernel(const GroupedArgs a) {
 #pragma unroll
   for (int i = 0; i < GR_NTB; ++i)
 #pragma unroll
-    for (int pt = 0; pt < GR_PT; ++pt) {
-      float* base = red + (warp * GR_PAIRS + 8 * pt + 2 * t) * GR_RED_STRIDE + i * 16 + g;
+    for (int pt = 0; pt < PT; ++pt) {
+      float* base = red + (warp * PAIRS + 8 * pt + 2 * t) * GR_RED_STRIDE + i * 16 + g;
       base[0] = acc[i][pt][0];
       base[GR_RED_STRIDE] = acc[i][pt][1];
       base[8] = acc[i][pt][2];
       base[GR_RED_STRIDE + 8] = acc[i][pt][3];
     }
   __syncthreads();
-  for (int o = tid; o < GR_PAIRS * GR_NTB * 16; o += GR_WARPS * 32) {
+  for (int o = tid; o < PAIRS * GR_NTB * 16; o += GR_WARPS * 32) {
     const int pi = o / (GR_NTB * 16), col = o % (GR_NTB * 16);
     const int p = pair_sh[pi];
     if (p < 0) continue;
     float s = red[pi * GR_RED_STRIDE + col];
 #pragma unroll
-    for (int w = 1; w < GR_WARPS; ++w) s += red[(w * GR_PAIRS + pi) * GR_RED_STRIDE + col];
+    for (int w = 1; w < GR_WARPS; ++w) s += red[(w * PAIRS + pi) * GR_RED_STRIDE + col];
     a.z[((size_t)mat * a.P + p) * a.N + nt0 * 16 + col] = s;
   }
   if (a.epi == GE_NONE) return;
@@ -475,7 +486,7 @@ grouped_kernel(const GroupedArgs a) {
   // a half warp a pair (the transform's shuffles need every lane of the warp: a half without a pair repeats the item's
   // first pair and stores nothing); pairs fill an item from the front, so a warp whose first pair is missing is done
   const int sub = lane & 15, half = lane >> 4;
-  for (int p0 = 2 * warp; p0 < GR_PAIRS && pair_sh[p0] >= 0; p0 += 2 * GR_WARPS) {
+  for (int p0 = 2 * warp; p0 < PAIRS && pair_sh[p0] >= 0; p0 += 2 * GR_WARPS) {
     const int p = pair_sh[p0 + half];
     const int q = p < 0 ? pair_sh[0] : p;
     const size_t at = (size_t)q * a.N + blk * 128, sc = (size_t)e * a.N + blk * 128;
@@ -532,7 +543,7 @@ exl3_prologue_kernel(const int* __restrict__ picks, int P, int E, int slots, int
   after_wait(picks, x);
   if (blockIdx.x == 0) {
     if (sort) {
-      plan_block<PLAN_THREADS>(picks, P, E, exl3::GR_PAIRS, members, items, counts, whist, first, tot2);
+      plan_block<PLAN_THREADS>(picks, P, E, sort, members, items, counts, whist, first, tot2);
       if (threadIdx.x == 0) ucount[0] = counts[1];    // written by this thread inside plan_block
       if (wo.sorted != nullptr) {
         // The items once more for each matrix, widest trellis first: blocks that run at the same time then decode the
@@ -595,6 +606,45 @@ exl3_prologue_kernel(const int* __restrict__ picks, int P, int E, int slots, int
       for (int i = 0; i < 8; ++i) v[i] = xv[i] * s[i];
       exl3::hadamard128(v, sub);
       if (routed) exl3::store8((m ? out1 : out0) + (size_t)p * K + blk * 128 + 8 * sub, v, exl3::HAD_SCALE);
+    }
+  }
+  pdl_launch_dependents();
+}
+
+// The prompt form's epilogue: out[m, block] = rotate(z[m, block]) / sqrt(128) * svh + bias for every row and
+// 128-column block of a product z [M, N] fp32, a half warp a block.
+// (the epilogue of src/tensorfold/cuda/exl3/prefill.py:15-44 `_gemm`)
+template <typename TOUT>
+__global__ void __launch_bounds__(256)
+exl3_rot_out_kernel(const float* __restrict__ z, const __half* __restrict__ svh, const __half* __restrict__ bias,
+                    TOUT* __restrict__ out, int64_t out_stride, int M, int N) {
+  const int lane = threadIdx.x & 31, sub = lane & 15, half = lane >> 4;
+  const int nblk = N >> 7;
+  const int64_t units = (int64_t)M * nblk;
+  const int64_t warps = (int64_t)gridDim.x * 8;
+  pdl_wait();
+  after_wait(z);
+  for (int64_t u0 = 2 * ((int64_t)blockIdx.x * 8 + (threadIdx.x >> 5)); u0 < units; u0 += 2 * warps) {
+    const bool have = u0 + half < units;              // the transform's shuffles need every lane: an idle half repeats u0
+    const int64_t u = have ? u0 + half : u0;
+    const int m = (int)(u / nblk), blk = (int)(u - (int64_t)m * nblk);
+    float v[8], s[8], b[8];
+    const float4* src = reinterpret_cast<const float4*>(z + (size_t)m * N + blk * 128 + 8 * sub);
+    const float4 lo = src[0], hi = src[1];
+    v[0] = lo.x; v[1] = lo.y; v[2] = lo.z; v[3] = lo.w; v[4] = hi.x; v[5] = hi.y; v[6] = hi.z; v[7] = hi.w;
+    exl3::load8(svh + blk * 128 + 8 * sub, s);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) b[i] = 0.f;
+    if (bias != nullptr) exl3::load8(bias + blk * 128 + 8 * sub, b);
+    exl3::hadamard128(v, sub);
+    if (!have) continue;
+    TOUT* dst = out + (size_t)m * out_stride + blk * 128 + 8 * sub;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float y = fmaf(v[i] * exl3::HAD_SCALE, s[i], b[i]);
+      if constexpr (sizeof(TOUT) == 4) dst[i] = y;
+      else if constexpr (std::is_same<TOUT, __half>::value) dst[i] = __float2half_rn(y);
+      else dst[i] = __float2bfloat16_rn(y);
     }
   }
   pdl_launch_dependents();
@@ -744,8 +794,9 @@ extern "C" int tfb_exl3_group_static(const int32_t* pick, int32_t* uids, int32_t
                     "exl3_group_static");
 }
 
-// The first launch of a routed call: sorts the pairs by expert (when `sort`: members [R * slots], items
-// [(min(R * slots, E) + R * slots / 16), 3] = (expert, first, count <= 16), counts [2], ucount [1] = distinct experts)
+// The first launch of a routed call: sorts the pairs by expert (when `sort`, which is then the pairs an item holds, 16
+// or 32: members [R * slots], items [(min(R * slots, E) + R * slots / sort), 3] = (expert, first, count <= sort),
+// counts [2], ucount [1] = distinct experts)
 // and rotates the inputs: out0 / out1 [R * slots, K] fp16 for the two matrices (suh1 / out1 null: one matrix).
 // sorted (or null): int32 [3, sorted_stride, 4], filled with the items as (expert, first, count, index), once in the
 // order of each matrix's widths k2_g / k2_u / k2_d [E] (widest first), for tfb_exl3_gateup / tfb_exl3_down of a layer
@@ -761,6 +812,8 @@ extern "C" int tfb_exl3_prologue(const void* x, int64_t x_stride, int x_is_fp16,
   const exl3::WidthOrder wo = {{k2_g, k2_u, k2_d}, sorted, sorted_stride};
   TFB_REQUIRE((suh1 == nullptr) == (out1 == nullptr), "exl3_prologue: the second matrix's scales and output come together");
   TFB_REQUIRE(!sort || (members && items && counts && ucount), "exl3_prologue: null sort table");
+  TFB_REQUIRE(sort == 0 || sort == 8 * exl3::GR_PT || sort == 8 * exl3::GR_WIDE_PT,
+              "exl3_prologue: sort is 0 (the caller sorted), %d or %d (pairs an item)", 8 * exl3::GR_PT, 8 * exl3::GR_WIDE_PT);
   TFB_REQUIRE(K > 0 && K % 128 == 0, "exl3_prologue: K must be a multiple of 128");
   TFB_REQUIRE(slots >= 1 && slots <= 32 && x_stride >= K && x_stride % 8 == 0, "exl3_prologue: bad slots or stride");
   TFB_REQUIRE(aligned16(x) && aligned16(suh0) && aligned16(out0) && aligned16(suh1) && aligned16(out1),
@@ -792,7 +845,10 @@ extern "C" int tfb_exl3_prologue(const void* x, int64_t x_stride, int x_is_fp16,
   return check_cuda(e, "exl3_prologue");
 }
 
-static int exl3_grouped_launch(const char* who, const exl3::GroupedArgs& a, int cb, int max_items, void* stream) {
+static int exl3_grouped_launch(const char* who, const exl3::GroupedArgs& a, int cb, int max_items, int item_pairs,
+                               void* stream) {
+  TFB_REQUIRE(item_pairs == 8 * exl3::GR_PT || item_pairs == 8 * exl3::GR_WIDE_PT, "%s: items of %d or %d pairs, not %d",
+              who, 8 * exl3::GR_PT, 8 * exl3::GR_WIDE_PT, item_pairs);
   TFB_REQUIRE(a.K > 0 && a.N > 0 && a.K % 128 == 0 && a.N % 128 == 0, "%s: K and N must be multiples of 128", who);
   TFB_REQUIRE(cb >= 0 && cb <= 2, "%s: codebook must be 0 (3inst), 1 (mcg) or 2 (mul1)", who);
   TFB_REQUIRE(max_items >= 0 && a.P >= 0, "%s: bad sizes", who);
@@ -800,13 +856,18 @@ static int exl3_grouped_launch(const char* who, const exl3::GroupedArgs& a, int 
   TFB_REQUIRE(max_items <= 65535, "%s: too many items for one launch", who);
   const dim3 grid(a.N / (16 * exl3::GR_NTB), max_items, a.mats);       // an item's column blocks run together
   auto st = static_cast<cudaStream_t>(stream);
+  const dim3 block(exl3::GR_WARPS * 32);
+  const bool wide = item_pairs == 8 * exl3::GR_WIDE_PT;
   cudaError_t e;
   if (cb == 0)
-    e = launch(exl3::grouped_kernel<0>, grid, dim3(exl3::GR_WARPS * 32), 0, st, a);
+    e = wide ? launch(exl3::grouped_kernel<0, exl3::GR_WIDE_PT>, grid, block, 0, st, a)
+             : launch(exl3::grouped_kernel<0, exl3::GR_PT>, grid, block, 0, st, a);
   else if (cb == 1)
-    e = launch(exl3::grouped_kernel<1>, grid, dim3(exl3::GR_WARPS * 32), 0, st, a);
+    e = wide ? launch(exl3::grouped_kernel<1, exl3::GR_WIDE_PT>, grid, block, 0, st, a)
+             : launch(exl3::grouped_kernel<1, exl3::GR_PT>, grid, block, 0, st, a);
   else
-    e = launch(exl3::grouped_kernel<2>, grid, dim3(exl3::GR_WARPS * 32), 0, st, a);
+    e = wide ? launch(exl3::grouped_kernel<2, exl3::GR_WIDE_PT>, grid, block, 0, st, a)
+             : launch(exl3::grouped_kernel<2, exl3::GR_PT>, grid, block, 0, st, a);
   return check_cuda(e, who);
 }
 
@@ -815,14 +876,17 @@ static int exl3_grouped_launch(const char* who, const exl3::GroupedArgs& a, int 
 // suh_d, rotation - one launch.  tp_*: int64 trellis pointers [E] (16-byte aligned trellises), k2_*: int32 [E];
 // items / counts / members: the prologue's sort; z: fp32 scratch [2, P, N]; arrive: int scratch
 // [max_items * N / 128], zero before the first call (every call leaves it zero); max_items >= the sort's items.
-// sorted_g / sorted_u (or null): the prologue's width orders of the two matrices ([., 4] each).
+// sorted_g / sorted_u (or null): the prologue's width orders of the two matrices ([., 4] each).  item_pairs: 16 or 32,
+// the most pairs an item of the sort holds (32: one decode of a weight tile serves up to 32 pairs, at more registers
+// a thread - for calls with many pairs an expert); a pair's bits do not depend on it.
 // (exl3/experts.cpp `grouped` + `gateup_epilogue`: src/tensorfold/cuda/exl3/experts_grouped.cuh:190-284,
 // src/tensorfold/cuda/exl3/experts.cu:116-158)
 extern "C" int tfb_exl3_gateup(const void* xg, const void* xu, const int64_t* tp_g, const int64_t* tp_u,
                                const int32_t* k2_g, const int32_t* k2_u, const int32_t* items, const int32_t* counts,
                                const int32_t* members, float* z, int32_t* arrive, const void* svh_g, const void* svh_u,
                                const void* suh_d, void* xd, int K, int N, int P, int cb, int max_items, float limit,
-                               int act_mode, const int32_t* sorted_g, const int32_t* sorted_u, void* stream) {
+                               int act_mode, const int32_t* sorted_g, const int32_t* sorted_u, int item_pairs,
+                               void* stream) {
   TFB_REQUIRE((sorted_g == nullptr) == (sorted_u == nullptr) && aligned16(sorted_g) && aligned16(sorted_u),
               "exl3_gateup: the two width orders come together, 16-byte aligned");
   TFB_REQUIRE(xg && xu && tp_g && tp_u && k2_g && k2_u && items && counts && members && z && arrive && svh_g && svh_u &&
@@ -856,7 +920,7 @@ extern "C" int tfb_exl3_gateup(const void* xg, const void* xu, const int64_t* tp
   a.epi = exl3::GE_GATEUP;
   a.act_mode = act_mode;
   a.limit = limit;
-  return exl3_grouped_launch("exl3_gateup", a, cb, max_items, stream);
+  return exl3_grouped_launch("exl3_gateup", a, cb, max_items, item_pairs, stream);
 }
 
 // y [P, N] fp32 = rotate(x [P, K] fp16 times W_q of each pair's expert) * svh of every routed pair (rows of other
@@ -866,7 +930,7 @@ extern "C" int tfb_exl3_gateup(const void* xg, const void* xu, const int64_t* tp
 extern "C" int tfb_exl3_down(const void* x, const int64_t* tp, const int32_t* k2, const int32_t* items,
                              const int32_t* counts, const int32_t* members, float* z, int32_t* arrive, const void* svh,
                              float* y, int K, int N, int P, int cb, int max_items, const int32_t* sorted,
-                             void* stream) {
+                             int item_pairs, void* stream) {
   TFB_REQUIRE(x && tp && k2 && items && counts && members && z && arrive && svh && y, "exl3_down: null pointer");
   TFB_REQUIRE(aligned16(sorted), "exl3_down: the width order must be 16-byte aligned");
   TFB_REQUIRE(aligned16(z) && aligned16(svh) && aligned16(y), "exl3_down: 16-byte aligned rows");
@@ -890,5 +954,33 @@ extern "C" int tfb_exl3_down(const void* x, const int64_t* tp, const int32_t* k2
   a.epi = exl3::GE_DOWN;
   a.act_mode = 1;
   a.limit = 0.f;
-  return exl3_grouped_launch("exl3_down", a, cb, max_items, stream);
+  return exl3_grouped_launch("exl3_down", a, cb, max_items, item_pairs, stream);
+}
+
+// out [M, N] (fp32: out_type 0, fp16: 1, bf16: 2; rows out_stride elements apart) = rotate(z) / sqrt(128) * svh + bias
+// for every 128-column block of z [M, N] fp32 (bias fp16 [N] or null): the output side of an EXL3 product formed
+// elsewhere (a dense GEMM over the decoded W_q for prompts).
+// (src/tensorfold/cuda/exl3/prefill.py:15-44: the rotation epilogue of `_gemm`)
+extern "C" int tfb_exl3_rot_out(const float* z, const void* svh, const void* bias, void* out, int64_t out_stride,
+                                int out_type, int M, int N, void* stream) {
+  TFB_REQUIRE(z && svh && out, "exl3_rot_out: null pointer");
+  TFB_REQUIRE(N > 0 && N % 128 == 0 && out_stride >= N, "exl3_rot_out: N must be a multiple of 128, rows at least N apart");
+  TFB_REQUIRE(out_type >= 0 && out_type <= 2, "exl3_rot_out: out_type 0 (fp32), 1 (fp16) or 2 (bf16)");
+  TFB_REQUIRE(aligned16(z) && aligned16(svh) && aligned16(bias), "exl3_rot_out: 16-byte aligned rows");
+  if (M <= 0) return TFB_OK;
+  const int64_t units = (int64_t)M * (N / 128);
+  const int64_t want = (units + 15) / 16;
+  const dim3 grid((unsigned)(want < 8 * sm_count() ? want : 8 * sm_count()));
+  auto st = static_cast<cudaStream_t>(stream);
+  auto* sv = static_cast<const __half*>(svh);
+  auto* bi = static_cast<const __half*>(bias);
+  cudaError_t e;
+  if (out_type == 0)
+    e = launch(exl3_rot_out_kernel<float>, grid, dim3(256), 0, st, z, sv, bi, static_cast<float*>(out), out_stride, M, N);
+  else if (out_type == 1)
+    e = launch(exl3_rot_out_kernel<__half>, grid, dim3(256), 0, st, z, sv, bi, static_cast<__half*>(out), out_stride, M, N);
+  else
+    e = launch(exl3_rot_out_kernel<__nv_bfloat16>, grid, dim3(256), 0, st, z, sv, bi, static_cast<__nv_bfloat16*>(out),
+               out_stride, M, N);
+  return check_cuda(e, "exl3_rot_out");
 }

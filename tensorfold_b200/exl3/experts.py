@@ -25,6 +25,8 @@ ACT_BF16, ACT_F32 = 0, 1          # SwiGLU with the GLM family's bf16 roundings 
 K2_SUPPORTED = tuple(range(2, 17))   # half-bits a value: 1..8 bits and every half-integer rate between
 LAUNCHES_PER_CALL = 4             # kernels one ``routed`` call with weights enqueues (3 without)
 ITEM_PAIRS = 16                   # pairs an item of the sort holds: two mma tiles share one decoded weight tile
+WIDE_ITEM_PAIRS = 32              # the same with four mma tiles, for calls with many pairs an expert
+WIDE_FROM = 12                    # pairs an expert on average from which a call sorts into the wide items
 
 # (16-column tiles a block, K-slice warps, K splits across blocks, tiles in flight): this library's one setting.
 # The split is by shape only; partial sums meet in warp order inside the block, so there is one split.
@@ -156,6 +158,12 @@ def default_config(K: int, N: int, gateup: bool) -> tuple[int, int, int, int]:
     return CONFIG
 
 
+def item_pairs(pairs: int, experts: int) -> int:
+    """Pairs an item of a call's sort holds: a function of the call's shape alone (a pair's bits depend on neither)."""
+
+    return WIDE_ITEM_PAIRS if pairs >= WIDE_FROM * experts else ITEM_PAIRS
+
+
 def max_items(pairs: int, experts: int) -> int:
     """Items the sort of ``pairs`` pairs over ``experts`` experts can make: one an expert in use, one more for every
     full ``ITEM_PAIRS`` pairs."""
@@ -234,21 +242,22 @@ def routed(x: torch.Tensor, pick: torch.Tensor, wts: torch.Tensor | None, ex: Ex
     if act_mode not in (ACT_BF16, ACT_F32):
         raise ValueError("act_mode is ACT_BF16 or ACT_F32")
     st, items = _stream(x), max_items(pairs, ex.count)
+    per_item = item_pairs(pairs, ex.count) if group_first else ITEM_PAIRS      # `group` sorts into the narrow items
     sort = (s.sort_members.data_ptr(), s.sort_items.data_ptr(), s.sort_counts.data_ptr())
     # a layer of mixed widths: the prologue lays the items out width by width, once a projection
     order = [s.by_width[m].data_ptr() for m in range(3)] if ex.mixed and group_first else [0, 0, 0]
     with torch.cuda.device(x.device):
         _lib.call("tfb_exl3_prologue", x.data_ptr(), x.stride(0), int(x.dtype == torch.float16), pick.data_ptr(),
                   ex.suh_g.data_ptr(), ex.suh_u.data_ptr(), s.xg.data_ptr(), s.xu.data_ptr(), R, dims, slots, ex.count,
-                  int(group_first), *sort, s.count.data_ptr(), ex.gate_k2.data_ptr(), ex.up_k2.data_ptr(),
+                  per_item if group_first else 0, *sort, s.count.data_ptr(), ex.gate_k2.data_ptr(), ex.up_k2.data_ptr(),
                   ex.down_k2.data_ptr(), order[0], s.by_width.shape[1], st)
         tables = (sort[1], sort[2], sort[0], s.z.data_ptr(), s.arrive.data_ptr())
         _lib.call("tfb_exl3_gateup", s.xg.data_ptr(), s.xu.data_ptr(), ex.gate_ptr.data_ptr(), ex.up_ptr.data_ptr(),
                   ex.gate_k2.data_ptr(), ex.up_k2.data_ptr(), *tables, ex.svh_g.data_ptr(), ex.svh_u.data_ptr(),
                   ex.suh_d.data_ptr(), s.xd.data_ptr(), dims, width, pairs, ex.cb, items, float(min(limit, 3.0e38)),
-                  act_mode, order[0], order[1], st)
+                  act_mode, order[0], order[1], per_item, st)
         _lib.call("tfb_exl3_down", s.xd.data_ptr(), ex.down_ptr.data_ptr(), ex.down_k2.data_ptr(), *tables,
-                  ex.svh_d.data_ptr(), s.y.data_ptr(), width, dims, pairs, ex.cb, items, order[2], st)
+                  ex.svh_d.data_ptr(), s.y.data_ptr(), width, dims, pairs, ex.cb, items, order[2], per_item, st)
         if wts is None:
             return s.y[:pairs]
         if out is None:

@@ -241,3 +241,46 @@ def test_dense_linear_against_float64_and_rows_alone(bits, cb, m):
     assert torch.equal(layer(x[r:r + 1], out_dtype=torch.float32), got[r:r + 1])
     with pytest.raises(ValueError):
         layer(torch.zeros((129, k), dtype=torch.bfloat16, device="cuda"))
+
+
+@pytest.mark.parametrize("bits,cb,bias", [(4, "3inst", True), (2.5, "mul1", False), (5, "mcg", True)])
+@pytest.mark.parametrize("m,odt", [(129, torch.float32), (700, torch.bfloat16)])
+def test_prompt_matmul_against_float64_and_the_decode_form(bits, cb, bias, m, odt):
+    """``exl3.prefill.matmul`` (W_q decoded once, dense GEMM, this library's rotations): against the float64
+    restatement of the reference's forward (the bar of its prompt path, tests/cuda/test_exl3_prefill.py: 2e-3 of the
+    max), rows in a strided output, a row's value independent of the rows beside it up to the GEMM's tiling (1e-3),
+    and agreement with the decode form on the rows that one takes."""
+
+    from oracle import exl3 as ref
+    from tensorfold_b200.exl3 import linear, prefill
+
+    k, n = 384, 256
+    g = torch.Generator(device="cuda").manual_seed(int(bits * 10) + m)
+    trellis = torch.randint(-32768, 32768, (k // 16, n // 16, int(16 * bits)), generator=g, device="cuda",
+                            dtype=torch.int32).to(torch.int16)
+    sign = lambda c: (torch.randint(0, 2, (c,), generator=g, device="cuda").float() * 2 - 1)          # noqa: E731
+    suh = (sign(k) * (torch.randn((k,), generator=g, device="cuda") * 0.02).abs()).half()
+    svh = (sign(n) * (torch.randn((n,), generator=g, device="cuda") * 0.02).abs()).half()
+    b = (torch.randn((n,), generator=g, device="cuda") * 0.01).half() if bias else None
+    layer = linear.Exl3Linear.from_tensors(trellis, suh, svh, cb, b)
+    x = torch.randn((m, k), generator=g, device="cuda").to(torch.bfloat16)
+    ws = prefill.Workspace()
+    wide = torch.full((m, n + 64), 7.0, dtype=odt, device="cuda")
+    out = prefill.matmul(layer, x, wide[:, :n], ws)
+    assert out.data_ptr() == wide.data_ptr() and bool((wide[:, n:] == 7.0).all())
+    want = ref.linear(x[:40].double().cpu().numpy(), trellis.cpu().numpy(), suh.cpu().numpy(), svh.cpu().numpy(),
+                      linear.CODEBOOK_IDS[cb])
+    if bias:
+        want = want + b.double().cpu().numpy()
+    tol = 2e-3 if odt == torch.float32 else 1e-2
+    err = np.abs(out[:40].double().cpu().numpy() - want).max() / np.abs(want).max()
+    assert err < tol, err
+    small = torch.empty((40, n), dtype=odt, device="cuda")
+    prefill.matmul(layer, x[:40], small, ws)                       # the workspace is reused, fewer rows
+    scale = float(out[:40].float().abs().max())
+    assert float((small.float() - out[:40].float()).abs().max()) <= (1e-3 if odt == torch.float32 else 1e-2) * scale
+    dec = layer(x[:40], out_dtype=torch.float32)
+    assert float((dec - out[:40].float()).abs().max()) <= tol * scale
+    assert ws.nbytes() >= k * n * 2 + m * k * 2 + m * n * 4
+    with pytest.raises(ValueError):
+        prefill.matmul(layer, x, torch.empty((m, n + 1), device="cuda"), ws)
