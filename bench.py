@@ -586,6 +586,16 @@ COLLECTIVE = {
 }
 
 
+C4_HOT_PAIRS = 32        # config 4: a rank's experts with at least this many pairs go through the prompt-form kernel
+
+
+def hot_pairs_for(config: str, asked: int) -> int:
+    """`--hot-pairs` when given; else the split plan for config 4's skewed routing (measured: 1643 -> 1424 us on one
+    GPU, 599 -> 503 us on four) and the plain plan for config 2's uniform routing."""
+
+    return asked if asked >= 0 else (C4_HOT_PAIRS if config == "c4" else 0)
+
+
 def ep_rows(config: str, rows: int, world: int) -> int:
     """Rows a rank: config 2 keeps `--rows` a GPU (weak scaling); config 4 splits its 256 tokens over the ranks."""
 
@@ -623,16 +633,18 @@ def one_gpu_layer(torch, x, router, full, shape, bias):
     return moe.combine(buf.y[:rows], buf.wts[:rows]), buf.pick[:rows].clone()
 
 
-def bench_rank_slice(torch, args, shape, dev, hbm: float) -> dict:
-    """One GPU doing what one rank of an `--as-rank-of N` group does between its two exchanges, for profiling that
-    regime under ncu (never wrap a multi-rank run in ncu): the rank's 128 / N experts, the 64 * N tokens of all ranks
-    routed over all experts, the plan over the rank's expert window, gate/up and down.  The slice's weight copies
-    rotate so every step reads DRAM.  Times the two expert launches together and gate/up alone."""
+def bench_rank_slice(torch, args, config: str, shape, dev, hbm: float) -> dict:
+    """One GPU doing what rank `--slice-rank` of an `--as-rank-of N` group does between its two exchanges, for profiling
+    that regime under ncu (never wrap a multi-rank run in ncu): the rank's E / N experts, the tokens of all ranks routed
+    over all experts (config 2: 64 a rank; config 4: its 256 tokens, Zipf-skewed), the plan over the rank's expert
+    window (`--hot-pairs`: the split plan), gate/up and down.  The slice's weight copies rotate so every step reads
+    DRAM.  Times the expert launches together and gate/up alone."""
 
     from tensorfold_b200 import _lib, experts, moe, synthetic
 
-    n = args.as_rank_of
-    rows, per = (args.rows or 64) * n, shape.experts // n
+    n, r = args.as_rank_of, args.slice_rank
+    rows = 256 if config == "c4" else (args.rows or 64) * n
+    per = shape.experts // n
     router = synthetic.router_rows(shape, dev)
     x = synthetic.activations(shape, rows, dev, index=100)
 
@@ -641,21 +653,29 @@ def bench_rank_slice(torch, args, shape, dev, hbm: float) -> dict:
         moe_intermediate_size, hidden_size = shape.width, shape.dims
 
     buf = moe.MoEBuffers(rows, _Cfg, dev, shared=False)
-    moe.router(x, router, buf.logits)
+    moe.router(x, router[:shape.experts], buf.logits)
+    if config == "c4":
+        buf.logits.add_(synthetic.zipf_bias(shape, 1.1, dev))
     moe.select_rows(buf.logits, buf, shape.top_k, shape.experts)
+    pick = buf.pick.contiguous()
     wide = rows * shape.top_k >= 24 * shape.experts              # the expert-parallel step's own rule for items of 16
-    plan = experts.Plan(rows, shape.top_k, per, dev, decode_tile=experts.WIDE_TILE if wide else experts.TILE)
+    hot = hot_pairs_for(config, args.hot_pairs)
+    plan = experts.Plan(rows, shape.top_k, per, dev, decode_tile=experts.WIDE_TILE if wide else experts.TILE, hot=hot)
     plan.tile = plan.decode_tile
     st = torch.cuda.current_stream(dev).cuda_stream
-    _lib.call("tfb_plan_window", buf.pick.data_ptr(), rows * shape.top_k, 0, per, plan.tile, plan.members.data_ptr(),
-              plan.items.data_ptr(), plan.counts.data_ptr(), st)
+    if hot:
+        experts.route_split(pick, plan, r * per)
+    else:
+        _lib.call("tfb_plan_window", pick.data_ptr(), rows * shape.top_k, r * per, per, plan.tile,
+                  plan.members.data_ptr(), plan.items.data_ptr(), plan.counts.data_ptr(), st)
     torch.cuda.synchronize()
-    pairs = int((buf.pick < per).sum())
+    mine = pick[(pick >= r * per) & (pick < (r + 1) * per)] - r * per
+    counts = torch.bincount(mine.long(), minlength=per)
     slices = []
-    for copy in range(2 * n):                                     # as a rank of the group does: 2 N copies of its slice
+    for copy in range(2 if config == "c4" else 2 * n):            # as a rank of the group does
         gate, up, down = synthetic.affine_layer(shape, dev, torch.float16 if args.scales == "fp16" else torch.bfloat16,
                                                 copy=copy)
-        cut = slice(0, per)
+        cut = slice(r * per, (r + 1) * per)
         slices.append(experts.make([tuple(t[cut].contiguous() for t in gate), tuple(t[cut].contiguous() for t in up)],
                                    tuple(t[cut].contiguous() for t in down), 64))
         del gate, up, down
@@ -685,10 +705,12 @@ def bench_rank_slice(torch, args, shape, dev, hbm: float) -> dict:
     k = len(slices)
     ms_both, _ = timed(torch, lambda i: g_both.replay(), max(args.steps // k, 3), args.warmup, 5)
     ms_first, _ = timed(torch, lambda i: g_first.replay(), max(args.steps // k, 3), args.warmup, 5)
-    nbytes = per * slices[0].bytes_per_expert()
-    return {"as_rank_of": n, "experts": per, "tokens": rows, "pairs_in_window": pairs, "items_of": plan.tile,
-            "weight_copies": k, "slice_bytes": nbytes, "gate_up_plus_down_us": ms_both / k * 1e3,
-            "gate_up_us": ms_first / k * 1e3, "frac_of_hbm": nbytes / (ms_both / k * 1e-3) / 1e9 / hbm,
+    nbytes = int((counts > 0).sum()) * slices[0].bytes_per_expert()
+    return {"as_rank_of": n, "rank": r, "config": config, "experts": per, "experts_in_use": int((counts > 0).sum()),
+            "tokens": rows, "pairs_in_window": int(counts.sum()), "most_pairs_an_expert": int(counts.max()),
+            "items_of": plan.tile, "hot_pairs": hot, "weight_copies": k, "slice_bytes": nbytes,
+            "gate_up_plus_down_us": ms_both / k * 1e3, "gate_up_us": ms_first / k * 1e3,
+            "frac_of_hbm": nbytes / (ms_both / k * 1e-3) / 1e9 / hbm,
             "gate_up_frac_of_hbm": nbytes * 2 / 3 / (ms_first / k * 1e-3) / 1e9 / hbm}
 
 
@@ -717,7 +739,7 @@ def bench_ep(torch, dist, args, config: str, shape, dev, rank: int, world: int) 
         if reduce == "peer":
             shared = cut(slice(shape.experts, shape.experts + 1)) if shape.shared else None
             layer = ep.PeerExpertParallel(router, local, shape.experts, shape.top_k, rows, shared_experts=shared,
-                                          logit_bias=bias, hot_pairs=max(args.hot_pairs, 0))
+                                          logit_bias=bias, hot_pairs=hot_pairs_for(config, args.hot_pairs))
         else:
             layer = ep.GatheredExpertParallel(router, local, shape.experts, shape.top_k, rows, reduce=reduce)
         copies.append(layer)
@@ -807,7 +829,8 @@ def bench_ep(torch, dist, args, config: str, shape, dev, rank: int, world: int) 
     dist.all_reduce(per_rank)
     return {"ms": ms, "all_ms": all_ms, "e2e_ms": e2e_ms, "e2e_all": e2e_all, "launches": layer.launches, "rows": rows,
             "rank_bytes": [int(v) for v in per_rank[:, 0].tolist()], "rank_pairs": [int(v) for v in per_rank[:, 1].tolist()],
-            "check": check, "steps": k, "reduce": reduce}
+            "check": check, "steps": k, "reduce": reduce,
+            "hot_pairs": hot_pairs_for(config, args.hot_pairs) if reduce == "peer" else 0}
 
 
 def c5_widths() -> dict:
@@ -983,7 +1006,8 @@ def ep_summary(res: dict, shape, config: str, world: int, hbm: float, which: str
     return {"config": {**workload_config(shape, rows, world, config),
                        "l2": f"each rank rotates {ep_copies(config, world)} copies of its {shape.experts // world}-expert "
                              "slice (inputs larger than the 126 MB L2)",
-                       "collective": COLLECTIVE[res["reduce"]] + "; the step is one CUDA graph"},
+                       "collective": COLLECTIVE[res["reduce"]] + "; the step is one CUDA graph",
+                       "hot_pairs": res.get("hot_pairs", 0)},
             "scaling": "weak" if config == "c2" else "strong", "n_gpus": world, "steps": res["steps"],
             "ms_per_step": ms, **spread(res["all_ms"]), "tokens_per_s": world * rows / (ms * 1e-3),
             "e2e_ms_per_step": res["e2e_ms"], "e2e_tokens_per_s": world * rows / (res["e2e_ms"] * 1e-3),
@@ -1033,9 +1057,11 @@ def run_ours(args) -> None:
         dist.destroy_process_group()
         return
     if args.as_rank_of:
-        if world != 1 or synthetic.C2.experts % args.as_rank_of:
-            raise SystemExit("--as-rank-of N runs on one GPU, N a divisor of the expert count")
-        print(json.dumps(bench_rank_slice(torch, args, synthetic.C2, dev, hbm)))
+        shape = synthetic.C4 if args.config == "c4" else synthetic.C2
+        if world != 1 or args.config == "c5" or shape.experts % args.as_rank_of or \
+                not 0 <= args.slice_rank < args.as_rank_of:
+            raise SystemExit("--as-rank-of N runs config 2 or 4 on one GPU, N a divisor of the expert count")
+        print(json.dumps(bench_rank_slice(torch, args, args.config, shape, dev, hbm)))
         dist.destroy_process_group()
         return
     shapes = {"c2": synthetic.C2, "c4": synthetic.C4, "c5": synthetic.C5}
@@ -1092,7 +1118,7 @@ def run_ours(args) -> None:
                         "steps": res["steps"], "warmup": args.warmup, "ms_per_step": res["ms"],
                         **spread(res["all_ms"]), "higher_is_better": True, "scaling": s["scaling"],
                         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-                        "config": {**s["config"], "hot_pairs": max(args.hot_pairs, 0)}, "clocks": clocks.summary(),
+                        "config": s["config"], "clocks": clocks.summary(),
                         "e2e": {"value": s["e2e_tokens_per_s"], "unit": UNIT, "ms_per_step": res["e2e_ms"],
                                 "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": nbytes},
                         "gpu_launches": res["launches"] * res["steps"],
@@ -1200,9 +1226,10 @@ def main() -> None:
                          "ranks; c5: only the 8-layer mixed-width EXL3 stack, 1..512 tokens split over the ranks")
     ap.add_argument("--hot-pairs", type=int, default=-1,
                     help="expert-parallel peer form: experts with at least this many pairs use the prompt-form kernel "
-                         "(default 0: never)")
+                         "(default: 32 for config 4, never for config 2)")
     ap.add_argument("--as-rank-of", type=int, default=0,
                     help="one GPU runs the expert launches of one rank of an N-rank config-2 group (for profiling)")
+    ap.add_argument("--slice-rank", type=int, default=0, help="which rank's expert window --as-rank-of runs")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline legs")
     ap.add_argument("--no-sweep", action="store_true", help="skip the 1-, 4-, 16- and 2048-token and EXL3 lines")
     ap.add_argument("--no-extra", action="store_true", help="skip configs 4 and 5")
