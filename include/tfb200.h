@@ -241,8 +241,10 @@ int tfb_experts_prefill(int gs, int epi, const void* x, int64_t x_stride, int sl
 int tfb_exl3_dequant(const void* trellis, void* out, int K, int N, int k2, int cb, void* stream);
 
 /* pick [R, slots] -> uids [maxu] = the distinct routed experts (< E) ascending, ucount [1], members [maxu, maxm] =
- * row * 32 + slot in row order, -1 after the last.  tmp_members [R * slots], tmp_items [3 * min(R * slots, E)] and
- * tmp_counts [2] are caller scratch.  E <= 1024, slots <= 32.
+ * row * 32 + slot in row order, -1 after the last.  members must hold maxu * maxm words: only the rows of the
+ * ucount experts found are written, experts past maxu are left out and an expert's members past maxm are cut off
+ * (maxu >= min(R * slots, E) and maxm >= R lose nothing).  tmp_members [R * slots], tmp_items [3 * min(R * slots, E)]
+ * and tmp_counts [2] are caller scratch.  E <= 1024, slots <= 32.
  * Replaces `group`: src/tensorfold/cuda/exl3/experts.cu:19-72,290-310. */
 int tfb_exl3_group(const int32_t* pick, int32_t* uids, int32_t* ucount, int32_t* members, int32_t* tmp_members,
                    int32_t* tmp_items, int32_t* tmp_counts, int R, int slots, int E, int maxu, int maxm, void* stream);
