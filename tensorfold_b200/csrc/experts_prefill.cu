@@ -305,20 +305,30 @@ prefill_kernel(const __nv_bfloat16* __restrict__ X, int64_t x_stride, int slots,
         if constexpr (M == 2) tmem_ld16(taddr + 256 + j0, b);
         tmem_ld_wait();
         if (col < N) {
+          // the sixteen values first (independent chains the compiler can interleave: one after the other, each
+          // behind its own row lookup and branch, they took 2 us a block), then their rows and the stores
+          float r[16];
+          int rows[16];
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
-            const int p = out_row[j0 + j];
-            if (p < 0) continue;
-            const size_t at = (size_t)p * N + col;
             const float v = __uint_as_float(a[j]);
-            if constexpr (EPI == EPI_F32) {
-              static_cast<float*>(out)[at] = v;
-            } else if constexpr (EPI == EPI_RELU2) {
-              static_cast<__nv_bfloat16*>(out)[at] = __float2bfloat16_rn(relu2(v));
+            rows[j] = out_row[j0 + j];
+            if constexpr (EPI == EPI_RELU2) {
+              r[j] = relu2(v);
             } else if constexpr (EPI == EPI_SWIGLU) {
-              static_cast<__nv_bfloat16*>(out)[at] = __float2bfloat16_rn(swiglu_fast(v, __uint_as_float(b[j]), limit));
+              r[j] = swiglu_fast(v, __uint_as_float(b[j]), limit);
             } else {
-              static_cast<__nv_bfloat16*>(out)[at] = __float2bfloat16_rn(v);
+              r[j] = v;
+            }
+          }
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            if (rows[j] < 0) continue;
+            const size_t at = (size_t)rows[j] * N + col;
+            if constexpr (EPI == EPI_F32) {
+              static_cast<float*>(out)[at] = r[j];
+            } else {
+              static_cast<__nv_bfloat16*>(out)[at] = __float2bfloat16_rn(r[j]);
             }
           }
         }
