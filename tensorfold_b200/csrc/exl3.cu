@@ -166,7 +166,7 @@ __device__ __forceinline__ bool warp_rows(const uint8_t* __restrict__ T, int nti
   constexpr int TW = Win<K2>::TW, NW = Win<K2>::NW;
   constexpr int TILE_B = 16 * K2, SEG = GR_NTB * TILE_B;              // bytes a tile / a row of the CTA's tiles
   constexpr int ROWS = GR_SLOT_BYTES / SEG < 1 ? 1 : (GR_SLOT_BYTES / SEG > 16 ? 16 : GR_SLOT_BYTES / SEG);
-  constexpr int RBMAX = NPT > 2 ? 2 : 4;                              // rows a block (their inputs sit in registers)
+  constexpr int RBMAX = 2;                            // rows a block (their inputs sit in registers; 4 was 3 % slower)
   constexpr int RB = ROWS < RBMAX ? ROWS : RBMAX;
   static_assert(ROWS * SEG <= GR_SLOT_BYTES, "a slot holds whole rows");
   const int nslot = (nkt + ROWS - 1) / ROWS;
