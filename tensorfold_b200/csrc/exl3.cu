@@ -372,7 +372,10 @@ enum GroupedEpilogue : int { GE_NONE = 0, GE_GATEUP = 1, GE_DOWN = 2 };
 
 // CTA (item, 64 columns, matrix).  PT: mma tiles of eight pairs an item may hold (2: items of 16 pairs; 4: items of 32,
 // for calls with many pairs an expert - every weight tile is then decoded once for up to 32 pairs).
-template <int CB, int PT>
+// K2F: 0, or the one width every tensor of the launch has (the host knows it): the kernel then holds that width's loop
+// alone - a tenth of the code, which matters where a CTA's life is short (one token: the dominant stall of the
+// all-widths kernel was the instruction fetch).
+template <int CB, int PT, int K2F>
 __global__ void __launch_bounds__(GR_WARPS * 32)
 grouped_kernel(const GroupedArgs a) {
   constexpr int PAIRS = 8 * PT;
@@ -426,24 +429,36 @@ grouped_kernel(const GroupedArgs a) {
   bool ok = true;
   uint8_t* my_ring = ring + warp * (GR_STAGES * GR_SLOT_BYTES);
   uint64_t* my_bars = bars + warp * GR_STAGES;
-  switch (k2) {
-#define TFB_K2(K2_)                                                                                       \
-  case K2_:                                                                                               \
+#define TFB_K2_BODY(K2_)                                                                                  \
     if constexpr (PT == 2)                                                                                \
       ok = live > 1 ? warp_rows<CB, K2_, 2, 2>(T, a.N >> 4, kt0, nkt, nt0, x, my_ring, my_bars, lane, acc)  \
                     : warp_rows<CB, K2_, 2, 1>(T, a.N >> 4, kt0, nkt, nt0, x, my_ring, my_bars, lane, acc); \
     else                                                                                                  \
       ok = live > 2 ? warp_rows<CB, K2_, 4, 4>(T, a.N >> 4, kt0, nkt, nt0, x, my_ring, my_bars, lane, acc)  \
-                    : warp_rows<CB, K2_, 4, 2>(T, a.N >> 4, kt0, nkt, nt0, x, my_ring, my_bars, lane, acc); \
+                    : warp_rows<CB, K2_, 4, 2>(T, a.N >> 4, kt0, nkt, nt0, x, my_ring, my_bars, lane, acc);
+#define TFB_K2(K2_) \
+  case K2_:         \
+    TFB_K2_BODY(K2_) \
     break;
-    TFB_K2(2) TFB_K2(3) TFB_K2(4) TFB_K2(5) TFB_K2(6) TFB_K2(7) TFB_K2(8) TFB_K2(9) TFB_K2(10) TFB_K2(11) TFB_K2(12)
-    TFB_K2(13) TFB_K2(14) TFB_K2(15) TFB_K2(16)
-#undef TFB_K2
-    default:
-      atomicCAS(&g_kernel_status, 0, ST_BAD_INDEX);   // a width the host should have refused
+  if constexpr (K2F != 0) {
+    if (k2 == K2F) {
+      TFB_K2_BODY(K2F)
+    } else {
+      atomicCAS(&g_kernel_status, 0, ST_BAD_INDEX);   // not the width the host promised
       ok = false;
-      break;
+    }
+  } else {
+    switch (k2) {
+      TFB_K2(2) TFB_K2(3) TFB_K2(4) TFB_K2(5) TFB_K2(6) TFB_K2(7) TFB_K2(8) TFB_K2(9) TFB_K2(10) TFB_K2(11) TFB_K2(12)
+      TFB_K2(13) TFB_K2(14) TFB_K2(15) TFB_K2(16)
+      default:
+        atomicCAS(&g_kernel_status, 0, ST_BAD_INDEX);   // a width the host should have refused
+        ok = false;
+        break;
+    }
   }
+#undef TFB_K2
+#undef TFB_K2_BODY
   pdl_launch_dependents();
   if (__syncthreads_or(ok ? 0 : 1)) return;           // a copy never landed (recorded): store nothing
   // the K slices meet in warp order (the ring's memory is free: every warp is past its loop)
@@ -846,7 +861,8 @@ extern "C" int tfb_exl3_prologue(const void* x, int64_t x_stride, int x_is_fp16,
 }
 
 static int exl3_grouped_launch(const char* who, const exl3::GroupedArgs& a, int cb, int max_items, int item_pairs,
-                               void* stream) {
+                               int k2_all, void* stream) {
+  TFB_REQUIRE(k2_all == 0 || (k2_all >= 2 && k2_all <= 16), "%s: k2_all is 0 or the one width of every tensor", who);
   TFB_REQUIRE(item_pairs == 8 * exl3::GR_PT || item_pairs == 8 * exl3::GR_WIDE_PT, "%s: items of %d or %d pairs, not %d",
               who, 8 * exl3::GR_PT, 8 * exl3::GR_WIDE_PT, item_pairs);
   TFB_REQUIRE(a.K > 0 && a.N > 0 && a.K % 128 == 0 && a.N % 128 == 0, "%s: K and N must be multiples of 128", who);
@@ -858,16 +874,21 @@ static int exl3_grouped_launch(const char* who, const exl3::GroupedArgs& a, int 
   auto st = static_cast<cudaStream_t>(stream);
   const dim3 block(exl3::GR_WARPS * 32);
   const bool wide = item_pairs == 8 * exl3::GR_WIDE_PT;
+  const bool four = k2_all == 8;                      // the one width with a kernel of its own (4.00 bits a weight)
   cudaError_t e;
-  if (cb == 0)
-    e = wide ? launch(exl3::grouped_kernel<0, exl3::GR_WIDE_PT>, grid, block, 0, st, a)
-             : launch(exl3::grouped_kernel<0, exl3::GR_PT>, grid, block, 0, st, a);
-  else if (cb == 1)
-    e = wide ? launch(exl3::grouped_kernel<1, exl3::GR_WIDE_PT>, grid, block, 0, st, a)
-             : launch(exl3::grouped_kernel<1, exl3::GR_PT>, grid, block, 0, st, a);
-  else
-    e = wide ? launch(exl3::grouped_kernel<2, exl3::GR_WIDE_PT>, grid, block, 0, st, a)
-             : launch(exl3::grouped_kernel<2, exl3::GR_PT>, grid, block, 0, st, a);
+#define TFB_GR(CB_)                                                                                     \
+  e = four ? (wide ? launch(exl3::grouped_kernel<CB_, exl3::GR_WIDE_PT, 8>, grid, block, 0, st, a)     \
+                   : launch(exl3::grouped_kernel<CB_, exl3::GR_PT, 8>, grid, block, 0, st, a))         \
+           : (wide ? launch(exl3::grouped_kernel<CB_, exl3::GR_WIDE_PT, 0>, grid, block, 0, st, a)     \
+                   : launch(exl3::grouped_kernel<CB_, exl3::GR_PT, 0>, grid, block, 0, st, a))
+  if (cb == 0) {
+    TFB_GR(0);
+  } else if (cb == 1) {
+    TFB_GR(1);
+  } else {
+    TFB_GR(2);
+  }
+#undef TFB_GR
   return check_cuda(e, who);
 }
 
@@ -878,7 +899,9 @@ static int exl3_grouped_launch(const char* who, const exl3::GroupedArgs& a, int 
 // [max_items * N / 128], zero before the first call (every call leaves it zero); max_items >= the sort's items.
 // sorted_g / sorted_u (or null): the prologue's width orders of the two matrices ([., 4] each).  item_pairs: 16 or 32,
 // the most pairs an item of the sort holds (32: one decode of a weight tile serves up to 32 pairs, at more registers
-// a thread - for calls with many pairs an expert); a pair's bits do not depend on it.
+// a thread - for calls with many pairs an expert); a pair's bits do not depend on it.  k2_all: 0, or the width that
+// every k2_g and k2_u entry has (a promise: the launch may then use a kernel built for that width alone; a tensor of
+// another width sets the status word and stores nothing).
 // (exl3/experts.cpp `grouped` + `gateup_epilogue`: src/tensorfold/cuda/exl3/experts_grouped.cuh:190-284,
 // src/tensorfold/cuda/exl3/experts.cu:116-158)
 extern "C" int tfb_exl3_gateup(const void* xg, const void* xu, const int64_t* tp_g, const int64_t* tp_u,
@@ -886,7 +909,7 @@ extern "C" int tfb_exl3_gateup(const void* xg, const void* xu, const int64_t* tp
                                const int32_t* members, float* z, int32_t* arrive, const void* svh_g, const void* svh_u,
                                const void* suh_d, void* xd, int K, int N, int P, int cb, int max_items, float limit,
                                int act_mode, const int32_t* sorted_g, const int32_t* sorted_u, int item_pairs,
-                               void* stream) {
+                               int k2_all, void* stream) {
   TFB_REQUIRE((sorted_g == nullptr) == (sorted_u == nullptr) && aligned16(sorted_g) && aligned16(sorted_u),
               "exl3_gateup: the two width orders come together, 16-byte aligned");
   TFB_REQUIRE(xg && xu && tp_g && tp_u && k2_g && k2_u && items && counts && members && z && arrive && svh_g && svh_u &&
@@ -920,7 +943,7 @@ extern "C" int tfb_exl3_gateup(const void* xg, const void* xu, const int64_t* tp
   a.epi = exl3::GE_GATEUP;
   a.act_mode = act_mode;
   a.limit = limit;
-  return exl3_grouped_launch("exl3_gateup", a, cb, max_items, item_pairs, stream);
+  return exl3_grouped_launch("exl3_gateup", a, cb, max_items, item_pairs, k2_all, stream);
 }
 
 // y [P, N] fp32 = rotate(x [P, K] fp16 times W_q of each pair's expert) * svh of every routed pair (rows of other
@@ -930,7 +953,7 @@ extern "C" int tfb_exl3_gateup(const void* xg, const void* xu, const int64_t* tp
 extern "C" int tfb_exl3_down(const void* x, const int64_t* tp, const int32_t* k2, const int32_t* items,
                              const int32_t* counts, const int32_t* members, float* z, int32_t* arrive, const void* svh,
                              float* y, int K, int N, int P, int cb, int max_items, const int32_t* sorted,
-                             int item_pairs, void* stream) {
+                             int item_pairs, int k2_all, void* stream) {
   TFB_REQUIRE(x && tp && k2 && items && counts && members && z && arrive && svh && y, "exl3_down: null pointer");
   TFB_REQUIRE(aligned16(sorted), "exl3_down: the width order must be 16-byte aligned");
   TFB_REQUIRE(aligned16(z) && aligned16(svh) && aligned16(y), "exl3_down: 16-byte aligned rows");
@@ -954,7 +977,7 @@ extern "C" int tfb_exl3_down(const void* x, const int64_t* tp, const int32_t* k2
   a.epi = exl3::GE_DOWN;
   a.act_mode = 1;
   a.limit = 0.f;
-  return exl3_grouped_launch("exl3_down", a, cb, max_items, item_pairs, stream);
+  return exl3_grouped_launch("exl3_down", a, cb, max_items, item_pairs, k2_all, stream);
 }
 
 // out [M, N] (fp32: out_type 0, fp16: 1, bf16: 2; rows out_stride elements apart) = rotate(z) / sqrt(128) * svh + bias

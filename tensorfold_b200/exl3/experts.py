@@ -255,9 +255,10 @@ def routed(x: torch.Tensor, pick: torch.Tensor, wts: torch.Tensor | None, ex: Ex
         _lib.call("tfb_exl3_gateup", s.xg.data_ptr(), s.xu.data_ptr(), ex.gate_ptr.data_ptr(), ex.up_ptr.data_ptr(),
                   ex.gate_k2.data_ptr(), ex.up_k2.data_ptr(), *tables, ex.svh_g.data_ptr(), ex.svh_u.data_ptr(),
                   ex.suh_d.data_ptr(), s.xd.data_ptr(), dims, width, pairs, ex.cb, items, float(min(limit, 3.0e38)),
-                  act_mode, order[0], order[1], per_item, st)
+                  act_mode, order[0], order[1], per_item, ex.k2_gu[0] if ex.k2_gu[0] == ex.k2_gu[1] else 0, st)
         _lib.call("tfb_exl3_down", s.xd.data_ptr(), ex.down_ptr.data_ptr(), ex.down_k2.data_ptr(), *tables,
-                  ex.svh_d.data_ptr(), s.y.data_ptr(), width, dims, pairs, ex.cb, items, order[2], per_item, st)
+                  ex.svh_d.data_ptr(), s.y.data_ptr(), width, dims, pairs, ex.cb, items, order[2], per_item,
+                  ex.k2_d[0] if ex.k2_d[0] == ex.k2_d[1] else 0, st)
         if wts is None:
             return s.y[:pairs]
         if out is None:
