@@ -613,28 +613,30 @@ plan_cluster_kernel(const int* __restrict__ picks, int P, int E, int T, int* __r
   pdl_launch_dependents();
 }
 
-// Selection and plan of a small call in one block: the 32 warps take rows in turn, the picks stay in shared memory
-// for the plan.  NP = E + (shared != 0) plan experts.  Results equal select_kernel's followed by plan_kernel's.
-template <int VPL>
-__global__ void __launch_bounds__(PLAN_THREADS)
+// Selection and plan of a small call in one block of NT threads: the warps take rows in turn, the picks stay in shared
+// memory for the plan.  NP = E + (shared != 0) plan experts.  Results equal select_kernel's followed by plan_kernel's
+// at any NT; a few rows take a block of four warps (its barriers and its histogram are a fraction of the full
+// block's: 6.4 -> about 3 us at one row).
+template <int VPL, int NT>
+__global__ void __launch_bounds__(NT)
 select_plan_kernel(const float* __restrict__ L, int NL, int* __restrict__ pick, float* __restrict__ wts, int T, int E,
                    int top_k, int shared, int tile, int* __restrict__ members, int* __restrict__ items,
                    int* __restrict__ counts, int plan_lo, int plan_n) {
-  extern __shared__ int dyn[];                   // whist [32][NP], then the picks [T * slots]
+  extern __shared__ int dyn[];                   // whist [NT / 32][NP], then the picks [T * slots]
   __shared__ int first[PLAN_EMAX];
-  __shared__ uint64_t tot2[2][PLAN_THREADS / 32];
+  __shared__ uint64_t tot2[2][NT / 32];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int slots = top_k + (shared ? 1 : 0);
-  int* picks_sh = dyn + 32 * plan_n;
+  int* picks_sh = dyn + (NT / 32) * plan_n;
   pdl_wait();
   after_wait(L);
-  for (int r = warp; r < T; r += PLAN_THREADS / 32) {
+  for (int r = warp; r < T; r += NT / 32) {
     const int mine = select_row<VPL>(L + (size_t)r * NL, E, top_k, shared, lane, pick + (size_t)r * slots,
                                      wts + (size_t)r * slots);
     if (lane < slots) picks_sh[r * slots + lane] = mine;
   }
   __syncthreads();
-  plan_block<PLAN_THREADS>(picks_sh, T * slots, plan_n, tile, members, items, counts, dyn, first, tot2, plan_lo);
+  plan_block<NT>(picks_sh, T * slots, plan_n, tile, members, items, counts, dyn, first, tot2, plan_lo);
   pdl_launch_dependents();
 }
 
@@ -1026,22 +1028,30 @@ static int select_plan_launch(const float* logits, int NL, int32_t* pick, float*
               tfb_select_plan_max_rows(), T);
   TFB_REQUIRE(tile >= 1, "select_plan: items hold at least one pair");
   const int slots = top_k + (shared ? 1 : 0);
-  const size_t smem = sizeof(int) * (32 * (size_t)plan_n + (size_t)T * slots);
   auto st = static_cast<cudaStream_t>(stream);
   const int vpl = (E + 31) / 32;
   int dev = 0;
   TFB_CUDA(cudaGetDevice(&dev), "select_plan: cudaGetDevice");
+  constexpr int SMALL_THREADS = 128, SMALL_ROWS = 4;      // a row a warp
 #define TFB_SP(V)                                                                                                  \
   do {                                                                                                             \
+    if (T <= SMALL_ROWS) {                                                                                         \
+      const size_t smem = sizeof(int) * ((SMALL_THREADS / 32) * (size_t)plan_n + (size_t)T * slots);              \
+      return check_cuda(launch(select_plan_kernel<V, SMALL_THREADS>, dim3(1), dim3(SMALL_THREADS), smem, st, logits, \
+                               NL, pick, wts, T, E, top_k, shared ? 1 : 0, tile, members, items, counts, plan_lo,  \
+                               plan_n),                                                                            \
+                        "select_plan");                                                                            \
+    }                                                                                                              \
+    const size_t smem = sizeof(int) * (32 * (size_t)plan_n + (size_t)T * slots);                                   \
     static int configured[64] = {0};                                                                               \
     if (dev < 64 && !configured[dev]) {                                                                            \
-      TFB_CUDA(cudaFuncSetAttribute(select_plan_kernel<V>, cudaFuncAttributeMaxDynamicSharedMemorySize,            \
+      TFB_CUDA(cudaFuncSetAttribute(select_plan_kernel<V, PLAN_THREADS>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
                                     (int)(sizeof(int) * (32 * PLAN_EMAX + 128 * 32))),                             \
                "select_plan: shared memory opt-in");                                                               \
       configured[dev] = 1;                                                                                         \
     }                                                                                                              \
-    return check_cuda(launch(select_plan_kernel<V>, dim3(1), dim3(PLAN_THREADS), smem, st, logits, NL, pick, wts, \
-                             T, E, top_k, shared ? 1 : 0, tile, members, items, counts, plan_lo, plan_n),        \
+    return check_cuda(launch(select_plan_kernel<V, PLAN_THREADS>, dim3(1), dim3(PLAN_THREADS), smem, st, logits, NL, \
+                             pick, wts, T, E, top_k, shared ? 1 : 0, tile, members, items, counts, plan_lo, plan_n), \
                       "select_plan");                                                                              \
   } while (0)
   if (vpl <= 4) TFB_SP(4);
