@@ -285,23 +285,25 @@ int tfb_exl3_prologue(const void* x, int64_t x_stride, int x_is_fp16, const int3
  * more registers a thread: for calls with many pairs an expert); a pair's bits do not depend on it.
  * k2_all: 0, or the width every entry of k2_g and k2_u has - a promise that lets the launch use a kernel built for
  * that width alone (a tenth of the code; it pays at a few tokens); a tensor of another width then sets the status
- * word and nothing is stored.
+ * word and nothing is stored.  col_tiles: 4 or 2, the 16-column tiles a thread block takes (2 doubles the blocks of
+ * a launch that would otherwise leave SMs idle: few experts in use); no result depends on it.
  * Replaces `grouped` + `gateup_epilogue`: src/tensorfold/cuda/exl3/experts_grouped.cuh:190-284,
  * src/tensorfold/cuda/exl3/experts.cu:116-158. */
 int tfb_exl3_gateup(const void* xg, const void* xu, const int64_t* tp_g, const int64_t* tp_u, const int32_t* k2_g,
                     const int32_t* k2_u, const int32_t* items, const int32_t* counts, const int32_t* members, float* z,
                     int32_t* arrive, const void* svh_g, const void* svh_u, const void* suh_d, void* xd, int K, int N,
                     int P, int cb, int max_items, float limit, int act_mode, const int32_t* sorted_g,
-                    const int32_t* sorted_u, int item_pairs, int k2_all, void* stream);
+                    const int32_t* sorted_u, int item_pairs, int k2_all, int col_tiles, void* stream);
 
 /* y [P, N] fp32 = rotate(x [P, K] fp16 times W_q of each pair's expert) * svh for every routed pair (other rows are
  * left as they are), in one launch; z: fp32 scratch [P, N]; the other arguments as tfb_exl3_gateup (sorted: the
- * prologue's width-ordered items of the down matrices, or null; k2_all: 0 or the one width of every k2 entry).  The weighted
+ * prologue's width-ordered items of the down matrices, or null; k2_all: 0 or the one width of every k2 entry; col_tiles as there).  The weighted
  * slot-order sum over a row's slots is tfb_combine on y.
  * Replaces `grouped` + `down_epilogue` (+ `combine`, `down_combine`): src/tensorfold/cuda/exl3/experts.cu:161-237. */
 int tfb_exl3_down(const void* x, const int64_t* tp, const int32_t* k2, const int32_t* items, const int32_t* counts,
                   const int32_t* members, float* z, int32_t* arrive, const void* svh, float* y, int K, int N, int P,
-                  int cb, int max_items, const int32_t* sorted, int item_pairs, int k2_all, void* stream);
+                  int cb, int max_items, const int32_t* sorted, int item_pairs, int k2_all, int col_tiles,
+                  void* stream);
 
 /* The output side of an EXL3 product formed elsewhere (prompts: a dense fp16 GEMM over the decoded W_q):
  * out [M, N] (out_type 0 fp32, 1 fp16, 2 bf16; rows out_stride elements apart) = rotate(z) / sqrt(128) * svh + bias

@@ -41,9 +41,9 @@ SIGNATURES: dict[str, tuple] = {
     "tfb_exl3_group": (P, P, P, P, P, P, P, I, I, I, I, I, P),
     "tfb_exl3_group_static": (P, P, P, P, I, I, I, I, I, P),
     "tfb_exl3_prologue": (P, L, I, P, P, P, P, P, I, I, I, I, I, P, P, P, P, P, P, P, P, I, P),
-    "tfb_exl3_gateup": (P, P, P, P, P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, F, I, P, P, I, I, P),
+    "tfb_exl3_gateup": (P, P, P, P, P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, F, I, P, P, I, I, I, P),
     "tfb_exl3_rot_out": (P, P, P, P, L, I, I, I, P),
-    "tfb_exl3_down": (P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, P, I, I, P),
+    "tfb_exl3_down": (P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, P, I, I, I, P),
     "tfb_peer_stage": (P, P, L, L, P),
     "tfb_peer_gather": (P, I, I, I, P, P, P, P, P),
     "tfb_combine_push": (P, P, P, I, I, P, L, I, I, I, I, I, P, P),

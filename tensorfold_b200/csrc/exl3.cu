@@ -28,13 +28,13 @@ namespace exl3 {
 
 constexpr float HAD_SCALE = 0.08838834764831845f;   // 1 / sqrt(128)
 constexpr int GR_WARPS = 4;                         // K slices a CTA (part of the arithmetic: they meet in warp order)
-constexpr int GR_NTB = 4;                           // 16-column tiles a CTA: 64 columns
+constexpr int GR_NTB = 4;                           // 16-column tiles a CTA: 64 columns (2: the narrow CTAs, 32 columns)
+constexpr int GR_NARROW_NTB = 2;
 constexpr int GR_PT = 2;                            // mma tiles of 8 pairs an item: 16 pairs (4: the wide items, 32 pairs)
 constexpr int GR_PAIRS = 8 * GR_PT;
 constexpr int GR_WIDE_PT = 4;
 constexpr int GR_SLOT_BYTES = 2048;                 // a ring slot: whole rows of the CTA's four tiles
 constexpr int GR_STAGES = 3;
-constexpr int GR_RED_STRIDE = GR_NTB * 16 + 1;
 
 __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) { return __byte_perm(a, b, sel); }
 
@@ -159,12 +159,12 @@ __device__ __forceinline__ void mma_f16(float (&d)[4], const uint32_t (&a)[4], u
 // four, whose inputs are loaded before the block's tiles are decoded.  x[pt]: the lane's pair (B column lane / 4 of
 // tile pt) at input 16 kt0 + 2 (lane % 4).  NPT: the mma tiles of eight pairs that are live (one decode feeds them all).
 // Returns false when a copy never landed.
-template <int CB, int K2, int PT, int NPT>
+template <int CB, int K2, int PT, int NPT, int NTB>
 __device__ __forceinline__ bool warp_rows(const uint8_t* __restrict__ T, int ntiles, int kt0, int nkt, int nt0,
                                           const __half* const (&x)[PT], uint8_t* ring, uint64_t* bars, int lane,
-                                          float (&acc)[GR_NTB][PT][4]) {
+                                          float (&acc)[NTB][PT][4]) {
   constexpr int TW = Win<K2>::TW, NW = Win<K2>::NW;
-  constexpr int TILE_B = 16 * K2, SEG = GR_NTB * TILE_B;              // bytes a tile / a row of the CTA's tiles
+  constexpr int TILE_B = 16 * K2, SEG = NTB * TILE_B;                 // bytes a tile / a row of the CTA's tiles
   constexpr int ROWS = GR_SLOT_BYTES / SEG < 1 ? 1 : (GR_SLOT_BYTES / SEG > 16 ? 16 : GR_SLOT_BYTES / SEG);
   constexpr int RBMAX = 2;                            // rows a block (their inputs sit in registers; 4 was 3 % slower)
   constexpr int RB = ROWS < RBMAX ? ROWS : RBMAX;
@@ -223,7 +223,7 @@ __device__ __forceinline__ bool warp_rows(const uint8_t* __restrict__ T, int nti
         for (int r = 0; r < RB; ++r) {
           if (r0 + r < rows) {
 #pragma unroll
-            for (int i = 0; i < GR_NTB; ++i) {
+            for (int i = 0; i < NTB; ++i) {
               const uint32_t* tile = slot + (r0 + r) * (SEG / 4) + i * TW;
               uint32_t w[NW], a[4];
 #pragma unroll
@@ -375,10 +375,11 @@ enum GroupedEpilogue : int { GE_NONE = 0, GE_GATEUP = 1, GE_DOWN = 2 };
 // K2F: 0, or the one width every tensor of the launch has (the host knows it): the kernel then holds that width's loop
 // alone - a tenth of the code, which matters where a CTA's life is short (one token: the dominant stall of the
 // all-widths kernel was the instruction fetch).
-template <int CB, int PT, int K2F>
+// NTB: 16-column tiles a CTA (4, or 2 where the launch would otherwise have too few CTAs to fill the GPU).
+template <int CB, int PT, int K2F, int NTB>
 __global__ void __launch_bounds__(GR_WARPS * 32)
 grouped_kernel(const GroupedArgs a) {
-  constexpr int PAIRS = 8 * PT;
+  constexpr int PAIRS = 8 * PT, GR_RED_STRIDE = NTB * 16 + 1;
   constexpr int RING_BYTES = GR_WARPS * GR_STAGES * GR_SLOT_BYTES, RED_BYTES = GR_WARPS * PAIRS * GR_RED_STRIDE * 4;
   // the K slices meet in the ring's memory (free by then)
   __shared__ __align__(128) uint8_t ring[RING_BYTES > RED_BYTES ? RING_BYTES : RED_BYTES];
@@ -386,7 +387,7 @@ grouped_kernel(const GroupedArgs a) {
   __shared__ int pair_sh[PAIRS];
   __shared__ int last_sh;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
-  const int nt0 = blockIdx.x * GR_NTB, mat = blockIdx.z;
+  const int nt0 = blockIdx.x * NTB, mat = blockIdx.z;
   if (lane == 0) {
 #pragma unroll
     for (int s = 0; s < GR_STAGES; ++s) mbar_init(bars + warp * GR_STAGES + s, 1);
@@ -421,9 +422,9 @@ grouped_kernel(const GroupedArgs a) {
     const int p = ld_dep(members + first + (8 * pt + g < cnt ? 8 * pt + g : 0));
     x[pt] = xin + (size_t)p * a.K + kt0 * 16 + 2 * t;
   }
-  float acc[GR_NTB][PT][4];
+  float acc[NTB][PT][4];
 #pragma unroll
-  for (int i = 0; i < GR_NTB; ++i)
+  for (int i = 0; i < NTB; ++i)
 #pragma unroll
     for (int pt = 0; pt < PT; ++pt) acc[i][pt][0] = acc[i][pt][1] = acc[i][pt][2] = acc[i][pt][3] = 0.f;
   bool ok = true;
@@ -431,11 +432,11 @@ grouped_kernel(const GroupedArgs a) {
   uint64_t* my_bars = bars + warp * GR_STAGES;
 #define TFB_K2_BODY(K2_)                                                                                  \
     if constexpr (PT == 2)                                                                                \
-      ok = live > 1 ? warp_rows<CB, K2_, 2, 2>(T, a.N >> 4, kt0, nkt, nt0, x, my_ring, my_bars, lane, acc)  \
-                    : warp_rows<CB, K2_, 2, 1>(T, a.N >> 4, kt0, nkt, nt0, x, my_ring, my_bars, lane, acc); \
+      ok = live > 1 ? warp_rows<CB, K2_, 2, 2, NTB>(T, a.N >> 4, kt0, nkt, nt0, x, my_ring, my_bars, lane, acc)  \
+                    : warp_rows<CB, K2_, 2, 1, NTB>(T, a.N >> 4, kt0, nkt, nt0, x, my_ring, my_bars, lane, acc); \
     else                                                                                                  \
-      ok = live > 2 ? warp_rows<CB, K2_, 4, 4>(T, a.N >> 4, kt0, nkt, nt0, x, my_ring, my_bars, lane, acc)  \
-                    : warp_rows<CB, K2_, 4, 2>(T, a.N >> 4, kt0, nkt, nt0, x, my_ring, my_bars, lane, acc);
+      ok = live > 2 ? warp_rows<CB, K2_, 4, 4, NTB>(T, a.N >> 4, kt0, nkt, nt0, x, my_ring, my_bars, lane, acc)  \
+                    : warp_rows<CB, K2_, 4, 2, NTB>(T, a.N >> 4, kt0, nkt, nt0, x, my_ring, my_bars, lane, acc);
 #define TFB_K2(K2_) \
   case K2_:         \
     TFB_K2_BODY(K2_) \
@@ -465,7 +466,7 @@ grouped_kernel(const GroupedArgs a) {
   // acc[i][pt]: d0 = (col g, pair 2t), d1 = (col g, pair 2t + 1), d2 = (col g + 8, pair 2t), d3 = (col g + 8, 2t + 1)
   float* red = reinterpret_cast<float*>(ring);
 #pragma unroll
-  for (int i = 0; i < GR_NTB; ++i)
+  for (int i = 0; i < NTB; ++i)
 #pragma unroll
     for (int pt = 0; pt < PT; ++pt) {
       float* base = red + (warp * PAIRS + 8 * pt + 2 * t) * GR_RED_STRIDE + i * 16 + g;
@@ -475,8 +476,8 @@ grouped_kernel(const GroupedArgs a) {
       base[GR_RED_STRIDE + 8] = acc[i][pt][3];
     }
   __syncthreads();
-  for (int o = tid; o < PAIRS * GR_NTB * 16; o += GR_WARPS * 32) {
-    const int pi = o / (GR_NTB * 16), col = o % (GR_NTB * 16);
+  for (int o = tid; o < PAIRS * NTB * 16; o += GR_WARPS * 32) {
+    const int pi = o / (NTB * 16), col = o % (NTB * 16);
     const int p = pair_sh[pi];
     if (p < 0) continue;
     float s = red[pi * GR_RED_STRIDE + col];
@@ -487,11 +488,12 @@ grouped_kernel(const GroupedArgs a) {
   if (a.epi == GE_NONE) return;
   // Whoever finishes last among the CTAs that share (item, 128 columns) - two column halves, times the matrices -
   // finds every part of the block in z and runs the block's epilogue.
-  const int blk = blockIdx.x >> 1;
+  constexpr int PER_BLOCK = 128 / (16 * NTB);          // CTAs that share a 128-column block of one matrix
+  const int blk = blockIdx.x / PER_BLOCK;
   int* counter = a.arrive + (size_t)it * (a.N >> 7) + blk;
   __syncthreads();
   if (tid == 0) {
-    const int need = 2 * a.mats;
+    const int need = PER_BLOCK * a.mats;
     const int seen = arrive_count(counter);
     last_sh = seen == need - 1;
     if (seen == need - 1) *counter = 0;               // nobody else touches it before the next launch
@@ -861,7 +863,9 @@ extern "C" int tfb_exl3_prologue(const void* x, int64_t x_stride, int x_is_fp16,
 }
 
 static int exl3_grouped_launch(const char* who, const exl3::GroupedArgs& a, int cb, int max_items, int item_pairs,
-                               int k2_all, void* stream) {
+                               int k2_all, int col_tiles, void* stream) {
+  TFB_REQUIRE(col_tiles == exl3::GR_NTB || col_tiles == exl3::GR_NARROW_NTB, "%s: %d or %d column tiles a block, not %d",
+              who, exl3::GR_NTB, exl3::GR_NARROW_NTB, col_tiles);
   TFB_REQUIRE(k2_all == 0 || (k2_all >= 2 && k2_all <= 16), "%s: k2_all is 0 or the one width of every tensor", who);
   TFB_REQUIRE(item_pairs == 8 * exl3::GR_PT || item_pairs == 8 * exl3::GR_WIDE_PT, "%s: items of %d or %d pairs, not %d",
               who, 8 * exl3::GR_PT, 8 * exl3::GR_WIDE_PT, item_pairs);
@@ -870,17 +874,18 @@ static int exl3_grouped_launch(const char* who, const exl3::GroupedArgs& a, int 
   TFB_REQUIRE(max_items >= 0 && a.P >= 0, "%s: bad sizes", who);
   if (max_items == 0 || a.P == 0) return TFB_OK;
   TFB_REQUIRE(max_items <= 65535, "%s: too many items for one launch", who);
-  const dim3 grid(a.N / (16 * exl3::GR_NTB), max_items, a.mats);       // an item's column blocks run together
+  const dim3 grid(a.N / (16 * col_tiles), max_items, a.mats);          // an item's column blocks run together
   auto st = static_cast<cudaStream_t>(stream);
   const dim3 block(exl3::GR_WARPS * 32);
   const bool wide = item_pairs == 8 * exl3::GR_WIDE_PT;
   const bool four = k2_all == 8;                      // the one width with a kernel of its own (4.00 bits a weight)
   cudaError_t e;
+#define TFB_GR4(CB_, PT_, K2F_)                                                                           \
+  (col_tiles == exl3::GR_NTB ? launch(exl3::grouped_kernel<CB_, PT_, K2F_, exl3::GR_NTB>, grid, block, 0, st, a) \
+                             : launch(exl3::grouped_kernel<CB_, PT_, K2F_, exl3::GR_NARROW_NTB>, grid, block, 0, st, a))
 #define TFB_GR(CB_)                                                                                     \
-  e = four ? (wide ? launch(exl3::grouped_kernel<CB_, exl3::GR_WIDE_PT, 8>, grid, block, 0, st, a)     \
-                   : launch(exl3::grouped_kernel<CB_, exl3::GR_PT, 8>, grid, block, 0, st, a))         \
-           : (wide ? launch(exl3::grouped_kernel<CB_, exl3::GR_WIDE_PT, 0>, grid, block, 0, st, a)     \
-                   : launch(exl3::grouped_kernel<CB_, exl3::GR_PT, 0>, grid, block, 0, st, a))
+  e = four ? (wide ? TFB_GR4(CB_, exl3::GR_WIDE_PT, 8) : TFB_GR4(CB_, exl3::GR_PT, 8))                   \
+           : (wide ? TFB_GR4(CB_, exl3::GR_WIDE_PT, 0) : TFB_GR4(CB_, exl3::GR_PT, 0))
   if (cb == 0) {
     TFB_GR(0);
   } else if (cb == 1) {
@@ -888,6 +893,7 @@ static int exl3_grouped_launch(const char* who, const exl3::GroupedArgs& a, int 
   } else {
     TFB_GR(2);
   }
+#undef TFB_GR4
 #undef TFB_GR
   return check_cuda(e, who);
 }
@@ -901,7 +907,8 @@ static int exl3_grouped_launch(const char* who, const exl3::GroupedArgs& a, int 
 // the most pairs an item of the sort holds (32: one decode of a weight tile serves up to 32 pairs, at more registers
 // a thread - for calls with many pairs an expert); a pair's bits do not depend on it.  k2_all: 0, or the width that
 // every k2_g and k2_u entry has (a promise: the launch may then use a kernel built for that width alone; a tensor of
-// another width sets the status word and stores nothing).
+// another width sets the status word and stores nothing).  col_tiles: 4 or 2, the 16-column tiles a block takes - 2
+// doubles the blocks of a launch that would otherwise not fill the GPU (few experts in use); no result depends on it.
 // (exl3/experts.cpp `grouped` + `gateup_epilogue`: src/tensorfold/cuda/exl3/experts_grouped.cuh:190-284,
 // src/tensorfold/cuda/exl3/experts.cu:116-158)
 extern "C" int tfb_exl3_gateup(const void* xg, const void* xu, const int64_t* tp_g, const int64_t* tp_u,
@@ -909,7 +916,7 @@ extern "C" int tfb_exl3_gateup(const void* xg, const void* xu, const int64_t* tp
                                const int32_t* members, float* z, int32_t* arrive, const void* svh_g, const void* svh_u,
                                const void* suh_d, void* xd, int K, int N, int P, int cb, int max_items, float limit,
                                int act_mode, const int32_t* sorted_g, const int32_t* sorted_u, int item_pairs,
-                               int k2_all, void* stream) {
+                               int k2_all, int col_tiles, void* stream) {
   TFB_REQUIRE((sorted_g == nullptr) == (sorted_u == nullptr) && aligned16(sorted_g) && aligned16(sorted_u),
               "exl3_gateup: the two width orders come together, 16-byte aligned");
   TFB_REQUIRE(xg && xu && tp_g && tp_u && k2_g && k2_u && items && counts && members && z && arrive && svh_g && svh_u &&
@@ -943,7 +950,7 @@ extern "C" int tfb_exl3_gateup(const void* xg, const void* xu, const int64_t* tp
   a.epi = exl3::GE_GATEUP;
   a.act_mode = act_mode;
   a.limit = limit;
-  return exl3_grouped_launch("exl3_gateup", a, cb, max_items, item_pairs, k2_all, stream);
+  return exl3_grouped_launch("exl3_gateup", a, cb, max_items, item_pairs, k2_all, col_tiles, stream);
 }
 
 // y [P, N] fp32 = rotate(x [P, K] fp16 times W_q of each pair's expert) * svh of every routed pair (rows of other
@@ -953,7 +960,7 @@ extern "C" int tfb_exl3_gateup(const void* xg, const void* xu, const int64_t* tp
 extern "C" int tfb_exl3_down(const void* x, const int64_t* tp, const int32_t* k2, const int32_t* items,
                              const int32_t* counts, const int32_t* members, float* z, int32_t* arrive, const void* svh,
                              float* y, int K, int N, int P, int cb, int max_items, const int32_t* sorted,
-                             int item_pairs, int k2_all, void* stream) {
+                             int item_pairs, int k2_all, int col_tiles, void* stream) {
   TFB_REQUIRE(x && tp && k2 && items && counts && members && z && arrive && svh && y, "exl3_down: null pointer");
   TFB_REQUIRE(aligned16(sorted), "exl3_down: the width order must be 16-byte aligned");
   TFB_REQUIRE(aligned16(z) && aligned16(svh) && aligned16(y), "exl3_down: 16-byte aligned rows");
@@ -977,7 +984,7 @@ extern "C" int tfb_exl3_down(const void* x, const int64_t* tp, const int32_t* k2
   a.epi = exl3::GE_DOWN;
   a.act_mode = 1;
   a.limit = 0.f;
-  return exl3_grouped_launch("exl3_down", a, cb, max_items, item_pairs, k2_all, stream);
+  return exl3_grouped_launch("exl3_down", a, cb, max_items, item_pairs, k2_all, col_tiles, stream);
 }
 
 // out [M, N] (fp32: out_type 0, fp16: 1, bf16: 2; rows out_stride elements apart) = rotate(z) / sqrt(128) * svh + bias

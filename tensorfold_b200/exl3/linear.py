@@ -129,7 +129,7 @@ class Exl3Linear:
             _lib.call("tfb_exl3_down", xh.data_ptr(), t["ptr"].data_ptr(), t["k2"].data_ptr(), t["items"].data_ptr(),
                       t["counts"].data_ptr(), t["members"].data_ptr(), z.data_ptr(), t["arrive"].data_ptr(),
                       self.svh.data_ptr(), y.data_ptr(), self.k, self.n, m, CODEBOOK_IDS[self.codebook], t["n_items"],
-                      0, routed.ITEM_PAIRS, self.k2, s)
+                      0, routed.ITEM_PAIRS, self.k2, routed.col_tiles(t["n_items"], t["n_items"], self.n, 1, self.k2), s)
         if self.bias is not None:
             y += self.bias.float()
         want = out_dtype or (out.dtype if out is not None else x.dtype)
