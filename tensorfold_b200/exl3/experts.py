@@ -179,9 +179,10 @@ def col_tiles(pairs: int, experts: int, n: int, mats: int, k2_all: int = 0, per_
 
 def max_items(pairs: int, experts: int) -> int:
     """Items the sort of ``pairs`` pairs over ``experts`` experts can make: one an expert in use, one more for every
-    full ``ITEM_PAIRS`` pairs."""
+    full ``ITEM_PAIRS`` pairs past an expert's first (u experts in use: at most u + (pairs - u) // ITEM_PAIRS)."""
 
-    return min(pairs, experts) + pairs // ITEM_PAIRS
+    used = min(pairs, experts)
+    return used + (pairs - used) // ITEM_PAIRS
 
 
 class Scratch:

@@ -130,9 +130,13 @@ def make(up: list[tuple], down: tuple, gs: int, *, limit: float = 0.0) -> Expert
 
 
 def max_items(pairs: int, experts: int, tile: int = TILE) -> int:
-    """Items a plan of ``pairs`` can hold: an item per used expert, plus one per ``tile`` pairs past its first."""
+    """Items a plan of ``pairs`` can hold: an expert with c pairs makes 1 + (c - 1) // tile items, so u experts in use
+    make at most u + (pairs - u) // tile, which grows with u <= min(pairs, experts).  (The reference's bound,
+    ``min(pairs, experts) + pairs // tile``, is the same idea with pairs not reduced; the grids sized by this one
+    launch fewer blocks that find no item.)"""
 
-    return min(pairs, experts) + pairs // tile
+    used = min(pairs, experts)
+    return used + (pairs - used) // tile
 
 
 class Plan:

@@ -187,3 +187,24 @@ def test_sigmoid_router_restatement_orders_by_choice_then_id():
     for r in (0, 1, 3):
         assert pick[r, :4].tolist() == np.argsort(-logits[r], kind="stable")[:4].tolist()   # sigmoid is monotone
     assert gap[2] == 0.0 and (wts[:, 4] == 1.0).all()
+
+
+def test_item_bound_holds_for_every_split_of_the_pairs():
+    """``max_items`` (what sizes the plan tables and the grids): never below the items a plan makes, for any way the
+    pairs fall on the experts, and exact for one expert."""
+
+    import random
+
+    from tensorfold_b200 import experts
+    from tensorfold_b200.exl3 import experts as x3
+
+    rnd = random.Random(7)
+    for _ in range(4000):
+        e, p, tile = rnd.randint(1, 12), rnd.randint(0, 70), rnd.choice([8, 16, 192])
+        counts = [0] * e
+        for _ in range(p):
+            counts[rnd.randrange(e) if rnd.random() < 0.7 else 0] += 1
+        made = sum((c + tile - 1) // tile for c in counts)
+        assert made <= experts.max_items(p, e, tile) <= min(p, e) + p // tile
+        assert sum((c + 15) // 16 for c in counts) <= x3.max_items(p, e)
+    assert experts.max_items(17, 1, 8) == 3 and experts.max_items(16, 1, 8) == 2 and experts.max_items(0, 5, 8) == 0
