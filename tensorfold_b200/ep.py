@@ -412,6 +412,10 @@ class PeerExpertParallel:
             self.act_s = torch.zeros((rows_local, shared_experts.width), dtype=torch.bfloat16, device=dev)
             self.y_s = torch.zeros((rows_local, d), dtype=torch.float32, device=dev)
             self.launches += 2
+            # the shared expert needs nothing from the exchange and is needed only by the final sum: its two launches
+            # run on a stream of their own beside the gather, the plan and the routed experts
+            self.side_s = torch.cuda.Stream(dev)
+            self.forked_s, self.joined_s = torch.cuda.Event(), torch.cuda.Event()
             torch.cuda.synchronize(dev)
 
     def forward(self, x_local: torch.Tensor | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
@@ -430,9 +434,14 @@ class PeerExpertParallel:
         with torch.cuda.device(w.device):
             st = w._stream()
             w.route_own(x_local)
-            if self.shared_ex is not None:                         # own rows only; runs while the peers arrive
-                g.gate_up(w.tokens, self.shared_ex, self.plan_s, self.act_s, self.rows_local)
-                g.down(self.act_s, self.shared_ex, self.plan_s, self.y_s, self.rows_local)
+            if self.shared_ex is not None:                         # own rows only; beside everything up to the sum
+                cur = torch.cuda.current_stream(w.device)
+                self.forked_s.record(cur)
+                self.side_s.wait_event(self.forked_s)
+                with torch.cuda.stream(self.side_s):
+                    g.gate_up(w.tokens, self.shared_ex, self.plan_s, self.act_s, self.rows_local)
+                    g.down(self.act_s, self.shared_ex, self.plan_s, self.y_s, self.rows_local)
+                self.joined_s.record(self.side_s)
             w.gather()
             if plan.hot:
                 g.route_split(w.pick_all, plan, w.lo)
@@ -444,6 +453,8 @@ class PeerExpertParallel:
             _lib.call("tfb_combine_push", self.y.data_ptr(), w.wts_all.data_ptr(), w.pick_all.data_ptr(), w.lo,
                       w.per_rank, w.windows.data_ptr(), w.p_offset, w.rank, self.rows_local, self.rows, w.slots, d,
                       w.step.data_ptr(), st)
+            if self.shared_ex is not None:
+                torch.cuda.current_stream(w.device).wait_event(self.joined_s)
             w.sum(out, self.y_s if self.shared_ex is not None else None)
         return out
 
