@@ -52,3 +52,23 @@ def test_traffic_is_quoted_only_for_the_captured_kernel_sources():
         assert 224985088 <= nbytes <= 1.2 * 224985088
     else:
         assert nbytes is None and "stale" in why
+
+
+def test_reference_arm_prints_its_line_without_a_gpu():
+    """`bench.py --impl reference` (the reference's CPU path restated, on the host cores) needs no GPU and prints the
+    contract's line: the same metric, unit and config as the GPU arm, its own `cpu_baseline` and a zero-copy `e2e`."""
+
+    import json
+    import subprocess
+    import sys
+
+    out = subprocess.run([sys.executable, str(ROOT / "bench.py"), "--impl", "reference", "--steps", "1", "--warmup", "1"],
+                         capture_output=True, text=True, timeout=600, cwd=str(ROOT))
+    assert out.returncode == 0, out.stderr[-2000:]
+    line = json.loads([ln for ln in out.stdout.splitlines() if ln.startswith("{")][-1])
+    assert line["impl"] == "reference" and line["metric"] == "moe_layer_tokens_per_s" and line["unit"] == "tokens/s"
+    assert line["higher_is_better"] is True and line["n_gpus"] == 1 and line["value"] > 0
+    assert "config 2" in line["config"]["workload"]
+    base = line["cpu_baseline"]
+    assert base["kind"] == "port" and base["cores"] >= 1 and base["value"] == line["value"] and base["sample"]
+    assert line["e2e"] == {"value": line["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
