@@ -890,13 +890,19 @@ def bench_c5(torch, dist, args, dev, rank: int, world: int, hbm: float) -> dict:
         return rows, active, layers
 
     def stack(layers, src, h_out, each=None):
+        """The 8 layers with h = bf16(h + layer(h)) between them.  Timed form (no `each`): the kernel that adds the
+        ranks' shares also adds the residual row and rounds.  Checked form: the layer's fp32 output is handed to
+        `each`, the residual add is torch's - the same arithmetic, and the two forms' results are compared below."""
+
         h = src
         for li, layer in enumerate(layers):
+            if each is None:
+                h = layer.forward(h, residual=True)               # bf16 [rows, D]
+                continue
             y = layer.forward(h)                                  # fp32 [rows, D]
             if li == 0:
                 h = layer.tokens                                  # the staged rows (src may be pinned host memory)
-            if each is not None:
-                each(li, h, y)
+            each(li, h, y)
             h = (h.float() + y).to(torch.bfloat16)                # the residual add between layers
         h_out.copy_(h)
 
@@ -920,10 +926,12 @@ def bench_c5(torch, dist, args, dev, rank: int, world: int, hbm: float) -> dict:
         worst = max(worst, rel_l2(torch, y[:active], want))
         del full
 
-    h_chk = torch.zeros_like(x)
+    h_chk, h_fused = torch.zeros_like(x), torch.zeros_like(x)
     stack(layers, x, h_chk, compare)
+    stack(layers, x, h_fused)                                     # the timed form: residual inside the last kernel
     torch.cuda.synchronize()
     status = _lib.kernel_status()
+    same = same and bool(torch.equal(h_fused[:active], h_chk[:active]))
     ok, worst_all = all_ok(torch, dist, same and worst <= TOL and status == 0, worst)
     check = {"picks_equal": ok or same, "rel_l2": worst_all, "tolerance": TOL, "tokens": 32, "layers": C5_LAYERS,
              "against": "the one-GPU EXL3 layer on the same layer input, every layer of the stack", "passed": ok}
@@ -982,7 +990,7 @@ def bench_c5(torch, dist, args, dev, rank: int, world: int, hbm: float) -> dict:
         per_rank[rank] = nbytes
         dist.all_reduce(per_rank)
         rb = [int(v) for v in per_rank.tolist()]
-        launches = sum(layer.launches for layer in layers) + 3 * C5_LAYERS + 2
+        launches = sum(layer.launches + 1 for layer in layers) + 2    # each layer stages its rows; two copies a step
         lines.append({"tokens": tokens, "rows_per_rank": rows, "ms_per_step": ms, **spread(all_ms),
                       "tokens_per_s": tokens / (ms * 1e-3), "e2e_ms_per_step": e2e_ms,
                       "e2e_tokens_per_s": tokens / (e2e_ms * 1e-3), "steps": k, "launches_per_step": launches,

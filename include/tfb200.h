@@ -151,10 +151,12 @@ int tfb_peer_push(const float* partial, void* const* windows, int64_t p_offset, 
 int tfb_window_picks(const int32_t* pick, const float* wts, int lo, int n, int32_t* pick_out, float* wts_out,
                      int count, void* stream);
 /* out[rows_local, D] (bf16, or fp32 with out_f32) = the ranks' partial sums added in rank order, then, when given,
- * extra_w[j * extra_w_stride] * extra[j, :] (the replicated shared expert of the rank's own rows); rounded once. */
+ * extra_w[j * extra_w_stride] * extra[j, :] (the replicated shared expert of the rank's own rows), then, when given,
+ * the residual rows [rows_local, D] bf16 (the layer's input: out = h + layer(h) with no pass of its own; not the same
+ * memory as out); rounded once. */
 int tfb_peer_sum(void* const* windows, int rank, int64_t p_offset, int world, int rows_local, int D, void* out,
-                 int out_f32, const float* extra, const float* extra_w, int extra_w_stride, const void* step,
-                 void* stream);
+                 int out_f32, const float* extra, const float* extra_w, int extra_w_stride, const void* residual,
+                 const void* step, void* stream);
 
 /* out[T, D] = sum over slots, in slot order, of wts[T, slots] * y[T, slots, D] (fp32 fma chain from 0), rounded once.
  * y is fp32 (y_bf16 = 0) or bf16; out is bf16 (out_f32 = 0) or fp32.

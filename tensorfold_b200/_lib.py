@@ -47,7 +47,7 @@ SIGNATURES: dict[str, tuple] = {
     "tfb_peer_stage": (P, P, L, L, P),
     "tfb_peer_gather": (P, I, I, I, P, P, P, P, P),
     "tfb_combine_push": (P, P, P, I, I, P, L, I, I, I, I, I, P, P),
-    "tfb_peer_sum": (P, I, L, I, I, I, P, I, P, P, I, P, P),
+    "tfb_peer_sum": (P, I, L, I, I, I, P, I, P, P, I, P, P, P),
     "tfb_peer_push": (P, P, L, I, I, I, I, P, P),
     "tfb_window_picks": (P, P, I, I, P, P, I, P),
     "tfb_kernel_status": (P, P),

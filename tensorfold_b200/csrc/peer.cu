@@ -181,12 +181,14 @@ window_picks_kernel(const int* __restrict__ pick, const float* __restrict__ wts,
 }
 
 // Results barrier, then out [rows, D] = the ranks' rows added in rank order, then (when given) extra_w[j] * extra[j, :]
-// (the replicated shared expert of the rank's own rows), rounded once to bf16 or stored as fp32.
+// (the replicated shared expert of the rank's own rows), then (when given) the residual row (bf16; the layer's input:
+// out = h + layer(h) without a pass of its own), rounded once to bf16 or stored as fp32.
 template <typename TO>
 __global__ void __launch_bounds__(256)
 peer_sum_kernel(uint8_t* const* __restrict__ windows, int rank, int64_t p_offset, int world, int rows, int D,
                 TO* __restrict__ out, const float* __restrict__ extra, const float* __restrict__ extra_w,
-                int extra_w_stride, const uint32_t* __restrict__ step, uint64_t limit_ns) {
+                int extra_w_stride, const __nv_bfloat16* __restrict__ residual, const uint32_t* __restrict__ step,
+                uint64_t limit_ns) {
   pdl_wait();
   if (step_failed()) return;                          // the tokens barrier ran out: out keeps what it held
   if (!peer_barrier(windows, rank, world, 1, step[0], limit_ns)) return;
@@ -208,6 +210,13 @@ peer_sum_kernel(uint8_t* const* __restrict__ windows, int rank, int64_t p_offset
       acc.y = fmaf(w, f.y, acc.y);
       acc.z = fmaf(w, f.z, acc.z);
       acc.w = fmaf(w, f.w, acc.w);
+    }
+    if (residual != nullptr) {
+      const uint2 h = reinterpret_cast<const uint2*>(residual)[i];
+      acc.x += bf16_lo(h.x);
+      acc.y += bf16_hi(h.x);
+      acc.z += bf16_lo(h.y);
+      acc.w += bf16_hi(h.y);
     }
     if constexpr (sizeof(TO) == 4) {
       reinterpret_cast<float4*>(out)[i] = acc;
@@ -301,12 +310,14 @@ extern "C" int tfb_window_picks(const int32_t* pick, const float* wts, int lo, i
 
 extern "C" int tfb_peer_sum(void* const* windows, int rank, int64_t p_offset, int world, int rows_local, int D,
                             void* out, int out_f32, const float* extra, const float* extra_w, int extra_w_stride,
-                            const void* step, void* stream) {
+                            const void* residual, const void* step, void* stream) {
   TFB_REQUIRE(windows && out && step, "peer_sum: null pointer");
   TFB_REQUIRE(world >= 1 && world <= 32 && rank >= 0 && rank < world, "peer_sum: rank %d of %d", rank, world);
   TFB_REQUIRE(D > 0 && D % 4 == 0 && rows_local >= 1, "peer_sum: bad sizes");
   TFB_REQUIRE((extra == nullptr) == (extra_w == nullptr), "peer_sum: extra and its weights come together");
   TFB_REQUIRE(extra == nullptr || (aligned16(extra) && extra_w_stride >= 1), "peer_sum: extra rows 16-byte aligned");
+  TFB_REQUIRE(aligned16(residual) && residual != out, "peer_sum: the residual rows are 16-byte aligned and not the output");
+  auto* res = static_cast<const __nv_bfloat16*>(residual);
   const int64_t n4 = (int64_t)rows_local * D / 4;
   const int grid = (int)((n4 + 255) / 256 < 592 ? (n4 + 255) / 256 : 592);
   auto st = static_cast<cudaStream_t>(stream);
@@ -314,11 +325,11 @@ extern "C" int tfb_peer_sum(void* const* windows, int rank, int64_t p_offset, in
   auto stp = static_cast<const uint32_t*>(step);
   if (out_f32)
     return check_cuda(launch(peer_sum_kernel<float>, dim3(grid), dim3(256), 0, st, wins, rank, p_offset, world,
-                             rows_local, D, static_cast<float*>(out), extra, extra_w, extra_w_stride, stp,
+                             rows_local, D, static_cast<float*>(out), extra, extra_w, extra_w_stride, res, stp,
                              wait_limit_ns()),
                       "peer_sum");
   return check_cuda(launch(peer_sum_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, st, wins, rank, p_offset, world,
-                           rows_local, D, static_cast<__nv_bfloat16*>(out), extra, extra_w, extra_w_stride, stp,
+                           rows_local, D, static_cast<__nv_bfloat16*>(out), extra, extra_w, extra_w_stride, res, stp,
                            wait_limit_ns()),
                     "peer_sum");
 }

@@ -356,14 +356,18 @@ class PeerWindow:
         _lib.call("tfb_peer_push", partial.data_ptr(), self.windows.data_ptr(), self.p_offset, self.rank,
                   self.rows_local, self.rows, self.dims, self.step.data_ptr(), self._stream())
 
-    def sum(self, out: torch.Tensor, extra: torch.Tensor | None = None) -> None:
+    def sum(self, out: torch.Tensor, extra: torch.Tensor | None = None, residual: torch.Tensor | None = None) -> None:
         """Results barrier, then out [rows_local, D] (bf16 or fp32) = the ranks' shares in rank order (+ the shared
-        expert's rows ``extra`` weighted by the own rows' last slot)."""
+        expert's rows ``extra`` weighted by the own rows' last slot, + the ``residual`` rows, bf16)."""
 
         ew = self.wts_mine.data_ptr() + 4 * self.top_k if extra is not None else 0
+        if residual is not None and (residual.dtype != torch.bfloat16 or not residual.is_contiguous()
+                                     or tuple(residual.shape) != (self.rows_local, self.dims)):
+            raise ValueError("the residual rows are contiguous bf16 [rows_local, D]")
         _lib.call("tfb_peer_sum", self.windows.data_ptr(), self.rank, self.p_offset, self.world, self.rows_local,
                   self.dims, out.data_ptr(), 1 if out.dtype == torch.float32 else 0,
-                  extra.data_ptr() if extra is not None else 0, ew, self.slots, self.step.data_ptr(), self._stream())
+                  extra.data_ptr() if extra is not None else 0, ew, self.slots,
+                  residual.data_ptr() if residual is not None else 0, self.step.data_ptr(), self._stream())
 
 
 class PeerExpertParallel:
@@ -481,10 +485,14 @@ class PeerExl3ExpertParallel:
         self.wts_local = torch.zeros((rows, top_k), dtype=torch.float32, device=dev)
         self.partial = torch.zeros((rows, d), dtype=torch.float32, device=dev)
         self.out = torch.zeros((rows_local, d), dtype=torch.float32, device=dev)
+        self.out_next = torch.zeros((rows_local, d), dtype=torch.bfloat16, device=dev)
         self.launches = 7 + exl3.LAUNCHES_PER_CALL               # + 1 when forward() is given rows to stage
         torch.cuda.synchronize(dev)
 
-    def forward(self, x_local: torch.Tensor | None = None) -> torch.Tensor:
+    def forward(self, x_local: torch.Tensor | None = None, residual: bool = False) -> torch.Tensor:
+        """The layer's output [rows_local, D] fp32; with ``residual`` the next hidden state bf16(h + layer(h)) instead
+        (h = the rank's rows as staged in the window), formed by the kernel that adds the ranks' shares."""
+
         w = self.win
         with torch.cuda.device(w.device):
             w.route_own(x_local)
@@ -494,5 +502,8 @@ class PeerExl3ExpertParallel:
             self.exl3.routed(w.x_all, self.pick_local, self.wts_local, self.local, self.scratch, self.partial,
                              self.rows, limit=self.limit)
             w.push(self.partial)
+            if residual:
+                w.sum(self.out_next, residual=w.tokens)
+                return self.out_next
             w.sum(self.out)
         return self.out

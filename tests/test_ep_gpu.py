@@ -156,6 +156,9 @@ def _peer_body(rank, world, port, out):
         moe.select_rows(buf.logits, buf, shape.top_k, shape.experts)
         want = x3.routed(x, buf.pick, buf.wts, ex_full, scratch, None, rows)
         flags.append(bool(torch.isfinite(got).all()) and bool((got - want).norm() / want.norm() < 1e-5))
+        # the next hidden state formed by the summing kernel itself: bf16(h + layer(h)), the same bits as the add after it
+        nxt = peer_x.forward(x, residual=True)
+        flags.append(bool(torch.equal(nxt, (x.float() + got).to(torch.bfloat16))))
     flags.append(_lib.kernel_status() == 0)
     torch.cuda.synchronize()
     out.put((rank, tuple(flags)))

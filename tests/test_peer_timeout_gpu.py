@@ -55,7 +55,7 @@ def test_tokens_barrier_names_the_rank_that_never_arrived(short_limit, rank, mis
               rows, world * rows, 1, dims, step.data_ptr(), st)
     out = torch.full((rows, dims), 3.0, dtype=torch.float32, device=DEV)
     _lib.call("tfb_peer_sum", table.data_ptr(), rank, p_off, world, rows, dims, out.data_ptr(), 1, 0, 0, 1,
-              step.data_ptr(), st)
+              0, step.data_ptr(), st)
     torch.cuda.synchronize()
     status = _lib.kernel_status()
     assert status & 0xFF == _lib.ST_WAIT_TIMEOUT
@@ -78,7 +78,7 @@ def test_results_barrier_is_told_apart(short_limit):
     out = torch.full((rows, dims), 3.0, dtype=torch.float32, device=DEV)
     st = torch.cuda.current_stream().cuda_stream
     _lib.call("tfb_peer_sum", table.data_ptr(), 0, p_off, world, rows, dims, out.data_ptr(), 1, 0, 0, 1,
-              step.data_ptr(), st)
+              0, step.data_ptr(), st)
     torch.cuda.synchronize()
     with pytest.raises(_lib.StepFailed) as err:
         _lib.check_status()
