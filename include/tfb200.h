@@ -287,8 +287,10 @@ int tfb_exl3_prologue(const void* x, int64_t x_stride, int x_is_fp16, const int3
  * more registers a thread: for calls with many pairs an expert); a pair's bits do not depend on it.
  * k2_all: 0, or the width every entry of k2_g and k2_u has - a promise that lets the launch use a kernel built for
  * that width alone (a tenth of the code; it pays at a few tokens); a tensor of another width then sets the status
- * word and nothing is stored.  col_tiles: 4 or 2, the 16-column tiles a thread block takes (2 doubles the blocks of
- * a launch that would otherwise leave SMs idle: few experts in use); no result depends on it.
+ * word and nothing is stored.  -1: the widths differ - the launch uses a build with short loops, so that blocks
+ * decoding different widths share an SM's instruction cache (col_tiles 4).  col_tiles: 4 or 2, the 16-column tiles a thread block takes (2 doubles the blocks of
+ * a launch that would otherwise leave SMs idle: few experts in use; offered with k2_all = 8 only); no result depends
+ * on it.
  * Replaces `grouped` + `gateup_epilogue`: src/tensorfold/cuda/exl3/experts_grouped.cuh:190-284,
  * src/tensorfold/cuda/exl3/experts.cu:116-158. */
 int tfb_exl3_gateup(const void* xg, const void* xu, const int64_t* tp_g, const int64_t* tp_u, const int32_t* k2_g,

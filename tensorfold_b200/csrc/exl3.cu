@@ -159,14 +159,17 @@ __device__ __forceinline__ void mma_f16(float (&d)[4], const uint32_t (&a)[4], u
 // four, whose inputs are loaded before the block's tiles are decoded.  x[pt]: the lane's pair (B column lane / 4 of
 // tile pt) at input 16 kt0 + 2 (lane % 4).  NPT: the mma tiles of eight pairs that are live (one decode feeds them all).
 // Returns false when a copy never landed.
-template <int CB, int K2, int PT, int NPT, int NTB>
+template <int CB, int K2, int PT, int NPT, int NTB, bool COMPACT>
 __device__ __forceinline__ bool warp_rows(const uint8_t* __restrict__ T, int ntiles, int kt0, int nkt, int nt0,
                                           const __half* const (&x)[PT], uint8_t* ring, uint64_t* bars, int lane,
                                           float (&acc)[NTB][PT][4]) {
   constexpr int TW = Win<K2>::TW, NW = Win<K2>::NW;
   constexpr int TILE_B = 16 * K2, SEG = NTB * TILE_B;                 // bytes a tile / a row of the CTA's tiles
   constexpr int ROWS = GR_SLOT_BYTES / SEG < 1 ? 1 : (GR_SLOT_BYTES / SEG > 16 ? 16 : GR_SLOT_BYTES / SEG);
-  constexpr int RBMAX = 2;                            // rows a block (their inputs sit in registers; 4 was 3 % slower)
+  // rows a block (their inputs sit in registers; 4 was 3 % slower).  COMPACT: one row a block and the blocks of a slot
+  // walked by a loop - a fifth of the code, for layers of mixed widths, where blocks that decode different widths
+  // share an SM and the unrolled loops of five or seven widths miss the instruction cache all the time
+  constexpr int RBMAX = COMPACT ? 1 : 2;
   constexpr int RB = ROWS < RBMAX ? ROWS : RBMAX;
   static_assert(ROWS * SEG <= GR_SLOT_BYTES, "a slot holds whole rows");
   const int nslot = (nkt + ROWS - 1) / ROWS;
@@ -200,7 +203,7 @@ __device__ __forceinline__ bool warp_rows(const uint8_t* __restrict__ T, int nti
   for (int f = 0; f < nslot; ++f) {
     const int rows = min(ROWS, nkt - f * ROWS);
     const uint32_t* slot = reinterpret_cast<const uint32_t*>(ring + stage * GR_SLOT_BYTES);
-#pragma unroll
+#pragma unroll(COMPACT ? 1 : 16)
     for (int r0 = 0; r0 < ROWS; r0 += RB) {
       if (r0 < rows) {
         uint32_t b[RB][NPT][2];
@@ -376,7 +379,7 @@ enum GroupedEpilogue : int { GE_NONE = 0, GE_GATEUP = 1, GE_DOWN = 2 };
 // alone - a tenth of the code, which matters where a CTA's life is short (one token: the dominant stall of the
 // all-widths kernel was the instruction fetch).
 // NTB: 16-column tiles a CTA (4, or 2 where the launch would otherwise have too few CTAs to fill the GPU).
-template <int CB, int PT, int K2F, int NTB>
+template <int CB, int PT, int K2F, int NTB, bool COMPACT>
 __global__ void __launch_bounds__(GR_WARPS * 32)
 grouped_kernel(const GroupedArgs a) {
   constexpr int PAIRS = 8 * PT, GR_RED_STRIDE = NTB * 16 + 1;
@@ -432,11 +435,11 @@ grouped_kernel(const GroupedArgs a) {
   uint64_t* my_bars = bars + warp * GR_STAGES;
 #define TFB_K2_BODY(K2_)                                                                                  \
     if constexpr (PT == 2)                                                                                \
-      ok = live > 1 ? warp_rows<CB, K2_, 2, 2, NTB>(T, a.N >> 4, kt0, nkt, nt0, x, my_ring, my_bars, lane, acc)  \
-                    : warp_rows<CB, K2_, 2, 1, NTB>(T, a.N >> 4, kt0, nkt, nt0, x, my_ring, my_bars, lane, acc); \
+      ok = live > 1 ? warp_rows<CB, K2_, 2, 2, NTB, COMPACT>(T, a.N >> 4, kt0, nkt, nt0, x, my_ring, my_bars, lane, acc)  \
+                    : warp_rows<CB, K2_, 2, 1, NTB, COMPACT>(T, a.N >> 4, kt0, nkt, nt0, x, my_ring, my_bars, lane, acc); \
     else                                                                                                  \
-      ok = live > 2 ? warp_rows<CB, K2_, 4, 4, NTB>(T, a.N >> 4, kt0, nkt, nt0, x, my_ring, my_bars, lane, acc)  \
-                    : warp_rows<CB, K2_, 4, 2, NTB>(T, a.N >> 4, kt0, nkt, nt0, x, my_ring, my_bars, lane, acc);
+      ok = live > 2 ? warp_rows<CB, K2_, 4, 4, NTB, COMPACT>(T, a.N >> 4, kt0, nkt, nt0, x, my_ring, my_bars, lane, acc)  \
+                    : warp_rows<CB, K2_, 4, 2, NTB, COMPACT>(T, a.N >> 4, kt0, nkt, nt0, x, my_ring, my_bars, lane, acc);
 #define TFB_K2(K2_) \
   case K2_:         \
     TFB_K2_BODY(K2_) \
@@ -866,7 +869,10 @@ static int exl3_grouped_launch(const char* who, const exl3::GroupedArgs& a, int 
                                int k2_all, int col_tiles, void* stream) {
   TFB_REQUIRE(col_tiles == exl3::GR_NTB || col_tiles == exl3::GR_NARROW_NTB, "%s: %d or %d column tiles a block, not %d",
               who, exl3::GR_NTB, exl3::GR_NARROW_NTB, col_tiles);
-  TFB_REQUIRE(k2_all == 0 || (k2_all >= 2 && k2_all <= 16), "%s: k2_all is 0 or the one width of every tensor", who);
+  TFB_REQUIRE(k2_all == 0 || k2_all == -1 || (k2_all >= 2 && k2_all <= 16),
+              "%s: k2_all is 0, -1 (the widths differ) or the one width of every tensor", who);
+  TFB_REQUIRE(k2_all == 8 || col_tiles == exl3::GR_NTB, "%s: only a launch of 4.00-bit tensors (k2_all 8) takes blocks of %d "
+              "column tiles", who, exl3::GR_NARROW_NTB);
   TFB_REQUIRE(item_pairs == 8 * exl3::GR_PT || item_pairs == 8 * exl3::GR_WIDE_PT, "%s: items of %d or %d pairs, not %d",
               who, 8 * exl3::GR_PT, 8 * exl3::GR_WIDE_PT, item_pairs);
   TFB_REQUIRE(a.K > 0 && a.N > 0 && a.K % 128 == 0 && a.N % 128 == 0, "%s: K and N must be multiples of 128", who);
@@ -879,13 +885,16 @@ static int exl3_grouped_launch(const char* who, const exl3::GroupedArgs& a, int 
   const dim3 block(exl3::GR_WARPS * 32);
   const bool wide = item_pairs == 8 * exl3::GR_WIDE_PT;
   const bool four = k2_all == 8;                      // the one width with a kernel of its own (4.00 bits a weight)
+  const bool narrow = col_tiles == exl3::GR_NARROW_NTB;
   cudaError_t e;
-#define TFB_GR4(CB_, PT_, K2F_)                                                                           \
-  (col_tiles == exl3::GR_NTB ? launch(exl3::grouped_kernel<CB_, PT_, K2F_, exl3::GR_NTB>, grid, block, 0, st, a) \
-                             : launch(exl3::grouped_kernel<CB_, PT_, K2F_, exl3::GR_NARROW_NTB>, grid, block, 0, st, a))
+#define TFB_GR4(CB_, PT_, K2F_) launch(exl3::grouped_kernel<CB_, PT_, K2F_, exl3::GR_NTB, false>, grid, block, 0, st, a)
+#define TFB_GRN(CB_, PT_) launch(exl3::grouped_kernel<CB_, PT_, 8, exl3::GR_NARROW_NTB, false>, grid, block, 0, st, a)
+#define TFB_GRC(CB_, PT_) launch(exl3::grouped_kernel<CB_, PT_, 0, exl3::GR_NTB, true>, grid, block, 0, st, a)
 #define TFB_GR(CB_)                                                                                     \
-  e = four ? (wide ? TFB_GR4(CB_, exl3::GR_WIDE_PT, 8) : TFB_GR4(CB_, exl3::GR_PT, 8))                   \
-           : (wide ? TFB_GR4(CB_, exl3::GR_WIDE_PT, 0) : TFB_GR4(CB_, exl3::GR_PT, 0))
+  e = k2_all == -1 ? (wide ? TFB_GRC(CB_, exl3::GR_WIDE_PT) : TFB_GRC(CB_, exl3::GR_PT))                 \
+      : narrow     ? (wide ? TFB_GRN(CB_, exl3::GR_WIDE_PT) : TFB_GRN(CB_, exl3::GR_PT))                 \
+      : four       ? (wide ? TFB_GR4(CB_, exl3::GR_WIDE_PT, 8) : TFB_GR4(CB_, exl3::GR_PT, 8))           \
+                   : (wide ? TFB_GR4(CB_, exl3::GR_WIDE_PT, 0) : TFB_GR4(CB_, exl3::GR_PT, 0))
   if (cb == 0) {
     TFB_GR(0);
   } else if (cb == 1) {
@@ -893,6 +902,8 @@ static int exl3_grouped_launch(const char* who, const exl3::GroupedArgs& a, int 
   } else {
     TFB_GR(2);
   }
+#undef TFB_GRC
+#undef TFB_GRN
 #undef TFB_GR4
 #undef TFB_GR
   return check_cuda(e, who);
@@ -907,8 +918,10 @@ static int exl3_grouped_launch(const char* who, const exl3::GroupedArgs& a, int 
 // the most pairs an item of the sort holds (32: one decode of a weight tile serves up to 32 pairs, at more registers
 // a thread - for calls with many pairs an expert); a pair's bits do not depend on it.  k2_all: 0, or the width that
 // every k2_g and k2_u entry has (a promise: the launch may then use a kernel built for that width alone; a tensor of
-// another width sets the status word and stores nothing).  col_tiles: 4 or 2, the 16-column tiles a block takes - 2
-// doubles the blocks of a launch that would otherwise not fill the GPU (few experts in use); no result depends on it.
+// another width sets the status word and stores nothing); -1: the widths differ (a build of the kernel with short
+// loops: blocks of different widths then share an SM's instruction cache).  col_tiles: 4 or 2, the 16-column tiles a block takes - 2
+// doubles the blocks of a launch that would otherwise not fill the GPU (few experts in use; built for k2_all = 8 only);
+// no result depends on it.
 // (exl3/experts.cpp `grouped` + `gateup_epilogue`: src/tensorfold/cuda/exl3/experts_grouped.cuh:190-284,
 // src/tensorfold/cuda/exl3/experts.cu:116-158)
 extern "C" int tfb_exl3_gateup(const void* xg, const void* xu, const int64_t* tp_g, const int64_t* tp_u,

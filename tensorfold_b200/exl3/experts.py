@@ -164,17 +164,19 @@ def item_pairs(pairs: int, experts: int) -> int:
     return WIDE_ITEM_PAIRS if pairs >= WIDE_FROM * experts else ITEM_PAIRS
 
 
+COMPACT_MIXED = True              # projections of mixed widths run the trellis kernel's build with short loops (same bits)
 FILL_BLOCKS = 1480                # thread blocks that fill a B200 twice over (148 SMs x 5 blocks x 2)
 
 
 def col_tiles(pairs: int, experts: int, n: int, mats: int, k2_all: int = 0, per_item: int = ITEM_PAIRS) -> int:
     """16-column tiles a block of the trellis kernel takes: 4, or 2 while the launch would have too few blocks to
     keep every SM busy (few experts in use) - a function of the call's shape; no result depends on it.  Only for
-    projections whose tensors all have 4 bits or more (a row of two narrower tiles is a bulk copy of 64-192 bytes,
-    too small to stream well: a mixed-width layer at one token lost a quarter) and for items of 16 pairs."""
+    projections whose tensors all have 4.00 bits (the kernel built for that width; a row of two narrower tiles is a
+    bulk copy of 64-192 bytes, too small to stream well: a mixed-width layer at one token lost a quarter) and for
+    items of 16 pairs."""
 
     few = min(pairs, experts) * (n // 64) * mats < FILL_BLOCKS
-    return 2 if few and k2_all >= 8 and per_item == ITEM_PAIRS else 4
+    return 2 if few and k2_all == 8 and per_item == ITEM_PAIRS else 4
 
 
 def max_items(pairs: int, experts: int) -> int:
@@ -258,9 +260,10 @@ def routed(x: torch.Tensor, pick: torch.Tensor, wts: torch.Tensor | None, ex: Ex
     st, items = _stream(x), max_items(pairs, ex.count)
     per_item = item_pairs(pairs, ex.count) if group_first else ITEM_PAIRS      # `group` sorts into the narrow items
     sort = (s.sort_members.data_ptr(), s.sort_items.data_ptr(), s.sort_counts.data_ptr())
-    # the one width of a projection's tensors, or 0
-    k2_gu = ex.k2_gu[0] if ex.k2_gu[0] == ex.k2_gu[1] else 0
-    k2_d = ex.k2_d[0] if ex.k2_d[0] == ex.k2_d[1] else 0
+    # the one width of a projection's tensors, or -1: they differ (the kernels then run a build with short loops)
+    differ = -1 if COMPACT_MIXED else 0
+    k2_gu = ex.k2_gu[0] if ex.k2_gu[0] == ex.k2_gu[1] else differ
+    k2_d = ex.k2_d[0] if ex.k2_d[0] == ex.k2_d[1] else differ
     # a layer of mixed widths: the prologue lays the items out width by width, once a projection
     order = [s.by_width[m].data_ptr() for m in range(3)] if ex.mixed and group_first else [0, 0, 0]
     with torch.cuda.device(x.device):

@@ -286,23 +286,44 @@ def test_prompt_matmul_against_float64_and_the_decode_form(bits, cb, bias, m, od
         prefill.matmul(layer, x, torch.empty((m, n + 1), device="cuda"), ws)
 
 
-@pytest.mark.parametrize("widths", [lambda e: (8, 8, 8), lambda e: ((2, 16, 7)[e % 3], (5, 3)[e % 2], (4, 9, 12, 6)[e % 4])],
-                         ids=["four_bits", "mixed_widths"])
 @pytest.mark.parametrize("R", [1, 37])
-def test_blocks_of_two_or_four_column_tiles_give_the_same_bits(widths, R, monkeypatch):
-    """The trellis kernel's thread blocks take four 16-column tiles, or two where a launch would leave SMs idle: the
-    choice is the host's (a function of the call's shape) and no bit depends on it, at any width."""
+def test_blocks_of_two_or_four_column_tiles_give_the_same_bits(R, monkeypatch):
+    """The trellis kernel's thread blocks take four 16-column tiles, or two where a launch of 4.00-bit tensors would
+    leave SMs idle: the choice is the host's (a function of the call's shape) and no bit depends on it."""
 
     from tensorfold_b200.exl3 import experts
 
     E, D, I, TOPK = 10, 256, 384, 3
-    ex, _ = _layer(E, D, I, [widths(e) for e in range(E)], 0, 31)
+    ex, _ = _layer(E, D, I, [(8, 8, 8)] * E, 0, 31)
     g = torch.Generator().manual_seed(14)
     x = torch.randn((R, D), generator=g).to(torch.bfloat16).to(DEV)
     sel, w = _picks(E, R, TOPK, g)
     outs = []
     for tiles in (4, 2):
         monkeypatch.setattr(experts, "col_tiles", lambda *a, tiles=tiles, **k: tiles)
+        s = experts.Scratch(ex, R, TOPK)
+        outs.append((experts.routed(x, sel, w, ex, s, None, R).clone(), s.y[:R * TOPK].clone()))
+    torch.cuda.synchronize()
+    assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
+    assert bool(torch.isfinite(outs[0][0]).all()) and float(outs[0][0].abs().max()) > 0
+
+
+@pytest.mark.parametrize("R", [1, 37, 200])
+def test_the_short_loop_build_for_mixed_widths_gives_the_same_bits(R, monkeypatch):
+    """A projection whose tensors differ in width runs the kernel's build with short loops (blocks of different widths
+    then share an SM's instruction cache); the all-widths build with unrolled loops gives the same bits."""
+
+    from tensorfold_b200.exl3 import experts
+
+    E, D, I, TOPK = 12, 256, 384, 3
+    ex, _ = _layer(E, D, I, [((2, 16, 7)[e % 3], (5, 3, 8)[e % 3], (4, 9, 12, 6)[e % 4]) for e in range(E)], 0, 33)
+    assert ex.mixed
+    g = torch.Generator().manual_seed(15)
+    x = torch.randn((R, D), generator=g).to(torch.bfloat16).to(DEV)
+    sel, w = _picks(E, R, TOPK, g)
+    outs = []
+    for compact in (True, False):
+        monkeypatch.setattr(experts, "COMPACT_MIXED", compact)
         s = experts.Scratch(ex, R, TOPK)
         outs.append((experts.routed(x, sel, w, ex, s, None, R).clone(), s.y[:R * TOPK].clone()))
     torch.cuda.synchronize()
