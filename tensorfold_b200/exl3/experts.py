@@ -165,6 +165,7 @@ def item_pairs(pairs: int, experts: int) -> int:
 
 
 COMPACT_MIXED = True              # projections of mixed widths run the trellis kernel's build with short loops (same bits)
+CROWDED_BLOCKS = 592              # thread blocks from which an SM of a B200 holds four of a launch at once
 FILL_BLOCKS = 1480                # thread blocks that fill a B200 twice over (148 SMs x 5 blocks x 2)
 
 
@@ -260,10 +261,15 @@ def routed(x: torch.Tensor, pick: torch.Tensor, wts: torch.Tensor | None, ex: Ex
     st, items = _stream(x), max_items(pairs, ex.count)
     per_item = item_pairs(pairs, ex.count) if group_first else ITEM_PAIRS      # `group` sorts into the narrow items
     sort = (s.sort_members.data_ptr(), s.sort_items.data_ptr(), s.sort_counts.data_ptr())
-    # the one width of a projection's tensors, or -1: they differ (the kernels then run a build with short loops)
-    differ = -1 if COMPACT_MIXED else 0
-    k2_gu = ex.k2_gu[0] if ex.k2_gu[0] == ex.k2_gu[1] else differ
-    k2_d = ex.k2_d[0] if ex.k2_d[0] == ex.k2_d[1] else differ
+    # the one width of a projection's tensors; or -1: they differ and the launch is large enough for blocks of several
+    # widths to share an SM (the kernels then run a build with short loops); or 0: they differ, a small launch
+    def width_of(k2: tuple[int, int], n: int, mats: int) -> int:
+        if k2[0] == k2[1]:
+            return k2[0]
+        crowded = min(pairs, ex.count) * (n // 64) * mats >= CROWDED_BLOCKS
+        return -1 if COMPACT_MIXED and crowded else 0
+
+    k2_gu, k2_d = width_of(ex.k2_gu, width, 2), width_of(ex.k2_d, dims, 1)
     # a layer of mixed widths: the prologue lays the items out width by width, once a projection
     order = [s.by_width[m].data_ptr() for m in range(3)] if ex.mixed and group_first else [0, 0, 0]
     with torch.cuda.device(x.device):
