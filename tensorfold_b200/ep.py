@@ -500,7 +500,7 @@ class PeerExl3ExpertParallel:
             _lib.call("tfb_window_picks", w.pick_all.data_ptr(), w.wts_all.data_ptr(), w.lo, w.per_rank,
                       self.pick_local.data_ptr(), self.wts_local.data_ptr(), self.rows * self.top_k, w._stream())
             self.exl3.routed(w.x_all, self.pick_local, self.wts_local, self.local, self.scratch, self.partial,
-                             self.rows, limit=self.limit)
+                             self.rows, limit=self.limit, share=w.per_rank / w.experts)
             w.push(self.partial)
             if residual:
                 w.sum(self.out_next, residual=w.tokens)

@@ -244,9 +244,11 @@ def group(pick: torch.Tensor, s: Scratch, R: int, experts: int) -> None:
 
 def routed(x: torch.Tensor, pick: torch.Tensor, wts: torch.Tensor | None, ex: Exl3RoutedExperts, s: Scratch,
            out: torch.Tensor | None, R: int, limit: float = math.inf, act_mode: int = ACT_F32,
-           group_first: bool = True) -> torch.Tensor:
+           group_first: bool = True, share: float = 1.0) -> torch.Tensor:
     """Routed experts of R rows (picks >= E skipped): y per slot [R * slots, D] fp32, or ``out`` [R, D] fp32 = the
-    wts-weighted slot-order sum when ``wts`` is given; no host sync."""
+    wts-weighted slot-order sum when ``wts`` is given; no host sync.  ``share``: the fraction of the slots that the
+    caller expects to hold one of these experts (an expert-parallel rank: its experts over all experts) - it only
+    steers which build of the kernels a call of mixed widths uses, never a result."""
 
     dims, width, slots = ex.dims, ex.width, s.slots
     pairs = R * slots
@@ -266,7 +268,7 @@ def routed(x: torch.Tensor, pick: torch.Tensor, wts: torch.Tensor | None, ex: Ex
     def width_of(k2: tuple[int, int], n: int, mats: int) -> int:
         if k2[0] == k2[1]:
             return k2[0]
-        crowded = min(pairs, ex.count) * (n // 64) * mats >= CROWDED_BLOCKS
+        crowded = min(pairs * share, ex.count) * (n // 64) * mats >= CROWDED_BLOCKS
         return -1 if COMPACT_MIXED and crowded else 0
 
     k2_gu, k2_d = width_of(ex.k2_gu, width, 2), width_of(ex.k2_d, dims, 1)
