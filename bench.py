@@ -714,6 +714,61 @@ def bench_rank_slice(torch, args, config: str, shape, dev, hbm: float) -> dict:
             "gate_up_frac_of_hbm": nbytes * 2 / 3 / (ms_first / k * 1e-3) / 1e9 / hbm}
 
 
+def bench_rank_slice_c5(torch, args, dev, hbm: float) -> dict:
+    """`--as-rank-of N --config c5`: one GPU running the routed EXL3 call of rank `--slice-rank` of an N-rank group for
+    layer 0 of config 5 (its 160 / N experts at their seeded mixed widths, the `--rows` tokens (128 unless given) of all
+    ranks routed over all experts, the selections renumbered to the rank's window), for profiling under ncu.
+    `--one-width B` gives every tensor B bits instead (the comparison that shows what the mix of widths costs)."""
+
+    from tensorfold_b200 import _lib, moe, synthetic
+    from tensorfold_b200.exl3 import experts as x3
+
+    shape = synthetic.C5
+    n, r, rows = args.as_rank_of, args.slice_rank, args.rows or 128
+    per = shape.experts // n
+    widths = c5_widths()
+    if args.one_width:
+        widths = {key: args.one_width for key in widths}
+    mine = list(range(r * per, (r + 1) * per))
+    g, u, d = c5_experts(torch, dev, 0, mine, widths)
+    ex = x3.prepare(g, u, d, x3.CB_3INST, device=dev)
+    router = synthetic.router_rows(shape, dev)
+    x = synthetic.activations(shape, rows, dev, index=100)
+
+    class _Cfg:
+        num_experts_per_tok, num_experts = shape.top_k, shape.experts
+        moe_intermediate_size, hidden_size = shape.width, shape.dims
+
+    buf = moe.MoEBuffers(rows, _Cfg, dev, shared=False)
+    moe.router(x, router, buf.logits)
+    moe.select_rows(buf.logits, buf, shape.top_k, shape.experts)
+    pick = torch.zeros((rows, shape.top_k), dtype=torch.int32, device=dev)
+    wts = torch.zeros((rows, shape.top_k), dtype=torch.float32, device=dev)
+    st = torch.cuda.current_stream(dev).cuda_stream
+    _lib.call("tfb_window_picks", buf.pick.data_ptr(), buf.wts.data_ptr(), r * per, per, pick.data_ptr(), wts.data_ptr(),
+              rows * shape.top_k, st)
+    scratch = x3.Scratch(ex, rows, shape.top_k, device=dev)
+    scratch.y.zero_()
+    out = torch.zeros((rows, shape.dims), dtype=torch.float32, device=dev)
+
+    def call():
+        x3.routed(x, pick, wts, ex, scratch, out, rows, share=per / shape.experts)
+
+    call()
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream(dev)
+    side.wait_stream(torch.cuda.current_stream())
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        call()
+    ms, _ = timed(torch, lambda i: graph.replay(), max(args.steps, 3), args.warmup, 5)
+    in_window = int((pick < per).sum())
+    nbytes = ex.nbytes_read(sorted(set(pick[pick < per].tolist())))
+    return {"as_rank_of": n, "rank": r, "config": "c5", "experts": per, "tokens": rows, "pairs_in_window": in_window,
+            "widths": f"{args.one_width} bits every tensor" if args.one_width else "seeded 2..8 bits a tensor",
+            "trellis_bytes": nbytes, "routed_call_us": ms * 1e3, "frac_of_hbm": nbytes / (ms * 1e-3) / 1e9 / hbm}
+
+
 def bench_ep(torch, dist, args, config: str, shape, dev, rank: int, world: int) -> dict:
     """Expert-parallel step of the affine layer: this rank's rows through the layer whose experts are sharded over the
     ranks.  Each rank keeps several copies of its expert slice and rotates them, so a step's weights never sit in L2.
@@ -1065,11 +1120,13 @@ def run_ours(args) -> None:
         dist.destroy_process_group()
         return
     if args.as_rank_of:
-        shape = synthetic.C4 if args.config == "c4" else synthetic.C2
-        if world != 1 or args.config == "c5" or shape.experts % args.as_rank_of or \
-                not 0 <= args.slice_rank < args.as_rank_of:
-            raise SystemExit("--as-rank-of N runs config 2 or 4 on one GPU, N a divisor of the expert count")
-        print(json.dumps(bench_rank_slice(torch, args, args.config, shape, dev, hbm)))
+        shape = {"c2": synthetic.C2, "c4": synthetic.C4, "c5": synthetic.C5}[args.config]
+        if world != 1 or shape.experts % args.as_rank_of or not 0 <= args.slice_rank < args.as_rank_of:
+            raise SystemExit("--as-rank-of N runs on one GPU, N a divisor of the expert count")
+        if args.config == "c5":
+            print(json.dumps(bench_rank_slice_c5(torch, args, dev, hbm)))
+        else:
+            print(json.dumps(bench_rank_slice(torch, args, args.config, shape, dev, hbm)))
         dist.destroy_process_group()
         return
     shapes = {"c2": synthetic.C2, "c4": synthetic.C4, "c5": synthetic.C5}
@@ -1238,6 +1295,8 @@ def main() -> None:
     ap.add_argument("--as-rank-of", type=int, default=0,
                     help="one GPU runs the expert launches of one rank of an N-rank config-2 group (for profiling)")
     ap.add_argument("--slice-rank", type=int, default=0, help="which rank's expert window --as-rank-of runs")
+    ap.add_argument("--one-width", type=int, default=0, choices=[0, 2, 3, 4, 5, 6, 7, 8],
+                    help="--as-rank-of with --config c5: every tensor at this many bits instead of the seeded mix")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline legs")
     ap.add_argument("--no-sweep", action="store_true", help="skip the 1-, 4-, 16- and 2048-token and EXL3 lines")
     ap.add_argument("--no-extra", action="store_true", help="skip configs 4 and 5")

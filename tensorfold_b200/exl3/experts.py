@@ -261,7 +261,8 @@ def routed(x: torch.Tensor, pick: torch.Tensor, wts: torch.Tensor | None, ex: Ex
     if act_mode not in (ACT_BF16, ACT_F32):
         raise ValueError("act_mode is ACT_BF16 or ACT_F32")
     st, items = _stream(x), max_items(pairs, ex.count)
-    per_item = item_pairs(pairs, ex.count) if group_first else ITEM_PAIRS      # `group` sorts into the narrow items
+    # `group` sorts into the narrow items; an expert-parallel rank expects only its share of the pairs
+    per_item = item_pairs(int(pairs * share), ex.count) if group_first else ITEM_PAIRS
     sort = (s.sort_members.data_ptr(), s.sort_items.data_ptr(), s.sort_counts.data_ptr())
     # the one width of a projection's tensors; or -1: they differ and the launch is large enough for blocks of several
     # widths to share an SM (the kernels then run a build with short loops); or 0: they differ, a small launch
